@@ -1,0 +1,266 @@
+"""CPU float64 oracle for the Mixture-of-Experts layer: a numpy restatement of the upstream
+pure-Python CPU path.
+
+TEST INFRASTRUCTURE ONLY.  This file is the checker, never the product: only the test-suite,
+the smoke check and the CPU-baseline / reference legs of the benchmark may import it.  The
+shipped package never does, and has no CPU fallback.
+
+Parity status: PINNED.  ``tests/golden/*.npz`` hold outputs of the upstream package itself
+(``SparseMoE`` on ``device="cpu"``, ``dtype="float64"``), produced by
+``tests/golden/make_golden.py``; ``tests/test_oracle_golden.py`` checks every function below
+against them (integer tables exactly, floats to 1e-12 relative), and also against the
+known-answer cases of the upstream tests (tests/test_lm_moe.py:65-71, :140-162;
+tests/test_lm_bfloat16.py:129-167).
+
+Each function cites the upstream file:line it follows.  Arrays are row-major numpy float64
+unless stated; integer tables are int64 like the upstream ``array('q')`` storages.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+# --------------------------------------------------------------------------------------
+# element-wise pieces
+# --------------------------------------------------------------------------------------
+def sigmoid(v):
+    """Two-branch stable logistic, as in src/qutai/backends/cpu_lm.py:107-111."""
+    v = np.asarray(v, dtype=np.float64)
+    out = np.empty_like(v)
+    pos = v >= 0
+    out[pos] = 1.0 / (1.0 + np.exp(-v[pos]))
+    ev = np.exp(v[~pos])
+    out[~pos] = ev / (1.0 + ev)
+    return out
+
+
+def silu(v):
+    """``x * sigmoid(x)``; src/qutai/backends/cpu_lm.py:107-111."""
+    return np.asarray(v, dtype=np.float64) * sigmoid(v)
+
+
+def silu_backward(g, v):
+    """``g * s * (1 + x * (1 - s))``; src/qutai/backends/cpu_lm.py:114-122."""
+    s = sigmoid(v)
+    return np.asarray(g, dtype=np.float64) * s * (1.0 + np.asarray(v, dtype=np.float64) * (1.0 - s))
+
+
+def softmax_rows(scores):
+    """Row softmax with the row maximum subtracted; src/qutai/backends/cpu.py:250-260.
+
+    The upstream code totals the exponentials with ``math.fsum``; ``np.sum`` differs from that
+    by at most a few ulp, far inside every tolerance used with this oracle.
+    """
+    scores = np.asarray(scores, dtype=np.float64)
+    weights = np.exp(scores - scores.max(axis=1, keepdims=True))
+    return weights / weights.sum(axis=1, keepdims=True)
+
+
+# --------------------------------------------------------------------------------------
+# routing
+# --------------------------------------------------------------------------------------
+def routing(scores, top_k):
+    """Softmax / top-k gating and the per-expert dispatch tables.
+
+    Follows ``routing`` in src/qutai/backends/cpu_lm.py:204-242:
+
+    * ``probs`` = row softmax of the scores;
+    * per row the ``top_k`` experts with the largest probability, ordered by descending
+      probability; Python's stable sort with ``reverse=True`` keeps EQUAL probabilities in
+      ascending expert index, which a stable argsort of ``-probs`` reproduces;
+    * ``weights[r, s] = probs[r, e_s] / sum_s' probs[r, e_s']``;
+    * per expert the list of token rows (``ids``) and slot numbers (``slots``) in increasing
+      (row, slot) scan order; ``counts``; ``utilization = counts / (rows * top_k)``;
+    * ``aux = experts * sum_e utilization[e] * mean_r probs[r, e]``.
+
+    ``locations[r, s]`` (row of assignment (r, s) inside its expert's group) is the extra table
+    the upstream CUDA path keeps (src/qutai/backends/cuda/lm.cu:353-383); it is implied by
+    ``ids``/``slots`` and is included so the device tables can be compared one to one.
+    """
+    scores = np.asarray(scores, dtype=np.float64)
+    rows, experts = scores.shape
+    probs = softmax_rows(scores)
+    order = np.argsort(-probs, axis=1, kind="stable")[:, :top_k]
+    indices = order.astype(np.int64)
+    picked = np.take_along_axis(probs, order, axis=1)
+    # Python's sum() over the selected probabilities is a left-to-right float64 sum.
+    total = np.zeros(rows, dtype=np.float64)
+    for slot in range(top_k):
+        total = total + picked[:, slot]
+    weights = picked / total[:, None]
+    flat = indices.reshape(-1)
+    ids, slots = [], []
+    locations = np.zeros(rows * top_k, dtype=np.int64)
+    for e in range(experts):
+        at = np.nonzero(flat == e)[0]
+        ids.append((at // top_k).astype(np.int64))
+        slots.append((at % top_k).astype(np.int64))
+        locations[at] = np.arange(at.size, dtype=np.int64)
+    counts = tuple(int(a.size) for a in ids)
+    utilization = np.array([c / (rows * top_k) for c in counts], dtype=np.float64)
+    aux = experts * float(sum(utilization[e] * probs[:, e].sum() / rows for e in range(experts)))
+    return dict(probs=probs, weights=weights, indices=indices, counts=counts, ids=ids,
+                slots=slots, locations=locations.reshape(rows, top_k), utilization=utilization,
+                aux=aux, rows=rows, experts=experts, top_k=top_k)
+
+
+def routing_backward(gradient, route, auxiliary=False):
+    """Gradient of the gate weights (or of the auxiliary loss) with respect to the scores.
+
+    Follows ``routing_backward`` in src/qutai/backends/cpu_lm.py:245-276.  Gate path:
+    ``d[r, e_s] = w[r, s] * (g[r, s] - sum_s' g[r, s'] * w[r, s'])`` and zero for experts that
+    were not selected.  Auxiliary path (``utilization`` held constant):
+    ``d[r, e] = g * E / T * p[r, e] * (util[e] - sum_j p[r, j] * util[j])``.
+    """
+    rows, experts, top_k = route["rows"], route["experts"], route["top_k"]
+    out = np.zeros((rows, experts), dtype=np.float64)
+    if auxiliary:
+        g = float(np.asarray(gradient, dtype=np.float64).reshape(-1)[0])
+        probs, util = route["probs"], route["utilization"]
+        center = probs @ util
+        out[:] = g * experts / rows * probs * (util[None, :] - center[:, None])
+        return out
+    g = np.asarray(gradient, dtype=np.float64).reshape(rows, top_k)
+    w = route["weights"]
+    center = (g * w).sum(axis=1, keepdims=True)
+    np.put_along_axis(out, route["indices"], w * (g - center), axis=1)
+    return out
+
+
+def route_gather(values, route, expert):
+    """Rows of ``values`` routed to ``expert``; src/qutai/backends/cpu_lm.py:279-283."""
+    return np.asarray(values)[route["ids"][expert]]
+
+
+def route_gather_backward(gradient, route, expert):
+    """Scatter-add into a zero (rows, width) array; src/qutai/backends/cpu_lm.py:286-291."""
+    gradient = np.asarray(gradient, dtype=np.float64)
+    out = np.zeros((route["rows"], gradient.shape[1]), dtype=np.float64)
+    np.add.at(out, route["ids"][expert], gradient)
+    return out
+
+
+def combine(outputs, weights, route):
+    """Weighted un-permute: ``out[row] += w[row, slot] * y_e[i]``, expert by expert.
+
+    Follows ``combine`` in src/qutai/backends/cpu_lm.py:294-303; ``outputs`` is a sequence of
+    ``(expert, array(c_e, width))`` pairs for the experts that received tokens.
+    """
+    weights = np.asarray(weights, dtype=np.float64).reshape(route["rows"], route["top_k"])
+    width = outputs[0][1].shape[1] if outputs else 0
+    result = np.zeros((route["rows"], width), dtype=np.float64)
+    for expert, values in outputs:
+        rows_e, slots_e = route["ids"][expert], route["slots"][expert]
+        # each token appears at most once per expert, so a plain indexed add is exact
+        result[rows_e] += weights[rows_e, slots_e][:, None] * np.asarray(values, dtype=np.float64)
+    return result
+
+
+def combine_backward(gradient, outputs, weights, route):
+    """``dy_e[i] = g[row] * w[row, slot]`` and ``dw[row, slot] = <g[row], y_e[i]>``.
+
+    Follows ``combine_backward`` in src/qutai/backends/cpu_lm.py:306-320.  Returns
+    ``([dy_e for each entry of outputs], dw)``.
+    """
+    gradient = np.asarray(gradient, dtype=np.float64)
+    weights = np.asarray(weights, dtype=np.float64).reshape(route["rows"], route["top_k"])
+    dw = np.zeros_like(weights)
+    grads = []
+    for expert, values in outputs:
+        rows_e, slots_e = route["ids"][expert], route["slots"][expert]
+        grads.append(gradient[rows_e] * weights[rows_e, slots_e][:, None])
+        dw[rows_e, slots_e] = (gradient[rows_e] * np.asarray(values, dtype=np.float64)).sum(axis=1)
+    return grads, dw
+
+
+# --------------------------------------------------------------------------------------
+# the layer
+# --------------------------------------------------------------------------------------
+def moe_forward(x, router, gate, up, down, top_k, scores=None):
+    """Forward of the sparse layer; src/qutai/lm/layers.py:376-402 with the expert body of
+    src/qutai/lm/layers.py:310-311 (``down(silu(gate(x)) * up(x))``, no biases) and the linear
+    maps of src/qutai/lm/layers.py:35-48 (``x @ W.T`` with ``W`` stored (out, in)).
+
+    ``x`` (T, d); ``router`` (E, d); ``gate``/``up`` sequences of (h, d); ``down`` sequence of
+    (d, h).  ``scores`` overrides the router product (used to feed identical fp32 logits).
+    Returns ``(y, aux, ctx)`` where ``ctx`` keeps what the backward needs.
+    """
+    x = np.asarray(x, dtype=np.float64)
+    router = np.asarray(router, dtype=np.float64)
+    if scores is None:
+        scores = x @ router.T
+    route = routing(scores, top_k)
+    saved, outputs = {}, []
+    for e in range(route["experts"]):
+        if not route["counts"][e]:
+            continue
+        xe = route_gather(x, route, e)
+        g = xe @ np.asarray(gate[e], dtype=np.float64).T
+        u = xe @ np.asarray(up[e], dtype=np.float64).T
+        hidden = silu(g) * u
+        ye = hidden @ np.asarray(down[e], dtype=np.float64).T
+        saved[e] = (xe, g, u, hidden)
+        outputs.append((e, ye))
+    y = combine(outputs, route["weights"], route)
+    ctx = dict(x=x, router=router, gate=gate, up=up, down=down, route=route, saved=saved,
+               outputs=outputs, scores=np.asarray(scores, dtype=np.float64))
+    return y, route["aux"], ctx
+
+
+def moe_backward(ctx, grad_y, grad_aux=0.0):
+    """Backward of the sparse layer, following the closures registered by the forward:
+    combine (src/qutai/lm/layers.py:144-152), the expert body (src/qutai/lm/layers.py:50-70,
+    :99-105, src/qutai/core/operations/elementwise.py:40-51), route_gather
+    (src/qutai/lm/layers.py:133-141), the two routing closures (src/qutai/lm/layers.py:382-391)
+    and the router projection.
+
+    Returns a dict with ``x``, ``router``, ``scores`` and per-expert lists ``gate``, ``up``,
+    ``down`` whose entries are ``None`` for experts that received no token (the upstream layer
+    never calls such an expert, so its parameters get no gradient object at all).
+    """
+    route = ctx["route"]
+    experts = route["experts"]
+    x = ctx["x"]
+    grad_y = np.asarray(grad_y, dtype=np.float64).reshape(x.shape)
+    dys, dw = combine_backward(grad_y, ctx["outputs"], route["weights"], route)
+    dx = np.zeros_like(x)
+    grads = dict(gate=[None] * experts, up=[None] * experts, down=[None] * experts)
+    for (e, _), dy in zip(ctx["outputs"], dys):
+        xe, g, u, hidden = ctx["saved"][e]
+        wg, wu, wd = (np.asarray(ctx[name][e], dtype=np.float64) for name in ("gate", "up", "down"))
+        d_hidden = dy @ wd
+        grads["down"][e] = dy.T @ hidden
+        d_up = d_hidden * silu(g)
+        d_gate = silu_backward(d_hidden * u, g)
+        grads["gate"][e] = d_gate.T @ xe
+        grads["up"][e] = d_up.T @ xe
+        dx += route_gather_backward(d_gate @ wg + d_up @ wu, route, e)
+    d_scores = routing_backward(dw, route)
+    if grad_aux:
+        d_scores = d_scores + routing_backward([grad_aux], route, True)
+    grads["scores"] = d_scores
+    grads["router"] = d_scores.T @ x
+    grads["x"] = dx + d_scores @ ctx["router"]
+    grads["weights"] = dw
+    return grads
+
+
+# --------------------------------------------------------------------------------------
+# helpers used by tests and by the benchmark's CPU leg
+# --------------------------------------------------------------------------------------
+def round_bf16(a):
+    """Round float values to the nearest bfloat16 (ties to even), returned as float64."""
+    a32 = np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+    bits = a32.view(np.uint32).astype(np.uint64)
+    rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return rounded.view(np.float32).astype(np.float64).reshape(a32.shape)
+
+
+def max_rel_err(actual, expected):
+    """``max |a - b| / max |b|`` — the layer-level relative error used for the parity bars."""
+    actual = np.asarray(actual, dtype=np.float64)
+    expected = np.asarray(expected, dtype=np.float64)
+    scale = float(np.abs(expected).max()) if expected.size else 0.0
+    if scale == 0.0:
+        return float(np.abs(actual).max()) if actual.size else 0.0
+    return float(np.abs(actual - expected).max() / scale)
