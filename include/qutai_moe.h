@@ -1,0 +1,271 @@
+/*
+ * libqutai_moe.so — C ABI of the B200 (sm_100a) Mixture-of-Experts layer.
+ *
+ * This is the boundary a host binds with ctypes (or any FFI).  It replaces, for the MoE layer of
+ * qutai.lm, the NVRTC source strings that the upstream CUDA backend launches from
+ * src/qutai/backends/cuda_lm.py through src/qutai/backends/cuda_runtime.py:299-328.  Every entry
+ * point is `extern "C"`, takes plain integers, sizes and device addresses (uint64_t, as the
+ * upstream `_p()` helper passes them, src/qutai/backends/cuda.py:61-70) and returns an int:
+ *
+ *      0            success
+ *    < 0            argument / state error (QMOE_ERR_*); the host raises ValueError, as the
+ *                   upstream dispatcher does before any launch (src/qutai/backends/cuda.py:307-334)
+ *    > 0            a cudaError_t (or 1000 + ncclResult_t); the host raises RuntimeError, as
+ *                   src/qutai/backends/cuda_runtime.py:165-177 does for CUresult
+ *
+ * qmoe_last_error() returns the message of the last failure on the calling thread.
+ *
+ * Ownership: the library never owns tensors.  Inputs, outputs and scratch are allocated by the
+ * caller and passed as device addresses; the library keeps only process-wide internals (cached
+ * TMA descriptors, timing events, an optional NCCL communicator).  All work is enqueued on the
+ * stream argument (0 = the legacy default stream, which is what the upstream runtime uses,
+ * src/qutai/backends/cuda_runtime.py:326) of the CURRENT device/context; nothing synchronises
+ * unless documented.
+ *
+ * Layouts.  T tokens, E experts, k = top_k, A = T*k assignments, d = model width, h = expert
+ * hidden width.  All matrices are dense row-major.  The "dispatched" layout holds the rows routed
+ * to expert 0, then expert 1, ...; inside one expert rows keep increasing (token, slot) order —
+ * the order of the upstream `ids`/`slots` lists (src/qutai/backends/cpu_lm.py:204-221,
+ * src/qutai/backends/cuda/lm.cu:353-383) — and each expert group starts at a multiple of
+ * QMOE_ROW_PAD rows; the pad rows hold zeros.  A buffer in that layout has
+ * qmoe_rows_bound(T, E, k) rows.
+ */
+#ifndef QUTAI_MOE_H
+#define QUTAI_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QMOE_VERSION 100
+#define QMOE_ROW_PAD 128
+#define QMOE_MAX_EXPERTS 256
+#define QMOE_MAX_TOP_K 8
+
+enum {
+    QMOE_OK = 0,
+    QMOE_ERR_ARGUMENT = -1,    /* bad size, null address, misaligned buffer */
+    QMOE_ERR_UNSUPPORTED = -2, /* shape or dtype this build has no kernel for */
+    QMOE_ERR_STATE = -3,       /* call order / initialisation problem */
+    QMOE_ERR_DEVICE_CHECK = -4 /* a kernel recorded a failed self-check (bounded wait ran out, bad table) */
+};
+
+enum { QMOE_F32 = 0, QMOE_BF16 = 1 };                     /* activation dtype */
+enum { QMOE_ENGINE_AUTO = 0, QMOE_ENGINE_SIMT = 1, QMOE_ENGINE_TCGEN05 = 2 };
+
+/* ---------------------------------------------------------------------------------------------
+ * Library, device memory and stream helpers.  They let a dependency-free host keep device
+ * buffers, the role src/qutai/backends/cuda_runtime.py:184-258 (allocate/free/upload/download)
+ * plays upstream.  A host that already owns device memory does not need them.
+ * ------------------------------------------------------------------------------------------- */
+int qmoe_version(void);
+const char* qmoe_last_error(void);
+int qmoe_device_info(int* sm_count, int* cc_major, int* cc_minor, uint64_t* total_bytes);
+int qmoe_malloc(uint64_t* address, uint64_t bytes);
+int qmoe_free(uint64_t address);
+int qmoe_host_alloc(void** host, uint64_t bytes);         /* pinned host memory */
+int qmoe_host_free(void* host);
+int qmoe_memcpy_h2d(uint64_t dst, const void* src, uint64_t bytes, uint64_t stream);
+int qmoe_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes, uint64_t stream); /* async; sync the stream before reading */
+int qmoe_memcpy_d2d(uint64_t dst, uint64_t src, uint64_t bytes, uint64_t stream);
+int qmoe_memset(uint64_t dst, int value, uint64_t bytes, uint64_t stream);
+int qmoe_stream_sync(uint64_t stream);
+/* launches made by this library since load (the upstream runtime keeps the same counter,
+ * src/qutai/backends/cuda_runtime.py:95, :327); tensor-core launches counted separately (:100). */
+int64_t qmoe_launch_count(void);
+int64_t qmoe_tensor_core_launch_count(void);
+/* Per-kernel-class device timing with CUDA events on the launching stream.  enable=1 starts a
+ * fresh measurement; qmoe_timing_read synchronises the device and returns, per class, the summed
+ * milliseconds and the number of timed scopes.  Class names via qmoe_timing_class_name. */
+int qmoe_timing_enable(int enable);
+int qmoe_timing_classes(void);
+const char* qmoe_timing_class_name(int kernel_class);
+int qmoe_timing_read(double* milliseconds, int64_t* scopes, int capacity);
+/* status word written by kernels that check themselves; 0 = clean.  Synchronises the stream. */
+int qmoe_device_status(uint64_t stream, int* status);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sizes
+ * ------------------------------------------------------------------------------------------- */
+/* Upper bound of rows in the dispatched layout: A + E*(QMOE_ROW_PAD-1), rounded up to the pad. */
+int64_t qmoe_rows_bound(int64_t tokens, int32_t experts, int32_t top_k);
+/* Blocks the routing kernels use for T tokens (first dimension of the block_* scratch tables). */
+int64_t qmoe_route_blocks(int64_t tokens);
+
+/* ---------------------------------------------------------------------------------------------
+ * Routing tables (caller-allocated; the struct only carries addresses)
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qmoe_route {
+    int64_t tokens;        /* T */
+    int32_t experts;       /* E  (<= QMOE_MAX_EXPERTS) */
+    int32_t top_k;         /* k  (<= min(E, QMOE_MAX_TOP_K)) */
+    int64_t rows_bound;    /* qmoe_rows_bound(T, E, k) */
+    uint64_t probs;        /* f32 [T, E]   softmax of the scores */
+    uint64_t gate_weights; /* f32 [T, k]   renormalised gate weights, slot order = descending prob */
+    uint64_t expert_index; /* i32 [A]      expert of assignment a = token*k + slot */
+    uint64_t dest_row;     /* i32 [A]      row of assignment a in the dispatched layout */
+    uint64_t row_source;   /* i32 [rows_bound]  assignment held by each dispatched row, -1 = pad */
+    uint64_t counts;       /* i32 [E]      rows routed to each expert */
+    uint64_t offsets;      /* i32 [E + 1]  first dispatched row of each expert (multiples of the pad) */
+    uint64_t tile_expert;  /* i32 [rows_bound / QMOE_ROW_PAD]  expert owning each 128-row tile */
+    uint64_t meta;         /* i32 [4]      {dispatched rows incl. pads, 128-row tiles, A, 0} */
+    uint64_t utilization;  /* f32 [E]      counts / A */
+    uint64_t aux;          /* f32 [1]      load-balancing loss */
+    uint64_t block_counts; /* i32 [blocks, E]  scratch */
+    uint64_t block_base;   /* i32 [blocks, E]  scratch */
+    uint64_t block_colsum; /* f32 [blocks, E]  scratch */
+} qmoe_route_t;
+
+/* Router logits: scores[T, E] = float(x)[T, d] . w_router[E, d]^T, fp32 arithmetic whatever the
+ * activation dtype.  Replaces the router `linear` call under `set_matmul_precision(None)`
+ * (src/qutai/lm/layers.py:377-378, gemm kernels src/qutai/backends/cuda/gemm.cu:35-101). */
+int qmoe_router_logits(uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t scores,
+                       int64_t tokens, int64_t width, int32_t experts, uint64_t stream);
+/* Router backward: dx_router[T, d] (f32) = d_scores . w_router ; d_w_router[E, d] (f32) =
+ * d_scores^T . float(x).  `partials` is f32 scratch of qmoe_router_grad_partials(T, E, d)
+ * elements (deterministic split over tokens).  Replaces the backward closure of `linear`
+ * (src/qutai/lm/layers.py:50-70) for the router. */
+int64_t qmoe_router_grad_partials(int64_t tokens, int32_t experts, int64_t width);
+int qmoe_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dtype, uint64_t w_router,
+                         uint64_t dx_router, uint64_t d_w_router, uint64_t partials,
+                         int64_t tokens, int64_t width, int32_t experts, uint64_t stream);
+
+/* Softmax, top-k (ties -> lowest expert index), gate renormalisation, per-expert counts, padded
+ * offsets, the stable dispatch permutation, utilisation and the auxiliary loss, all on the device
+ * and without a host synchronisation.  Replaces `routing` (src/qutai/backends/cuda_lm.py:368-449:
+ * softmax, lm_route, lm_route_pack, lm_route_util, lm_route_aux; CPU statement
+ * src/qutai/backends/cpu_lm.py:204-242). */
+int qmoe_route(const qmoe_route_t* route, uint64_t scores, uint64_t stream);
+/* The same tables in the upstream layout, for hosts that keep the upstream `route` dict
+ * (src/qutai/backends/cuda_lm.py:435-449): int64 indices[A], ids[E*capacity], slots[E*capacity]
+ * (row e holds expert e's token rows / slot numbers), locations[A], counts[E]. */
+int qmoe_route_export_i64(const qmoe_route_t* route, uint64_t indices, uint64_t ids, uint64_t slots,
+                          uint64_t locations, uint64_t counts, int64_t capacity, uint64_t stream);
+/* d_scores[T, E] (f32) = gate-weight path (grad_weights f32 [T, k], may be 0) + auxiliary-loss path
+ * (grad_aux f32 [1], may be 0).  Replaces the two `routing_backward` calls and the add that joins
+ * them (src/qutai/backends/cuda_lm.py:452-468, src/qutai/backends/cuda/lm.cu:388-393,
+ * src/qutai/backends/cpu_lm.py:245-276). */
+int qmoe_route_backward(const qmoe_route_t* route, uint64_t grad_weights, uint64_t grad_aux,
+                        uint64_t d_scores, uint64_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Permute / combine (memory-bound, 128-bit accesses when the row pitch allows)
+ * ------------------------------------------------------------------------------------------- */
+/* dispatched[r, :] = x[token(r), :], pad rows zero.  Replaces the E `route_gather` launches
+ * (src/qutai/backends/cuda_lm.py:471-485, src/qutai/backends/cuda/lm.cu:394-396). */
+int qmoe_permute(const qmoe_route_t* route, uint64_t x, uint64_t dispatched, int32_t dtype,
+                 int64_t width, uint64_t stream);
+/* dx[t, :] = sum_s d_dispatched[dest_row(t, s), :] (+ extra_f32[t, :] when extra != 0), summed in
+ * fp32 and rounded once.  Replaces `route_gather_backward` (E zero-filled T x d buffers,
+ * src/qutai/backends/cuda_lm.py:488-502) and the pairwise adds of src/qutai/core/grad.py:62. */
+int qmoe_unpermute_reduce(const qmoe_route_t* route, uint64_t d_dispatched, uint64_t extra_f32,
+                          uint64_t dx, int32_t dtype, int64_t width, uint64_t stream);
+/* out[t, :] = sum_s gate_weights[t, s] * y_dispatched[dest_row(t, s), :], fp32 sum, one rounding.
+ * Replaces `combine` (src/qutai/backends/cuda_lm.py:521-541, lm_combine_all lm.cu:406-416). */
+int qmoe_combine(const qmoe_route_t* route, uint64_t y_dispatched, uint64_t out, int32_t dtype,
+                 int64_t width, uint64_t stream);
+/* dy_dispatched[r, :] = g[token(r), :] * w(r) (pad rows zero); d_gate_weights[a] (f32) =
+ * <g[token, :], y_dispatched[r, :]>.  Replaces `combine_backward`
+ * (src/qutai/backends/cuda_lm.py:544-581, lm.cu:417-429). */
+int qmoe_combine_backward(const qmoe_route_t* route, uint64_t grad_out, uint64_t y_dispatched,
+                          uint64_t dy_dispatched, uint64_t d_gate_weights, int32_t dtype,
+                          int64_t width, uint64_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Expert FFN (grouped GEMMs)
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qmoe_experts {
+    int32_t experts;   /* E */
+    int32_t dtype;     /* activation dtype: QMOE_BF16 -> bf16 operands, fp32 accumulate (tcgen05);
+                          QMOE_F32 -> fp32 everywhere (CUDA cores) */
+    int32_t engine;    /* QMOE_ENGINE_* ; AUTO = tcgen05 whenever dtype is bf16 and d, h are multiples of 8 */
+    int32_t reserved;
+    int64_t width;     /* d */
+    int64_t hidden;    /* h */
+    /* stacked expert weights in the OPERAND dtype (bf16 shadows for QMOE_BF16, the fp32 masters
+     * for QMOE_F32): gate, up [E, h, d]; down [E, d, h]  (upstream `Projection.weight` is
+     * (outputs, inputs), src/qutai/lm/layers.py:260-266) */
+    uint64_t w_gate, w_up, w_down;
+} qmoe_experts_t;
+
+/* fp32 -> bf16 (round to nearest even) of n elements: refreshes the bf16 operand copies of the
+ * fp32 master weights.  Upstream rounds the same way while staging tiles
+ * (src/qutai/backends/cuda/gemm.cu:23-24, :122-127). */
+int qmoe_cast_bf16(uint64_t src_f32, uint64_t dst_bf16, int64_t n, uint64_t stream);
+
+/* For every expert group of the dispatched input X:  G = X Wg^T, U = X Wu^T, H = silu(G) * U,
+ * Y = H Wd^T.  G, U, H are [rows_bound, h]; X, Y are [rows_bound, d].  Replaces the per-expert
+ * `SwiGLU.__call__` (src/qutai/lm/layers.py:310-311: 3 gemm + lm_silu + multiply per expert). */
+int qmoe_expert_forward(const qmoe_route_t* route, const qmoe_experts_t* experts, uint64_t x_dispatched,
+                        uint64_t g, uint64_t u, uint64_t h, uint64_t y_dispatched, uint64_t stream);
+/* Backward of the above.  dH (scratch [rows_bound, h]), dG, dU [rows_bound, h]; dX [rows_bound, d];
+ * d_w_gate, d_w_up [E, h, d] and d_w_down [E, d, h] are fp32 and are WRITTEN (not accumulated) for
+ * experts that received rows and left untouched for the others (upstream such experts get no
+ * gradient at all, src/qutai/lm/layers.py:396).  Replaces the closures of
+ * src/qutai/lm/layers.py:50-70, :104 and src/qutai/core/operations/elementwise.py:44-51. */
+int qmoe_expert_backward(const qmoe_route_t* route, const qmoe_experts_t* experts,
+                         uint64_t dy_dispatched, uint64_t x_dispatched, uint64_t g, uint64_t u,
+                         uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx_dispatched,
+                         uint64_t d_w_gate, uint64_t d_w_up, uint64_t d_w_down, uint64_t stream);
+
+/* Plain (single-group) product C[M, N] = op(A) op(B) with the upstream dispatcher's meaning of
+ * the arguments (src/qutai/backends/cuda.py:305-362): A is [M, K] ([K, M] when transpose_a),
+ * B is [K, N] ([N, K] when transpose_b); dtypes per operand; accumulate adds into C. */
+int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtype, uint64_t c, int32_t c_dtype,
+              int64_t m, int64_t k, int64_t n, int32_t transpose_a, int32_t transpose_b,
+              int32_t accumulate, uint64_t stream);
+/* silu(v) (backward == 0) or g * silu'(v) (backward != 0), element-wise over n values.
+ * Replaces lm_silu (src/qutai/backends/cuda/lm.cu:54). */
+int qmoe_silu(uint64_t values, uint64_t gradient, uint64_t out, int32_t dtype, int64_t n,
+              int32_t backward, uint64_t stream);
+
+/* out = a + b element-wise (the sum autograd applies when a tensor receives several gradient
+ * contributions, src/qutai/core/grad.py:62, and when a leaf accumulates, src/qutai/core/tensor.py:207-209). */
+int qmoe_add(uint64_t a, uint64_t b, uint64_t out, int32_t dtype, int64_t n, uint64_t stream);
+/* Fill n values with N(mean, std) from a counter-based generator keyed by (seed, index).  Plays
+ * the role of `normal` (src/qutai/backends/cuda_lm.py:27-28, normal_fill
+ * src/qutai/backends/cuda/gemm.cu:146-161); like upstream, the stream differs from the CPU
+ * generator's for the same seed, so parity tests copy weights instead of comparing draws. */
+int qmoe_normal_fill(uint64_t out, int32_t dtype, int64_t n, double mean, double std, uint64_t seed,
+                     uint64_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Whole layer in one call (removes the per-stage host round trips; same kernels as above)
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qmoe_layer {
+    qmoe_route_t route;
+    qmoe_experts_t experts;
+    uint64_t x;            /* [T, d] activations (experts.dtype) */
+    uint64_t w_router;     /* f32 [E, d] */
+    uint64_t scores;       /* f32 [T, E] */
+    uint64_t x_dispatched, g, u, h, y_dispatched;   /* saved for the backward */
+    uint64_t out;          /* [T, d] */
+    /* backward */
+    uint64_t grad_out;     /* [T, d] */
+    uint64_t grad_aux;     /* f32 [1] or 0 */
+    uint64_t dy_dispatched, d_h, d_g, d_u, dx_dispatched;  /* dx_dispatched may alias dy_dispatched */
+    uint64_t d_gate_weights; /* f32 [T, k] */
+    uint64_t d_scores;     /* f32 [T, E] */
+    uint64_t dx_router;    /* f32 [T, d] */
+    uint64_t router_partials;
+    uint64_t dx;           /* [T, d] */
+    uint64_t d_w_router;   /* f32 [E, d] */
+    uint64_t d_w_gate, d_w_up, d_w_down; /* f32 stacked */
+    /* fp32 master weights to refresh the bf16 operand copies from before the forward (0 = skip) */
+    uint64_t master_gate, master_up, master_down;
+} qmoe_layer_t;
+
+/* Forward of `SparseMoE.__call__` (src/qutai/lm/layers.py:376-402): router logits, routing,
+ * permute, grouped expert FFN, weighted combine. */
+int qmoe_layer_forward(const qmoe_layer_t* layer, uint64_t stream);
+/* Backward of the same call (the closures listed above, in the order src/qutai/core/grad.py:34-65
+ * would run them), producing dx, d_w_router and the stacked expert weight gradients. */
+int qmoe_layer_backward(const qmoe_layer_t* layer, uint64_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUTAI_MOE_H */

@@ -1,0 +1,564 @@
+// Grouped expert GEMMs on the 5th-generation tensor cores (sm_100a): tcgen05.mma with bf16
+// operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast),
+// fp32 accumulators in tensor memory (TMEM), read back with tcgen05.ld for the epilogue.
+//
+// One persistent kernel, one CTA per SM, 6 warps:
+//   warp 0      TMA producer (one lane): fills a 4-stage ring of {A 128x64, B 256x64} bf16 tiles
+//   warp 1      MMA issuer (one lane): 4 x tcgen05.mma (128x256x16) per stage, commits free the stage;
+//               also allocates / frees the 512 TMEM columns (two 128x256 fp32 accumulators)
+//   warps 2-5   epilogue: each owns 32 TMEM lanes (= 32 tile rows), converts and stores to HBM while
+//               the MMA warp already works on the next tile in the other accumulator
+//
+// Three problem kinds share the kernel (template MODE):
+//   MODE_PLAIN   C[rows, N] (bf16) = A[rows, K] . B_e  (+ A2 . B2_e), rows in the dispatched layout,
+//                the expert e of a 128-row tile picks the weight slab.  B either [E*N, K] (K-major,
+//                "x W^T") or [E*K, N] (MN-major, "g W").
+//   MODE_SWIGLU  G = X Wg_e^T, U = X Wu_e^T (128 + 128 accumulator columns), H = silu(G) * U, all
+//                three stored as bf16.
+//   MODE_WGRAD   C_e[M, N] (fp32) = A_e^T . B_e, contraction over the rows of expert e (both
+//                operands MN-major); experts without rows are skipped and their slab is not written.
+//
+// Every wait on an mbarrier is bounded (about one second of %globaltimer); when one runs out the
+// CTA records a code in the status word, stops issuing work, waits a bounded time for copies in
+// flight, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace qmoe {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64 x 64 bf16 TMA box (8 KiB)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
+
+enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2 };
+enum { STATUS_WAIT_PRODUCER = 101, STATUS_WAIT_MMA = 102, STATUS_WAIT_EPILOGUE = 103 };
+
+struct alignas(64) GemmParams {
+    CUtensorMap map_a, map_b, map_a2, map_b2;
+    const int* offsets;   // [E + 1] first dispatched row of each expert
+    const int* counts;    // [E]
+    int* status;
+    void* out0;           // PLAIN: C bf16; SWIGLU: G; WGRAD: C fp32 (stacked per expert)
+    void* out1;           // SWIGLU: U
+    void* out2;           // SWIGLU: H
+    long long ldc;        // row pitch of the outputs, in elements
+    long long c_slab;     // WGRAD: elements per expert
+    int experts;
+    int n_tiles;          // PLAIN/WGRAD: ceil(N / 256); SWIGLU: ceil(N / 128)
+    int m_tiles;          // WGRAD: ceil(M / 128)
+    int M, N, K;          // WGRAD: M, N of one expert's output; others: N = output columns, K = inner size of one segment
+    int b_rows;           // rows of the stacked B operand per expert
+    int segments;         // 1, or 2 when (A2, B2) is accumulated into the same tile
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long start = global_ns();
+    for (unsigned i = 1;; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - start > WAIT_LIMIT_NS) return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t dst, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (bit layout per the PTX ISA "matrix descriptor" for tcgen05):
+// [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) version = 1, [61,64) swizzle mode (2 = 128-byte).
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M = 128, N = 256.
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct Tile {
+    int expert, row0, n0, kblocks, krow0;
+    bool valid;
+};
+
+template <int MODE>
+__device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_start, int t) {
+    Tile tile;
+    tile.valid = true;
+    if (MODE == MODE_WGRAD) {
+        const int per = p.m_tiles * p.n_tiles;
+        const int e = t / per, rem = t - e * per;
+        tile.expert = e;
+        tile.row0 = (rem % p.m_tiles) * BM;
+        tile.n0 = (rem / p.m_tiles) * BN;
+        const int count = p.counts[e];
+        tile.kblocks = (count + BK - 1) / BK;
+        tile.krow0 = s_start[e] * kRowPad;
+        tile.valid = count > 0;
+    } else {
+        int lo = 0, hi = p.experts;  // largest e with s_start[e] * n_tiles <= t
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if ((long long)s_start[mid] * p.n_tiles <= t) lo = mid; else hi = mid;
+        }
+        const int e = lo;
+        const int mt = s_start[e + 1] - s_start[e];
+        const int local = t - s_start[e] * p.n_tiles;
+        tile.expert = e;
+        tile.row0 = (s_start[e] + local % mt) * BM;
+        tile.n0 = (local / mt) * (MODE == MODE_SWIGLU ? 128 : BN);
+        tile.kblocks = ((p.K + BK - 1) / BK) * p.segments;
+        tile.krow0 = 0;
+    }
+    return tile;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// store 32 consecutive bf16 of one row; `valid` = number of columns inside the matrix
+__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16* dst, const float* v, int valid) {
+    if (valid >= 32) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint4 w = make_uint4(pack_bf16(v[8 * q], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
+                                 pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
+            *reinterpret_cast<uint4*>(dst + 8 * q) = w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+
+template <int MODE, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int s_start[kMaxExperts + 1];  // first 128-row tile of each expert
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+
+    for (int i = threadIdx.x; i <= p.experts; i += NUM_THREADS) s_start[i] = p.offsets[i] / kRowPad;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_map(&p.map_a);
+        prefetch_map(&p.map_b);
+        if (MODE == MODE_SWIGLU || p.segments == 2) prefetch_map(&p.map_b2);
+        if (p.segments == 2) prefetch_map(&p.map_a2);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+
+    int total_tiles;
+    if (MODE == MODE_WGRAD) total_tiles = p.experts * p.m_tiles * p.n_tiles;
+    else total_tiles = s_start[p.experts] * p.n_tiles;
+    volatile int* abort_flag = &s_abort;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+                const Tile tile = decode_tile<MODE>(p, s_start, t);
+                if (!tile.valid) continue;
+                const int kb_per_seg = tile.kblocks / (MODE == MODE_WGRAD ? 1 : p.segments);
+                for (int kb = 0; kb < tile.kblocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_PRODUCER); }
+                        break;
+                    }
+                    const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+                    const uint32_t bar = full_bar(stage);
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    if (MODE == MODE_WGRAD) {
+                        const int krow = tile.krow0 + kb * BK;
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(&p.map_a, sa + j * CHUNK_BYTES, bar, tile.row0 + 64 * j, krow);
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(&p.map_b, sb + j * CHUNK_BYTES, bar, tile.n0 + 64 * j, krow);
+                    } else {
+                        const int seg = kb / kb_per_seg;
+                        const int k0 = (kb - seg * kb_per_seg) * BK;
+                        const CUtensorMap* ma = seg ? &p.map_a2 : &p.map_a;
+                        const CUtensorMap* mb = seg ? &p.map_b2 : &p.map_b;
+                        tma_load_2d(ma, sa, bar, k0, tile.row0);  // A is K-major in these modes
+                        if (MODE == MODE_SWIGLU) {
+                            tma_load_2d(&p.map_b, sb, bar, k0, tile.expert * p.b_rows + tile.n0);
+                            tma_load_2d(&p.map_b2, sb + B_STAGE_BYTES / 2, bar, k0, tile.expert * p.b_rows + tile.n0);
+                        } else if (B_MN) {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j)
+                                tma_load_2d(mb, sb + j * CHUNK_BYTES, bar, tile.n0 + 64 * j, tile.expert * p.b_rows + k0);
+                        } else {
+                            tma_load_2d(mb, sb, bar, k0, tile.expert * p.b_rows + tile.n0);
+                        }
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc<A_MN, B_MN>();
+            int stage = 0;
+            uint32_t phase = 0;
+            int iter = 0;
+            for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+                const Tile tile = decode_tile<MODE>(p, s_start, t);
+                if (!tile.valid) continue;
+                const int acc = iter & 1;
+                const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+                bool ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
+                for (int kb = 0; ok && kb < tile.kblocks; ++kb) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // K-major: 128-byte rows, 8-row groups 1024 B apart, +32 B per 16 k.
+                        // MN-major: 64-wide chunks 8 KiB apart (LBO), 8-k groups 1024 B apart, +2 KiB per 16 k.
+                        const uint64_t adesc = A_MN ? make_desc(sa + kk * 2048, CHUNK_BYTES, 1024)
+                                                    : make_desc(sa + kk * 32, 16, 1024);
+                        const uint64_t bdesc = B_MN ? make_desc(sb + kk * 2048, CHUNK_BYTES, 1024)
+                                                    : make_desc(sb + kk * 32, 16, 1024);
+                        umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | kk) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_MMA); }
+                    break;
+                }
+                umma_commit(tfull_bar(acc));
+                ++iter;
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int quad = warp & 3;  // TMEM lanes [32 * quad, 32 * quad + 32) belong to this warp
+        int iter = 0;
+        for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+            const Tile tile = decode_tile<MODE>(p, s_start, t);
+            if (!tile.valid) continue;
+            const int acc = iter & 1;
+            const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+                if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_EPILOGUE); }
+                break;
+            }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
+            const long long row = (long long)tile.row0 + quad * 32 + lane;
+            if (MODE == MODE_SWIGLU) {
+                __nv_bfloat16* G = (__nv_bfloat16*)p.out0 + row * p.ldc + tile.n0;
+                __nv_bfloat16* U = (__nv_bfloat16*)p.out1 + row * p.ldc + tile.n0;
+                __nv_bfloat16* H = (__nv_bfloat16*)p.out2 + row * p.ldc + tile.n0;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld32(taddr + c * 32, rg);
+                    tmem_ld32(taddr + 128 + c * 32, ru);
+                    tmem_ld_wait();
+                    float g[32], u[32], h[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        // rounding points of the bf16 activations: G and U are stored as bf16, and
+                        // silu(G) is rounded before the product, as separate kernels would do
+                        g[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[i])));
+                        u[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[i])));
+                        const float act = __bfloat162float(__float2bfloat16_rn(g[i] * sigmoid_stable(g[i])));
+                        h[i] = act * u[i];
+                    }
+                    const int valid = p.N - (tile.n0 + c * 32);
+                    if (valid > 0) {
+                        store_row32_bf16(G + c * 32, g, valid);
+                        store_row32_bf16(U + c * 32, u, valid);
+                        store_row32_bf16(H + c * 32, h, valid);
+                    }
+                }
+            } else if (MODE == MODE_PLAIN) {
+                __nv_bfloat16* C = (__nv_bfloat16*)p.out0 + row * p.ldc + tile.n0;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    const int valid = p.N - (tile.n0 + c * 32);
+                    if (valid > 0) store_row32_bf16(C + c * 32, v, valid);
+                }
+            } else {
+                float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
+                const bool row_ok = row < p.M;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    const int valid = p.N - (tile.n0 + c * 32);
+                    if (row_ok && valid >= 32) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<uint4*>(C + c * 32 + 4 * q) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    } else if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) C[c * 32 + i] = __uint_as_float(r[i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            ++iter;
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (s_abort) {
+        // give copies and MMAs in flight a bounded time to land before shared memory and TMEM go away
+        const unsigned long long start = global_ns();
+        while (global_ns() - start < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side: tensor maps ------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+std::mutex g_map_mutex;
+std::map<std::tuple<uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> g_maps;
+
+// 2-D bf16 row-major matrix [outer, inner], box {box_inner = 64, box_outer}, 128-byte swizzle.
+int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uint32_t box_outer) {
+    const uint32_t box_inner = 64;
+    auto key = std::make_tuple(ptr, inner, outer, box_inner, box_outer);
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        auto it = g_maps.find(key);
+        if (it != g_maps.end()) { *out = it->second; return 0; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return QMOE_ERR_STATE; }
+    if (ptr & 15u) return fail_arg("tensor-core GEMM operand address must be 16-byte aligned");
+    if ((inner * 2) % 16) return fail_arg("tensor-core GEMM operand row pitch must be a multiple of 16 bytes");
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner %llu, outer %llu, box %u x %u)", (int)rc,
+                  (unsigned long long)inner, (unsigned long long)outer, box_inner, box_outer);
+        return 999;
+    }
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps[key] = *out;
+    return 0;
+}
+
+template <int MODE, bool A_MN, bool B_MN>
+int launch(const GemmParams& p, cudaStream_t stream) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    QMOE_CUDA(cudaGetDevice(&dev));
+    auto kernel = grouped_gemm_kernel<MODE, A_MN, B_MN>;
+    if (dev < 64 && !configured[dev]) {
+        QMOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[dev] = true;
+    }
+    kernel<<<sm_count(), NUM_THREADS, SMEM_BYTES, stream>>>(p);
+    count_tensor_core_launch();
+    QMOE_LAUNCH_CHECK("grouped_gemm_kernel");
+    return 0;
+}
+
+}  // namespace
+
+bool tcgen05_shape_ok(long long width, long long hidden) { return width % 8 == 0 && hidden % 8 == 0 && width >= 8 && hidden >= 8; }
+
+// G, U, H [rows, h] = SwiGLU(X [rows, d]; Wg, Wu [E*h, d])
+int tc_swiglu_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t x, uint64_t g, uint64_t u, uint64_t h,
+                      cudaStream_t stream) {
+    GemmParams p = {};
+    const uint64_t rows = (uint64_t)r->rows_bound, d = (uint64_t)ex->width, hd = (uint64_t)ex->hidden, E = (uint64_t)ex->experts;
+    if (int rc = make_map(&p.map_a, x, d, rows, BM)) return rc;
+    if (int rc = make_map(&p.map_b, ex->w_gate, d, E * hd, 128)) return rc;
+    if (int rc = make_map(&p.map_b2, ex->w_up, d, E * hd, 128)) return rc;
+    p.map_a2 = p.map_a;
+    p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
+    p.out0 = (void*)g; p.out1 = (void*)u; p.out2 = (void*)h;
+    p.ldc = (long long)hd; p.experts = ex->experts; p.n_tiles = ceil_div((long long)hd, 128);
+    p.N = (int)hd; p.K = (int)d; p.b_rows = (int)hd; p.segments = 1;
+    return launch<MODE_SWIGLU, false, false>(p, stream);
+}
+
+// C [rows, N] = A [rows, K] . B_e^T with B stacked [E*N, K]
+int tc_rows_nt(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long K, long long N,
+               cudaStream_t stream) {
+    GemmParams p = {};
+    if (int rc = make_map(&p.map_a, a, (uint64_t)K, (uint64_t)r->rows_bound, BM)) return rc;
+    if (int rc = make_map(&p.map_b, b, (uint64_t)K, (uint64_t)experts * N, BN)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
+    p.out0 = (void*)c; p.ldc = N; p.experts = experts; p.n_tiles = ceil_div(N, BN);
+    p.N = (int)N; p.K = (int)K; p.b_rows = (int)N; p.segments = 1;
+    return launch<MODE_PLAIN, false, false>(p, stream);
+}
+
+// C [rows, N] = A [rows, K] . B_e (+ A2 . B2_e) with B stacked [E*K, N]
+int tc_rows_nn(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t a2, uint64_t b2, uint64_t c,
+               long long K, long long N, cudaStream_t stream) {
+    GemmParams p = {};
+    if (int rc = make_map(&p.map_a, a, (uint64_t)K, (uint64_t)r->rows_bound, BM)) return rc;
+    if (int rc = make_map(&p.map_b, b, (uint64_t)N, (uint64_t)experts * K, 64)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    p.segments = 1;
+    if (a2) {
+        if (int rc = make_map(&p.map_a2, a2, (uint64_t)K, (uint64_t)r->rows_bound, BM)) return rc;
+        if (int rc = make_map(&p.map_b2, b2, (uint64_t)N, (uint64_t)experts * K, 64)) return rc;
+        p.segments = 2;
+    }
+    p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
+    p.out0 = (void*)c; p.ldc = N; p.experts = experts; p.n_tiles = ceil_div(N, BN);
+    p.N = (int)N; p.K = (int)K; p.b_rows = (int)K;
+    return launch<MODE_PLAIN, false, true>(p, stream);
+}
+
+// C_e [M, N] (fp32) = A_e^T . B_e, A [rows, M], B [rows, N], contraction over the rows of expert e
+int tc_wgrad(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long M, long long N,
+             cudaStream_t stream) {
+    GemmParams p = {};
+    if (int rc = make_map(&p.map_a, a, (uint64_t)M, (uint64_t)r->rows_bound, 64)) return rc;
+    if (int rc = make_map(&p.map_b, b, (uint64_t)N, (uint64_t)r->rows_bound, 64)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    if (c & 15u || (N * 4) % 16) return fail_arg("weight-gradient output must be 16-byte aligned with a 16-byte row pitch");
+    p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
+    p.out0 = (void*)c; p.ldc = N; p.c_slab = M * N; p.experts = experts;
+    p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, BN);
+    p.M = (int)M; p.N = (int)N; p.K = 0; p.segments = 1;
+    return launch<MODE_WGRAD, true, true>(p, stream);
+}
+
+}  // namespace qmoe

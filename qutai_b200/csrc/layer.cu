@@ -1,0 +1,171 @@
+// Expert FFN forward/backward (engine selection between the tcgen05 kernels and the CUDA-core
+// kernels), the single-group GEMM of the host function table, and the whole-layer entry points.
+#include "common.cuh"
+
+namespace qmoe {
+
+namespace {
+
+int check_experts(const qmoe_route_t* r, const qmoe_experts_t* ex, int* engine) {
+    if (int rc = route_check(r)) return rc;
+    if (!ex) return fail_arg("experts is null");
+    if (ex->experts != r->experts) return fail_arg("experts.experts (%d) differs from route.experts (%d)", ex->experts, r->experts);
+    if (ex->dtype != QMOE_F32 && ex->dtype != QMOE_BF16) return fail_arg("experts.dtype must be QMOE_F32 or QMOE_BF16");
+    if (ex->width <= 0 || ex->hidden <= 0) return fail_arg("experts.width and experts.hidden must be positive");
+    if (!ex->w_gate || !ex->w_up || !ex->w_down) return fail_arg("experts has a null weight address");
+    int e = ex->engine;
+    const bool tc_ok = ex->dtype == QMOE_BF16 && tcgen05_shape_ok(ex->width, ex->hidden);
+    if (e == QMOE_ENGINE_AUTO) e = tc_ok ? QMOE_ENGINE_TCGEN05 : QMOE_ENGINE_SIMT;
+    if (e == QMOE_ENGINE_TCGEN05 && !tc_ok) {
+        set_error("the tcgen05 engine needs bf16 activations and widths that are multiples of 8 (d %lld, h %lld, dtype %d)",
+                  (long long)ex->width, (long long)ex->hidden, ex->dtype);
+        return QMOE_ERR_UNSUPPORTED;
+    }
+    if (e != QMOE_ENGINE_TCGEN05 && e != QMOE_ENGINE_SIMT) return fail_arg("experts.engine %d is unknown", ex->engine);
+    *engine = e;
+    return 0;
+}
+
+// C[rows, N] = A[rows, K] . op(B_e) on CUDA cores; b_kfast: B_e is [N, K] ("x W^T"), else [K, N]
+int simt_rows(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t a, uint64_t b, uint64_t a2, uint64_t b2, uint64_t c,
+              long long K, long long N, bool b_kfast, cudaStream_t stream) {
+    SimtGemmArgs g = {};
+    g.A = (const void*)a; g.B = (const void*)b; g.A2 = (const void*)a2; g.B2 = (const void*)b2; g.C = (void*)c;
+    g.M = r->rows_bound; g.N = N; g.K = K;
+    g.a_rs = K; g.a_cs = 1;
+    g.b_rs = b_kfast ? 1 : N; g.b_cs = b_kfast ? K : 1;
+    g.ldc = N; g.mode = SG_ROWS;
+    g.tile_expert = (const int*)r->tile_expert; g.meta = (const int*)r->meta;
+    g.b_slab = K * N;
+    return launch_simt_gemm(g, ex->dtype, ex->dtype, ex->dtype, r->rows_bound, 1, stream);
+}
+
+// C_e[M, N] (fp32) = A_e^T . B_e, A [rows, M], B [rows, N]
+int simt_wgrad(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t a, uint64_t b, uint64_t c, long long M, long long N,
+               cudaStream_t stream) {
+    SimtGemmArgs g = {};
+    g.A = (const void*)a; g.B = (const void*)b; g.C = (void*)c;
+    g.M = M; g.N = N; g.K = 0;
+    g.a_rs = 1; g.a_cs = M;
+    g.b_rs = N; g.b_cs = 1;
+    g.ldc = N; g.mode = SG_K;
+    g.offsets = (const int*)r->offsets; g.counts = (const int*)r->counts;
+    g.c_slab = M * N;
+    return launch_simt_gemm(g, ex->dtype, ex->dtype, QMOE_F32, M, ex->experts, stream);
+}
+
+}  // namespace
+}  // namespace qmoe
+
+using namespace qmoe;
+
+extern "C" int qmoe_expert_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t x, uint64_t g, uint64_t u,
+                                   uint64_t h, uint64_t y, uint64_t stream_) {
+    int engine = 0;
+    if (int rc = check_experts(r, ex, &engine)) return rc;
+    if (!x || !g || !u || !h || !y) return fail_arg("expert_forward: null buffer address");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const long long d = ex->width, hd = ex->hidden;
+    if (engine == QMOE_ENGINE_TCGEN05) {
+        TimedScope timed(KC_EXPERT_GEMM, stream);
+        if (int rc = tc_swiglu_forward(r, ex, x, g, u, h, stream)) return rc;
+        return tc_rows_nt(r, ex->experts, h, ex->w_down, y, hd, d, stream);
+    }
+    {
+        TimedScope timed(KC_EXPERT_GEMM, stream);
+        if (int rc = simt_rows(r, ex, x, ex->w_gate, 0, 0, g, d, hd, true, stream)) return rc;
+        if (int rc = simt_rows(r, ex, x, ex->w_up, 0, 0, u, d, hd, true, stream)) return rc;
+    }
+    if (int rc = launch_swiglu(r, g, u, h, ex->dtype, hd, stream)) return rc;
+    TimedScope timed(KC_EXPERT_GEMM, stream);
+    return simt_rows(r, ex, h, ex->w_down, 0, 0, y, hd, d, true, stream);
+}
+
+extern "C" int qmoe_expert_backward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t dy, uint64_t x, uint64_t g,
+                                    uint64_t u, uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx,
+                                    uint64_t d_w_gate, uint64_t d_w_up, uint64_t d_w_down, uint64_t stream_) {
+    int engine = 0;
+    if (int rc = check_experts(r, ex, &engine)) return rc;
+    if (!dy || !x || !g || !u || !h || !d_h || !d_g || !d_u || !dx || !d_w_gate || !d_w_up || !d_w_down)
+        return fail_arg("expert_backward: null buffer address");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const long long d = ex->width, hd = ex->hidden;
+    const bool tc = engine == QMOE_ENGINE_TCGEN05;
+    {   // dH = dY . Wd
+        TimedScope timed(KC_EXPERT_GEMM, stream);
+        if (int rc = tc ? tc_rows_nn(r, ex->experts, dy, ex->w_down, 0, 0, d_h, d, hd, stream)
+                        : simt_rows(r, ex, dy, ex->w_down, 0, 0, d_h, d, hd, false, stream)) return rc;
+    }
+    if (int rc = launch_swiglu_backward(r, d_h, g, u, d_g, d_u, ex->dtype, hd, stream)) return rc;
+    {   // weight gradients (dY is still intact here; dX may alias it and is written last)
+        TimedScope timed(KC_WGRAD_GEMM, stream);
+        if (int rc = tc ? tc_wgrad(r, ex->experts, dy, h, d_w_down, d, hd, stream)
+                        : simt_wgrad(r, ex, dy, h, d_w_down, d, hd, stream)) return rc;
+        if (int rc = tc ? tc_wgrad(r, ex->experts, d_g, x, d_w_gate, hd, d, stream)
+                        : simt_wgrad(r, ex, d_g, x, d_w_gate, hd, d, stream)) return rc;
+        if (int rc = tc ? tc_wgrad(r, ex->experts, d_u, x, d_w_up, hd, d, stream)
+                        : simt_wgrad(r, ex, d_u, x, d_w_up, hd, d, stream)) return rc;
+    }
+    TimedScope timed(KC_EXPERT_GEMM, stream);  // dX = dG . Wg + dU . Wu
+    return tc ? tc_rows_nn(r, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, stream)
+              : simt_rows(r, ex, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, false, stream);
+}
+
+extern "C" int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtype, uint64_t c, int32_t c_dtype, int64_t m,
+                         int64_t k, int64_t n, int32_t transpose_a, int32_t transpose_b, int32_t accumulate, uint64_t stream_) {
+    if (!a || !b || !c) return fail_arg("gemm: null address");
+    if (m <= 0 || n <= 0 || k <= 0) return fail_arg("gemm: sizes must be positive");
+    for (int dt : {a_dtype, b_dtype, c_dtype})
+        if (dt != QMOE_F32 && dt != QMOE_BF16) return fail_arg("gemm: dtype must be QMOE_F32 or QMOE_BF16");
+    if (c == a || c == b) return fail_arg("gemm: the output must not alias an input");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_OTHER, stream);
+    SimtGemmArgs g = {};
+    g.A = (const void*)a; g.B = (const void*)b; g.C = (void*)c;
+    g.M = m; g.N = n; g.K = k;
+    g.a_rs = transpose_a ? 1 : k; g.a_cs = transpose_a ? m : 1;
+    g.b_rs = transpose_b ? 1 : n; g.b_cs = transpose_b ? k : 1;
+    g.ldc = n; g.accumulate = accumulate; g.mode = SG_PLAIN;
+    return launch_simt_gemm(g, a_dtype, b_dtype, c_dtype, m, 1, stream);
+}
+
+extern "C" int qmoe_layer_forward(const qmoe_layer_t* L, uint64_t stream) {
+    if (!L) return fail_arg("layer is null");
+    const qmoe_route_t* r = &L->route;
+    const qmoe_experts_t* ex = &L->experts;
+    int engine = 0;
+    if (int rc = check_experts(r, ex, &engine)) return rc;
+    if (!L->x || !L->w_router || !L->scores || !L->x_dispatched || !L->g || !L->u || !L->h || !L->y_dispatched || !L->out)
+        return fail_arg("layer_forward: null buffer address");
+    const long long d = ex->width, hd = ex->hidden, E = ex->experts;
+    if (ex->dtype == QMOE_BF16 && L->master_gate) {
+        if (!L->master_up || !L->master_down) return fail_arg("layer_forward: master weights must be given together");
+        if (int rc = qmoe_cast_bf16(L->master_gate, ex->w_gate, E * hd * d, stream)) return rc;
+        if (int rc = qmoe_cast_bf16(L->master_up, ex->w_up, E * hd * d, stream)) return rc;
+        if (int rc = qmoe_cast_bf16(L->master_down, ex->w_down, E * hd * d, stream)) return rc;
+    }
+    if (int rc = qmoe_router_logits(L->x, ex->dtype, L->w_router, L->scores, r->tokens, d, r->experts, stream)) return rc;
+    if (int rc = qmoe_route(r, L->scores, stream)) return rc;
+    if (int rc = qmoe_permute(r, L->x, L->x_dispatched, ex->dtype, d, stream)) return rc;
+    if (int rc = qmoe_expert_forward(r, ex, L->x_dispatched, L->g, L->u, L->h, L->y_dispatched, stream)) return rc;
+    return qmoe_combine(r, L->y_dispatched, L->out, ex->dtype, d, stream);
+}
+
+extern "C" int qmoe_layer_backward(const qmoe_layer_t* L, uint64_t stream) {
+    if (!L) return fail_arg("layer is null");
+    const qmoe_route_t* r = &L->route;
+    const qmoe_experts_t* ex = &L->experts;
+    int engine = 0;
+    if (int rc = check_experts(r, ex, &engine)) return rc;
+    if (!L->grad_out || !L->dy_dispatched || !L->d_h || !L->d_g || !L->d_u || !L->dx_dispatched || !L->d_gate_weights ||
+        !L->d_scores || !L->dx_router || !L->router_partials || !L->dx || !L->d_w_router)
+        return fail_arg("layer_backward: null buffer address");
+    const long long d = ex->width;
+    if (int rc = qmoe_combine_backward(r, L->grad_out, L->y_dispatched, L->dy_dispatched, L->d_gate_weights, ex->dtype, d, stream)) return rc;
+    if (int rc = qmoe_expert_backward(r, ex, L->dy_dispatched, L->x_dispatched, L->g, L->u, L->h, L->d_h, L->d_g, L->d_u,
+                                      L->dx_dispatched, L->d_w_gate, L->d_w_up, L->d_w_down, stream)) return rc;
+    if (int rc = qmoe_route_backward(r, L->d_gate_weights, L->grad_aux, L->d_scores, stream)) return rc;
+    if (int rc = qmoe_router_backward(L->d_scores, L->x, ex->dtype, L->w_router, L->dx_router, L->d_w_router,
+                                      L->router_partials, r->tokens, d, r->experts, stream)) return rc;
+    return qmoe_unpermute_reduce(r, L->dx_dispatched, L->dx_router, L->dx, ex->dtype, d, stream);
+}

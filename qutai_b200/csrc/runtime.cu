@@ -1,0 +1,200 @@
+// Process-wide plumbing of libqutai_moe.so: error text, launch counters, per-kernel-class event
+// timing, the device status word, and the small memory/stream helpers of the C ABI.
+#include <atomic>
+#include <mutex>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <vector>
+
+#include "common.cuh"
+
+namespace qmoe {
+
+namespace {
+thread_local char g_error[1024] = "";
+std::atomic<long long> g_launches{0};
+std::atomic<long long> g_tc_launches{0};
+bool g_sync_each_launch = getenv("QUTAI_MOE_SYNC") && atoi(getenv("QUTAI_MOE_SYNC")) != 0;
+
+// timing
+std::mutex g_timing_mutex;
+bool g_timing = false;
+struct Scope { int kc; cudaEvent_t start, stop; };
+std::vector<Scope> g_scopes;
+const char* kClassNames[KC_COUNT] = {"router_gemm", "route", "permute", "expert_gemm", "swiglu", "combine",
+                                     "combine_backward", "wgrad_gemm", "unpermute", "route_backward",
+                                     "cast", "other"};
+__device__ int g_device_status;
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int fail_arg(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return QMOE_ERR_ARGUMENT;
+}
+
+int check_cuda(cudaError_t code, const char* what) {
+    if (code == cudaSuccess) return 0;
+    set_error("%s failed: %s (%s)", what, cudaGetErrorName(code), cudaGetErrorString(code));
+    return (int)code;
+}
+
+int after_launch(const char* name) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t code = cudaGetLastError();
+    if (code == cudaSuccess && g_sync_each_launch) code = cudaDeviceSynchronize();
+    if (code == cudaSuccess) return 0;
+    set_error("kernel %s failed: %s (%s)", name, cudaGetErrorName(code), cudaGetErrorString(code));
+    return (int)code;
+}
+
+void count_tensor_core_launch() { g_tc_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int* device_status_address() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_device_status) != cudaSuccess) return nullptr;
+    return p;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+TimedScope::TimedScope(KernelClass kc, cudaStream_t s) : slot(-1), stream(s) {
+    if (!g_timing) return;
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    Scope sc;
+    sc.kc = kc;
+    if (cudaEventCreate(&sc.start) != cudaSuccess) return;
+    if (cudaEventCreate(&sc.stop) != cudaSuccess) { cudaEventDestroy(sc.start); return; }
+    cudaEventRecord(sc.start, stream);
+    g_scopes.push_back(sc);
+    slot = (int)g_scopes.size() - 1;
+}
+
+TimedScope::~TimedScope() {
+    if (slot < 0) return;
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    if (slot < (int)g_scopes.size()) cudaEventRecord(g_scopes[slot].stop, stream);
+}
+
+}  // namespace qmoe
+
+using namespace qmoe;
+
+extern "C" int qmoe_version(void) { return QMOE_VERSION; }
+extern "C" const char* qmoe_last_error(void) { return g_error; }
+
+extern "C" int qmoe_device_info(int* sms, int* cc_major, int* cc_minor, uint64_t* total_bytes) {
+    int dev = 0;
+    QMOE_CUDA(cudaGetDevice(&dev));
+    cudaDeviceProp prop;
+    QMOE_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (sms) *sms = prop.multiProcessorCount;
+    if (cc_major) *cc_major = prop.major;
+    if (cc_minor) *cc_minor = prop.minor;
+    if (total_bytes) *total_bytes = (uint64_t)prop.totalGlobalMem;
+    return 0;
+}
+
+extern "C" int qmoe_malloc(uint64_t* address, uint64_t bytes) {
+    if (!address) return fail_arg("malloc: address is null");
+    void* p = nullptr;
+    QMOE_CUDA(cudaMalloc(&p, bytes ? bytes : 1));
+    *address = (uint64_t)p;
+    return 0;
+}
+extern "C" int qmoe_free(uint64_t address) {
+    if (!address) return 0;
+    QMOE_CUDA(cudaFree((void*)address));
+    return 0;
+}
+extern "C" int qmoe_host_alloc(void** host, uint64_t bytes) {
+    if (!host) return fail_arg("host_alloc: host is null");
+    QMOE_CUDA(cudaMallocHost(host, bytes ? bytes : 1));
+    return 0;
+}
+extern "C" int qmoe_host_free(void* host) {
+    if (!host) return 0;
+    QMOE_CUDA(cudaFreeHost(host));
+    return 0;
+}
+extern "C" int qmoe_memcpy_h2d(uint64_t dst, const void* src, uint64_t bytes, uint64_t stream) {
+    if (!bytes) return 0;
+    if (!dst || !src) return fail_arg("memcpy_h2d: null address");
+    QMOE_CUDA(cudaMemcpyAsync((void*)dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qmoe_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes, uint64_t stream) {
+    if (!bytes) return 0;
+    if (!dst || !src) return fail_arg("memcpy_d2h: null address");
+    QMOE_CUDA(cudaMemcpyAsync(dst, (const void*)src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qmoe_memcpy_d2d(uint64_t dst, uint64_t src, uint64_t bytes, uint64_t stream) {
+    if (!bytes) return 0;
+    if (!dst || !src) return fail_arg("memcpy_d2d: null address");
+    QMOE_CUDA(cudaMemcpyAsync((void*)dst, (const void*)src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qmoe_memset(uint64_t dst, int value, uint64_t bytes, uint64_t stream) {
+    if (!bytes) return 0;
+    if (!dst) return fail_arg("memset: null address");
+    QMOE_CUDA(cudaMemsetAsync((void*)dst, value, bytes, (cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qmoe_stream_sync(uint64_t stream) {
+    QMOE_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return 0;
+}
+extern "C" int64_t qmoe_launch_count(void) { return g_launches.load(); }
+extern "C" int64_t qmoe_tensor_core_launch_count(void) { return g_tc_launches.load(); }
+
+extern "C" int qmoe_timing_enable(int enable) {
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    for (auto& s : g_scopes) { cudaEventDestroy(s.start); cudaEventDestroy(s.stop); }
+    g_scopes.clear();
+    g_timing = enable != 0;
+    return 0;
+}
+extern "C" int qmoe_timing_classes(void) { return KC_COUNT; }
+extern "C" const char* qmoe_timing_class_name(int kc) { return kc >= 0 && kc < KC_COUNT ? kClassNames[kc] : ""; }
+extern "C" int qmoe_timing_read(double* ms, int64_t* scopes, int capacity) {
+    if (!ms || !scopes || capacity < KC_COUNT) return fail_arg("timing_read: need %d slots", KC_COUNT);
+    QMOE_CUDA(cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    for (int i = 0; i < KC_COUNT; ++i) { ms[i] = 0; scopes[i] = 0; }
+    for (auto& s : g_scopes) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, s.start, s.stop) == cudaSuccess) { ms[s.kc] += t; scopes[s.kc] += 1; }
+    }
+    return 0;
+}
+
+extern "C" int qmoe_device_status(uint64_t stream, int* status) {
+    if (!status) return fail_arg("device_status: status is null");
+    int* p = device_status_address();
+    if (!p) { set_error("device status symbol is not available"); return QMOE_ERR_STATE; }
+    QMOE_CUDA(cudaMemcpyAsync(status, p, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    QMOE_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return 0;
+}

@@ -1,0 +1,262 @@
+"""``SparseMoE`` for ``device="cuda"`` on B200: the host-side mirror of the upstream layer
+(src/qutai/lm/layers.py:354-408) over ``libqutai_moe.so``.
+
+Same constructor (``SparseMoE(config, *, device, dtype, seed)``), same attributes (``router``,
+``experts[i].gate/up/down`` with ``.weight`` of shape (outputs, inputs), ``top_k``, ``n_experts``,
+``utilization``, ``last_counts``) and the same ``parameters()`` order, so the parameter naming used
+by checkpoints (src/qutai/lm/decoder.py:57-68) is unchanged.  What differs is how the work runs:
+one fused call per direction (router logits, routing, permute, grouped expert FFN, combine) instead
+of a Python loop over experts, with no host synchronisation inside the layer.  The expert weights
+of one kind live in ONE stacked buffer ([E, h, d] / [E, d, h]); every ``weight`` is a view into it.
+
+``__call__``/``forward`` returns ``(y, aux)``; ``backward(grad_y, grad_aux)`` plays the role of the
+closures the upstream layer registers with autograd and leaves gradients in ``parameter.grad``
+(``None`` for an expert that received no token, as upstream, src/qutai/lm/layers.py:396).  A
+gradient produced by ``backward`` is a view of the layer's stacked gradient buffer and stays valid
+until the next ``backward`` of the same layer (which first copies out any gradient still in use).
+"""
+from __future__ import annotations
+
+import ctypes
+from math import prod, sqrt
+
+from . import lib
+from .storage import DeviceStorage
+
+
+class Tensor:
+    """Shape + storage + grad, with the attribute names of the upstream ``Tensor``
+    (src/qutai/core/tensor.py:14-33); just enough for parameters and activations of this layer."""
+
+    def __init__(self, storage, shape=None, requires_grad=False):
+        self.storage = storage
+        self.shape = tuple(shape) if shape is not None else (storage.size,)
+        if prod(self.shape) != storage.size:
+            raise ValueError("element count does not match the shape")
+        self.requires_grad = requires_grad
+        self.grad = None
+
+    device = "cuda"
+
+    @property
+    def dtype(self):
+        return self.storage.dtype
+
+    @property
+    def size(self):
+        return self.storage.size
+
+    def tolist(self):
+        return self.storage.tolist()
+
+    def zero_grad(self):
+        self.grad = None
+
+
+class Projection:
+    """Bias-free linear map with ``weight`` of shape (outputs, inputs) (src/qutai/lm/layers.py:260-272)."""
+
+    def __init__(self, weight):
+        self.weight = weight
+
+    def parameters(self):
+        return (self.weight,)
+
+
+class SwiGLU:
+    """Holder of one expert's three projections (src/qutai/lm/layers.py:291-314)."""
+
+    def __init__(self, gate, up, down):
+        self.gate, self.up, self.down = Projection(gate), Projection(up), Projection(down)
+
+    def parameters(self):
+        return (*self.gate.parameters(), *self.up.parameters(), *self.down.parameters())
+
+
+def _accumulate(parameter, view, stream):
+    """Leaf accumulation (src/qutai/core/tensor.py:203-210).  The first contribution is handed out
+    as a view of the layer's stacked gradient buffer (no copy); a later one is summed into a fresh
+    storage."""
+    if parameter.grad is None:
+        parameter.grad = view
+        return
+    out = DeviceStorage(view.size, view.storage.dtype)
+    lib.call("qmoe_add", parameter.grad.storage.ptr, view.storage.ptr, out.ptr,
+             lib.DTYPE_CODES[view.storage.dtype], view.size, stream)
+    parameter.grad = Tensor(out, parameter.shape)
+
+
+class SparseMoE:
+    def __init__(self, config, *, device="cuda", dtype="float32", seed=None, engine="auto", stream=0):
+        if device != "cuda":
+            raise ValueError("this layer only runs on device='cuda' (there is no CPU fallback)")
+        if dtype != "float32":
+            raise ValueError("parameters are float32 (bf16 is an activation dtype, as upstream)")
+        d, E, h = config.d_model, config.n_experts, config.d_expert
+        if not 1 <= config.top_k <= min(E, lib.MAX_TOP_K) or E > lib.MAX_EXPERTS:
+            raise ValueError(f"need 1 <= top_k <= min(n_experts, {lib.MAX_TOP_K}) and n_experts <= {lib.MAX_EXPERTS}")
+        self.top_k, self.n_experts, self.d_model, self.d_expert = config.top_k, E, d, h
+        self.stream = stream
+        self.engine = {"auto": lib.ENGINE_AUTO, "simt": lib.ENGINE_SIMT, "tcgen05": lib.ENGINE_TCGEN05}[engine]
+        self._gate = DeviceStorage(E * h * d, "float32")
+        self._up = DeviceStorage(E * h * d, "float32")
+        self._down = DeviceStorage(E * d * h, "float32")
+        router = DeviceStorage(E * d, "float32")
+        down_std = 0.02 / sqrt(2 * config.n_layers)
+
+        def fill(storage, std, tensor_seed):
+            # one generator stream per parameter tensor, keyed like upstream: router seed, expert i
+            # gate seed+1+3i, up +1, down +2 (src/qutai/lm/layers.py:355-371, :292-308)
+            key = 0x5EED if tensor_seed is None else tensor_seed
+            lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std, key & (2 ** 64 - 1), stream)
+
+        fill(router, 0.02, seed)
+        self.router = Projection(Tensor(router, (E, d), requires_grad=True))
+        experts = []
+        for i in range(E):
+            views = (self._gate.view(i * h * d, h * d), self._up.view(i * h * d, h * d), self._down.view(i * d * h, d * h))
+            base = None if seed is None else seed + 1 + 3 * i
+            fill(views[0], 0.02, base)
+            fill(views[1], 0.02, None if base is None else base + 1)
+            fill(views[2], down_std, None if base is None else base + 2)
+            experts.append(SwiGLU(Tensor(views[0], (h, d), requires_grad=True),
+                                  Tensor(views[1], (h, d), requires_grad=True),
+                                  Tensor(views[2], (d, h), requires_grad=True)))
+        self.experts = tuple(experts)
+        self.utilization = None
+        self._counts_host = None
+        self._counts_valid = False
+        self._zero_counts = (0,) * E
+        self._work = {}
+        self._saved = None
+
+    # ------------------------------------------------------------------------------------------
+    def parameters(self):
+        return (*self.router.parameters(), *(p for expert in self.experts for p in expert.parameters()))
+
+    @property
+    def last_counts(self):
+        """Tokens routed to each expert in the last forward, as Python ints.  Reading it is the
+        only thing that waits for the device (upstream downloads the counts inside every forward,
+        src/qutai/backends/cuda_lm.py:432-434)."""
+        if not self._counts_valid:
+            return self._zero_counts
+        lib.call("qmoe_stream_sync", self.stream)
+        return tuple(self._counts_host[i] for i in range(self.n_experts))
+
+    # ------------------------------------------------------------------------------------------
+    def _workspace(self, tokens, dtype):
+        key = (tokens, dtype)
+        work = self._work.get(key)
+        if work is not None:
+            return work
+        E, k, d, h = self.n_experts, self.top_k, self.d_model, self.d_expert
+        A = tokens * k
+        R = lib.rows_bound(tokens, E, k)
+        blocks = lib.route_blocks(tokens)
+        S = DeviceStorage
+        buf = dict(
+            probs=S(tokens * E, "float32"), gate_weights=S(A, "float32"), expert_index=S(A, "int32"),
+            dest_row=S(A, "int32"), row_source=S(R, "int32"), counts=S(E, "int32"), offsets=S(E + 1, "int32"),
+            tile_expert=S(R // lib.ROW_PAD, "int32"), meta=S(4, "int32"), utilization=S(E, "float32"),
+            aux=S(1, "float32"), block_counts=S(blocks * E, "int32"), block_base=S(blocks * E, "int32"),
+            block_colsum=S(blocks * E, "float32"),
+            scores=S(tokens * E, "float32"),
+            x_dispatched=S(R * d, dtype), g=S(R * h, dtype), u=S(R * h, dtype), h=S(R * h, dtype),
+            y_dispatched=S(R * d, dtype),
+            dy_dispatched=S(R * d, dtype), d_h=S(R * h, dtype), d_g=S(R * h, dtype), d_u=S(R * h, dtype),
+            d_gate_weights=S(A, "float32"), d_scores=S(tokens * E, "float32"), dx_router=S(tokens * d, "float32"),
+            router_partials=S(int(lib.load().qmoe_router_grad_partials(tokens, E, d)), "float32"),
+            d_w_router=S(E * d, "float32"), d_w_gate=S(E * h * d, "float32"), d_w_up=S(E * h * d, "float32"),
+            d_w_down=S(E * d * h, "float32"),
+        )
+        if dtype == "bfloat16":
+            buf.update(w_gate=S(E * h * d, "bfloat16"), w_up=S(E * h * d, "bfloat16"), w_down=S(E * d * h, "bfloat16"))
+        layer = lib.Layer()
+        route = layer.route
+        route.tokens, route.experts, route.top_k, route.rows_bound = tokens, E, k, R
+        for name in ("probs", "gate_weights", "expert_index", "dest_row", "row_source", "counts", "offsets",
+                     "tile_expert", "meta", "utilization", "aux", "block_counts", "block_base", "block_colsum"):
+            setattr(route, name, buf[name].ptr)
+        ex = layer.experts
+        ex.experts, ex.dtype, ex.engine, ex.width, ex.hidden = E, lib.DTYPE_CODES[dtype], self.engine, d, h
+        if dtype == "bfloat16":
+            ex.w_gate, ex.w_up, ex.w_down = buf["w_gate"].ptr, buf["w_up"].ptr, buf["w_down"].ptr
+            layer.master_gate, layer.master_up, layer.master_down = self._gate.ptr, self._up.ptr, self._down.ptr
+        else:
+            ex.w_gate, ex.w_up, ex.w_down = self._gate.ptr, self._up.ptr, self._down.ptr
+        layer.w_router = self.router.weight.storage.ptr
+        for name in ("scores", "x_dispatched", "g", "u", "h", "y_dispatched", "dy_dispatched", "d_h", "d_g", "d_u",
+                     "d_gate_weights", "d_scores", "dx_router", "router_partials", "d_w_router", "d_w_gate",
+                     "d_w_up", "d_w_down"):
+            setattr(layer, name, buf[name].ptr)
+        layer.dx_dispatched = buf["dy_dispatched"].ptr  # dX reuses dY's buffer (written after its last reader)
+        if self._counts_host is None:
+            host = ctypes.c_void_p()
+            lib.call("qmoe_host_alloc", ctypes.byref(host), 4 * E)
+            self._counts_host = ctypes.cast(host, ctypes.POINTER(ctypes.c_int32))
+        grad_views = [Tensor(buf["d_w_router"], (E, d))]
+        for i in range(E):
+            grad_views.append((Tensor(buf["d_w_gate"].view(i * h * d, h * d), (h, d)),
+                               Tensor(buf["d_w_up"].view(i * h * d, h * d), (h, d)),
+                               Tensor(buf["d_w_down"].view(i * d * h, d * h), (d, h))))
+        work = dict(buf=buf, layer=layer, rows_bound=R, grad_views=grad_views)
+        self._work = {key: work}  # one token count at a time keeps memory bounded
+        return work
+
+    def __call__(self, x):
+        return self.forward(x)
+
+    def forward(self, x):
+        """``x``: Tensor (or storage + implicit (T, d)) of float32 or bfloat16 activations on the
+        device.  Returns ``(y, aux)``: ``y`` shaped like ``x`` in the same dtype, ``aux`` a float32
+        scalar tensor (src/qutai/lm/layers.py:376-402)."""
+        storage = x.storage if hasattr(x, "storage") else x
+        shape = tuple(x.shape) if hasattr(x, "shape") and not hasattr(x, "ptr") else (storage.size // self.d_model, self.d_model)
+        if shape[-1] != self.d_model or storage.dtype not in lib.DTYPE_CODES:
+            raise ValueError("input must be (..., d_model) float32 or bfloat16")
+        tokens = storage.size // self.d_model
+        work = self._workspace(tokens, storage.dtype)
+        layer, buf = work["layer"], work["buf"]
+        out = DeviceStorage(storage.size, storage.dtype)
+        layer.x, layer.out = storage.ptr, out.ptr
+        lib.call("qmoe_layer_forward", ctypes.byref(layer), self.stream)
+        lib.call("qmoe_memcpy_d2h", ctypes.cast(self._counts_host, ctypes.c_void_p), buf["counts"].ptr,
+                 4 * self.n_experts, self.stream)
+        self._counts_valid = True
+        self.utilization = Tensor(buf["utilization"], (self.n_experts,))
+        self._saved = (work, storage, shape)
+        return Tensor(out, shape), Tensor(buf["aux"], ())
+
+    def backward(self, grad_y, grad_aux=None):
+        """Propagate ``grad_y`` (shaped like the output) and optionally ``grad_aux`` (float32
+        scalar storage/tensor) through the last forward.  Accumulates into ``parameter.grad`` and
+        returns the gradient of the input as a Tensor."""
+        if self._saved is None:
+            raise RuntimeError("backward called before forward")
+        work, x_storage, shape = self._saved
+        layer, buf = work["layer"], work["buf"]
+        g = grad_y.storage if hasattr(grad_y, "storage") else grad_y
+        if g.size != x_storage.size or g.dtype != x_storage.dtype:
+            raise ValueError("grad_y must match the output's size and dtype")
+        ga = None if grad_aux is None else (grad_aux.storage if hasattr(grad_aux, "storage") else grad_aux)
+        # which experts get a gradient is host logic: wait for the forward's counts (long done)
+        counts = self.last_counts
+        views = work["grad_views"]
+        owned = {id(views[0])} | {id(t) for group in views[1:] for t in group}
+        for parameter in self.parameters():
+            # a gradient that still aliases the buffers about to be overwritten is copied out first
+            if parameter.grad is not None and id(parameter.grad) in owned:
+                parameter.grad = Tensor(parameter.grad.storage.copy(self.stream), parameter.shape)
+        dx = DeviceStorage(x_storage.size, x_storage.dtype)
+        layer.grad_out, layer.grad_aux, layer.dx = g.ptr, 0 if ga is None else ga.ptr, dx.ptr
+        lib.call("qmoe_layer_backward", ctypes.byref(layer), self.stream)
+        _accumulate(self.router.weight, views[0], self.stream)
+        for i, expert in enumerate(self.experts):
+            if not counts[i]:
+                continue
+            gate, up, down = views[1 + i]
+            _accumulate(expert.gate.weight, gate, self.stream)
+            _accumulate(expert.up.weight, up, self.stream)
+            _accumulate(expert.down.weight, down, self.stream)
+        return Tensor(dx, shape)

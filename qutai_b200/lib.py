@@ -1,0 +1,174 @@
+"""ctypes binding of ``libqutai_moe.so`` (declared in ``include/qutai_moe.h``).
+
+Dependency-free: only the standard library.  Importing this module never touches CUDA; the
+library is loaded on first use (the upstream package behaves the same way,
+tests/test_cuda.py:12-16).  There is no CPU fallback: when the library cannot be loaded every
+operation raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_int, c_int32, c_int64,
+                    c_uint64, c_void_p)
+
+QMOE_F32, QMOE_BF16 = 0, 1
+ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05 = 0, 1, 2
+ROW_PAD, MAX_EXPERTS, MAX_TOP_K = 128, 256, 8
+DTYPE_CODES = {"float32": QMOE_F32, "bfloat16": QMOE_BF16}
+ITEM_BYTES = {"float32": 4, "bfloat16": 2, "int32": 4, "int64": 8, "float64": 8}
+
+
+class Route(Structure):
+    """``qmoe_route_t``."""
+    _fields_ = [("tokens", c_int64), ("experts", c_int32), ("top_k", c_int32), ("rows_bound", c_int64)] + [
+        (name, c_uint64) for name in (
+            "probs", "gate_weights", "expert_index", "dest_row", "row_source", "counts", "offsets",
+            "tile_expert", "meta", "utilization", "aux", "block_counts", "block_base", "block_colsum")]
+
+
+class Experts(Structure):
+    """``qmoe_experts_t``."""
+    _fields_ = [("experts", c_int32), ("dtype", c_int32), ("engine", c_int32), ("reserved", c_int32),
+                ("width", c_int64), ("hidden", c_int64),
+                ("w_gate", c_uint64), ("w_up", c_uint64), ("w_down", c_uint64)]
+
+
+class Layer(Structure):
+    """``qmoe_layer_t``."""
+    _fields_ = [("route", Route), ("experts", Experts)] + [
+        (name, c_uint64) for name in (
+            "x", "w_router", "scores", "x_dispatched", "g", "u", "h", "y_dispatched", "out",
+            "grad_out", "grad_aux", "dy_dispatched", "d_h", "d_g", "d_u", "dx_dispatched",
+            "d_gate_weights", "d_scores", "dx_router", "router_partials", "dx", "d_w_router",
+            "d_w_gate", "d_w_up", "d_w_down", "master_gate", "master_up", "master_down")]
+
+
+_U, _I32, _I64 = c_uint64, c_int32, c_int64
+_RP, _EP, _LP = POINTER(Route), POINTER(Experts), POINTER(Layer)
+
+# name -> (restype, argtypes); every symbol declared in include/qutai_moe.h
+SIGNATURES = {
+    "qmoe_version": (c_int, []),
+    "qmoe_last_error": (c_char_p, []),
+    "qmoe_device_info": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_uint64)]),
+    "qmoe_malloc": (c_int, [POINTER(c_uint64), _U]),
+    "qmoe_free": (c_int, [_U]),
+    "qmoe_host_alloc": (c_int, [POINTER(c_void_p), _U]),
+    "qmoe_host_free": (c_int, [c_void_p]),
+    "qmoe_memcpy_h2d": (c_int, [_U, c_void_p, _U, _U]),
+    "qmoe_memcpy_d2h": (c_int, [c_void_p, _U, _U, _U]),
+    "qmoe_memcpy_d2d": (c_int, [_U, _U, _U, _U]),
+    "qmoe_memset": (c_int, [_U, c_int, _U, _U]),
+    "qmoe_stream_sync": (c_int, [_U]),
+    "qmoe_launch_count": (c_int64, []),
+    "qmoe_tensor_core_launch_count": (c_int64, []),
+    "qmoe_timing_enable": (c_int, [c_int]),
+    "qmoe_timing_classes": (c_int, []),
+    "qmoe_timing_class_name": (c_char_p, [c_int]),
+    "qmoe_timing_read": (c_int, [POINTER(c_double), POINTER(c_int64), c_int]),
+    "qmoe_device_status": (c_int, [_U, POINTER(c_int)]),
+    "qmoe_rows_bound": (c_int64, [_I64, _I32, _I32]),
+    "qmoe_route_blocks": (c_int64, [_I64]),
+    "qmoe_router_logits": (c_int, [_U, _I32, _U, _U, _I64, _I64, _I32, _U]),
+    "qmoe_router_grad_partials": (c_int64, [_I64, _I32, _I64]),
+    "qmoe_router_backward": (c_int, [_U, _U, _I32, _U, _U, _U, _U, _I64, _I64, _I32, _U]),
+    "qmoe_route": (c_int, [_RP, _U, _U]),
+    "qmoe_route_export_i64": (c_int, [_RP, _U, _U, _U, _U, _U, _I64, _U]),
+    "qmoe_route_backward": (c_int, [_RP, _U, _U, _U, _U]),
+    "qmoe_permute": (c_int, [_RP, _U, _U, _I32, _I64, _U]),
+    "qmoe_unpermute_reduce": (c_int, [_RP, _U, _U, _U, _I32, _I64, _U]),
+    "qmoe_combine": (c_int, [_RP, _U, _U, _I32, _I64, _U]),
+    "qmoe_combine_backward": (c_int, [_RP, _U, _U, _U, _U, _I32, _I64, _U]),
+    "qmoe_cast_bf16": (c_int, [_U, _U, _I64, _U]),
+    "qmoe_expert_forward": (c_int, [_RP, _EP, _U, _U, _U, _U, _U, _U]),
+    "qmoe_expert_backward": (c_int, [_RP, _EP] + [_U] * 13),
+    "qmoe_gemm": (c_int, [_U, _I32, _U, _I32, _U, _I32, _I64, _I64, _I64, _I32, _I32, _I32, _U]),
+    "qmoe_silu": (c_int, [_U, _U, _U, _I32, _I64, _I32, _U]),
+    "qmoe_add": (c_int, [_U, _U, _U, _I32, _I64, _U]),
+    "qmoe_normal_fill": (c_int, [_U, _I32, _I64, c_double, c_double, _U, _U]),
+    "qmoe_layer_forward": (c_int, [_LP, _U]),
+    "qmoe_layer_backward": (c_int, [_LP, _U]),
+}
+
+_lock = threading.Lock()
+_library = None
+
+
+def library_path():
+    override = os.environ.get("QUTAI_MOE_LIBRARY")
+    if override:
+        return override
+    from . import build
+
+    return build.ensure_built()
+
+
+def load(path=None):
+    """Load the shared library (once) and attach the signatures."""
+    global _library
+    with _lock:
+        if _library is not None and path is None:
+            return _library
+        handle = ctypes.CDLL(path or library_path())
+        for name, (restype, argtypes) in SIGNATURES.items():
+            function = getattr(handle, name)  # AttributeError if an export is missing
+            function.restype, function.argtypes = restype, argtypes
+        if path is None:
+            _library = handle
+        return handle
+
+
+def last_error():
+    text = load().qmoe_last_error()
+    return text.decode("utf-8", "replace") if text else ""
+
+
+def check(code):
+    """Turn a return code into the upstream error convention: ValueError for argument errors
+    (raised upstream before any launch, src/qutai/backends/cuda.py:307-334), RuntimeError for
+    CUDA failures (src/qutai/backends/cuda_runtime.py:165-177)."""
+    if code == 0:
+        return
+    message = last_error() or f"libqutai_moe error {code}"
+    if code in (-1, -2):
+        raise ValueError(message)
+    raise RuntimeError(f"{message} [code {code}]")
+
+
+def call(name, *args):
+    check(getattr(load(), name)(*args))
+
+
+def rows_bound(tokens, experts, top_k):
+    return int(load().qmoe_rows_bound(tokens, experts, top_k))
+
+
+def route_blocks(tokens):
+    return int(load().qmoe_route_blocks(tokens))
+
+
+def device_info():
+    sms, major, minor, total = c_int(), c_int(), c_int(), c_uint64()
+    call("qmoe_device_info", byref(sms), byref(major), byref(minor), byref(total))
+    return dict(sm_count=sms.value, compute_capability=(major.value, minor.value), total_bytes=total.value)
+
+
+def timing(enable):
+    call("qmoe_timing_enable", 1 if enable else 0)
+
+
+def timing_read():
+    """{class name: (milliseconds, scopes)} since ``timing(True)``; synchronises the device."""
+    handle = load()
+    n = handle.qmoe_timing_classes()
+    ms, scopes = (c_double * n)(), (c_int64 * n)()
+    call("qmoe_timing_read", ms, scopes, n)
+    return {handle.qmoe_timing_class_name(i).decode(): (ms[i], scopes[i]) for i in range(n)}
+
+
+def device_status(stream=0):
+    status = c_int()
+    call("qmoe_device_status", stream, byref(status))
+    return status.value

@@ -1,0 +1,168 @@
+"""Device buffers for the host side of the MoE layer.
+
+``DeviceStorage`` carries the same fields the upstream ``CUDAStorage`` exposes (``ptr``, ``size``,
+``dtype``, ``nbytes``, ``device``; src/qutai/backends/cuda.py:20-58), so every function of
+``qutai_b200.cuda_lm`` accepts either kind — all they read is ``ptr``/``size``/``dtype``.  A storage
+either owns an allocation made through the library, or wraps memory owned by someone else (an
+upstream ``CUDAStorage``, a ``torch`` tensor's ``data_ptr()``), or is a view into another storage
+(how the stacked expert weights are handed out as separate parameters).
+"""
+from __future__ import annotations
+
+import ctypes
+import struct
+from array import array
+
+from . import lib
+
+_FORMATS = {"float32": "f", "float64": "d", "int32": "i", "int64": "q"}
+_cache: dict[int, list[int]] = {}
+_cached_bytes = 0
+CACHE_LIMIT_BYTES = 1 << 30
+
+
+def _bucket(nbytes):
+    step = 512 if nbytes < (1 << 16) else 1 << 16
+    return max(step, (nbytes + step - 1) // step * step)
+
+
+def _allocate(nbytes):
+    global _cached_bytes
+    size = _bucket(nbytes)
+    free = _cache.get(size)
+    if free:
+        _cached_bytes -= size
+        return free.pop(), size
+    address = ctypes.c_uint64()
+    try:
+        lib.call("qmoe_malloc", ctypes.byref(address), size)
+    except RuntimeError:
+        empty_cache()  # out of memory: drop cached blocks and try once more
+        lib.call("qmoe_malloc", ctypes.byref(address), size)
+    return address.value, size
+
+
+def _release(address, size):
+    global _cached_bytes
+    if _cached_bytes + size > CACHE_LIMIT_BYTES:
+        lib.load().qmoe_free(address)
+        return
+    _cache.setdefault(size, []).append(address)
+    _cached_bytes += size
+
+
+def empty_cache():
+    global _cached_bytes
+    handle = lib.load()
+    for blocks in _cache.values():
+        for address in blocks:
+            handle.qmoe_free(address)
+    _cache.clear()
+    _cached_bytes = 0
+
+
+def bf16_bits(value):
+    """Round one float to bfloat16 (nearest, ties to even) and return its 16 bits."""
+    bits = struct.unpack("<I", struct.pack("<f", value))[0]
+    if (bits & 0x7F800000) == 0x7F800000 and bits & 0x007FFFFF:
+        return (bits >> 16) | 0x40  # NaN stays NaN
+    return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) & 0xFFFF
+
+
+class DeviceStorage:
+    device = "cuda"
+
+    def __init__(self, size, dtype="float32", *, ptr=None, owner=None):
+        if dtype not in lib.ITEM_BYTES:
+            raise ValueError(f"unsupported dtype {dtype!r}")
+        if size < 0:
+            raise ValueError("size must not be negative")
+        self.size, self.dtype = int(size), dtype
+        self.nbytes = self.size * lib.ITEM_BYTES[dtype]
+        self._owner = owner
+        self._block = None
+        if ptr is None:
+            self.ptr, self._block = _allocate(max(self.nbytes, 1))
+        else:
+            self.ptr = int(ptr)
+
+    def __del__(self):
+        block, self._block = getattr(self, "_block", None), None
+        if block is not None:
+            try:
+                _release(self.ptr, block)
+            except Exception:
+                pass
+
+    # -- construction ---------------------------------------------------------------------
+    @classmethod
+    def wrap(cls, ptr, size, dtype, owner=None):
+        """Storage over memory owned elsewhere; ``owner`` is kept alive with it."""
+        return cls(size, dtype, ptr=ptr, owner=owner)
+
+    def view(self, start, size):
+        """Elements [start, start + size) of this storage as a storage of their own."""
+        if start < 0 or size < 0 or start + size > self.size:
+            raise ValueError("view exceeds the storage")
+        return DeviceStorage(size, self.dtype, ptr=self.ptr + start * lib.ITEM_BYTES[self.dtype], owner=self)
+
+    @classmethod
+    def zeros(cls, size, dtype="float32", stream=0):
+        out = cls(size, dtype)
+        out.fill_zero(stream)
+        return out
+
+    @classmethod
+    def from_bytes(cls, data, dtype, stream=0):
+        item = lib.ITEM_BYTES[dtype]
+        if len(data) % item:
+            raise ValueError("byte length is not a multiple of the item size")
+        out = cls(len(data) // item, dtype)
+        out.upload_bytes(data, stream)
+        return out
+
+    @classmethod
+    def from_values(cls, values, dtype="float32", stream=0):
+        values = list(values)
+        if dtype == "bfloat16":
+            data = array("H", (bf16_bits(float(v)) for v in values)).tobytes()
+        else:
+            data = array(_FORMATS[dtype], values).tobytes()
+        return cls.from_bytes(data, dtype, stream)
+
+    # -- transfers ------------------------------------------------------------------------
+    def fill_zero(self, stream=0):
+        lib.call("qmoe_memset", self.ptr, 0, self.nbytes, stream)
+
+    def upload_bytes(self, data, stream=0):
+        if len(data) != self.nbytes:
+            raise ValueError("byte length does not match the storage")
+        buffer = (ctypes.c_char * len(data)).from_buffer_copy(data) if len(data) else None
+        if buffer is not None:
+            lib.call("qmoe_memcpy_h2d", self.ptr, ctypes.cast(buffer, ctypes.c_void_p), self.nbytes, stream)
+            lib.call("qmoe_stream_sync", stream)  # the staging buffer dies with this call
+
+    def tobytes(self, stream=0):
+        buffer = ctypes.create_string_buffer(self.nbytes)
+        if self.nbytes:
+            lib.call("qmoe_memcpy_d2h", ctypes.cast(buffer, ctypes.c_void_p), self.ptr, self.nbytes, stream)
+            lib.call("qmoe_stream_sync", stream)
+        return buffer.raw
+
+    def tolist(self, stream=0):
+        data = self.tobytes(stream)
+        if self.dtype == "bfloat16":
+            halves = array("H")
+            halves.frombytes(data)
+            return [struct.unpack("<f", struct.pack("<I", h << 16))[0] for h in halves]
+        out = array(_FORMATS[self.dtype])
+        out.frombytes(data)
+        return out.tolist()
+
+    def copy(self, stream=0):
+        out = DeviceStorage(self.size, self.dtype)
+        lib.call("qmoe_memcpy_d2d", out.ptr, self.ptr, self.nbytes, stream)
+        return out
+
+    def __len__(self):
+        return self.size

@@ -1,0 +1,291 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the golden fixtures.
+Needs a B200: run with ``-m gpu``."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import golden_files
+from oracle import moe_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-4   # max relative error of outputs and gradients, fp32 activations
+BF16_TOL = 2e-2   # the same bar for bf16 activations
+
+
+def rel(a, b):
+    return oracle.max_rel_err(a, b)
+
+
+# ------------------------------------------------------------------------------------------------
+# routing: bit-exact integer tables
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("path", golden_files("routing"), ids=os.path.basename)
+def test_routing_golden(path):
+    from gpu_util import RouteTables, check_route_against_oracle, to_device, to_host
+    from qutai_b200 import lib
+    from qutai_b200.storage import DeviceStorage
+
+    g = np.load(path)
+    scores, k = g["scores"], int(g["top_k"])
+    T, E = scores.shape
+    tables = RouteTables(T, E, k)
+    dev_scores = to_device(scores, "float32")
+    expected = oracle.routing(scores.astype(np.float32).astype(np.float64), k)
+    assert np.array_equal(expected["indices"], g["indices"])  # the fixture itself
+    for _ in range(3):  # run-to-run identical, like the upstream test repeats it (tests/test_lm_moe.py:151)
+        tables.run(dev_scores)
+        check_route_against_oracle(tables, expected)
+    # backward of both paths, separately and fused
+    gw, ga = to_device(g["grad_weights"], "float32"), to_device(np.array([float(g["grad_aux"])]), "float32")
+    out = DeviceStorage(T * E, "float32")
+    lib.call("qmoe_route_backward", tables.ref, gw.ptr, 0, out.ptr, 0)
+    assert np.abs(to_host(out, (T, E)) - g["d_scores_gate"]).max() <= 2e-6
+    lib.call("qmoe_route_backward", tables.ref, 0, ga.ptr, out.ptr, 0)
+    assert np.abs(to_host(out, (T, E)) - g["d_scores_aux"]).max() <= 2e-6
+    lib.call("qmoe_route_backward", tables.ref, gw.ptr, ga.ptr, out.ptr, 0)
+    assert np.abs(to_host(out, (T, E)) - (g["d_scores_gate"] + g["d_scores_aux"])).max() <= 4e-6
+
+
+@pytest.mark.parametrize("T,E,k,skew", [(1, 1, 1, 0.0), (1, 8, 2, 0.0), (127, 8, 2, 0.0), (129, 9, 3, 0.0),
+                                        (5000, 64, 6, 0.5), (16384, 8, 2, 0.0), (4099, 256, 8, 1.0),
+                                        (3000, 33, 8, 0.0)])
+def test_routing_random_and_quantised(T, E, k, skew):
+    from gpu_util import RouteTables, check_route_against_oracle, to_device
+
+    rng = np.random.default_rng(T * 131 + E)
+    for quantise in (False, True):
+        scores = rng.standard_normal((T, E)) + skew * rng.standard_normal(E)[None, :]
+        if quantise:  # many exact ties in every row
+            scores = np.round(scores * 2) / 2
+        scores = scores.astype(np.float32)
+        tables = RouteTables(T, E, k)
+        tables.run(to_device(scores, "float32"))
+        check_route_against_oracle(tables, oracle.routing(scores.astype(np.float64), k), float_tol=4e-6)
+
+
+def test_routing_rejects_bad_arguments():
+    from gpu_util import RouteTables, to_device
+    from qutai_b200 import lib
+
+    tables = RouteTables(8, 4, 2)
+    scores = to_device(np.zeros((8, 4)), "float32")
+    tables.struct.top_k = 5
+    with pytest.raises(ValueError):
+        lib.call("qmoe_route", tables.ref, scores.ptr, 0)
+    tables.struct.top_k = 2
+    tables.struct.counts = 0
+    with pytest.raises(ValueError):
+        lib.call("qmoe_route", tables.ref, scores.ptr, 0)
+
+
+# ------------------------------------------------------------------------------------------------
+# permute / combine and their backwards
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,E,k,d", [(5, 3, 2, 4), (37, 4, 2, 16), (300, 8, 3, 72), (1000, 64, 6, 256), (64, 5, 1, 1030)])
+def test_permute_combine_and_backwards(T, E, k, d, dtype):
+    from gpu_util import RouteTables, to_device, to_host
+    from qutai_b200 import lib
+    from qutai_b200.storage import DeviceStorage
+
+    rng = np.random.default_rng(T + d)
+    code = lib.DTYPE_CODES[dtype]
+    rnd = oracle.round_bf16 if dtype == "bfloat16" else (lambda a: np.asarray(a, dtype=np.float32).astype(np.float64))
+    tol = 1e-2 if dtype == "bfloat16" else 2e-6
+    scores = rng.standard_normal((T, E)).astype(np.float32)
+    x, gout = rnd(rng.standard_normal((T, d))), rnd(rng.standard_normal((T, d)))
+    route = oracle.routing(scores.astype(np.float64), k)
+    tables = RouteTables(T, E, k)
+    tables.run(to_device(scores, "float32"))
+    R = tables.rows_bound
+    offsets, counts = tables.host("offsets"), tables.host("counts")
+    weights = tables.host("gate_weights", (T, k))
+
+    xd = DeviceStorage(R * d, dtype)
+    lib.call("qmoe_memset", xd.ptr, 0x7f, xd.nbytes, 0)  # stale data must not survive in pad rows
+    lib.call("qmoe_permute", tables.ref, to_device(x, dtype).ptr, xd.ptr, code, d, 0)
+    xh = to_host(xd, (R, d))
+    for e in range(E):
+        assert np.array_equal(xh[offsets[e]: offsets[e] + counts[e]], oracle.route_gather(x, route, e))
+        assert np.all(xh[offsets[e] + counts[e]: offsets[e + 1]] == 0)
+
+    # expert outputs: any values in the dispatched layout
+    yd_host = np.zeros((R, d))
+    outputs = []
+    for e in range(E):
+        if counts[e]:
+            ye = rnd(rng.standard_normal((counts[e], d)))
+            yd_host[offsets[e]: offsets[e] + counts[e]] = ye
+            outputs.append((e, ye))
+    yd = to_device(yd_host, dtype)
+    out = DeviceStorage(T * d, dtype)
+    lib.call("qmoe_combine", tables.ref, yd.ptr, out.ptr, code, d, 0)
+    route_w = dict(route, weights=weights)
+    assert rel(to_host(out, (T, d)), oracle.combine(outputs, weights, route_w)) <= tol
+
+    dy, dw = DeviceStorage(R * d, dtype), DeviceStorage(T * k, "float32")
+    lib.call("qmoe_memset", dy.ptr, 0x7f, dy.nbytes, 0)
+    lib.call("qmoe_combine_backward", tables.ref, to_device(gout, dtype).ptr, yd.ptr, dy.ptr, dw.ptr, code, d, 0)
+    want_dy, want_dw = oracle.combine_backward(gout, outputs, weights, route_w)
+    dyh = to_host(dy, (R, d))
+    for (e, _), want in zip(outputs, want_dy):
+        assert rel(dyh[offsets[e]: offsets[e] + counts[e]], want) <= tol
+        assert np.all(dyh[offsets[e] + counts[e]: offsets[e + 1]] == 0)
+    assert rel(to_host(dw, (T, k)), want_dw) <= 1e-5
+
+    # unpermute-reduce == sum over experts of route_gather_backward, plus the optional fp32 addend
+    extra = rng.standard_normal((T, d)).astype(np.float32)
+    dx = DeviceStorage(T * d, dtype)
+    lib.call("qmoe_unpermute_reduce", tables.ref, yd.ptr, to_device(extra, "float32").ptr, dx.ptr, code, d, 0)
+    want = extra.astype(np.float64)
+    for e, ye in outputs:
+        want = want + oracle.route_gather_backward(ye, route, e)
+    assert rel(to_host(dx, (T, d)), want) <= tol
+    lib.call("qmoe_unpermute_reduce", tables.ref, yd.ptr, 0, dx.ptr, code, d, 0)
+    assert rel(to_host(dx, (T, d)), want - extra) <= tol
+
+
+# ------------------------------------------------------------------------------------------------
+# the layer against the golden fixtures (fp32 activations, 1e-4) and against the oracle (bf16, 2e-2)
+# ------------------------------------------------------------------------------------------------
+def check_layer(out, g, y, aux, grads, counts, tol, sample=1):
+    assert out["counts"] == tuple(counts)
+    assert rel(out["y"], y) <= tol
+    assert abs(out["aux"] - aux) <= 1e-4 * max(1.0, abs(aux))
+    assert rel(out["dx"], grads["x"]) <= tol
+    assert rel(out["d_router"], grads["router"]) <= tol
+    for e in range(len(counts)):
+        for key in ("gate", "up", "down"):
+            mine, want = out["d_" + key][e], grads[key][e]
+            if counts[e] == 0:
+                assert mine is None and want is None  # upstream: such an expert gets no gradient object
+            else:
+                assert rel(mine.reshape(-1)[::sample], np.asarray(want).reshape(-1)[::sample]) <= tol
+
+
+@pytest.mark.parametrize("path", golden_files("layer"), ids=os.path.basename)
+def test_layer_fp32_matches_golden(path):
+    from gpu_util import make_layer, run_layer
+
+    g = np.load(path)
+    layer = make_layer(g["x"].shape, g["router"], g["gate"], g["up"], g["down"], int(g["top_k"]))
+    out = run_layer(layer, g["x"], g["grad_y"], float(g["grad_aux"]), "float32")
+    E, step = g["gate"].shape[0], int(g["sample"])
+    grads = dict(x=g["dx"], router=g["d_router"])
+    for key in ("gate", "up", "down"):
+        grads[key] = [g[f"d_{key}_{e}"] if g["has_grad"][e] else None for e in range(E)]
+    assert out["counts"] == tuple(g["counts"].tolist())
+    assert rel(out["y"], g["y"]) <= FP32_TOL
+    assert abs(out["aux"] - float(g["aux"])) <= 1e-5
+    assert rel(out["dx"], g["dx"]) <= FP32_TOL
+    assert rel(out["d_router"], g["d_router"]) <= FP32_TOL
+    assert rel(out["utilization"], g["utilization"]) <= 1e-6
+    for e in range(E):
+        for key in ("gate", "up", "down"):
+            mine = out["d_" + key][e]
+            if not g["has_grad"][e]:
+                assert mine is None
+            else:
+                assert rel(mine.reshape(-1)[::step], grads[key][e]) <= FP32_TOL
+    # a second pass gives bit-identical results (no floating-point atomics anywhere)
+    again = run_layer(layer, g["x"], g["grad_y"], float(g["grad_aux"]), "float32")
+    assert np.array_equal(again["y"], out["y"]) and np.array_equal(again["dx"], out["dx"])
+    assert np.array_equal(again["d_router"], out["d_router"])
+
+
+def oracle_for(x, router, gate, up, down, k, grad_y, grad_aux, scores):
+    y, aux, ctx = oracle.moe_forward(x, router, gate, up, down, k, scores=scores)
+    grads = oracle.moe_backward(ctx, grad_y, grad_aux)
+    return y, aux, grads, ctx["route"]["counts"]
+
+
+LAYER_SHAPES = [
+    # T, d, E, k, h
+    (64, 64, 4, 2, 128),      # single tile per expert
+    (300, 72, 5, 2, 136),     # widths that are multiples of 8 but not of the tile sizes
+    (1000, 256, 8, 2, 512),   # several tiles, several k blocks
+    (777, 128, 16, 4, 264),   # ragged counts, partial N tile
+    (2048, 512, 8, 2, 1408),  # half-filled last N tile (1408 = 5.5 x 256)
+]
+
+
+@pytest.mark.parametrize("engine", ["simt", "tcgen05"])
+@pytest.mark.parametrize("T,d,E,k,h", LAYER_SHAPES)
+def test_layer_bf16_matches_oracle(T, d, E, k, h, engine):
+    from gpu_util import make_layer, run_layer
+
+    rng = np.random.default_rng(T + d + E)
+    r16 = oracle.round_bf16
+    x, grad_y = r16(rng.standard_normal((T, d))), r16(rng.standard_normal((T, d)))
+    router = rng.standard_normal((E, d)).astype(np.float32) * 0.05
+    gate = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    up = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    down = rng.standard_normal((E, d, h)).astype(np.float32) / np.sqrt(h)
+    layer = make_layer(x.shape, router, gate, up, down, k, engine=engine)
+    out = run_layer(layer, x, grad_y, 0.37, "bfloat16")
+    # router logits: fp32 arithmetic on exactly these inputs
+    assert rel(out["scores"], x @ router.astype(np.float64).T) <= FP32_TOL
+    # everything downstream is checked given the device's own fp32 logits (identical routing)
+    y, aux, grads, counts = oracle_for(x, router, r16(gate), r16(up), r16(down), k, grad_y, 0.37, out["scores"])
+    check_layer(out, None, y, aux, grads, counts, BF16_TOL)
+
+
+def test_tcgen05_agrees_with_cuda_core_engine():
+    from gpu_util import make_layer, run_layer
+
+    T, d, E, k, h = 1500, 256, 6, 2, 768
+    rng = np.random.default_rng(5)
+    x, grad_y = oracle.round_bf16(rng.standard_normal((T, d))), oracle.round_bf16(rng.standard_normal((T, d)))
+    router = rng.standard_normal((E, d)).astype(np.float32) * 0.05
+    gate = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    up = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    down = rng.standard_normal((E, d, h)).astype(np.float32) / np.sqrt(h)
+    results = {}
+    for engine in ("simt", "tcgen05"):
+        layer = make_layer(x.shape, router, gate, up, down, k, engine=engine)
+        results[engine] = run_layer(layer, x, grad_y, None, "bfloat16")
+    a, b = results["simt"], results["tcgen05"]
+    assert a["counts"] == b["counts"]
+    # same operands, same fp32 accumulation up to summation order: differences are bf16 roundings
+    assert rel(b["y"], a["y"]) <= 1e-2 and rel(b["dx"], a["dx"]) <= 1e-2
+    for e in range(E):
+        for key in ("d_gate", "d_up", "d_down"):
+            assert rel(b[key][e], a[key][e]) <= 1e-2
+
+
+def test_empty_expert_gets_no_gradient_and_its_buffer_is_untouched():
+    from gpu_util import make_layer, run_layer
+
+    T, d, E, k, h = 200, 64, 4, 1, 128
+    rng = np.random.default_rng(9)
+    x = np.abs(oracle.round_bf16(rng.standard_normal((T, d))))
+    router = rng.standard_normal((E, d)).astype(np.float32) * 0.01
+    router[2] = -1.0  # expert 2 is never the arg-max
+    gate = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    up = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    down = rng.standard_normal((E, d, h)).astype(np.float32) / np.sqrt(h)
+    for engine in ("simt", "tcgen05"):
+        layer = make_layer(x.shape, router, gate, up, down, k, engine=engine)
+        out = run_layer(layer, x, oracle.round_bf16(rng.standard_normal((T, d))), 0.1, "bfloat16")
+        assert out["counts"][2] == 0 and sum(out["counts"]) == T
+        assert out["d_gate"][2] is None and out["d_up"][2] is None and out["d_down"][2] is None
+        assert all(g is not None for i, g in enumerate(out["d_gate"]) if out["counts"][i])
+
+
+def test_gradient_accumulates_over_two_backwards():
+    from gpu_util import make_layer, run_layer, to_device, to_host
+    from qutai_b200.layers import Tensor
+
+    g = np.load(os.path.join(os.path.dirname(golden_files("layer")[0]), "layer_mid.npz"))
+    layer = make_layer(g["x"].shape, g["router"], g["gate"], g["up"], g["down"], int(g["top_k"]))
+    once = run_layer(layer, g["x"], g["grad_y"], float(g["grad_aux"]), "float32")
+    T, d = g["x"].shape
+    layer(Tensor(to_device(g["x"], "float32"), (T, d)))
+    layer.backward(Tensor(to_device(g["grad_y"], "float32"), (T, d)), to_device(np.array([float(g["grad_aux"])]), "float32"))
+    twice = to_host(layer.router.weight.grad.storage, once["d_router"].shape)
+    assert rel(twice, 2 * once["d_router"]) <= 1e-6
+    e = int(np.argmax(g["counts"]))
+    got = to_host(layer.experts[e].down.weight.grad.storage, once["d_down"][e].shape)
+    assert rel(got, 2 * once["d_down"][e]) <= 1e-6
