@@ -1,0 +1,385 @@
+"""Benchmark of the MoE layer: forward + backward tokens/s on synthetic inputs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c2|c4layer|c5] [--impl reference]
+
+Prints ONE JSON line (rank 0).  ``value`` is whole-job tokens/s with inputs resident in HBM;
+``e2e`` is the same metric through the public layer with HOST buffers (pinned inputs copied in,
+outputs copied back, inside the timed region); ``roofline`` describes the dominant kernel (the
+tcgen05 grouped GEMM) against the measured bf16 peak; ``cpu_baseline`` is the CPU oracle timed on
+this host on a bounded token sample.  ``--impl reference`` times that CPU implementation alone.
+
+Workloads are the synthetic shapes of the upstream project's MoE layer study: c2 = 16384 tokens,
+d 1024, 8 experts top-2, hidden 2816; c3 = 32768 tokens, d 2048, 64 experts top-6, hidden 1408,
+skewed routing (per-expert router bias N(0, 0.5), realised as a constant-one input column);
+c4layer = one layer of the 12-layer decoder (65536 tokens, d 1024, 16 experts top-2, hidden 2048);
+c5 = c3's layer on 64 tokens (decode latency, forward only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "c2": dict(tokens=16384, d=1024, E=8, k=2, h=2816, router_std=0.01, bias_std=0.0),
+    "c3": dict(tokens=32768, d=2048, E=64, k=6, h=1408, router_std=0.02, bias_std=0.5),
+    "c4layer": dict(tokens=65536, d=1024, E=16, k=2, h=2048, router_std=0.02, bias_std=0.0),
+    "c5": dict(tokens=64, d=2048, E=64, k=6, h=1408, router_std=0.02, bias_std=0.5),
+}
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as handle:
+            peaks = json.load(handle)
+        return dict(hbm_gbs=float(peaks["hbm_gbs"]), bf16_tflops=float(peaks["bf16_tflops"]),
+                    bf16_tflops_sustained=float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])),
+                    source="measured")
+    except Exception:
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+def layer_flops(w, tokens=None):
+    """Algorithmic FLOPs of one forward + backward: expert GEMMs 18*A*d*h, router 6*T*d*E."""
+    T = w["tokens"] if tokens is None else tokens
+    return 18.0 * T * w["k"] * w["d"] * w["h"], 6.0 * T * w["d"] * w["E"]
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        # samples under load: the upper half (the sampler also sees the idle edges of the region)
+        busy = clocks[len(clocks) // 2:] if clocks else []
+        median = busy[len(busy) // 2] if busy else None
+        return dict(sm_mhz=median, sm_max_mhz=max_clock, samples=len(clocks), reasons=sorted(reasons))
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (a numpy float64 restatement of the upstream pure-Python CPU path)
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_inputs(w, sample_tokens, seed=0):
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    d, E, h = w["d"], w["E"], w["h"]
+    x = rng.standard_normal((sample_tokens, d))
+    router = rng.standard_normal((E, d)) * w["router_std"]
+    if w["bias_std"]:
+        x[:, d - 1] = 1.0
+        router[:, d - 1] = rng.standard_normal(E) * w["bias_std"]
+    # one weight block shared by all experts: values do not change the cost, and 64 distinct
+    # float64 expert matrices would need several GB and tens of seconds just to draw
+    gate = [rng.standard_normal((h, d)) / np.sqrt(d)] * E
+    up = [rng.standard_normal((h, d)) / np.sqrt(d)] * E
+    down = [rng.standard_normal((d, h)) / np.sqrt(h)] * E
+    grad = rng.standard_normal((sample_tokens, d))
+    return x, router, gate, up, down, grad
+
+
+def cpu_step(w, inputs):
+    from oracle import moe_oracle as oracle
+
+    x, router, gate, up, down, grad = inputs
+    y, aux, ctx = oracle.moe_forward(x, router, gate, up, down, w["k"])
+    oracle.moe_backward(ctx, grad, 0.01)
+    return y
+
+
+def pure_python_rate():
+    """Multiply-accumulates per second of the scalar triple loop the upstream CPU path runs
+    (measured on a small product; the upstream layer is that loop almost entirely)."""
+    from array import array
+    from oracle import moe_pure
+
+    n = 48
+    a = array("d", [0.5] * (n * n))
+    start = time.perf_counter()
+    moe_pure.gemm(a, a, n, n, n, transpose_right=True)
+    return n ** 3 / (time.perf_counter() - start)
+
+
+def time_cpu(w, steps, warmup, sample_tokens):
+    inputs = cpu_sample_inputs(w, sample_tokens)
+    for _ in range(warmup):
+        cpu_step(w, inputs)
+    start = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(w, inputs)
+    seconds = (time.perf_counter() - start) / steps
+    return sample_tokens / seconds, seconds
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_sample_tokens(w):
+    # about 1e11 algorithmic FLOP per step: a second or two of multi-threaded float64 BLAS
+    flops_per_token = sum(layer_flops(w, 1))
+    return int(max(16, min(w["tokens"], 1.0e11 // flops_per_token)))
+
+
+def run_reference(args, w, rank):
+    if rank != 0:
+        return
+    sample = cpu_sample_tokens(w)
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    value, seconds = time_cpu(w, steps, warmup, sample)
+    cores = host_cores()
+    line = dict(
+        impl="reference", metric="moe_layer_fwd_bwd_tokens_per_s", value=value, unit="tokens/s",
+        n_gpus=args.gpus, steps=steps, warmup=warmup, ms_per_step=seconds * 1e3, higher_is_better=True,
+        scaling="strong", vs_baseline=None, dtype="f64", data="synthetic",
+        config=workload_config(args.workload, w, args.gpus),
+        cpu_baseline=dict(value=value, unit="tokens/s", cores=cores, kind="port",
+                          sample=f"{sample} of {w['tokens']} tokens per step, full d/E/k/h, numpy float64 "
+                                 f"restatement of the upstream pure-Python CPU path, BLAS on {cores} threads"),
+        e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, w, gpus):
+    return dict(workload=f"{name}: MoE layer fwd+bwd, tokens {w['tokens']}, d_model {w['d']}, experts {w['E']}, "
+                         f"top_k {w['k']}, d_expert {w['h']}", tokens=w["tokens"], d_model=w["d"], n_experts=w["E"],
+                top_k=w["k"], d_expert=w["h"], parallelism=f"ep{gpus}" if gpus > 1 else "single",
+                l2="inputs larger than L2 (weights and activations are re-streamed every step)")
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def build_layer(w, torch, device, seed=0):
+    import numpy as np
+
+    from qutai_b200 import lib
+    from qutai_b200.layers import SparseMoE
+
+    class Cfg:
+        d_model, n_experts, top_k, d_expert, n_layers = w["d"], w["E"], w["k"], w["h"], 1
+
+    layer = SparseMoE(Cfg, device="cuda", dtype="float32", seed=seed)
+    d, E, h = w["d"], w["E"], w["h"]
+    fill = lambda storage, std, key: lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std, key, 0)
+    fill(layer._gate, d ** -0.5, 101)
+    fill(layer._up, d ** -0.5, 102)
+    fill(layer._down, h ** -0.5, 103)
+    rng = np.random.default_rng(seed)
+    router = (rng.standard_normal((E, d)) * w["router_std"]).astype(np.float32)
+    if w["bias_std"]:
+        router[:, d - 1] = (rng.standard_normal(E) * w["bias_std"]).astype(np.float32)
+    layer.router.weight.storage.upload_bytes(router.tobytes())
+    return layer
+
+
+def host_inputs(w, torch, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(w["tokens"], w["d"], generator=gen, dtype=torch.float32)
+    if w["bias_std"]:
+        x[:, w["d"] - 1] = 1.0
+    g = torch.randn(w["tokens"], w["d"], generator=gen, dtype=torch.float32)
+    return x.to(torch.bfloat16).pin_memory(), g.to(torch.bfloat16).pin_memory()
+
+
+def run_gpu(args, w, rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from qutai_b200 import lib
+    from qutai_b200.layers import Tensor
+    from qutai_b200.storage import DeviceStorage
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        raise SystemExit("expert-parallel bench is not wired yet")
+    device = torch.device("cuda", local)
+    stream = torch.cuda.current_stream().cuda_stream
+    layer = build_layer(w, torch, device)
+    layer.stream = stream
+    x_host, g_host = host_inputs(w, torch)
+    T, d = w["tokens"], w["d"]
+    x_dev, g_dev = x_host.to(device), g_host.to(device)
+    aux_grad = torch.full((1,), 0.01, dtype=torch.float32, device=device)
+    y_host = torch.empty_like(x_host).pin_memory()
+    dx_host = torch.empty_like(x_host).pin_memory()
+    wrap = lambda t, dtype: DeviceStorage.wrap(t.data_ptr(), t.numel(), dtype, owner=t)
+    xs, gs, ga = Tensor(wrap(x_dev, "bfloat16"), (T, d)), Tensor(wrap(g_dev, "bfloat16"), (T, d)), wrap(aux_grad, "float32")
+    forward_only = args.workload == "c5"
+
+    parameters = layer.parameters()
+
+    def step():
+        for parameter in parameters:  # what optimizer.zero_grad() does before every training step
+            parameter.grad = None
+        y, aux = layer(xs)
+        dx = None if forward_only else layer.backward(gs, ga)
+        return y, aux, dx
+
+    def step_e2e():
+        x_dev.copy_(x_host, non_blocking=True)
+        if not forward_only:
+            g_dev.copy_(g_host, non_blocking=True)
+        y, aux, dx = step()
+        lib.call("qmoe_memcpy_d2h", y_host.data_ptr(), y.storage.ptr, y.storage.nbytes, stream)
+        if dx is not None:
+            lib.call("qmoe_memcpy_d2h", dx_host.data_ptr(), dx.storage.ptr, dx.storage.nbytes, stream)
+        aux_value = aux.storage.tolist(stream)[0]  # waits for the step: the caller reads its result
+        return aux_value
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    counts = layer.last_counts
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches_before = lib.load().qmoe_launch_count()
+    ms = timed(step, args.steps)
+    launches = (lib.load().qmoe_launch_count() - launches_before) // args.steps
+    clocks = sampler.stop()
+    for _ in range(max(1, args.warmup // 2)):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    # per-kernel-class device time, measured in a separate pass so the events do not sit inside the headline timing
+    lib.timing(True)
+    for _ in range(args.steps):
+        step()
+    classes = lib.timing_read()
+    lib.timing(False)
+    status = lib.device_status(stream)
+
+    peaks = load_peaks()
+    gemm_flops, router_flops = layer_flops(w)
+    if forward_only:
+        gemm_flops, router_flops = gemm_flops / 3, router_flops / 3
+    gemm_ms = (classes["expert_gemm"][0] + classes["wgrad_gemm"][0]) / args.steps
+    gemm_launches = (classes["expert_gemm"][1] + classes["wgrad_gemm"][1]) // args.steps
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    peak = peaks["bf16_tflops_sustained"]
+    A, h, E, k = T * w["k"], w["h"], w["E"], w["k"]
+    hbm_bytes = dict(permute=T * d * 2 + A * d * 2 + A * 4, combine=A * d * 2 + 3 * A * 4 + T * d * 2,
+                     combine_backward=T * d * 2 + 2 * A * d * 2 + A * 4, unpermute=A * d * 2 + T * d * 2 + A * 4,
+                     route=2 * T * E * 4 + 2 * A * 4)
+    hbm = {}
+    for name, nbytes in hbm_bytes.items():
+        t = classes[name][0] / args.steps
+        if t > 0:
+            gbs = nbytes / (t * 1e-3) / 1e9
+            hbm[name] = dict(ms=round(t, 4), achieved_gbs=round(gbs, 1), frac=round(gbs / peaks["hbm_gbs"], 3))
+    tokens_per_s = T / (ms * 1e-3)
+    bytes_in = x_host.numel() * 2 * (1 if forward_only else 2)
+    bytes_out = x_host.numel() * 2 * (1 if forward_only else 2) + 4
+    line = dict(
+        metric="moe_layer_fwd_bwd_tokens_per_s" if not forward_only else "moe_layer_fwd_tokens_per_s",
+        value=tokens_per_s, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
+        higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+        config=workload_config(args.workload, w, world),
+        e2e=dict(value=T / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=bytes_in,
+                 d2h_bytes_per_step=bytes_out),
+        gpu_launches=int(launches), clocks=clocks,
+        roofline=dict(bound="tensor", kernel="grouped_gemm_kernel (tcgen05)", achieved=achieved, peak=peak,
+                      unit="TFLOP/s", frac=achieved / peak, peak_source=peaks["source"] + " (sustained cuBLAS bf16)",
+                      traffic=None, launches_per_step=int(gemm_launches), ms_per_step=gemm_ms,
+                      algorithmic_flops_per_step=gemm_flops, whole_layer_frac=(gemm_flops + router_flops) / (ms * 1e-3) / 1e12 / peak),
+        hbm_kernels=hbm,
+        class_ms_per_step={name: round(v[0] / args.steps, 4) for name, v in classes.items() if v[1]},
+        expert_counts=dict(max=max(counts), mean=sum(counts) / len(counts), max_over_mean=max(counts) * len(counts) / max(1, sum(counts))),
+        device_status=status,
+    )
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample = cpu_sample_tokens(w)
+        value, seconds = time_cpu(w, 2, 1, sample)
+        cores = host_cores()
+        line["cpu_baseline"] = dict(
+            value=value, unit="tokens/s", cores=cores, kind="port",
+            sample=f"{sample} of {T} tokens, full d/E/k/h, numpy float64 restatement of the upstream CPU path on "
+                   f"{cores} threads, {seconds:.2f} s per forward+backward",
+            pure_python_estimate=dict(
+                mac_per_s=pure_python_rate(), cores=1,
+                note="scalar triple-loop rate of the upstream pure-Python path; tokens/s = rate / (9*k*d*h + 3*d*E) MAC per token"))
+        rate = line["cpu_baseline"]["pure_python_estimate"]["mac_per_s"]
+        line["cpu_baseline"]["pure_python_estimate"]["tokens_per_s"] = rate / (9.0 * k * d * h + 3.0 * d * E)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(3, args.warmup)
+    w = WORKLOADS[args.workload]
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+    run_gpu(args, w, rank, world)
+
+
+if __name__ == "__main__":
+    main()

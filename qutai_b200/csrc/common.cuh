@@ -147,6 +147,8 @@ int tc_swiglu_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t 
 int tc_rows_nt(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long K, long long N, cudaStream_t stream);
 int tc_rows_nn(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t a2, uint64_t b2, uint64_t c, long long K,
                long long N, cudaStream_t stream);
+int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down, uint64_t g, uint64_t u, uint64_t dg,
+               uint64_t du, long long d, long long h, cudaStream_t stream);
 int tc_wgrad(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long M, long long N, cudaStream_t stream);
 void count_tensor_core_launch();
 int* device_status_address();

@@ -2,12 +2,13 @@
 // operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast),
 // fp32 accumulators in tensor memory (TMEM), read back with tcgen05.ld for the epilogue.
 //
-// One persistent kernel, one CTA per SM, 6 warps:
+// One persistent kernel, one CTA per SM, 10 warps:
 //   warp 0      TMA producer (one lane): fills a 4-stage ring of {A 128x64, B 256x64} bf16 tiles
 //   warp 1      MMA issuer (one lane): 4 x tcgen05.mma (128x256x16) per stage, commits free the stage;
 //               also allocates / frees the 512 TMEM columns (two 128x256 fp32 accumulators)
-//   warps 2-5   epilogue: each owns 32 TMEM lanes (= 32 tile rows), converts and stores to HBM while
-//               the MMA warp already works on the next tile in the other accumulator
+//   warps 2-9   epilogue: two warps per 32-lane TMEM quadrant (= 32 tile rows), each taking half of
+//               the columns; they convert and store to HBM while the MMA warp already works on the
+//               next tile in the other accumulator
 //
 // Three problem kinds share the kernel (template MODE):
 //   MODE_PLAIN   C[rows, N] (bf16) = A[rows, K] . B_e  (+ A2 . B2_e), rows in the dispatched layout,
@@ -15,6 +16,7 @@
 //                "x W^T") or [E*K, N] (MN-major, "g W").
 //   MODE_SWIGLU  G = X Wg_e^T, U = X Wu_e^T (128 + 128 accumulator columns), H = silu(G) * U, all
 //                three stored as bf16.
+//   MODE_DSWIGLU dH = dY Wd_e (never stored): dU = dH * silu(G), dG = dH * U * silu'(G), bf16.
 //   MODE_WGRAD   C_e[M, N] (fp32) = A_e^T . B_e, contraction over the rows of expert e (both
 //                operands MN-major); experts without rows are skipped and their slab is not written.
 //
@@ -39,11 +41,12 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64 x 64 bf16 TMA box (8 KiB)
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
+constexpr int EPILOGUE_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
-enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2 };
+enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2, MODE_DSWIGLU = 3 };
 enum { STATUS_WAIT_PRODUCER = 101, STATUS_WAIT_MMA = 102, STATUS_WAIT_EPILOGUE = 103 };
 
 struct alignas(64) GemmParams {
@@ -51,9 +54,11 @@ struct alignas(64) GemmParams {
     const int* offsets;   // [E + 1] first dispatched row of each expert
     const int* counts;    // [E]
     int* status;
-    void* out0;           // PLAIN: C bf16; SWIGLU: G; WGRAD: C fp32 (stacked per expert)
-    void* out1;           // SWIGLU: U
+    void* out0;           // PLAIN: C bf16; SWIGLU: G; WGRAD: C fp32 (stacked per expert); DSWIGLU: dG
+    void* out1;           // SWIGLU: U; DSWIGLU: dU
     void* out2;           // SWIGLU: H
+    const void* in0;      // DSWIGLU: G (saved by the forward)
+    const void* in1;      // DSWIGLU: U
     long long ldc;        // row pitch of the outputs, in elements
     long long c_slab;     // WGRAD: elements per expert
     int experts;
@@ -181,6 +186,17 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_st
     return tile;
 }
 
+// 1 / (1 + 2^(-v log2 e)) with the approximate exp2 / reciprocal units (relative error ~1e-6,
+// far below one bf16 ulp); saturates cleanly to 0 and 1 for large |v|
+__device__ __forceinline__ float fast_sigmoid(float v) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * v));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+}
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -222,7 +238,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPILOGUE_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_map(&p.map_a);
         prefetch_map(&p.map_b);
@@ -330,7 +346,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
-        const int quad = warp & 3;  // TMEM lanes [32 * quad, 32 * quad + 32) belong to this warp
+        const int quad = warp & 3;         // TMEM lanes [32 * quad, 32 * quad + 32) belong to this warp
+        const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp converts
         int iter = 0;
         for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
             const Tile tile = decode_tile<MODE>(p, s_start, t);
@@ -349,32 +366,96 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 __nv_bfloat16* U = (__nv_bfloat16*)p.out1 + row * p.ldc + tile.n0;
                 __nv_bfloat16* H = (__nv_bfloat16*)p.out2 + row * p.ldc + tile.n0;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 2 * half; c < 2 * half + 2; ++c) {
                     uint32_t rg[32], ru[32];
                     tmem_ld32(taddr + c * 32, rg);
                     tmem_ld32(taddr + 128 + c * 32, ru);
                     tmem_ld_wait();
-                    float g[32], u[32], h[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        // rounding points of the bf16 activations: G and U are stored as bf16, and
-                        // silu(G) is rounded before the product, as separate kernels would do
-                        g[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[i])));
-                        u[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[i])));
-                        const float act = __bfloat162float(__float2bfloat16_rn(g[i] * sigmoid_stable(g[i])));
-                        h[i] = act * u[i];
-                    }
                     const int valid = p.N - (tile.n0 + c * 32);
-                    if (valid > 0) {
-                        store_row32_bf16(G + c * 32, g, valid);
-                        store_row32_bf16(U + c * 32, u, valid);
-                        store_row32_bf16(H + c * 32, h, valid);
+                    if (valid >= 32) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t wg[4], wu[4], wh[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int i = 8 * q + 2 * j;
+                                // G and U are stored as bf16 and H is computed from the stored values,
+                                // so the backward (which re-reads G and U) sees exactly what H was built from
+                                wg[j] = pack_bf16(__uint_as_float(rg[i]), __uint_as_float(rg[i + 1]));
+                                wu[j] = pack_bf16(__uint_as_float(ru[i]), __uint_as_float(ru[i + 1]));
+                                const float g0 = bf16_lo(wg[j]), g1 = bf16_hi(wg[j]);
+                                wh[j] = pack_bf16(g0 * fast_sigmoid(g0) * bf16_lo(wu[j]), g1 * fast_sigmoid(g1) * bf16_hi(wu[j]));
+                            }
+                            *reinterpret_cast<uint4*>(G + c * 32 + 8 * q) = make_uint4(wg[0], wg[1], wg[2], wg[3]);
+                            *reinterpret_cast<uint4*>(U + c * 32 + 8 * q) = make_uint4(wu[0], wu[1], wu[2], wu[3]);
+                            *reinterpret_cast<uint4*>(H + c * 32 + 8 * q) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                        }
+                    } else if (valid > 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) {
+                                const __nv_bfloat16 gb = __float2bfloat16_rn(__uint_as_float(rg[i]));
+                                const __nv_bfloat16 ub = __float2bfloat16_rn(__uint_as_float(ru[i]));
+                                const float g = __bfloat162float(gb);
+                                G[c * 32 + i] = gb;
+                                U[c * 32 + i] = ub;
+                                H[c * 32 + i] = __float2bfloat16_rn(g * fast_sigmoid(g) * __bfloat162float(ub));
+                            }
+                    }
+                }
+            } else if (MODE == MODE_DSWIGLU) {
+                const __nv_bfloat16* G = (const __nv_bfloat16*)p.in0 + row * p.ldc + tile.n0;
+                const __nv_bfloat16* U = (const __nv_bfloat16*)p.in1 + row * p.ldc + tile.n0;
+                __nv_bfloat16* dG = (__nv_bfloat16*)p.out0 + row * p.ldc + tile.n0;
+                __nv_bfloat16* dU = (__nv_bfloat16*)p.out1 + row * p.ldc + tile.n0;
+#pragma unroll 1
+                for (int c = 4 * half; c < 4 * half + 4; ++c) {
+                    const int valid = p.N - (tile.n0 + c * 32);
+                    uint4 vg[4], vu[4];
+                    if (valid >= 32) {  // issue the loads of the saved activations before waiting on TMEM
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            vg[q] = *reinterpret_cast<const uint4*>(G + c * 32 + 8 * q);
+                            vu[q] = *reinterpret_cast<const uint4*>(U + c * 32 + 8 * q);
+                        }
+                    }
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    if (valid >= 32) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t gw[4] = {vg[q].x, vg[q].y, vg[q].z, vg[q].w};
+                            const uint32_t uw[4] = {vu[q].x, vu[q].y, vu[q].z, vu[q].w};
+                            uint32_t og[4], ou[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int i = 8 * q + 2 * j;
+                                const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
+                                const float u0 = bf16_lo(uw[j]), u1 = bf16_hi(uw[j]);
+                                const float s0 = fast_sigmoid(g0), s1 = fast_sigmoid(g1);
+                                const float h0 = __uint_as_float(r[i]), h1 = __uint_as_float(r[i + 1]);
+                                ou[j] = pack_bf16(h0 * g0 * s0, h1 * g1 * s1);
+                                og[j] = pack_bf16(h0 * u0 * s0 * (1.f + g0 * (1.f - s0)), h1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
+                            }
+                            *reinterpret_cast<uint4*>(dG + c * 32 + 8 * q) = make_uint4(og[0], og[1], og[2], og[3]);
+                            *reinterpret_cast<uint4*>(dU + c * 32 + 8 * q) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+                        }
+                    } else if (valid > 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) {
+                                const float g = __bfloat162float(G[c * 32 + i]), u = __bfloat162float(U[c * 32 + i]);
+                                const float sg = fast_sigmoid(g), dh = __uint_as_float(r[i]);
+                                dU[c * 32 + i] = __float2bfloat16_rn(dh * g * sg);
+                                dG[c * 32 + i] = __float2bfloat16_rn(dh * u * sg * (1.f + g * (1.f - sg)));
+                            }
                     }
                 }
             } else if (MODE == MODE_PLAIN) {
                 __nv_bfloat16* C = (__nv_bfloat16*)p.out0 + row * p.ldc + tile.n0;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 4 * half; c < 4 * half + 4; ++c) {
                     uint32_t r[32];
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
@@ -388,7 +469,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
                 const bool row_ok = row < p.M;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 4 * half; c < 4 * half + 4; ++c) {
                     uint32_t r[32];
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
@@ -544,6 +625,21 @@ int tc_rows_nn(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint6
     p.out0 = (void*)c; p.ldc = N; p.experts = experts; p.n_tiles = ceil_div(N, BN);
     p.N = (int)N; p.K = (int)K; p.b_rows = (int)K;
     return launch<MODE_PLAIN, false, true>(p, stream);
+}
+
+// dG, dU [rows, h] from dY [rows, d], Wd stacked [E*d, h] and the saved G, U: the product dH = dY . Wd_e
+// only ever lives in tensor memory
+int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down, uint64_t g, uint64_t u, uint64_t dg,
+               uint64_t du, long long d, long long h, cudaStream_t stream) {
+    GemmParams p = {};
+    if (int rc = make_map(&p.map_a, dy, (uint64_t)d, (uint64_t)r->rows_bound, BM)) return rc;
+    if (int rc = make_map(&p.map_b, w_down, (uint64_t)h, (uint64_t)experts * d, 64)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
+    p.out0 = (void*)dg; p.out1 = (void*)du; p.in0 = (const void*)g; p.in1 = (const void*)u;
+    p.ldc = h; p.experts = experts; p.n_tiles = ceil_div(h, BN);
+    p.N = (int)h; p.K = (int)d; p.b_rows = (int)d; p.segments = 1;
+    return launch<MODE_DSWIGLU, false, true>(p, stream);
 }
 
 // C_e [M, N] (fp32) = A_e^T . B_e, A [rows, M], B [rows, N], contraction over the rows of expert e

@@ -91,12 +91,16 @@ extern "C" int qmoe_expert_backward(const qmoe_route_t* r, const qmoe_experts_t*
     cudaStream_t stream = (cudaStream_t)stream_;
     const long long d = ex->width, hd = ex->hidden;
     const bool tc = engine == QMOE_ENGINE_TCGEN05;
-    {   // dH = dY . Wd
+    if (tc) {  // dG, dU straight from the accumulator of dH = dY . Wd (dH itself is never stored)
         TimedScope timed(KC_EXPERT_GEMM, stream);
-        if (int rc = tc ? tc_rows_nn(r, ex->experts, dy, ex->w_down, 0, 0, d_h, d, hd, stream)
-                        : simt_rows(r, ex, dy, ex->w_down, 0, 0, d_h, d, hd, false, stream)) return rc;
+        if (int rc = tc_dswiglu(r, ex->experts, dy, ex->w_down, g, u, d_g, d_u, d, hd, stream)) return rc;
+    } else {
+        {
+            TimedScope timed(KC_EXPERT_GEMM, stream);
+            if (int rc = simt_rows(r, ex, dy, ex->w_down, 0, 0, d_h, d, hd, false, stream)) return rc;
+        }
+        if (int rc = launch_swiglu_backward(r, d_h, g, u, d_g, d_u, ex->dtype, hd, stream)) return rc;
     }
-    if (int rc = launch_swiglu_backward(r, d_h, g, u, d_g, d_u, ex->dtype, hd, stream)) return rc;
     {   // weight gradients (dY is still intact here; dX may alias it and is written last)
         TimedScope timed(KC_WGRAD_GEMM, stream);
         if (int rc = tc ? tc_wgrad(r, ex->experts, dy, h, d_w_down, d, hd, stream)
