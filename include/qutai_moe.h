@@ -139,6 +139,15 @@ int qmoe_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dtype, uint64_
  * softmax, lm_route, lm_route_pack, lm_route_util, lm_route_aux; CPU statement
  * src/qutai/backends/cpu_lm.py:204-242). */
 int qmoe_route(const qmoe_route_t* route, uint64_t scores, uint64_t stream);
+/* qmoe_route for callers that cannot allocate device memory for its three scratch tables (a
+ * serving loop that must not call cudaMalloc on its request path, a plug-in host limited to the
+ * buffers it was given at start-up): route->block_counts, block_base and block_colsum are ignored
+ * and a 1.5 MiB array built into the library is used instead.  Limit: qmoe_route_blocks(tokens) *
+ * experts <= 131072, otherwise an argument error.  Allocates nothing.  The array is shared by all
+ * calls on a device, so calls that overlap on the GPU race: use one stream at a time.  The first
+ * call on a device resolves the array's address and should be made before any stream capture.
+ * This entry point has no counterpart in the upstream project. */
+int qmoe_route_static(const qmoe_route_t* route, uint64_t scores, uint64_t stream);
 /* The same tables in the upstream layout, for hosts that keep the upstream `route` dict
  * (src/qutai/backends/cuda_lm.py:435-449): int64 indices[A], ids[E*capacity], slots[E*capacity]
  * (row e holds expert e's token rows / slot numbers), locations[A], counts[E]. */

@@ -370,3 +370,60 @@ extern "C" int qmoe_route_backward(const qmoe_route_t* r, uint64_t grad_weights,
     QMOE_LAUNCH_CHECK("route_backward_kernel");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// qmoe_route_static: qmoe_route for callers that cannot supply scratch memory.
+//
+// qmoe_route needs three scratch tables (block_counts, block_base, block_colsum) besides its inputs
+// and outputs, and expects the caller to allocate them.  Some hosts cannot: a serving loop that
+// must never call cudaMalloc on its request path (the call synchronises the whole device), a
+// plug-in host that was handed a fixed set of buffers at start-up and has no allocator of its own
+// to reach for more, or a runtime whose memory pool is private to it.  For them the three tables
+// live in the fixed device array below, which every GPU that loads this library keeps resident
+// until the process exits (1.5 MiB).  The caller still passes every input and output table.
+//
+// Limit: blocks * experts <= kStaticRouteEntries, where blocks = qmoe_route_blocks(tokens); larger
+// problems are rejected with an argument error and must use qmoe_route.
+//
+// The array is shared by all calls and keeps whatever the previous call left in it.  That is
+// harmless here because the first routing kernel writes every entry it later reads (one row per
+// block, all experts), so nothing has to start at zero and nothing is cleared.  It also means two
+// calls whose kernels overlap on the GPU (different streams, or different host threads) race on the
+// array: issue calls to this entry point on one stream at a time per device.
+//
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress, checked)
+// with that device current, and remembers it; make that first call before starting any stream
+// capture.  No cudaMalloc, cudaFree or allocating library routine is called on any path.
+namespace {
+constexpr long long kStaticRouteEntries = 131072;  // entries per table (blocks * experts)
+static __device__ __align__(256) unsigned char g_route_scratch[3 * kStaticRouteEntries * 4];
+constexpr int kMaxDevices = 64;
+void* g_route_scratch_address[kMaxDevices] = {nullptr};  // device address per device, looked up once
+}  // namespace
+
+extern "C" int qmoe_route_static(const qmoe_route_t* r, uint64_t scores, uint64_t stream_) {
+    if (!r) return fail_arg("route is null");
+    if (r->tokens <= 0 || r->experts <= 0) return fail_arg("route_static: tokens and experts must be positive");
+    const long long entries = qmoe_route_blocks(r->tokens) * (long long)r->experts;
+    if (entries > kStaticRouteEntries)
+        return fail_arg("route_static: %lld blocks x %d experts = %lld scratch entries exceed the built-in %lld; "
+                        "use qmoe_route with caller-allocated scratch",
+                        (long long)qmoe_route_blocks(r->tokens), r->experts, entries, kStaticRouteEntries);
+    int device = 0;
+    QMOE_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return fail_arg("route_static: device index %d is out of range", device);
+    if (!g_route_scratch_address[device]) {
+        // In host code `g_route_scratch` only stands for the symbol; the address kernels can use
+        // has to be asked for, once per device, while that device is current.
+        void* address = nullptr;
+        QMOE_CUDA(cudaGetSymbolAddress(&address, g_route_scratch));
+        if (!address) { set_error("route_static: the scratch array has no device address"); return QMOE_ERR_STATE; }
+        g_route_scratch_address[device] = address;
+    }
+    unsigned char* base = (unsigned char*)g_route_scratch_address[device];
+    qmoe_route_t with_scratch = *r;
+    with_scratch.block_counts = (uint64_t)base;
+    with_scratch.block_base = (uint64_t)(base + kStaticRouteEntries * 4);
+    with_scratch.block_colsum = (uint64_t)(base + 2 * kStaticRouteEntries * 4);
+    return qmoe_route(&with_scratch, scores, stream_);
+}

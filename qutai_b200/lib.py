@@ -75,6 +75,7 @@ SIGNATURES = {
     "qmoe_router_grad_partials": (c_int64, [_I64, _I32, _I64]),
     "qmoe_router_backward": (c_int, [_U, _U, _I32, _U, _U, _U, _U, _I64, _I64, _I32, _U]),
     "qmoe_route": (c_int, [_RP, _U, _U]),
+    "qmoe_route_static": (c_int, [_RP, _U, _U]),
     "qmoe_route_export_i64": (c_int, [_RP, _U, _U, _U, _U, _U, _I64, _U]),
     "qmoe_route_backward": (c_int, [_RP, _U, _U, _U, _U]),
     "qmoe_permute": (c_int, [_RP, _U, _U, _I32, _I64, _U]),
