@@ -274,6 +274,52 @@ int qmoe_layer_forward(const qmoe_layer_t* layer, uint64_t stream);
  * would run them), producing dx, d_w_router and the stacked expert weight gradients. */
 int qmoe_layer_backward(const qmoe_layer_t* layer, uint64_t stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Expert parallelism (one process per GPU, NCCL over NVLink / NVSwitch).  The upstream project is
+ * single-GPU (src/qutai/backends/cuda_runtime.py:82, :105), so these entry points have no upstream
+ * counterpart; they keep the layer's semantics when tokens are sharded T/N per rank (contiguous
+ * shards) and experts E/N per rank (contiguous blocks): an expert's rows arrive ordered by source
+ * rank, which is the upstream global (token, slot) order (src/qutai/backends/cuda/lm.cu:353-383),
+ * and utilisation / auxiliary loss are computed over all ranks' tokens
+ * (src/qutai/backends/cpu_lm.py:221-229).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qmoe_ep_segment {
+    int32_t peer;          /* rank on the other side */
+    int32_t reserved;
+    int64_t offset_rows;   /* first row of the segment in the local buffer */
+    int64_t rows;          /* rows to move (0 = skipped on both sides) */
+} qmoe_ep_segment_t;
+
+/* Rank 0 creates a 128-byte id and hands it to every rank by any host channel; every rank then
+ * calls qmoe_ep_init with its device current.  One communicator per process. */
+int qmoe_ep_unique_id(void* id128);
+int qmoe_ep_init(int32_t rank, int32_t world, const void* id128);
+/* abort_communicator != 0 tears the communicator down without waiting for outstanding work (the
+ * path to take after the host learned that a peer is gone). */
+int qmoe_ep_finalize(int32_t abort_communicator);
+int qmoe_ep_info(int32_t* rank, int32_t* world);
+/* After qmoe_route on the local tokens: pack {counts[E], probability column sums[E] (float bits)}
+ * into stats_local (i32 [2E]), all-gather into stats_all (i32 [world, 2E]) and, when host_stats is
+ * not null, start its copy to (pinned) host memory; synchronise the stream before reading it. */
+int qmoe_ep_gather_stats(const qmoe_route_t* route, uint64_t stats_local, uint64_t stats_all,
+                         void* host_stats, uint64_t stream);
+/* From stats_all: overwrite token_route->utilization and ->aux with the values over all ranks'
+ * tokens, and fill expert_route's counts / offsets / tile_expert / meta for this rank's
+ * E / world experts (rows of all ranks, padded like the single-GPU dispatched layout). */
+int qmoe_ep_plan(uint64_t stats_all, const qmoe_route_t* token_route, const qmoe_route_t* expert_route,
+                 int64_t tokens_global, uint64_t stream);
+/* Zero the pad rows of every expert group of a buffer in expert_route's dispatched layout. */
+int qmoe_ep_zero_pad_rows(const qmoe_route_t* expert_route, uint64_t buffer, int32_t dtype,
+                          int64_t width, uint64_t stream);
+/* One grouped exchange: every send segment [offset_rows, +rows) of send_buffer goes to its peer,
+ * every receive segment of recv_buffer is filled from its peer.  Between a pair of ranks segments
+ * are matched in list order.  This is the dispatch / combine all-to-all(v). */
+int qmoe_ep_exchange(uint64_t send_buffer, const qmoe_ep_segment_t* sends, int32_t n_sends,
+                     uint64_t recv_buffer, const qmoe_ep_segment_t* recvs, int32_t n_recvs,
+                     int64_t width, int32_t dtype, uint64_t stream);
+/* In-place sum over ranks (router weight gradient). */
+int qmoe_ep_all_reduce_f32(uint64_t buffer, int64_t n, uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

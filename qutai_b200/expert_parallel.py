@@ -1,0 +1,324 @@
+"""Expert-parallel ``SparseMoE``: one process per GPU, tokens sharded by rank (contiguous shards of
+equal size), experts sharded by rank (contiguous blocks of E / world), NCCL all-to-all for dispatch
+and combine.
+
+The upstream project is single-GPU; this module keeps its layer semantics across ranks: routing is
+decided per token exactly as on one GPU, an expert's rows arrive ordered by source rank — with
+contiguous token shards that is the upstream global (token, slot) order
+(src/qutai/backends/cuda/lm.cu:353-383) — and utilisation / auxiliary loss are taken over all ranks'
+tokens (src/qutai/backends/cpu_lm.py:221-229).  Host code is standard-library Python; the NCCL id
+travels through a small file rendezvous (or any callable the caller supplies).
+
+Per step the host waits once for the device: to read the [world, E] matrix of counts that sizes
+the exchanges (the upstream layer also reads its counts in every forward,
+src/qutai/backends/cuda_lm.py:432-434).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import time
+from math import sqrt
+
+from . import lib
+from .layers import Projection, SwiGLU, Tensor, _accumulate
+from .storage import DeviceStorage
+
+
+# ------------------------------------------------------------------------------------------------
+# host logic (no GPU needed)
+# ------------------------------------------------------------------------------------------------
+def padded_offsets(counts, pad=lib.ROW_PAD):
+    """First row of each group when every group is padded to a multiple of ``pad`` rows."""
+    offsets, at = [], 0
+    for c in counts:
+        offsets.append(at)
+        at += -(-c // pad) * pad
+    offsets.append(at)
+    return offsets
+
+
+def plan_exchange(counts, rank, world, pad=lib.ROW_PAD):
+    """Segments of the dispatch all-to-all for ``rank``.
+
+    ``counts[p][e]`` = rows that rank ``p`` routes to global expert ``e``.  Token side: this rank's
+    dispatched buffer holds expert ``e``'s rows at ``send_offsets[e]`` (padded groups, all E
+    experts).  Expert side: local expert ``j`` (global ``rank * E_loc + j``) receives the rows of
+    rank 0, rank 1, ... one after the other, groups padded to ``pad``.
+
+    Returns a dict: ``sends`` / ``recvs`` lists of ``(peer, offset_rows, rows)`` in the order they
+    must be posted (for a fixed pair of ranks both lists walk the experts in ascending order, so
+    the i-th send matches the i-th receive), ``expert_counts``, ``expert_offsets``.  The combine
+    all-to-all is the same plan with the two lists swapped.
+    """
+    experts = len(counts[0])
+    if experts % world:
+        raise ValueError("the number of experts must be a multiple of the number of ranks")
+    local = experts // world
+    send_offsets = padded_offsets(counts[rank], pad)
+    sends = [(e // local, send_offsets[e], counts[rank][e]) for e in range(experts) if counts[rank][e]]
+    mine = range(rank * local, (rank + 1) * local)
+    expert_counts = [sum(counts[p][e] for p in range(world)) for e in mine]
+    expert_offsets = padded_offsets(expert_counts, pad)
+    recvs = []
+    for p in range(world):
+        for j, e in enumerate(mine):
+            if counts[p][e]:
+                before = sum(counts[q][e] for q in range(p))
+                recvs.append((p, expert_offsets[j] + before, counts[p][e]))
+    return dict(sends=sends, recvs=recvs, expert_counts=expert_counts, expert_offsets=expert_offsets,
+                send_offsets=send_offsets)
+
+
+def file_rendezvous(path, rank, payload=None, timeout=60.0, poll=0.02):
+    """Share ``payload`` (bytes, given by rank 0) with every rank through a file.  Rank 0 publishes
+    atomically; the others poll until the file appears or ``timeout`` seconds pass (TimeoutError:
+    rank 0 never arrived)."""
+    if rank == 0:
+        tmp = f"{path}.tmp.{os.getpid()}"
+        with open(tmp, "wb") as handle:
+            handle.write(payload)
+        os.replace(tmp, path)
+        return payload
+    deadline = time.monotonic() + timeout
+    while True:
+        try:
+            with open(path, "rb") as handle:
+                data = handle.read()
+            if data:
+                return data
+        except FileNotFoundError:
+            pass
+        if time.monotonic() > deadline:
+            raise TimeoutError(f"rank {rank}: no NCCL id at {path} after {timeout:.0f} s (is rank 0 alive?)")
+        time.sleep(poll)
+
+
+def init_communicator(rank, world, share=None, rendezvous_path=None, timeout=60.0):
+    """Create the process' NCCL communicator.  ``share(payload_or_None) -> bytes`` broadcasts rank
+    0's 128-byte id (rank 0 passes it, the others pass None); without it a file rendezvous at
+    ``rendezvous_path`` is used."""
+    payload = None
+    if rank == 0:
+        buffer = ctypes.create_string_buffer(128)
+        lib.call("qmoe_ep_unique_id", ctypes.cast(buffer, ctypes.c_void_p))
+        payload = buffer.raw
+    if share is not None:
+        payload = share(payload)
+    else:
+        if rendezvous_path is None:
+            rendezvous_path = os.path.join(
+                "/tmp", "qutai_moe_id_%s_%s" % (os.environ.get("MASTER_ADDR", "local"), os.environ.get("MASTER_PORT", "0")))
+        payload = file_rendezvous(rendezvous_path, rank, payload, timeout)
+    if len(payload) != 128:
+        raise ValueError("the NCCL id must be 128 bytes")
+    buffer = ctypes.create_string_buffer(payload, 128)
+    lib.call("qmoe_ep_init", rank, world, ctypes.cast(buffer, ctypes.c_void_p))
+
+
+def finalize_communicator(abort=False):
+    lib.call("qmoe_ep_finalize", 1 if abort else 0)
+
+
+def _segments(triples):
+    array = (lib.Segment * max(1, len(triples)))()
+    for i, (peer, offset, rows) in enumerate(triples):
+        array[i].peer, array[i].offset_rows, array[i].rows = peer, offset, rows
+    return array, len(triples)
+
+
+# ------------------------------------------------------------------------------------------------
+# the layer
+# ------------------------------------------------------------------------------------------------
+class ExpertParallelMoE:
+    """``SparseMoE`` over ``world`` GPUs.  Same constructor fields as the single-GPU layer plus
+    ``rank`` / ``world``; ``experts`` holds only this rank's E / world experts (global expert
+    ``rank * E_loc + j``), ``router`` is replicated and its gradient is summed over ranks."""
+
+    def __init__(self, config, *, rank, world, device="cuda", dtype="float32", seed=None, engine="auto", stream=0):
+        if device != "cuda" or dtype != "float32":
+            raise ValueError("parameters are float32 on device='cuda'")
+        d, E, h = config.d_model, config.n_experts, config.d_expert
+        if E % world:
+            raise ValueError("n_experts must be a multiple of the number of ranks")
+        self.rank, self.world, self.stream = rank, world, stream
+        self.top_k, self.n_experts, self.d_model, self.d_expert = config.top_k, E, d, h
+        self.local_experts = L = E // world
+        self.engine = {"auto": lib.ENGINE_AUTO, "simt": lib.ENGINE_SIMT, "tcgen05": lib.ENGINE_TCGEN05}[engine]
+        self._gate = DeviceStorage(L * h * d, "float32")
+        self._up = DeviceStorage(L * h * d, "float32")
+        self._down = DeviceStorage(L * d * h, "float32")
+        router = DeviceStorage(E * d, "float32")
+
+        def fill(storage, std, key):
+            lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std,
+                     (0x5EED if key is None else key) & (2 ** 64 - 1), stream)
+
+        fill(router, 0.02, seed)
+        self.router = Projection(Tensor(router, (E, d), requires_grad=True))
+        experts = []
+        for j in range(L):
+            i = rank * L + j  # global expert index decides the generator key, as on one GPU
+            views = (self._gate.view(j * h * d, h * d), self._up.view(j * h * d, h * d), self._down.view(j * d * h, d * h))
+            base = None if seed is None else seed + 1 + 3 * i
+            fill(views[0], 0.02, base)
+            fill(views[1], 0.02, None if base is None else base + 1)
+            fill(views[2], 0.02 / sqrt(2 * config.n_layers), None if base is None else base + 2)
+            experts.append(SwiGLU(Tensor(views[0], (h, d), requires_grad=True), Tensor(views[1], (h, d), requires_grad=True),
+                                  Tensor(views[2], (d, h), requires_grad=True)))
+        self.experts = tuple(experts)
+        self.utilization = None
+        self.last_counts = (0,) * E        # global counts (all ranks' tokens), as on one GPU
+        self._work = None
+        self._saved = None
+
+    def parameters(self):
+        return (*self.router.parameters(), *(p for expert in self.experts for p in expert.parameters()))
+
+    # ------------------------------------------------------------------------------------------
+    def _workspace(self, tokens, dtype):
+        if self._work is not None and self._work["key"] == (tokens, dtype):
+            return self._work
+        E, L, k, d, h, N = self.n_experts, self.local_experts, self.top_k, self.d_model, self.d_expert, self.world
+        A = tokens * k
+        Rt = lib.rows_bound(tokens, E, k)
+        Rx = lib.rows_bound(tokens * N, L, k)
+        blocks = lib.route_blocks(tokens)
+        S = DeviceStorage
+        buf = dict(
+            probs=S(tokens * E, "float32"), gate_weights=S(A, "float32"), expert_index=S(A, "int32"),
+            dest_row=S(A, "int32"), row_source=S(Rt, "int32"), counts=S(E, "int32"), offsets=S(E + 1, "int32"),
+            tile_expert=S(Rt // lib.ROW_PAD, "int32"), meta=S(4, "int32"), utilization=S(E, "float32"),
+            aux=S(1, "float32"), block_counts=S(blocks * E, "int32"), block_base=S(blocks * E, "int32"),
+            block_colsum=S(blocks * E, "float32"),
+            scores=S(tokens * E, "float32"), stats_local=S(2 * E, "int32"), stats_all=S(N * 2 * E, "int32"),
+            x_send=S(Rt * d, dtype), y_send=S(Rt * d, dtype), dy_send=S(Rt * d, dtype),
+            x_counts=S(L, "int32"), x_offsets=S(L + 1, "int32"), x_tile_expert=S(Rx // lib.ROW_PAD, "int32"), x_meta=S(4, "int32"),
+            x_recv=S(Rx * d, dtype), g=S(Rx * h, dtype), u=S(Rx * h, dtype), h=S(Rx * h, dtype), y_recv=S(Rx * d, dtype),
+            dy_recv=S(Rx * d, dtype), d_h=S(Rx * h, dtype), d_g=S(Rx * h, dtype), d_u=S(Rx * h, dtype),
+            d_gate_weights=S(A, "float32"), d_scores=S(tokens * E, "float32"), dx_router=S(tokens * d, "float32"),
+            router_partials=S(int(lib.load().qmoe_router_grad_partials(tokens, E, d)), "float32"),
+            d_w_router=S(E * d, "float32"), d_w_gate=S(L * h * d, "float32"), d_w_up=S(L * h * d, "float32"),
+            d_w_down=S(L * d * h, "float32"), aux_grad=S(1, "float32"),
+        )
+        if dtype == "bfloat16":
+            buf.update(w_gate=S(L * h * d, "bfloat16"), w_up=S(L * h * d, "bfloat16"), w_down=S(L * d * h, "bfloat16"))
+        token_route = lib.Route()
+        token_route.tokens, token_route.experts, token_route.top_k, token_route.rows_bound = tokens, E, k, Rt
+        for name in ("probs", "gate_weights", "expert_index", "dest_row", "row_source", "counts", "offsets", "tile_expert",
+                     "meta", "utilization", "aux", "block_counts", "block_base", "block_colsum"):
+            setattr(token_route, name, buf[name].ptr)
+        # expert side: only counts / offsets / tile_expert / meta are meaningful; the other tables
+        # are never touched through this struct and just need valid addresses
+        expert_route = lib.Route()
+        expert_route.tokens, expert_route.experts, expert_route.top_k, expert_route.rows_bound = tokens * N, L, k, Rx
+        for name in ("probs", "gate_weights", "expert_index", "dest_row", "row_source", "utilization", "aux",
+                     "block_counts", "block_base", "block_colsum"):
+            setattr(expert_route, name, buf["x_meta"].ptr)
+        expert_route.counts, expert_route.offsets = buf["x_counts"].ptr, buf["x_offsets"].ptr
+        expert_route.tile_expert, expert_route.meta = buf["x_tile_expert"].ptr, buf["x_meta"].ptr
+        ex = lib.Experts()
+        ex.experts, ex.dtype, ex.engine, ex.width, ex.hidden = L, lib.DTYPE_CODES[dtype], self.engine, d, h
+        if dtype == "bfloat16":
+            ex.w_gate, ex.w_up, ex.w_down = buf["w_gate"].ptr, buf["w_up"].ptr, buf["w_down"].ptr
+        else:
+            ex.w_gate, ex.w_up, ex.w_down = self._gate.ptr, self._up.ptr, self._down.ptr
+        host = ctypes.c_void_p()
+        lib.call("qmoe_host_alloc", ctypes.byref(host), 4 * N * 2 * E)
+        grad_views = [Tensor(buf["d_w_router"], (E, d))]
+        for j in range(L):
+            grad_views.append((Tensor(buf["d_w_gate"].view(j * h * d, h * d), (h, d)),
+                               Tensor(buf["d_w_up"].view(j * h * d, h * d), (h, d)),
+                               Tensor(buf["d_w_down"].view(j * d * h, d * h), (d, h))))
+        self._work = dict(key=(tokens, dtype), buf=buf, token_route=token_route, expert_route=expert_route, experts=ex,
+                          host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), grad_views=grad_views)
+        return self._work
+
+    def __call__(self, x):
+        return self.forward(x)
+
+    def forward(self, x):
+        """``x``: this rank's (T / world, d) shard.  Returns ``(y, aux)``; ``aux`` is the global
+        auxiliary loss (identical on every rank)."""
+        storage = x.storage if hasattr(x, "storage") else x
+        d, E, L, k, h, N = self.d_model, self.n_experts, self.local_experts, self.top_k, self.d_expert, self.world
+        tokens, dtype = storage.size // d, storage.dtype
+        shape = tuple(x.shape) if hasattr(x, "storage") else (tokens, d)
+        code, s = lib.DTYPE_CODES[dtype], self.stream
+        w = self._workspace(tokens, dtype)
+        buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
+        if dtype == "bfloat16":
+            n = L * h * d
+            lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, s)
+            lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, s)
+            lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, s)
+        lib.call("qmoe_router_logits", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr, tokens, d, E, s)
+        lib.call("qmoe_route", tr, buf["scores"].ptr, s)
+        lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
+                 ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
+        lib.call("qmoe_permute", tr, storage.ptr, buf["x_send"].ptr, code, d, s)       # overlaps the host wait below
+        lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
+        lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
+        lib.call("qmoe_stream_sync", s)                                                  # the one host wait of the step
+        stats = w["host_stats"]
+        counts = [[stats[p * 2 * E + e] for e in range(E)] for p in range(N)]
+        plan = plan_exchange(counts, self.rank, N)
+        w["sends"], w["recvs"] = _segments(plan["sends"]), _segments(plan["recvs"])
+        (sa, sn), (ra, rn) = w["sends"], w["recvs"]
+        lib.call("qmoe_ep_exchange", buf["x_send"].ptr, sa, sn, buf["x_recv"].ptr, ra, rn, d, code, s)
+        lib.call("qmoe_expert_forward", xr, ex, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr, s)
+        lib.call("qmoe_ep_exchange", buf["y_recv"].ptr, ra, rn, buf["y_send"].ptr, sa, sn, d, code, s)
+        out = DeviceStorage(storage.size, dtype)
+        lib.call("qmoe_combine", tr, buf["y_send"].ptr, out.ptr, code, d, s)
+        self.last_counts = tuple(sum(counts[p][e] for p in range(N)) for e in range(E))
+        self.utilization = Tensor(buf["utilization"], (E,))
+        self._saved = (w, storage, shape, plan)
+        return Tensor(out, shape), Tensor(buf["aux"], ())
+
+    def backward(self, grad_y, grad_aux=None):
+        """Backward of the last forward.  ``grad_aux`` (host float or None) is the gradient of the
+        GLOBAL auxiliary loss; every rank passes the same value.  Leaves local expert gradients and
+        the all-reduced router gradient in ``parameter.grad``; returns this rank's ``dx``."""
+        if self._saved is None:
+            raise RuntimeError("backward called before forward")
+        w, x_storage, shape, plan = self._saved
+        g = grad_y.storage if hasattr(grad_y, "storage") else grad_y
+        d, E, L, k, h, N = self.d_model, self.n_experts, self.local_experts, self.top_k, self.d_expert, self.world
+        tokens, dtype = x_storage.size // d, x_storage.dtype
+        code, s = lib.DTYPE_CODES[dtype], self.stream
+        buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
+        (sa, sn), (ra, rn) = w["sends"], w["recvs"]
+        ga = 0
+        if grad_aux is not None:
+            # the routing-backward kernel scales by E / (local tokens); the loss is over all ranks' tokens.
+            # Uploaded before anything is launched, because the small copy waits for the stream.
+            value = float(grad_aux) / N
+            buf["aux_grad"].upload_bytes(ctypes.string_at(ctypes.byref(ctypes.c_float(value)), 4), s)
+            ga = buf["aux_grad"].ptr
+        views = w["grad_views"]
+        owned = {id(views[0])} | {id(t) for group in views[1:] for t in group}
+        for parameter in self.parameters():
+            if parameter.grad is not None and id(parameter.grad) in owned:
+                parameter.grad = Tensor(parameter.grad.storage.copy(s), parameter.shape)
+        lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
+        lib.call("qmoe_ep_zero_pad_rows", xr, buf["dy_recv"].ptr, code, d, s)
+        lib.call("qmoe_ep_exchange", buf["dy_send"].ptr, sa, sn, buf["dy_recv"].ptr, ra, rn, d, code, s)
+        lib.call("qmoe_expert_backward", xr, ex, buf["dy_recv"].ptr, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr,
+                 buf["d_h"].ptr, buf["d_g"].ptr, buf["d_u"].ptr, buf["dy_recv"].ptr,  # dX reuses dY's buffer
+                 buf["d_w_gate"].ptr, buf["d_w_up"].ptr, buf["d_w_down"].ptr, s)
+        lib.call("qmoe_ep_exchange", buf["dy_recv"].ptr, ra, rn, buf["dy_send"].ptr, sa, sn, d, code, s)
+        lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
+        lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
+                 buf["dx_router"].ptr, buf["d_w_router"].ptr, buf["router_partials"].ptr, tokens, d, E, s)
+        lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, s)
+        dx = DeviceStorage(x_storage.size, dtype)
+        lib.call("qmoe_unpermute_reduce", tr, buf["dy_send"].ptr, buf["dx_router"].ptr, dx.ptr, code, d, s)
+        _accumulate(self.router.weight, views[0], s)
+        for j, expert in enumerate(self.experts):
+            if not plan["expert_counts"][j]:
+                continue
+            gate, up, down = views[1 + j]
+            _accumulate(expert.gate.weight, gate, s)
+            _accumulate(expert.up.weight, up, s)
+            _accumulate(expert.down.weight, down, s)
+        return Tensor(dx, shape)

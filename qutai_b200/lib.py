@@ -35,6 +35,11 @@ class Experts(Structure):
                 ("w_gate", c_uint64), ("w_up", c_uint64), ("w_down", c_uint64)]
 
 
+class Segment(Structure):
+    """``qmoe_ep_segment_t``."""
+    _fields_ = [("peer", c_int32), ("reserved", c_int32), ("offset_rows", c_int64), ("rows", c_int64)]
+
+
 class Layer(Structure):
     """``qmoe_layer_t``."""
     _fields_ = [("route", Route), ("experts", Experts)] + [
@@ -46,7 +51,7 @@ class Layer(Structure):
 
 
 _U, _I32, _I64 = c_uint64, c_int32, c_int64
-_RP, _EP, _LP = POINTER(Route), POINTER(Experts), POINTER(Layer)
+_RP, _EP, _LP, _SP = POINTER(Route), POINTER(Experts), POINTER(Layer), POINTER(Segment)
 
 # name -> (restype, argtypes); every symbol declared in include/qutai_moe.h
 SIGNATURES = {
@@ -91,6 +96,15 @@ SIGNATURES = {
     "qmoe_normal_fill": (c_int, [_U, _I32, _I64, c_double, c_double, _U, _U]),
     "qmoe_layer_forward": (c_int, [_LP, _U]),
     "qmoe_layer_backward": (c_int, [_LP, _U]),
+    "qmoe_ep_unique_id": (c_int, [c_void_p]),
+    "qmoe_ep_init": (c_int, [_I32, _I32, c_void_p]),
+    "qmoe_ep_finalize": (c_int, [_I32]),
+    "qmoe_ep_info": (c_int, [POINTER(c_int32), POINTER(c_int32)]),
+    "qmoe_ep_gather_stats": (c_int, [_RP, _U, _U, c_void_p, _U]),
+    "qmoe_ep_plan": (c_int, [_U, _RP, _RP, _I64, _U]),
+    "qmoe_ep_zero_pad_rows": (c_int, [_RP, _U, _I32, _I64, _U]),
+    "qmoe_ep_exchange": (c_int, [_U, _SP, _I32, _U, _SP, _I32, _I64, _I32, _U]),
+    "qmoe_ep_all_reduce_f32": (c_int, [_U, _I64, _U]),
 }
 
 _lock = threading.Lock()

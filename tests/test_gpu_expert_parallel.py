@@ -1,0 +1,75 @@
+"""Expert-parallel layer on real GPUs: every rank is a child process that sees one GPU.  world = 1
+runs on any box (all exchanges are self-sends through NCCL); world = 2 needs two GPUs.  The parent
+assembles the ranks' results and checks them against the oracle run on the whole problem with the
+devices' own fp32 logits."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from oracle import moe_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+BF16_TOL = 2e-2
+
+
+def gpu_count():
+    try:
+        out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
+        return sum(1 for line in out.splitlines() if line.startswith("GPU "))
+    except Exception:
+        return 0
+
+
+def run_ranks(world, out_dir):
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES=str(rank), NCCL_DEBUG="WARN")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "ep_gpu_worker.py"), str(rank), str(world), out_dir],
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env))
+    for rank, proc in enumerate(procs):
+        try:
+            out, _ = proc.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            out, _ = proc.communicate()
+        assert proc.returncode == 0 and f"rank {rank} done" in out, out[-3000:]
+    return [np.load(os.path.join(out_dir, f"rank{rank}.npz")) for rank in range(world)]
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, tmp_path):
+    if gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    sys.path.insert(0, HERE)
+    from ep_gpu_worker import problem
+
+    p = problem()
+    T, E, k = p["T"], p["E"], p["k"]
+    ranks = run_ranks(world, str(tmp_path))
+    scores = np.concatenate([r["scores"] for r in ranks])
+    assert oracle.max_rel_err(scores, p["x"] @ p["router"].astype(np.float64).T) <= 1e-4
+    r16 = oracle.round_bf16
+    y, aux, ctx = oracle.moe_forward(p["x"], p["router"], r16(p["gate"]), r16(p["up"]), r16(p["down"]), k, scores=scores)
+    grads = oracle.moe_backward(ctx, p["grad"], p["grad_aux"])
+    route = ctx["route"]
+    L = E // world
+    for rank, r in enumerate(ranks):
+        shard = slice(rank * T // world, (rank + 1) * T // world)
+        assert tuple(r["counts"].tolist()) == route["counts"]            # global counts, bit-exact, on every rank
+        assert abs(float(r["aux"][0]) - aux) <= 1e-5                      # global auxiliary loss
+        assert np.abs(r["utilization"] - route["utilization"]).max() <= 1e-6
+        assert oracle.max_rel_err(r["y"], y[shard]) <= BF16_TOL
+        assert oracle.max_rel_err(r["dx"], grads["x"][shard]) <= BF16_TOL
+        assert oracle.max_rel_err(r["d_router"], grads["router"]) <= BF16_TOL   # summed over ranks
+        for j in range(L):
+            e = rank * L + j
+            assert bool(r["has_grad"][j]) == (route["counts"][e] > 0)
+            if route["counts"][e]:
+                for key in ("gate", "up", "down"):
+                    assert oracle.max_rel_err(r[f"d_{key}_{j}"], grads[key][e]) <= BF16_TOL
+    if world > 1:  # the router gradient is identical on every rank after the all-reduce
+        assert np.array_equal(ranks[0]["d_router"], ranks[1]["d_router"])
