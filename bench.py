@@ -221,6 +221,44 @@ def build_layer(w, torch, device, seed=0):
     return layer
 
 
+def build_ep_layer(w, rank, world, seed=0):
+    import numpy as np
+
+    from qutai_b200 import lib
+    from qutai_b200.expert_parallel import ExpertParallelMoE
+
+    class Cfg:
+        d_model, n_experts, top_k, d_expert, n_layers = w["d"], w["E"], w["k"], w["h"], 1
+
+    layer = ExpertParallelMoE(Cfg, rank=rank, world=world, seed=seed)
+    d, E, h = w["d"], w["E"], w["h"]
+    fill = lambda storage, std, key: lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std, key, 0)
+    fill(layer._gate, d ** -0.5, 101 + 10 * rank)
+    fill(layer._up, d ** -0.5, 102 + 10 * rank)
+    fill(layer._down, h ** -0.5, 103 + 10 * rank)
+    rng = np.random.default_rng(seed)   # the replicated router: same draws on every rank
+    router = (rng.standard_normal((E, d)) * w["router_std"]).astype(np.float32)
+    if w["bias_std"]:
+        router[:, d - 1] = (rng.standard_normal(E) * w["bias_std"]).astype(np.float32)
+    layer.router.weight.storage.upload_bytes(router.tobytes())
+    layer.router_host = router
+    return layer
+
+
+def balanced_placement(counts, world):
+    """Static load-aware expert placement: longest-processing-time greedy.  Returns ``order`` with
+    ``order[new_index] = old_index`` such that rank p owns new indices [p*L, (p+1)*L) and the rows
+    per rank are as even as the per-expert loads allow."""
+    E = len(counts)
+    L = E // world
+    loads, members = [0] * world, [[] for _ in range(world)]
+    for e in sorted(range(E), key=lambda i: (-counts[i], i)):
+        p = min((r for r in range(world) if len(members[r]) < L), key=lambda r: (loads[r], r))
+        members[p].append(e)
+        loads[p] += counts[e]
+    return [e for p in range(world) for e in sorted(members[p])]
+
+
 def host_inputs(w, torch, seed=0):
     gen = torch.Generator().manual_seed(seed)
     x = torch.randn(w["tokens"], w["d"], generator=gen, dtype=torch.float32)
@@ -240,22 +278,44 @@ def run_gpu(args, w, rank, world):
 
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        raise SystemExit("expert-parallel bench is not wired yet")
     device = torch.device("cuda", local)
     stream = torch.cuda.current_stream().cuda_stream
-    layer = build_layer(w, torch, device)
+    if world > 1:
+        from qutai_b200.expert_parallel import init_communicator
+
+        dist.init_process_group("nccl", device_id=device)
+
+        def share(payload):
+            box = [payload]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+
+        init_communicator(rank, world, share=share)
+        layer = build_ep_layer(w, rank, world)
+    else:
+        layer = build_layer(w, torch, device)
     layer.stream = stream
     x_host, g_host = host_inputs(w, torch)
-    T, d = w["tokens"], w["d"]
+    T_global, d = w["tokens"], w["d"]
+    T = T_global // world                      # tokens of this rank (contiguous shard)
+    x_host = x_host[rank * T:(rank + 1) * T].clone().pin_memory()
+    g_host = g_host[rank * T:(rank + 1) * T].clone().pin_memory()
     x_dev, g_dev = x_host.to(device), g_host.to(device)
     aux_grad = torch.full((1,), 0.01, dtype=torch.float32, device=device)
     y_host = torch.empty_like(x_host).pin_memory()
     dx_host = torch.empty_like(x_host).pin_memory()
     wrap = lambda t, dtype: DeviceStorage.wrap(t.data_ptr(), t.numel(), dtype, owner=t)
-    xs, gs, ga = Tensor(wrap(x_dev, "bfloat16"), (T, d)), Tensor(wrap(g_dev, "bfloat16"), (T, d)), wrap(aux_grad, "float32")
+    xs, gs = Tensor(wrap(x_dev, "bfloat16"), (T, d)), Tensor(wrap(g_dev, "bfloat16"), (T, d))
+    ga = wrap(aux_grad, "float32") if world == 1 else 0.01
     forward_only = args.workload == "c5"
+    placement = "contiguous"
+    if world > 1 and args.placement == "balanced":
+        # Experts are placed on ranks by measured load (one profiling forward), not by index.  With
+        # synthetic iid expert weights this is a relabelling of the experts, i.e. of the router rows.
+        layer(xs)
+        order = balanced_placement(layer.last_counts, world)
+        layer.router.weight.storage.upload_bytes(layer.router_host[order].copy().tobytes())
+        placement = "balanced (LPT greedy on the counts of a profiling forward)"
 
     parameters = layer.parameters()
 
@@ -279,13 +339,22 @@ def run_gpu(args, w, rank, world):
 
     def timed(fn, steps):
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for _ in range(steps):
             fn()
         stop.record()
         torch.cuda.synchronize()
-        return start.elapsed_time(stop) / steps
+        ms = start.elapsed_time(stop) / steps
+        if world > 1:  # the job is as slow as its slowest rank
+            worst = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = float(worst.item())
+        return ms
 
     for _ in range(args.warmup):
         step()
@@ -310,6 +379,10 @@ def run_gpu(args, w, rank, world):
 
     peaks = load_peaks()
     gemm_flops, router_flops = layer_flops(w)
+    if world > 1:  # this rank's share: the rows its experts received, its own tokens for the router
+        L = w["E"] // world
+        gemm_flops = 18.0 * sum(counts[rank * L:(rank + 1) * L]) * w["d"] * w["h"]
+        router_flops /= world
     if forward_only:
         gemm_flops, router_flops = gemm_flops / 3, router_flops / 3
     gemm_ms = (classes["expert_gemm"][0] + classes["wgrad_gemm"][0]) / args.steps
@@ -326,7 +399,7 @@ def run_gpu(args, w, rank, world):
         if t > 0:
             gbs = nbytes / (t * 1e-3) / 1e9
             hbm[name] = dict(ms=round(t, 4), achieved_gbs=round(gbs, 1), frac=round(gbs / peaks["hbm_gbs"], 3))
-    tokens_per_s = T / (ms * 1e-3)
+    tokens_per_s = T_global / (ms * 1e-3)
     bytes_in = x_host.numel() * 2 * (1 if forward_only else 2)
     bytes_out = x_host.numel() * 2 * (1 if forward_only else 2) + 4
     line = dict(
@@ -334,7 +407,7 @@ def run_gpu(args, w, rank, world):
         value=tokens_per_s, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
         higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
         config=workload_config(args.workload, w, world),
-        e2e=dict(value=T / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=bytes_in,
+        e2e=dict(value=T_global / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=bytes_in,
                  d2h_bytes_per_step=bytes_out),
         gpu_launches=int(launches), clocks=clocks,
         roofline=dict(bound="tensor", kernel="grouped_gemm_kernel (tcgen05)", achieved=achieved, peak=peak,
@@ -352,15 +425,24 @@ def run_gpu(args, w, rank, world):
         cores = host_cores()
         line["cpu_baseline"] = dict(
             value=value, unit="tokens/s", cores=cores, kind="port",
-            sample=f"{sample} of {T} tokens, full d/E/k/h, numpy float64 restatement of the upstream CPU path on "
+            sample=f"{sample} of {T_global} tokens, full d/E/k/h, numpy float64 restatement of the upstream CPU path on "
                    f"{cores} threads, {seconds:.2f} s per forward+backward",
             pure_python_estimate=dict(
                 mac_per_s=pure_python_rate(), cores=1,
                 note="scalar triple-loop rate of the upstream pure-Python path; tokens/s = rate / (9*k*d*h + 3*d*E) MAC per token"))
         rate = line["cpu_baseline"]["pure_python_estimate"]["mac_per_s"]
         line["cpu_baseline"]["pure_python_estimate"]["tokens_per_s"] = rate / (9.0 * k * d * h + 3.0 * d * E)
+    if world > 1:
+        line["config"]["expert_placement"] = placement
+        line["per_rank_rows"] = [sum(counts[p * (w["E"] // world):(p + 1) * (w["E"] // world)]) for p in range(world)]
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if world > 1:
+        from qutai_b200.expert_parallel import finalize_communicator
+
+        dist.barrier()
+        finalize_communicator()
+        dist.destroy_process_group()
 
 
 def main():
@@ -371,6 +453,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"])
     args = parser.parse_args()
     args.warmup = max(3, args.warmup)
     w = WORKLOADS[args.workload]
