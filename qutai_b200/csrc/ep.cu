@@ -251,7 +251,7 @@ extern "C" int qmoe_ep_exchange(uint64_t send_buf, const qmoe_ep_segment_t* send
         return fail_arg("ep_exchange: null buffer or segment list");
     if (width <= 0 || (dtype != QMOE_BF16 && dtype != QMOE_F32)) return fail_arg("ep_exchange: bad width or dtype");
     cudaStream_t stream = (cudaStream_t)stream_;
-    TimedScope timed(KC_OTHER, stream);
+    TimedScope timed(KC_EXCHANGE, stream);
     const size_t item = dtype == QMOE_BF16 ? 2 : 4;
     const ncclDataType_t type = dtype == QMOE_BF16 ? ncclBfloat16 : ncclFloat32;
     for (int i = 0; i < n_sends; ++i)
@@ -260,14 +260,29 @@ extern "C" int qmoe_ep_exchange(uint64_t send_buf, const qmoe_ep_segment_t* send
     for (int i = 0; i < n_recvs; ++i)
         if (recvs[i].peer < 0 || recvs[i].peer >= g_world || recvs[i].rows < 0 || recvs[i].offset_rows < 0)
             return fail_arg("ep_exchange: receive segment %d is invalid", i);
+    // Segments that stay on this rank are plain device-to-device copies, matched in list order
+    // like any other pair; only rows that really change GPU go through NCCL.
+    {
+        int r = 0;
+        for (int i = 0; i < n_sends; ++i) {
+            if (sends[i].peer != g_rank || !sends[i].rows) continue;
+            while (r < n_recvs && (recvs[r].peer != g_rank || !recvs[r].rows)) ++r;
+            if (r >= n_recvs || recvs[r].rows != sends[i].rows)
+                return fail_arg("ep_exchange: local send segment %d has no matching local receive segment", i);
+            QMOE_CUDA(cudaMemcpyAsync((char*)recv_buf + (size_t)recvs[r].offset_rows * width * item,
+                                      (const char*)send_buf + (size_t)sends[i].offset_rows * width * item,
+                                      (size_t)sends[i].rows * width * item, cudaMemcpyDeviceToDevice, stream));
+            ++r;
+        }
+    }
     QMOE_NCCL(g_nccl.GroupStart());
     int rc = 0;
     for (int i = 0; i < n_sends && !rc; ++i)
-        if (sends[i].rows)
+        if (sends[i].rows && sends[i].peer != g_rank)
             rc = check_nccl(g_nccl.Send((const char*)send_buf + (size_t)sends[i].offset_rows * width * item,
                                         (size_t)sends[i].rows * width, type, sends[i].peer, g_comm, stream), "ncclSend");
     for (int i = 0; i < n_recvs && !rc; ++i)
-        if (recvs[i].rows)
+        if (recvs[i].rows && recvs[i].peer != g_rank)
             rc = check_nccl(g_nccl.Recv((char*)recv_buf + (size_t)recvs[i].offset_rows * width * item,
                                         (size_t)recvs[i].rows * width, type, recvs[i].peer, g_comm, stream), "ncclRecv");
     const int end = check_nccl(g_nccl.GroupEnd(), "ncclGroupEnd");
