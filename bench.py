@@ -221,7 +221,7 @@ def build_layer(w, torch, device, seed=0):
     return layer
 
 
-def build_ep_layer(w, rank, world, seed=0):
+def build_ep_layer(w, rank, world, seed=0, transport="p2p", gather=None):
     import numpy as np
 
     from qutai_b200 import lib
@@ -230,7 +230,7 @@ def build_ep_layer(w, rank, world, seed=0):
     class Cfg:
         d_model, n_experts, top_k, d_expert, n_layers = w["d"], w["E"], w["k"], w["h"], 1
 
-    layer = ExpertParallelMoE(Cfg, rank=rank, world=world, seed=seed)
+    layer = ExpertParallelMoE(Cfg, rank=rank, world=world, seed=seed, transport=transport, gather=gather)
     d, E, h = w["d"], w["E"], w["h"]
     fill = lambda storage, std, key: lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std, key, 0)
     fill(layer._gate, d ** -0.5, 101 + 10 * rank)
@@ -290,8 +290,13 @@ def run_gpu(args, w, rank, world):
             dist.broadcast_object_list(box, src=0)
             return box[0]
 
+        def gather(payload):
+            box = [None] * world
+            dist.all_gather_object(box, payload)
+            return box
+
         init_communicator(rank, world, share=share)
-        layer = build_ep_layer(w, rank, world)
+        layer = build_ep_layer(w, rank, world, transport=args.transport, gather=gather)
     else:
         layer = build_layer(w, torch, device)
     layer.stream = stream
@@ -434,6 +439,7 @@ def run_gpu(args, w, rank, world):
         line["cpu_baseline"]["pure_python_estimate"]["tokens_per_s"] = rate / (9.0 * k * d * h + 3.0 * d * E)
     if world > 1:
         line["config"]["expert_placement"] = placement
+        line["config"]["transport"] = args.transport
         line["per_rank_rows"] = [sum(counts[p * (w["E"] // world):(p + 1) * (w["E"] // world)]) for p in range(world)]
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -454,6 +460,8 @@ def main():
     parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"])
+    parser.add_argument("--transport", default="p2p", choices=["p2p", "nccl"],
+                        help="expert-parallel exchange: direct peer-memory stores, or NCCL send/receive")
     args = parser.parse_args()
     args.warmup = max(3, args.warmup)
     w = WORKLOADS[args.workload]

@@ -320,6 +320,42 @@ int qmoe_ep_exchange(uint64_t send_buffer, const qmoe_ep_segment_t* sends, int32
 /* In-place sum over ranks (router weight gradient). */
 int qmoe_ep_all_reduce_f32(uint64_t buffer, int64_t n, uint64_t stream);
 
+/* Direct transport over peer memory (no upstream counterpart).  Instead of NCCL send/receive, rows
+ * are pushed into the destination rank's buffer with plain stores over NVLink; destinations are
+ * computed on the device from the gathered counts, so the host does not read them.  Buffers that
+ * other ranks write into must come from one cudaMalloc each (qmoe_malloc), are exported with
+ * qmoe_ep_ipc_export, and opened by every other rank with qmoe_ep_ipc_open (all GPUs of the job
+ * must be visible to every process).  After a push, qmoe_ep_barrier orders it against the readers
+ * on every rank.  No kernel waits on another GPU. */
+#define QMOE_EP_MAX_RANKS 16
+typedef struct qmoe_ep_peers {
+    int32_t world;
+    int32_t rank;
+    uint64_t buffer[QMOE_EP_MAX_RANKS]; /* the same buffer on every rank (own entry: local address) */
+    uint64_t ret[QMOE_EP_MAX_RANKS];    /* i32 return-address table of every rank (dispatch only) */
+} qmoe_ep_peers_t;
+int qmoe_set_device(int32_t device);
+int qmoe_ep_ipc_export(uint64_t address, void* handle64);
+int qmoe_ep_ipc_open(const void* handle64, uint64_t* address);
+int qmoe_ep_ipc_close(uint64_t address);
+/* A 1-element all-reduce on scratch_i32: when it has run on a rank, every rank has finished the
+ * work it enqueued before its own call. */
+int qmoe_ep_barrier(uint64_t scratch_i32, uint64_t stream);
+/* dest_base[e] (i32 [E]) = row, in the expert-side layout of the rank owning expert e, where this
+ * rank's rows for e start (after the rows of lower ranks). */
+int qmoe_ep_dest_base(uint64_t stats_all, int32_t experts, int32_t local_experts, uint64_t dest_base,
+                      uint64_t stream);
+/* Token side -> expert side: every real row of `src` (local dispatched layout of token_route) is
+ * stored into the owner's buffer; with write_return_addresses the owner's return table gets
+ * (source rank, source row) for each row. */
+int qmoe_ep_push_dispatch(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t src,
+                          const qmoe_ep_peers_t* peers, int32_t write_return_addresses, int32_t dtype,
+                          int64_t width, uint64_t stream);
+/* Expert side -> token side: every real row of `src` (expert-side layout) is stored at the return
+ * address recorded for it. */
+int qmoe_ep_push_return(const qmoe_route_t* expert_route, uint64_t return_addresses, uint64_t src,
+                        const qmoe_ep_peers_t* peers, int32_t dtype, int64_t width, uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -298,3 +298,214 @@ extern "C" int qmoe_ep_all_reduce_f32(uint64_t buf, int64_t n, uint64_t stream_)
     QMOE_NCCL(g_nccl.AllReduce((const void*)buf, (void*)buf, (size_t)n, ncclFloat32, ncclSum, g_comm, stream));
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Direct transport: rows are pushed into the destination GPU's buffer with plain 16-byte stores
+// over NVLink (peer memory mapped through CUDA IPC), one warp per row.  Sizes and destinations are
+// computed on the device from the gathered counts, so the host never has to read them; the only
+// cross-GPU ordering is a tiny NCCL collective after each push (qmoe_ep_barrier).  No kernel here
+// waits on another GPU.
+// ---------------------------------------------------------------------------------------------
+namespace qmoe {
+namespace {
+
+constexpr int kMaxPeers = QMOE_EP_MAX_RANKS;
+constexpr int kRetRankShift = 26;  // return address = (source rank << 26) | source row
+
+struct PeerTable {
+    uint4* buffer[kMaxPeers];
+    int* ret[kMaxPeers];
+};
+
+// dest_base[e]: row, inside the owner's expert-side layout, where THIS rank's rows for expert e start
+__global__ void __launch_bounds__(kMaxExperts)
+ep_dest_base_kernel(const int* __restrict__ stats_all, int world, int rank, int E, int E_loc, int* __restrict__ dest_base) {
+    __shared__ int s_total[kMaxExperts];
+    const int e = threadIdx.x;
+    if (e < E) {
+        int total = 0;
+        for (int p = 0; p < world; ++p) total += stats_all[(long long)p * 2 * E + e];
+        s_total[e] = total;
+    }
+    __syncthreads();
+    if (e >= E) return;
+    int off = 0;
+    for (int j = (e / E_loc) * E_loc; j < e; ++j) off += (s_total[j] + kRowPad - 1) / kRowPad * kRowPad;
+    for (int q = 0; q < rank; ++q) off += stats_all[(long long)q * 2 * E + e];
+    dest_base[e] = off;
+}
+
+// Token side -> expert side.  Row r of the local dispatched layout (expert e = tile_expert[r / 128],
+// index i = r - offsets[e] inside the expert, a real row when i < counts[e]) goes to rank e / E_loc,
+// row dest_base[e] + i, and its return address is recorded next to it.
+__global__ void __launch_bounds__(256)
+ep_push_dispatch_kernel(const uint4* __restrict__ src, long long row_vecs, const int* __restrict__ tile_expert,
+                        const int* __restrict__ offsets, const int* __restrict__ counts, const int* __restrict__ meta,
+                        const int* __restrict__ dest_base, int E_loc, int rank, PeerTable peers) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    const int rows = meta[0];
+    for (long long r = warp; r < rows; r += nwarps) {
+        const int e = tile_expert[r / kRowPad];
+        const int i = (int)r - offsets[e];
+        if (i >= counts[e]) continue;  // pad row: nothing to send
+        const int p = e / E_loc;
+        const long long dest = (long long)dest_base[e] + i;
+        const uint4* s = src + r * row_vecs;
+        uint4* d = peers.buffer[p] + dest * row_vecs;
+        long long c = lane;
+        for (; c + 96 < row_vecs; c += 128) {
+            const uint4 v0 = s[c], v1 = s[c + 32], v2 = s[c + 64], v3 = s[c + 96];
+            d[c] = v0; d[c + 32] = v1; d[c + 64] = v2; d[c + 96] = v3;
+        }
+        for (; c < row_vecs; c += 32) d[c] = s[c];
+        if (lane == 0 && peers.ret[p]) peers.ret[p][dest] = (rank << kRetRankShift) | (int)r;
+    }
+    __threadfence_system();
+}
+
+// Expert side -> token side.  Row j of the local expert-side layout (a real row when it lies in
+// [offsets[x], offsets[x] + counts[x])) goes back to the rank and row recorded in ret[j].
+__global__ void __launch_bounds__(256)
+ep_push_return_kernel(const uint4* __restrict__ src, long long row_vecs, const int* __restrict__ tile_expert,
+                      const int* __restrict__ offsets, const int* __restrict__ counts, const int* __restrict__ meta,
+                      const int* __restrict__ ret, PeerTable peers) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    const int rows = meta[0];
+    for (long long j = warp; j < rows; j += nwarps) {
+        const int x = tile_expert[j / kRowPad];
+        if ((int)j - offsets[x] >= counts[x]) continue;
+        const int address = ret[j];
+        const int q = address >> kRetRankShift;
+        const long long dest = address & ((1 << kRetRankShift) - 1);
+        const uint4* s = src + j * row_vecs;
+        uint4* d = peers.buffer[q] + dest * row_vecs;
+        long long c = lane;
+        for (; c + 96 < row_vecs; c += 128) {
+            const uint4 v0 = s[c], v1 = s[c + 32], v2 = s[c + 64], v3 = s[c + 96];
+            d[c] = v0; d[c + 32] = v1; d[c + 64] = v2; d[c + 96] = v3;
+        }
+        for (; c < row_vecs; c += 32) d[c] = s[c];
+    }
+    __threadfence_system();
+}
+
+int check_peers(const qmoe_ep_peers_t* peers, bool need_ret) {
+    if (!peers) return fail_arg("peers is null");
+    if (peers->world <= 0 || peers->world > kMaxPeers || peers->rank < 0 || peers->rank >= peers->world)
+        return fail_arg("peers: world must be in [1, %d] and rank inside it", kMaxPeers);
+    for (int p = 0; p < peers->world; ++p) {
+        if (!peers->buffer[p] || (peers->buffer[p] & 15u)) return fail_arg("peers: buffer of rank %d is null or misaligned", p);
+        if (need_ret && !peers->ret[p]) return fail_arg("peers: return table of rank %d is null", p);
+    }
+    return 0;
+}
+
+PeerTable make_table(const qmoe_ep_peers_t* peers, bool with_ret) {
+    PeerTable t = {};
+    for (int p = 0; p < peers->world; ++p) {
+        t.buffer[p] = (uint4*)peers->buffer[p];
+        t.ret[p] = with_ret ? (int*)peers->ret[p] : nullptr;
+    }
+    return t;
+}
+
+int push_grid(long long rows) {
+    long long blocks = (rows + 7) / 8;
+    const long long cap = (long long)sm_count() * 8;
+    return (int)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
+}
+
+}  // namespace
+}  // namespace qmoe
+
+extern "C" int qmoe_set_device(int32_t device) {
+    QMOE_CUDA(cudaSetDevice(device));
+    return 0;
+}
+
+extern "C" int qmoe_ep_ipc_export(uint64_t address, void* handle64) {
+    if (!address || !handle64) return fail_arg("ep_ipc_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+    QMOE_CUDA(cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle64, (void*)address));
+    return 0;
+}
+
+extern "C" int qmoe_ep_ipc_open(const void* handle64, uint64_t* address) {
+    if (!handle64 || !address) return fail_arg("ep_ipc_open: null argument");
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, handle64, sizeof(handle));
+    void* p = nullptr;
+    QMOE_CUDA(cudaIpcOpenMemHandle(&p, handle, cudaIpcMemLazyEnablePeerAccess));
+    *address = (uint64_t)p;
+    return 0;
+}
+
+extern "C" int qmoe_ep_ipc_close(uint64_t address) {
+    if (!address) return 0;
+    QMOE_CUDA(cudaIpcCloseMemHandle((void*)address));
+    return 0;
+}
+
+extern "C" int qmoe_ep_barrier(uint64_t scratch_i32, uint64_t stream_) {
+    if (int rc = need_comm()) return rc;
+    if (!scratch_i32) return fail_arg("ep_barrier: scratch is null");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXCHANGE, stream);
+    QMOE_NCCL(g_nccl.AllReduce((const void*)scratch_i32, (void*)scratch_i32, 1, ncclInt32, ncclSum, g_comm, stream));
+    return 0;
+}
+
+extern "C" int qmoe_ep_dest_base(uint64_t stats_all, int32_t experts, int32_t local_experts, uint64_t dest_base,
+                                 uint64_t stream_) {
+    if (int rc = need_comm()) return rc;
+    if (!stats_all || !dest_base) return fail_arg("ep_dest_base: null buffer");
+    if (experts <= 0 || experts > kMaxExperts || local_experts * g_world != experts)
+        return fail_arg("ep_dest_base: %d local experts x %d ranks != %d experts", local_experts, g_world, experts);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_OTHER, stream);
+    ep_dest_base_kernel<<<1, kMaxExperts, 0, stream>>>((const int*)stats_all, g_world, g_rank, experts, local_experts,
+                                                        (int*)dest_base);
+    QMOE_LAUNCH_CHECK("ep_dest_base_kernel");
+    return 0;
+}
+
+extern "C" int qmoe_ep_push_dispatch(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t src,
+                                     const qmoe_ep_peers_t* peers, int32_t write_return_addresses, int32_t dtype,
+                                     int64_t width, uint64_t stream_) {
+    if (int rc = route_check(token_route)) return rc;
+    if (int rc = check_peers(peers, write_return_addresses != 0)) return rc;
+    if (!dest_base || !src || (src & 15u)) return fail_arg("ep_push_dispatch: null or misaligned buffer");
+    const long long row_bytes = width * (dtype == QMOE_BF16 ? 2 : 4);
+    if (width <= 0 || row_bytes % 16) return fail_arg("ep_push_dispatch: rows must be multiples of 16 bytes");
+    if (token_route->experts % peers->world) return fail_arg("ep_push_dispatch: experts must divide evenly over the ranks");
+    if (token_route->rows_bound >= (1ll << kRetRankShift)) return fail_arg("ep_push_dispatch: too many rows for the return-address encoding");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXCHANGE, stream);
+    ep_push_dispatch_kernel<<<push_grid(token_route->rows_bound), 256, 0, stream>>>(
+        (const uint4*)src, row_bytes / 16, (const int*)token_route->tile_expert, (const int*)token_route->offsets,
+        (const int*)token_route->counts, (const int*)token_route->meta, (const int*)dest_base,
+        token_route->experts / peers->world, peers->rank, make_table(peers, write_return_addresses != 0));
+    QMOE_LAUNCH_CHECK("ep_push_dispatch_kernel");
+    return 0;
+}
+
+extern "C" int qmoe_ep_push_return(const qmoe_route_t* expert_route, uint64_t return_addresses, uint64_t src,
+                                   const qmoe_ep_peers_t* peers, int32_t dtype, int64_t width, uint64_t stream_) {
+    if (int rc = route_check(expert_route)) return rc;
+    if (int rc = check_peers(peers, false)) return rc;
+    if (!return_addresses || !src || (src & 15u)) return fail_arg("ep_push_return: null or misaligned buffer");
+    const long long row_bytes = width * (dtype == QMOE_BF16 ? 2 : 4);
+    if (width <= 0 || row_bytes % 16) return fail_arg("ep_push_return: rows must be multiples of 16 bytes");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXCHANGE, stream);
+    ep_push_return_kernel<<<push_grid(expert_route->rows_bound), 256, 0, stream>>>(
+        (const uint4*)src, row_bytes / 16, (const int*)expert_route->tile_expert, (const int*)expert_route->offsets,
+        (const int*)expert_route->counts, (const int*)expert_route->meta, (const int*)return_addresses,
+        make_table(peers, false));
+    QMOE_LAUNCH_CHECK("ep_push_return_kernel");
+    return 0;
+}

@@ -16,6 +16,7 @@ src/qutai/backends/cuda_lm.py:432-434).
 from __future__ import annotations
 
 import ctypes
+import hashlib
 import os
 import time
 from math import sqrt
@@ -94,6 +95,40 @@ def file_rendezvous(path, rank, payload=None, timeout=60.0, poll=0.02):
         time.sleep(poll)
 
 
+_JOB = {"token": "job"}
+
+
+def default_rendezvous_dir():
+    return os.path.join("/tmp", "qutai_moe_%s_%s" % (os.environ.get("MASTER_ADDR", "local"), os.environ.get("MASTER_PORT", "0")))
+
+
+def file_all_gather(directory, tag, rank, world, payload, timeout=120.0, poll=0.02):
+    """All-gather of one bytes object per rank through files in ``directory`` (every rank publishes
+    ``tag.rank`` atomically and polls for the others; TimeoutError names the ranks that never came)."""
+    os.makedirs(directory, exist_ok=True)
+    tmp = os.path.join(directory, f"{tag}.{rank}.tmp.{os.getpid()}")
+    with open(tmp, "wb") as handle:
+        handle.write(payload)
+    os.replace(tmp, os.path.join(directory, f"{tag}.{rank}"))
+    deadline, result = time.monotonic() + timeout, [None] * world
+    while True:
+        for p in range(world):
+            if result[p] is None:
+                try:
+                    with open(os.path.join(directory, f"{tag}.{p}"), "rb") as handle:
+                        data = handle.read()
+                    if data:
+                        result[p] = data
+                except FileNotFoundError:
+                    pass
+        if all(item is not None for item in result):
+            return result
+        if time.monotonic() > deadline:
+            missing = [p for p in range(world) if result[p] is None]
+            raise TimeoutError(f"rank {rank}: ranks {missing} never published '{tag}' in {directory}")
+        time.sleep(poll)
+
+
 def init_communicator(rank, world, share=None, rendezvous_path=None, timeout=60.0):
     """Create the process' NCCL communicator.  ``share(payload_or_None) -> bytes`` broadcasts rank
     0's 128-byte id (rank 0 passes it, the others pass None); without it a file rendezvous at
@@ -112,6 +147,7 @@ def init_communicator(rank, world, share=None, rendezvous_path=None, timeout=60.
         payload = file_rendezvous(rendezvous_path, rank, payload, timeout)
     if len(payload) != 128:
         raise ValueError("the NCCL id must be 128 bytes")
+    _JOB["token"] = hashlib.sha1(payload).hexdigest()[:12]  # names this job's rendezvous files
     buffer = ctypes.create_string_buffer(payload, 128)
     lib.call("qmoe_ep_init", rank, world, ctypes.cast(buffer, ctypes.c_void_p))
 
@@ -135,9 +171,20 @@ class ExpertParallelMoE:
     ``rank`` / ``world``; ``experts`` holds only this rank's E / world experts (global expert
     ``rank * E_loc + j``), ``router`` is replicated and its gradient is summed over ranks."""
 
-    def __init__(self, config, *, rank, world, device="cuda", dtype="float32", seed=None, engine="auto", stream=0):
+    def __init__(self, config, *, rank, world, device="cuda", dtype="float32", seed=None, engine="auto", stream=0,
+                 transport="nccl", gather=None):
+        """``transport``: "nccl" = grouped NCCL send/receive sized by counts the host reads once per
+        step; "p2p" = rows pushed straight into the peers' buffers over NVLink (CUDA IPC mappings,
+        destinations computed on the device, no host read in the forward).  ``gather(payload) ->
+        [payload of rank 0, ...]`` all-gathers a bytes object between the ranks (needed once for
+        "p2p" to swap the IPC handles); without it a directory rendezvous is used."""
         if device != "cuda" or dtype != "float32":
             raise ValueError("parameters are float32 on device='cuda'")
+        if transport not in ("nccl", "p2p"):
+            raise ValueError("transport must be 'nccl' or 'p2p'")
+        if world > lib.EP_MAX_RANKS:
+            raise ValueError(f"at most {lib.EP_MAX_RANKS} ranks")
+        self.transport, self._gather = transport, gather
         d, E, h = config.d_model, config.n_experts, config.d_expert
         if E % world:
             raise ValueError("n_experts must be a multiple of the number of ranks")
@@ -168,7 +215,6 @@ class ExpertParallelMoE:
                                   Tensor(views[2], (d, h), requires_grad=True)))
         self.experts = tuple(experts)
         self.utilization = None
-        self.last_counts = (0,) * E        # global counts (all ranks' tokens), as on one GPU
         self._work = None
         self._saved = None
 
@@ -200,6 +246,7 @@ class ExpertParallelMoE:
             router_partials=S(int(lib.load().qmoe_router_grad_partials(tokens, E, d)), "float32"),
             d_w_router=S(E * d, "float32"), d_w_gate=S(L * h * d, "float32"), d_w_up=S(L * h * d, "float32"),
             d_w_down=S(L * d * h, "float32"), aux_grad=S(1, "float32"),
+            ret_table=S(Rx, "int32"), dest_base=S(E, "int32"), barrier=S.zeros(1, "int32"),
         )
         if dtype == "bfloat16":
             buf.update(w_gate=S(L * h * d, "bfloat16"), w_up=S(L * h * d, "bfloat16"), w_down=S(L * d * h, "bfloat16"))
@@ -232,10 +279,58 @@ class ExpertParallelMoE:
                                Tensor(buf["d_w_down"].view(j * d * h, d * h), (d, h))))
         self._work = dict(key=(tokens, dtype), buf=buf, token_route=token_route, expert_route=expert_route, experts=ex,
                           host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), grad_views=grad_views)
+        if self.transport == "p2p":
+            self._work["peers"] = self._open_peers(buf)
         return self._work
+
+    def _open_peers(self, buf):
+        """Swap CUDA IPC handles of the five buffers other ranks write into and map every peer's."""
+        names = ("x_recv", "dy_recv", "y_send", "dy_send", "ret_table")
+        payload = b""
+        for name in names:
+            handle = ctypes.create_string_buffer(64)
+            lib.call("qmoe_ep_ipc_export", buf[name].ptr, ctypes.cast(handle, ctypes.c_void_p))
+            payload += handle.raw
+        gather = self._gather or (lambda data: file_all_gather(default_rendezvous_dir(), "ipc_" + _JOB["token"], self.rank, self.world, data))
+        everyone = gather(payload)
+        if len(everyone) != self.world or any(len(item) != 64 * len(names) for item in everyone):
+            raise ValueError("the IPC handle all-gather returned a wrong shape")
+        address = {name: [0] * self.world for name in names}
+        for p in range(self.world):
+            for i, name in enumerate(names):
+                if p == self.rank:
+                    address[name][p] = buf[name].ptr
+                else:
+                    opened = ctypes.c_uint64()
+                    handle = ctypes.create_string_buffer(everyone[p][64 * i: 64 * (i + 1)], 64)
+                    lib.call("qmoe_ep_ipc_open", ctypes.cast(handle, ctypes.c_void_p), ctypes.byref(opened))
+                    address[name][p] = opened.value
+        peers = {}
+        for name in ("x_recv", "dy_recv", "y_send", "dy_send"):
+            table = lib.Peers()
+            table.world, table.rank = self.world, self.rank
+            for p in range(self.world):
+                table.buffer[p] = address[name][p]
+                table.ret[p] = address["ret_table"][p]
+            peers[name] = table
+        return peers
 
     def __call__(self, x):
         return self.forward(x)
+
+    def _host_counts(self, w):
+        """[world][E] counts of the last forward as Python ints (waits for the stream)."""
+        lib.call("qmoe_stream_sync", self.stream)
+        stats, E = w["host_stats"], self.n_experts
+        return [[stats[p * 2 * E + e] for e in range(E)] for p in range(self.world)]
+
+    @property
+    def last_counts(self):
+        """Global per-expert counts (all ranks' tokens) of the last forward."""
+        if self._saved is None:
+            return (0,) * self.n_experts
+        counts = self._host_counts(self._saved[0])
+        return tuple(sum(counts[p][e] for p in range(self.world)) for e in range(self.n_experts))
 
     def forward(self, x):
         """``x``: this rank's (T / world, d) shard.  Returns ``(y, aux)``; ``aux`` is the global
@@ -254,25 +349,32 @@ class ExpertParallelMoE:
             lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, s)
         lib.call("qmoe_router_logits", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr, tokens, d, E, s)
         lib.call("qmoe_route", tr, buf["scores"].ptr, s)
+        # the all-gather is also the point no rank passes before every rank has finished its previous step
         lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
                  ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
-        lib.call("qmoe_permute", tr, storage.ptr, buf["x_send"].ptr, code, d, s)       # overlaps the host wait below
+        lib.call("qmoe_permute", tr, storage.ptr, buf["x_send"].ptr, code, d, s)
         lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
         lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
-        lib.call("qmoe_stream_sync", s)                                                  # the one host wait of the step
-        stats = w["host_stats"]
-        counts = [[stats[p * 2 * E + e] for e in range(E)] for p in range(N)]
-        plan = plan_exchange(counts, self.rank, N)
-        w["sends"], w["recvs"] = _segments(plan["sends"]), _segments(plan["recvs"])
-        (sa, sn), (ra, rn) = w["sends"], w["recvs"]
-        lib.call("qmoe_ep_exchange", buf["x_send"].ptr, sa, sn, buf["x_recv"].ptr, ra, rn, d, code, s)
-        lib.call("qmoe_expert_forward", xr, ex, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr, s)
-        lib.call("qmoe_ep_exchange", buf["y_recv"].ptr, ra, rn, buf["y_send"].ptr, sa, sn, d, code, s)
         out = DeviceStorage(storage.size, dtype)
+        if self.transport == "p2p":
+            peers = w["peers"]
+            lib.call("qmoe_ep_dest_base", buf["stats_all"].ptr, E, L, buf["dest_base"].ptr, s)
+            lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["x_send"].ptr, ctypes.byref(peers["x_recv"]), 1, code, d, s)
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            lib.call("qmoe_expert_forward", xr, ex, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr, s)
+            lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["y_recv"].ptr, ctypes.byref(peers["y_send"]), code, d, s)
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+        else:
+            counts = self._host_counts(w)                                              # the one host wait of the step
+            plan = plan_exchange(counts, self.rank, N)
+            w["sends"], w["recvs"] = _segments(plan["sends"]), _segments(plan["recvs"])
+            (sa, sn), (ra, rn) = w["sends"], w["recvs"]
+            lib.call("qmoe_ep_exchange", buf["x_send"].ptr, sa, sn, buf["x_recv"].ptr, ra, rn, d, code, s)
+            lib.call("qmoe_expert_forward", xr, ex, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr, s)
+            lib.call("qmoe_ep_exchange", buf["y_recv"].ptr, ra, rn, buf["y_send"].ptr, sa, sn, d, code, s)
         lib.call("qmoe_combine", tr, buf["y_send"].ptr, out.ptr, code, d, s)
-        self.last_counts = tuple(sum(counts[p][e] for p in range(N)) for e in range(E))
         self.utilization = Tensor(buf["utilization"], (E,))
-        self._saved = (w, storage, shape, plan)
+        self._saved = (w, storage, shape)
         return Tensor(out, shape), Tensor(buf["aux"], ())
 
     def backward(self, grad_y, grad_aux=None):
@@ -281,17 +383,18 @@ class ExpertParallelMoE:
         the all-reduced router gradient in ``parameter.grad``; returns this rank's ``dx``."""
         if self._saved is None:
             raise RuntimeError("backward called before forward")
-        w, x_storage, shape, plan = self._saved
+        w, x_storage, shape = self._saved
         g = grad_y.storage if hasattr(grad_y, "storage") else grad_y
         d, E, L, k, h, N = self.d_model, self.n_experts, self.local_experts, self.top_k, self.d_expert, self.world
         tokens, dtype = x_storage.size // d, x_storage.dtype
         code, s = lib.DTYPE_CODES[dtype], self.stream
         buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
-        (sa, sn), (ra, rn) = w["sends"], w["recvs"]
+        # which local experts received rows decides who gets a gradient: host logic on the forward's counts
+        counts = self._host_counts(w)
+        received = [sum(counts[p][self.rank * L + j] for p in range(N)) for j in range(L)]
         ga = 0
         if grad_aux is not None:
-            # the routing-backward kernel scales by E / (local tokens); the loss is over all ranks' tokens.
-            # Uploaded before anything is launched, because the small copy waits for the stream.
+            # the routing-backward kernel scales by E / (local tokens); the loss is over all ranks' tokens
             value = float(grad_aux) / N
             buf["aux_grad"].upload_bytes(ctypes.string_at(ctypes.byref(ctypes.c_float(value)), 4), s)
             ga = buf["aux_grad"].ptr
@@ -302,11 +405,21 @@ class ExpertParallelMoE:
                 parameter.grad = Tensor(parameter.grad.storage.copy(s), parameter.shape)
         lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
         lib.call("qmoe_ep_zero_pad_rows", xr, buf["dy_recv"].ptr, code, d, s)
-        lib.call("qmoe_ep_exchange", buf["dy_send"].ptr, sa, sn, buf["dy_recv"].ptr, ra, rn, d, code, s)
+        if self.transport == "p2p":
+            peers = w["peers"]
+            lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["dy_send"].ptr, ctypes.byref(peers["dy_recv"]), 0, code, d, s)
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+        else:
+            (sa, sn), (ra, rn) = w["sends"], w["recvs"]
+            lib.call("qmoe_ep_exchange", buf["dy_send"].ptr, sa, sn, buf["dy_recv"].ptr, ra, rn, d, code, s)
         lib.call("qmoe_expert_backward", xr, ex, buf["dy_recv"].ptr, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr,
                  buf["d_h"].ptr, buf["d_g"].ptr, buf["d_u"].ptr, buf["dy_recv"].ptr,  # dX reuses dY's buffer
                  buf["d_w_gate"].ptr, buf["d_w_up"].ptr, buf["d_w_down"].ptr, s)
-        lib.call("qmoe_ep_exchange", buf["dy_recv"].ptr, ra, rn, buf["dy_send"].ptr, sa, sn, d, code, s)
+        if self.transport == "p2p":
+            lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dy_recv"].ptr, ctypes.byref(peers["dy_send"]), code, d, s)
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+        else:
+            lib.call("qmoe_ep_exchange", buf["dy_recv"].ptr, ra, rn, buf["dy_send"].ptr, sa, sn, d, code, s)
         lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
         lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
                  buf["dx_router"].ptr, buf["d_w_router"].ptr, buf["router_partials"].ptr, tokens, d, E, s)
@@ -315,7 +428,7 @@ class ExpertParallelMoE:
         lib.call("qmoe_unpermute_reduce", tr, buf["dy_send"].ptr, buf["dx_router"].ptr, dx.ptr, code, d, s)
         _accumulate(self.router.weight, views[0], s)
         for j, expert in enumerate(self.experts):
-            if not plan["expert_counts"][j]:
+            if not received[j]:
                 continue
             gate, up, down = views[1 + j]
             _accumulate(expert.gate.weight, gate, s)

@@ -40,6 +40,15 @@ class Segment(Structure):
     _fields_ = [("peer", c_int32), ("reserved", c_int32), ("offset_rows", c_int64), ("rows", c_int64)]
 
 
+EP_MAX_RANKS = 16
+
+
+class Peers(Structure):
+    """``qmoe_ep_peers_t``."""
+    _fields_ = [("world", c_int32), ("rank", c_int32), ("buffer", c_uint64 * EP_MAX_RANKS),
+                ("ret", c_uint64 * EP_MAX_RANKS)]
+
+
 class Layer(Structure):
     """``qmoe_layer_t``."""
     _fields_ = [("route", Route), ("experts", Experts)] + [
@@ -105,6 +114,14 @@ SIGNATURES = {
     "qmoe_ep_zero_pad_rows": (c_int, [_RP, _U, _I32, _I64, _U]),
     "qmoe_ep_exchange": (c_int, [_U, _SP, _I32, _U, _SP, _I32, _I64, _I32, _U]),
     "qmoe_ep_all_reduce_f32": (c_int, [_U, _I64, _U]),
+    "qmoe_set_device": (c_int, [_I32]),
+    "qmoe_ep_ipc_export": (c_int, [_U, c_void_p]),
+    "qmoe_ep_ipc_open": (c_int, [c_void_p, POINTER(c_uint64)]),
+    "qmoe_ep_ipc_close": (c_int, [_U]),
+    "qmoe_ep_barrier": (c_int, [_U, _U]),
+    "qmoe_ep_dest_base": (c_int, [_U, _I32, _I32, _U, _U]),
+    "qmoe_ep_push_dispatch": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I64, _U]),
+    "qmoe_ep_push_return": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I64, _U]),
 }
 
 _lock = threading.Lock()

@@ -1,7 +1,7 @@
 """Child process of the expert-parallel GPU test: one rank = one GPU (picked through
 CUDA_VISIBLE_DEVICES by the parent).  Runs forward + backward of ExpertParallelMoE on this rank's
 token shard and writes its results to OUT/rank{r}.npz for the parent to check against the oracle.
-Usage: python ep_gpu_worker.py RANK WORLD OUT_DIR"""
+Usage: python ep_gpu_worker.py RANK WORLD OUT_DIR TRANSPORT"""
 import os
 import sys
 
@@ -27,16 +27,20 @@ def problem():
 
 
 def main():
-    rank, world, out_dir = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    rank, world, out_dir, transport = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
     from gpu_util import Config, to_device, to_host
     from qutai_b200 import lib
-    from qutai_b200.expert_parallel import ExpertParallelMoE, finalize_communicator, init_communicator
+    from qutai_b200.expert_parallel import ExpertParallelMoE, file_all_gather, finalize_communicator, init_communicator
     from qutai_b200.layers import Tensor
+
+    if transport == "p2p":  # every GPU of the job is visible to every rank; pick ours
+        lib.call("qmoe_set_device", rank)
 
     p = problem()
     T, d, E, k, h = p["T"], p["d"], p["E"], p["k"], p["h"]
     init_communicator(rank, world, rendezvous_path=os.path.join(out_dir, "nccl_id"), timeout=120)
-    layer = ExpertParallelMoE(Config(d, E, k, h), rank=rank, world=world, seed=3, engine="tcgen05")
+    layer = ExpertParallelMoE(Config(d, E, k, h), rank=rank, world=world, seed=3, engine="tcgen05", transport=transport,
+                              gather=lambda data: file_all_gather(out_dir, "ipc", rank, world, data))
     L = E // world
     mine = slice(rank * L, (rank + 1) * L)
     layer.router.weight.storage.upload_bytes(p["router"].tobytes())

@@ -24,11 +24,13 @@ def gpu_count():
         return 0
 
 
-def run_ranks(world, out_dir):
+def run_ranks(world, out_dir, transport):
     procs = []
     for rank in range(world):
-        env = dict(os.environ, CUDA_VISIBLE_DEVICES=str(rank), NCCL_DEBUG="WARN")
-        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "ep_gpu_worker.py"), str(rank), str(world), out_dir],
+        env = dict(os.environ, NCCL_DEBUG="WARN")
+        if transport == "nccl":  # one visible GPU per process, the upstream runtime's "device 0" assumption
+            env["CUDA_VISIBLE_DEVICES"] = str(rank)
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "ep_gpu_worker.py"), str(rank), str(world), out_dir, transport],
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env))
     for rank, proc in enumerate(procs):
         try:
@@ -40,8 +42,9 @@ def run_ranks(world, out_dir):
     return [np.load(os.path.join(out_dir, f"rank{rank}.npz")) for rank in range(world)]
 
 
+@pytest.mark.parametrize("transport", ["nccl", "p2p"])
 @pytest.mark.parametrize("world", [1, 2])
-def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, tmp_path):
+def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, transport, tmp_path):
     if gpu_count() < world:
         pytest.skip(f"needs {world} GPUs")
     sys.path.insert(0, HERE)
@@ -49,7 +52,7 @@ def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, tmp_path
 
     p = problem()
     T, E, k = p["T"], p["E"], p["k"]
-    ranks = run_ranks(world, str(tmp_path))
+    ranks = run_ranks(world, str(tmp_path), transport)
     scores = np.concatenate([r["scores"] for r in ranks])
     assert oracle.max_rel_err(scores, p["x"] @ p["router"].astype(np.float64).T) <= 1e-4
     r16 = oracle.round_bf16
