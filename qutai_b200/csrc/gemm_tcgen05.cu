@@ -40,7 +40,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64 x 64 bf16 TMA box (8 KiB)
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 32 * 80 /*epilogue transpose*/;
 constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
 constexpr int EPILOGUE_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;
@@ -218,6 +218,50 @@ __device__ __forceinline__ void store_row32_bf16(__nv_bfloat16* dst, const float
     }
 }
 
+// Per-warp transpose buffer: 32 rows of 64 bytes, row pitch 80 bytes (keeps 16-byte alignment and
+// spreads the rows over the banks).
+constexpr int STAGE_PITCH = 80;
+constexpr int EPI_STAGE_BYTES = 32 * STAGE_PITCH;
+
+// Thread `lane` holds 32 consecutive bf16 (16 packed words) of row `lane`.  Write the 32 x 32 block to
+// global memory (dst = first element of the block, row pitch ldc elements) so that every store
+// instruction covers 8 rows x 64 contiguous bytes.
+__device__ __forceinline__ void store_block32(uint32_t stage, int lane, const uint32_t* w, __nv_bfloat16* dst, long long ldc) {
+    const uint32_t mine = stage + lane * STAGE_PITCH;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16 * q), "r"(w[4 * q]), "r"(w[4 * q + 1]),
+                     "r"(w[4 * q + 2]), "r"(w[4 * q + 3]) : "memory");
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int row = j * 8 + (lane >> 2), piece = lane & 3;
+        uint4 v;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "r"(stage + row * STAGE_PITCH + 16 * piece) : "memory");
+        *reinterpret_cast<uint4*>(dst + (long long)row * ldc + piece * 8) = v;
+    }
+    __syncwarp();
+}
+
+// The inverse: `v[j]` was loaded by this lane from row j * 8 + lane / 4, piece lane % 4 (the coalesced
+// pattern); return the 16 packed words of row `lane`.
+__device__ __forceinline__ void gather_block32(uint32_t stage, int lane, const uint4* v, uint32_t* w) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int row = j * 8 + (lane >> 2), piece = lane & 3;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + row * STAGE_PITCH + 16 * piece), "r"(v[j].x),
+                     "r"(v[j].y), "r"(v[j].z), "r"(v[j].w) : "memory");
+    }
+    __syncwarp();
+    const uint32_t mine = stage + lane * STAGE_PITCH;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4 * q]), "=r"(w[4 * q + 1]), "=r"(w[4 * q + 2]),
+                     "=r"(w[4 * q + 3]) : "r"(mine + 16 * q) : "memory");
+    __syncwarp();
+}
+
 template <int MODE, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
@@ -347,6 +391,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int quad = warp & 3;         // TMEM lanes [32 * quad, 32 * quad + 32) belong to this warp
+        const uint32_t stage = bars + 256u + (uint32_t)(warp - 2) * EPI_STAGE_BYTES;  // this warp's transpose buffer
         const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp converts
         int iter = 0;
         for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
@@ -361,10 +406,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
             const long long row = (long long)tile.row0 + quad * 32 + lane;
+            // Row-major pointers of this warp's 32 rows (row0w) for the coalesced paths: a warp moves a
+            // 32-row x 32-column bf16 block as 8 rows x 64 contiguous bytes per instruction, transposing
+            // between "one thread = one row" (the TMEM read layout) and that shape through shared memory.
+            const long long row0w = (long long)tile.row0 + quad * 32;
             if (MODE == MODE_SWIGLU) {
-                __nv_bfloat16* G = (__nv_bfloat16*)p.out0 + row * p.ldc + tile.n0;
-                __nv_bfloat16* U = (__nv_bfloat16*)p.out1 + row * p.ldc + tile.n0;
-                __nv_bfloat16* H = (__nv_bfloat16*)p.out2 + row * p.ldc + tile.n0;
+                __nv_bfloat16* G = (__nv_bfloat16*)p.out0 + row0w * p.ldc + tile.n0;
+                __nv_bfloat16* U = (__nv_bfloat16*)p.out1 + row0w * p.ldc + tile.n0;
+                __nv_bfloat16* H = (__nv_bfloat16*)p.out2 + row0w * p.ldc + tile.n0;
 #pragma unroll 1
                 for (int c = 2 * half; c < 2 * half + 2; ++c) {
                     uint32_t rg[32], ru[32];
@@ -373,23 +422,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     tmem_ld_wait();
                     const int valid = p.N - (tile.n0 + c * 32);
                     if (valid >= 32) {
+                        uint32_t wg[16], wu[16], wh[16];
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t wg[4], wu[4], wh[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int i = 8 * q + 2 * j;
-                                // G and U are stored as bf16 and H is computed from the stored values,
-                                // so the backward (which re-reads G and U) sees exactly what H was built from
-                                wg[j] = pack_bf16(__uint_as_float(rg[i]), __uint_as_float(rg[i + 1]));
-                                wu[j] = pack_bf16(__uint_as_float(ru[i]), __uint_as_float(ru[i + 1]));
-                                const float g0 = bf16_lo(wg[j]), g1 = bf16_hi(wg[j]);
-                                wh[j] = pack_bf16(g0 * fast_sigmoid(g0) * bf16_lo(wu[j]), g1 * fast_sigmoid(g1) * bf16_hi(wu[j]));
-                            }
-                            *reinterpret_cast<uint4*>(G + c * 32 + 8 * q) = make_uint4(wg[0], wg[1], wg[2], wg[3]);
-                            *reinterpret_cast<uint4*>(U + c * 32 + 8 * q) = make_uint4(wu[0], wu[1], wu[2], wu[3]);
-                            *reinterpret_cast<uint4*>(H + c * 32 + 8 * q) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                        for (int j = 0; j < 16; ++j) {
+                            // G and U are stored as bf16 and H is computed from the stored values,
+                            // so the backward (which re-reads G and U) sees exactly what H was built from
+                            wg[j] = pack_bf16(__uint_as_float(rg[2 * j]), __uint_as_float(rg[2 * j + 1]));
+                            wu[j] = pack_bf16(__uint_as_float(ru[2 * j]), __uint_as_float(ru[2 * j + 1]));
+                            const float g0 = bf16_lo(wg[j]), g1 = bf16_hi(wg[j]);
+                            wh[j] = pack_bf16(g0 * fast_sigmoid(g0) * bf16_lo(wu[j]), g1 * fast_sigmoid(g1) * bf16_hi(wu[j]));
                         }
+                        store_block32(stage, lane, wg, G + c * 32, p.ldc);
+                        store_block32(stage, lane, wu, U + c * 32, p.ldc);
+                        store_block32(stage, lane, wh, H + c * 32, p.ldc);
                     } else if (valid > 0) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
@@ -397,73 +442,78 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                 const __nv_bfloat16 gb = __float2bfloat16_rn(__uint_as_float(rg[i]));
                                 const __nv_bfloat16 ub = __float2bfloat16_rn(__uint_as_float(ru[i]));
                                 const float g = __bfloat162float(gb);
-                                G[c * 32 + i] = gb;
-                                U[c * 32 + i] = ub;
-                                H[c * 32 + i] = __float2bfloat16_rn(g * fast_sigmoid(g) * __bfloat162float(ub));
+                                G[lane * p.ldc + c * 32 + i] = gb;
+                                U[lane * p.ldc + c * 32 + i] = ub;
+                                H[lane * p.ldc + c * 32 + i] = __float2bfloat16_rn(g * fast_sigmoid(g) * __bfloat162float(ub));
                             }
                     }
                 }
             } else if (MODE == MODE_DSWIGLU) {
-                const __nv_bfloat16* G = (const __nv_bfloat16*)p.in0 + row * p.ldc + tile.n0;
-                const __nv_bfloat16* U = (const __nv_bfloat16*)p.in1 + row * p.ldc + tile.n0;
-                __nv_bfloat16* dG = (__nv_bfloat16*)p.out0 + row * p.ldc + tile.n0;
-                __nv_bfloat16* dU = (__nv_bfloat16*)p.out1 + row * p.ldc + tile.n0;
+                const __nv_bfloat16* G = (const __nv_bfloat16*)p.in0 + row0w * p.ldc + tile.n0;
+                const __nv_bfloat16* U = (const __nv_bfloat16*)p.in1 + row0w * p.ldc + tile.n0;
+                __nv_bfloat16* dG = (__nv_bfloat16*)p.out0 + row0w * p.ldc + tile.n0;
+                __nv_bfloat16* dU = (__nv_bfloat16*)p.out1 + row0w * p.ldc + tile.n0;
 #pragma unroll 1
                 for (int c = 4 * half; c < 4 * half + 4; ++c) {
                     const int valid = p.N - (tile.n0 + c * 32);
-                    uint4 vg[4], vu[4];
-                    if (valid >= 32) {  // issue the loads of the saved activations before waiting on TMEM
+                    uint4 lg[4], lu[4];
+                    if (valid >= 32) {  // coalesced loads of the saved activations, issued before waiting on TMEM
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            vg[q] = *reinterpret_cast<const uint4*>(G + c * 32 + 8 * q);
-                            vu[q] = *reinterpret_cast<const uint4*>(U + c * 32 + 8 * q);
+                        for (int j = 0; j < 4; ++j) {
+                            const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + c * 32 + (lane & 3) * 8;
+                            lg[j] = *reinterpret_cast<const uint4*>(G + at);
+                            lu[j] = *reinterpret_cast<const uint4*>(U + at);
                         }
                     }
                     uint32_t r[32];
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
                     if (valid >= 32) {
+                        uint32_t gw[16], uw[16], og[16], ou[16];
+                        gather_block32(stage, lane, lg, gw);
+                        gather_block32(stage, lane, lu, uw);
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const uint32_t gw[4] = {vg[q].x, vg[q].y, vg[q].z, vg[q].w};
-                            const uint32_t uw[4] = {vu[q].x, vu[q].y, vu[q].z, vu[q].w};
-                            uint32_t og[4], ou[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int i = 8 * q + 2 * j;
-                                const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
-                                const float u0 = bf16_lo(uw[j]), u1 = bf16_hi(uw[j]);
-                                const float s0 = fast_sigmoid(g0), s1 = fast_sigmoid(g1);
-                                const float h0 = __uint_as_float(r[i]), h1 = __uint_as_float(r[i + 1]);
-                                ou[j] = pack_bf16(h0 * g0 * s0, h1 * g1 * s1);
-                                og[j] = pack_bf16(h0 * u0 * s0 * (1.f + g0 * (1.f - s0)), h1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
-                            }
-                            *reinterpret_cast<uint4*>(dG + c * 32 + 8 * q) = make_uint4(og[0], og[1], og[2], og[3]);
-                            *reinterpret_cast<uint4*>(dU + c * 32 + 8 * q) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+                        for (int j = 0; j < 16; ++j) {
+                            const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
+                            const float u0 = bf16_lo(uw[j]), u1 = bf16_hi(uw[j]);
+                            const float s0 = fast_sigmoid(g0), s1 = fast_sigmoid(g1);
+                            const float h0 = __uint_as_float(r[2 * j]), h1 = __uint_as_float(r[2 * j + 1]);
+                            ou[j] = pack_bf16(h0 * g0 * s0, h1 * g1 * s1);
+                            og[j] = pack_bf16(h0 * u0 * s0 * (1.f + g0 * (1.f - s0)), h1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
                         }
+                        store_block32(stage, lane, og, dG + c * 32, p.ldc);
+                        store_block32(stage, lane, ou, dU + c * 32, p.ldc);
                     } else if (valid > 0) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             if (i < valid) {
-                                const float g = __bfloat162float(G[c * 32 + i]), u = __bfloat162float(U[c * 32 + i]);
+                                const long long at = lane * p.ldc + c * 32 + i;
+                                const float g = __bfloat162float(G[at]), u = __bfloat162float(U[at]);
                                 const float sg = fast_sigmoid(g), dh = __uint_as_float(r[i]);
-                                dU[c * 32 + i] = __float2bfloat16_rn(dh * g * sg);
-                                dG[c * 32 + i] = __float2bfloat16_rn(dh * u * sg * (1.f + g * (1.f - sg)));
+                                dU[at] = __float2bfloat16_rn(dh * g * sg);
+                                dG[at] = __float2bfloat16_rn(dh * u * sg * (1.f + g * (1.f - sg)));
                             }
                     }
                 }
             } else if (MODE == MODE_PLAIN) {
-                __nv_bfloat16* C = (__nv_bfloat16*)p.out0 + row * p.ldc + tile.n0;
+                __nv_bfloat16* C = (__nv_bfloat16*)p.out0 + row0w * p.ldc + tile.n0;
 #pragma unroll 1
                 for (int c = 4 * half; c < 4 * half + 4; ++c) {
                     uint32_t r[32];
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
-                    float v[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
                     const int valid = p.N - (tile.n0 + c * 32);
-                    if (valid > 0) store_row32_bf16(C + c * 32, v, valid);
+                    if (valid >= 32) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) w[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                        store_block32(stage, lane, w, C + c * 32, p.ldc);
+                    } else if (valid > 0) {
+                        float v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                        store_row32_bf16(C + lane * p.ldc + c * 32, v, valid);
+                    }
                 }
             } else {
                 float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
