@@ -119,18 +119,25 @@ typedef struct qmoe_route {
     uint64_t block_colsum; /* f32 [blocks, E]  scratch */
 } qmoe_route_t;
 
-/* Router logits: scores[T, E] = float(x)[T, d] . w_router[E, d]^T, fp32 arithmetic whatever the
+/* Router logits: scores[T, E] = float(x)[T, d] . w_router[E, d]^T in fp32 semantics whatever the
  * activation dtype.  Replaces the router `linear` call under `set_matmul_precision(None)`
- * (src/qutai/lm/layers.py:377-378, gemm kernels src/qutai/backends/cuda/gemm.cu:35-101). */
+ * (src/qutai/lm/layers.py:377-378, gemm kernels src/qutai/backends/cuda/gemm.cu:35-101).
+ * With bf16 activations, at most 64 experts and a scratch buffer of qmoe_router_scratch_bytes(T, E, d)
+ * bytes (256-byte aligned) the product runs on the tensor cores with the fp32 weights split into three
+ * bf16 terms (exact products, fp32 accumulation); otherwise on the CUDA cores.  qmoe_router_logits is
+ * the scratch-free form. */
+int64_t qmoe_router_scratch_bytes(int64_t tokens, int32_t experts, int64_t width);
+int qmoe_router_forward(uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t scores, uint64_t scratch,
+                        int64_t tokens, int64_t width, int32_t experts, uint64_t stream);
 int qmoe_router_logits(uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t scores,
                        int64_t tokens, int64_t width, int32_t experts, uint64_t stream);
 /* Router backward: dx_router[T, d] (f32) = d_scores . w_router ; d_w_router[E, d] (f32) =
- * d_scores^T . float(x).  `partials` is f32 scratch of qmoe_router_grad_partials(T, E, d)
- * elements (deterministic split over tokens).  Replaces the backward closure of `linear`
- * (src/qutai/lm/layers.py:50-70) for the router. */
+ * d_scores^T . float(x), deterministic (token blocks reduced in a fixed order).  `scratch` as above
+ * (qmoe_router_grad_partials gives the same size in 4-byte units).  Replaces the backward closure
+ * of `linear` (src/qutai/lm/layers.py:50-70) for the router. */
 int64_t qmoe_router_grad_partials(int64_t tokens, int32_t experts, int64_t width);
 int qmoe_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dtype, uint64_t w_router,
-                         uint64_t dx_router, uint64_t d_w_router, uint64_t partials,
+                         uint64_t dx_router, uint64_t d_w_router, uint64_t scratch,
                          int64_t tokens, int64_t width, int32_t experts, uint64_t stream);
 
 /* Softmax, top-k (ties -> lowest expert index), gate renormalisation, per-expert counts, padded

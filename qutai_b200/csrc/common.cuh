@@ -150,6 +150,17 @@ int tc_rows_nn(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint6
 int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down, uint64_t g, uint64_t u, uint64_t dg,
                uint64_t du, long long d, long long h, cudaStream_t stream);
 int tc_wgrad(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long M, long long N, cudaStream_t stream);
+int tc_router_forward(uint64_t x, uint64_t w3, uint64_t scores, long long T, long long d, int E, int S, cudaStream_t stream);
+int tc_plain_f32_nn(uint64_t a, uint64_t b, uint64_t c, long long T, long long K, long long N, cudaStream_t stream);
+int tc_split_wgrad(uint64_t a, long long a_pitch, uint64_t b, uint64_t partial, const int* offsets, const int* counts,
+                   int splits, long long T, long long M, long long N, cudaStream_t stream);
+int simt_router_logits(uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t scores, int64_t tokens, int64_t width,
+                       int32_t experts, cudaStream_t stream);
+int simt_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t dx_router,
+                         uint64_t d_w_router, uint64_t partials, int64_t tokens, int64_t width, int32_t experts,
+                         cudaStream_t stream);
+long long simt_router_partials(int64_t tokens, int32_t experts, int64_t width);
+int launch_reduce_partials(const float* partials, float* out, long long n, int splits, cudaStream_t stream);
 void count_tensor_core_launch();
 int* device_status_address();
 

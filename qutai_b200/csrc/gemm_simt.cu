@@ -160,18 +160,13 @@ int launch_reduce_partials(const float* partials, float* out, long long n, int s
 
 }  // namespace qmoe
 
-using namespace qmoe;
-
+namespace qmoe {
 namespace {
 constexpr long long kRouterSplitTokens = 2048;
 }
 
-extern "C" int qmoe_router_logits(uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t scores,
-                                  int64_t tokens, int64_t width, int32_t experts, uint64_t stream_) {
-    if (!x || !w_router || !scores) return fail_arg("router_logits: null address");
-    if (tokens <= 0 || width <= 0 || experts <= 0) return fail_arg("router_logits: sizes must be positive");
-    if (x_dtype != QMOE_F32 && x_dtype != QMOE_BF16) return fail_arg("router_logits: bad dtype %d", x_dtype);
-    cudaStream_t stream = (cudaStream_t)stream_;
+int simt_router_logits(uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t scores, int64_t tokens, int64_t width,
+                       int32_t experts, cudaStream_t stream) {
     TimedScope timed(KC_ROUTER_GEMM, stream);
     SimtGemmArgs g = {};
     g.A = (const void*)x; g.B = (const void*)w_router; g.C = (void*)scores;
@@ -183,18 +178,14 @@ extern "C" int qmoe_router_logits(uint64_t x, int32_t x_dtype, uint64_t w_router
     return launch_simt_gemm(g, x_dtype, QMOE_F32, QMOE_F32, tokens, 1, stream);
 }
 
-extern "C" int64_t qmoe_router_grad_partials(int64_t tokens, int32_t experts, int64_t width) {
+long long simt_router_partials(int64_t tokens, int32_t experts, int64_t width) {
     const int64_t splits = (tokens + kRouterSplitTokens - 1) / kRouterSplitTokens;
     return splits * experts * width;
 }
 
-extern "C" int qmoe_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dtype, uint64_t w_router,
-                                    uint64_t dx_router, uint64_t d_w_router, uint64_t partials,
-                                    int64_t tokens, int64_t width, int32_t experts, uint64_t stream_) {
-    if (!d_scores || !x || !w_router) return fail_arg("router_backward: null address");
-    if (tokens <= 0 || width <= 0 || experts <= 0) return fail_arg("router_backward: sizes must be positive");
-    if (x_dtype != QMOE_F32 && x_dtype != QMOE_BF16) return fail_arg("router_backward: bad dtype %d", x_dtype);
-    cudaStream_t stream = (cudaStream_t)stream_;
+int simt_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dtype, uint64_t w_router, uint64_t dx_router,
+                         uint64_t d_w_router, uint64_t partials, int64_t tokens, int64_t width, int32_t experts,
+                         cudaStream_t stream) {
     TimedScope timed(KC_ROUTER_GEMM, stream);
     if (dx_router) {  // [T, d] = d_scores[T, E] . W[E, d]
         SimtGemmArgs g = {};
@@ -207,7 +198,7 @@ extern "C" int qmoe_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dty
         if (int rc = launch_simt_gemm(g, QMOE_F32, QMOE_F32, QMOE_F32, tokens, 1, stream)) return rc;
     }
     if (d_w_router) {  // [E, d] = d_scores^T[E, T] . x[T, d], split over tokens, reduced in fixed order
-        if (!partials) return fail_arg("router_backward: partials scratch is null");
+        if (!partials) return fail_arg("router_backward: scratch is null");
         const int splits = (int)((tokens + kRouterSplitTokens - 1) / kRouterSplitTokens);
         SimtGemmArgs g = {};
         g.A = (const void*)d_scores; g.B = (const void*)x; g.C = (void*)partials;
@@ -224,3 +215,5 @@ extern "C" int qmoe_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dty
     }
     return 0;
 }
+
+}  // namespace qmoe

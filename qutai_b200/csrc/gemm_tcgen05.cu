@@ -46,7 +46,7 @@ constexpr int EPILOGUE_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
-enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2, MODE_DSWIGLU = 3 };
+enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2, MODE_DSWIGLU = 3, MODE_ROUTER = 4, MODE_PLAIN_F32 = 5 };
 enum { STATUS_WAIT_PRODUCER = 101, STATUS_WAIT_MMA = 102, STATUS_WAIT_EPILOGUE = 103 };
 
 struct alignas(64) GemmParams {
@@ -67,6 +67,8 @@ struct alignas(64) GemmParams {
     int M, N, K;          // WGRAD: M, N of one expert's output; others: N = output columns, K = inner size of one segment
     int b_rows;           // rows of the stacked B operand per expert
     int segments;         // 1, or 2 when (A2, B2) is accumulated into the same tile
+    int plain_rows;       // > 0: one group of this many rows instead of the expert groups of `offsets`
+    int group_stride;     // ROUTER: accumulator columns [0,S), [S,2S), [2S,3S) hold the three bf16 terms of the weights
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -278,7 +280,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
 
-    for (int i = threadIdx.x; i <= p.experts; i += NUM_THREADS) s_start[i] = p.offsets[i] / kRowPad;
+    if (p.plain_rows > 0) {
+        if (threadIdx.x == 0) { s_start[0] = 0; s_start[1] = (p.plain_rows + kRowPad - 1) / kRowPad; }
+    } else {
+        for (int i = threadIdx.x; i <= p.experts; i += NUM_THREADS) s_start[i] = p.offsets[i] / kRowPad;
+    }
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -515,9 +521,28 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         store_row32_bf16(C + lane * p.ldc + c * 32, v, valid);
                     }
                 }
+            } else if (MODE == MODE_ROUTER) {
+                // scores = x . (W_hi + W_mid + W_lo)^T: the three partial products sit S columns apart
+                float* C = (float*)p.out0 + row * p.ldc;
+                const int S = p.group_stride;
+#pragma unroll 1
+                for (int c = half; c * 32 < S; c += 2) {
+                    uint32_t r0[32], r1[32], r2[32];
+                    tmem_ld32(taddr + c * 32, r0);
+                    tmem_ld32(taddr + S + c * 32, r1);
+                    tmem_ld32(taddr + 2 * S + c * 32, r2);
+                    tmem_ld_wait();
+                    const int valid = p.N - c * 32;
+                    if (row < p.M) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid)
+                                C[c * 32 + i] = (__uint_as_float(r2[i]) + __uint_as_float(r1[i])) + __uint_as_float(r0[i]);
+                    }
+                }
             } else {
                 float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
-                const bool row_ok = row < p.M;
+                const bool row_ok = row < p.M;  // WGRAD: rows of one expert's output; PLAIN_F32: rows of the single group
 #pragma unroll 1
                 for (int c = 4 * half; c < 4 * half + 4; ++c) {
                     uint32_t r[32];
@@ -579,9 +604,10 @@ std::mutex g_map_mutex;
 std::map<std::tuple<uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> g_maps;
 
 // 2-D bf16 row-major matrix [outer, inner], box {box_inner = 64, box_outer}, 128-byte swizzle.
-int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uint32_t box_outer) {
+int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uint32_t box_outer, uint64_t pitch = 0) {
     const uint32_t box_inner = 64;
-    auto key = std::make_tuple(ptr, inner, outer, box_inner, box_outer);
+    if (!pitch) pitch = inner;  // elements between consecutive rows
+    auto key = std::make_tuple(ptr, inner | (pitch << 32), outer, box_inner, box_outer);
     {
         std::lock_guard<std::mutex> lock(g_map_mutex);
         auto it = g_maps.find(key);
@@ -590,9 +616,9 @@ int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uin
     EncodeTiledFn fn = encode_fn();
     if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return QMOE_ERR_STATE; }
     if (ptr & 15u) return fail_arg("tensor-core GEMM operand address must be 16-byte aligned");
-    if ((inner * 2) % 16) return fail_arg("tensor-core GEMM operand row pitch must be a multiple of 16 bytes");
+    if ((pitch * 2) % 16) return fail_arg("tensor-core GEMM operand row pitch must be a multiple of 16 bytes");
     cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {inner * 2};
+    cuuint64_t strides[1] = {pitch * 2};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
@@ -690,6 +716,46 @@ int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down,
     p.ldc = h; p.experts = experts; p.n_tiles = ceil_div(h, BN);
     p.N = (int)h; p.K = (int)d; p.b_rows = (int)d; p.segments = 1;
     return launch<MODE_DSWIGLU, false, true>(p, stream);
+}
+
+// scores [T, E] (fp32) = x [T, d] . (W_hi + W_mid + W_lo)^T, w3 = [3S, d] bf16 with the three terms S rows apart
+int tc_router_forward(uint64_t x, uint64_t w3, uint64_t scores, long long T, long long d, int E, int S, cudaStream_t stream) {
+    GemmParams p = {};
+    if (int rc = make_map(&p.map_a, x, (uint64_t)d, (uint64_t)T, BM)) return rc;
+    if (int rc = make_map(&p.map_b, w3, (uint64_t)d, (uint64_t)3 * S, BN)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    p.status = device_status_address();
+    p.out0 = (void*)scores; p.ldc = E; p.experts = 1; p.n_tiles = 1;
+    p.M = (int)T; p.N = E; p.K = (int)d; p.b_rows = 0; p.segments = 1; p.plain_rows = (int)T; p.group_stride = S;
+    return launch<MODE_ROUTER, false, false>(p, stream);
+}
+
+// C [T, N] (fp32) = A [T, K] . B [K, N] (one group, rows masked at T)
+int tc_plain_f32_nn(uint64_t a, uint64_t b, uint64_t c, long long T, long long K, long long N, cudaStream_t stream) {
+    GemmParams p = {};
+    if (int rc = make_map(&p.map_a, a, (uint64_t)K, (uint64_t)T, BM)) return rc;
+    if (int rc = make_map(&p.map_b, b, (uint64_t)N, (uint64_t)K, 64)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    if (c & 15u || (N * 4) % 16) return fail_arg("fp32 output must be 16-byte aligned with a 16-byte row pitch");
+    p.status = device_status_address();
+    p.out0 = (void*)c; p.ldc = N; p.c_slab = 0; p.experts = 1; p.n_tiles = ceil_div(N, BN);
+    p.M = (int)T; p.N = (int)N; p.K = (int)K; p.b_rows = 0; p.segments = 1; p.plain_rows = (int)T;
+    return launch<MODE_PLAIN_F32, false, true>(p, stream);
+}
+
+// partial[s] [M, N] (fp32) = A[rows of split s]^T . B[rows of split s]; A [T, M] with row pitch a_pitch, B [T, N]
+int tc_split_wgrad(uint64_t a, long long a_pitch, uint64_t b, uint64_t partial, const int* offsets, const int* counts,
+                   int splits, long long T, long long M, long long N, cudaStream_t stream) {
+    GemmParams p = {};
+    if (int rc = make_map(&p.map_a, a, (uint64_t)M, (uint64_t)T, 64, (uint64_t)a_pitch)) return rc;
+    if (int rc = make_map(&p.map_b, b, (uint64_t)N, (uint64_t)T, 64)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    if (partial & 15u || (N * 4) % 16) return fail_arg("fp32 output must be 16-byte aligned with a 16-byte row pitch");
+    p.offsets = offsets; p.counts = counts; p.status = device_status_address();
+    p.out0 = (void*)partial; p.ldc = N; p.c_slab = M * N; p.experts = splits;
+    p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, BN);
+    p.M = (int)M; p.N = (int)N; p.K = 0; p.segments = 1;
+    return launch<MODE_WGRAD, true, true>(p, stream);
 }
 
 // C_e [M, N] (fp32) = A_e^T . B_e, A [rows, M], B [rows, N], contraction over the rows of expert e

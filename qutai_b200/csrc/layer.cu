@@ -148,7 +148,7 @@ extern "C" int qmoe_layer_forward(const qmoe_layer_t* L, uint64_t stream) {
         if (int rc = qmoe_cast_bf16(L->master_up, ex->w_up, E * hd * d, stream)) return rc;
         if (int rc = qmoe_cast_bf16(L->master_down, ex->w_down, E * hd * d, stream)) return rc;
     }
-    if (int rc = qmoe_router_logits(L->x, ex->dtype, L->w_router, L->scores, r->tokens, d, r->experts, stream)) return rc;
+    if (int rc = qmoe_router_forward(L->x, ex->dtype, L->w_router, L->scores, L->router_partials, r->tokens, d, r->experts, stream)) return rc;
     if (int rc = qmoe_route(r, L->scores, stream)) return rc;
     if (int rc = qmoe_permute(r, L->x, L->x_dispatched, ex->dtype, d, stream)) return rc;
     if (int rc = qmoe_expert_forward(r, ex, L->x_dispatched, L->g, L->u, L->h, L->y_dispatched, stream)) return rc;

@@ -347,7 +347,8 @@ class ExpertParallelMoE:
             lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, s)
             lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, s)
             lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, s)
-        lib.call("qmoe_router_logits", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr, tokens, d, E, s)
+        lib.call("qmoe_router_forward", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr,
+                 buf["router_partials"].ptr, tokens, d, E, s)
         lib.call("qmoe_route", tr, buf["scores"].ptr, s)
         # the all-gather is also the point no rank passes before every rank has finished its previous step
         lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,

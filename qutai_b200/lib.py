@@ -86,6 +86,8 @@ SIGNATURES = {
     "qmoe_rows_bound": (c_int64, [_I64, _I32, _I32]),
     "qmoe_route_blocks": (c_int64, [_I64]),
     "qmoe_router_logits": (c_int, [_U, _I32, _U, _U, _I64, _I64, _I32, _U]),
+    "qmoe_router_scratch_bytes": (c_int64, [_I64, _I32, _I64]),
+    "qmoe_router_forward": (c_int, [_U, _I32, _U, _U, _U, _I64, _I64, _I32, _U]),
     "qmoe_router_grad_partials": (c_int64, [_I64, _I32, _I64]),
     "qmoe_router_backward": (c_int, [_U, _U, _I32, _U, _U, _U, _U, _I64, _I64, _I32, _U]),
     "qmoe_route": (c_int, [_RP, _U, _U]),

@@ -289,3 +289,35 @@ def test_gradient_accumulates_over_two_backwards():
     e = int(np.argmax(g["counts"]))
     got = to_host(layer.experts[e].down.weight.grad.storage, once["d_down"][e].shape)
     assert rel(got, 2 * once["d_down"][e]) <= 1e-6
+
+
+# ------------------------------------------------------------------------------------------------
+# router projection: fp32 semantics on the tensor cores (split bf16 terms) and on the CUDA cores
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("T,d,E", [(1000, 256, 8), (4133, 2048, 64), (300, 512, 33), (128, 64, 1), (77, 72, 5)])
+def test_router_forward_backward_fp32_semantics(T, d, E, dtype):
+    from gpu_util import to_device, to_host
+    from qutai_b200 import lib
+    from qutai_b200.storage import DeviceStorage
+
+    rng = np.random.default_rng(T + E)
+    x = rng.standard_normal((T, d))
+    x = oracle.round_bf16(x) if dtype == "bfloat16" else x.astype(np.float32).astype(np.float64)
+    w = (rng.standard_normal((E, d)) * 0.05).astype(np.float32)
+    ds = (rng.standard_normal((T, E)) * 0.01).astype(np.float32)
+    code = lib.DTYPE_CODES[dtype]
+    scratch = DeviceStorage(int(lib.load().qmoe_router_scratch_bytes(T, E, d)) // 4 + 64, "float32")
+    xd, wd, dsd = to_device(x, dtype), to_device(w, "float32"), to_device(ds, "float32")
+    scores, dxr, dwr = DeviceStorage(T * E, "float32"), DeviceStorage(T * d, "float32"), DeviceStorage(E * d, "float32")
+    lib.call("qmoe_router_forward", xd.ptr, code, wd.ptr, scores.ptr, scratch.ptr, T, d, E, 0)
+    lib.call("qmoe_router_backward", dsd.ptr, xd.ptr, code, wd.ptr, dxr.ptr, dwr.ptr, scratch.ptr, T, d, E, 0)
+    w64, ds64 = w.astype(np.float64), ds.astype(np.float64)
+    # fp32 accumulation over up to thousands of terms: a few 1e-6 relative; the bar for logits is 1e-4
+    assert rel(to_host(scores, (T, E)), x @ w64.T) <= 1e-5
+    assert rel(to_host(dwr, (E, d)), ds64.T @ x) <= 1e-5
+    assert rel(to_host(dxr, (T, d)), ds64 @ w64) <= 2e-5
+    first = to_host(dwr, (E, d))
+    lib.call("qmoe_router_backward", dsd.ptr, xd.ptr, code, wd.ptr, dxr.ptr, dwr.ptr, scratch.ptr, T, d, E, 0)
+    assert np.array_equal(first, to_host(dwr, (E, d)))  # fixed reduction order: bit-identical
+    assert lib.device_status() == 0
