@@ -331,16 +331,58 @@ def run_gpu(args, w, rank, world):
         dx = None if forward_only else layer.backward(gs, ga)
         return y, aux, dx
 
+    # End-to-end arm: every step's inputs come from pinned host memory and every step's outputs (y, dx,
+    # aux) go back to pinned host memory.  The copies run on their own streams, double-buffered, so the
+    # H2D of step i+1 and the D2H of step i-1 overlap the compute of step i — the way a host that feeds
+    # the layer from its own buffers would drive it.
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    x_buf = [x_dev, torch.empty_like(x_dev)]
+    g_buf = [g_dev, torch.empty_like(g_dev)]
+    xs_buf = [Tensor(wrap(t, "bfloat16"), (T, d)) for t in x_buf]
+    gs_buf = [Tensor(wrap(t, "bfloat16"), (T, d)) for t in g_buf]
+    aux_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    e2e_state = dict(i=0, ready=[None, None], free=[None, None], pending=[])
+
+    def issue_h2d(b):
+        with torch.cuda.stream(copy_in):
+            if e2e_state["free"][b] is not None:
+                copy_in.wait_event(e2e_state["free"][b])      # the step that last read this buffer is done
+            x_buf[b].copy_(x_host, non_blocking=True)
+            if not forward_only:
+                g_buf[b].copy_(g_host, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(copy_in)
+            e2e_state["ready"][b] = event
+
     def step_e2e():
-        x_dev.copy_(x_host, non_blocking=True)
-        if not forward_only:
-            g_dev.copy_(g_host, non_blocking=True)
-        y, aux, dx = step()
-        lib.call("qmoe_memcpy_d2h", y_host.data_ptr(), y.storage.ptr, y.storage.nbytes, stream)
-        if dx is not None:
-            lib.call("qmoe_memcpy_d2h", dx_host.data_ptr(), dx.storage.ptr, dx.storage.nbytes, stream)
-        aux_value = aux.storage.tolist(stream)[0]  # waits for the step: the caller reads its result
-        return aux_value
+        i = e2e_state["i"]
+        b = i % 2
+        if e2e_state["ready"][b] is None:
+            issue_h2d(b)
+        issue_h2d(1 - b)                                       # next step's inputs travel during this step
+        main.wait_event(e2e_state["ready"][b])
+        e2e_state["ready"][b] = None
+        for parameter in parameters:
+            parameter.grad = None
+        y, aux = layer(xs_buf[b])
+        dx = None if forward_only else layer.backward(gs_buf[b], ga)
+        done = torch.cuda.Event()
+        done.record(main)
+        e2e_state["free"][b] = done
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(done)
+            s_out = copy_out.cuda_stream
+            lib.call("qmoe_memcpy_d2h", y_host.data_ptr(), y.storage.ptr, y.storage.nbytes, s_out)
+            if dx is not None:
+                lib.call("qmoe_memcpy_d2h", dx_host.data_ptr(), dx.storage.ptr, dx.storage.nbytes, s_out)
+            lib.call("qmoe_memcpy_d2h", aux_host.data_ptr(), aux.storage.ptr, 4, s_out)
+            copied = torch.cuda.Event()
+            copied.record(copy_out)
+        # outputs stay alive until their copy has finished (two steps later at most)
+        e2e_state["pending"] = [item for item in e2e_state["pending"] if not item[0].query()] + [(copied, y, dx)]
+        main.wait_event(copied) if i + 1 == e2e_state.get("last", -1) else None
+        e2e_state["i"] = i + 1
 
     def timed(fn, steps):
         torch.cuda.synchronize()
@@ -371,9 +413,12 @@ def run_gpu(args, w, rank, world):
     ms = timed(step, args.steps)
     launches = (lib.load().qmoe_launch_count() - launches_before) // args.steps
     clocks = sampler.stop()
-    for _ in range(max(1, args.warmup // 2)):
+    for _ in range(max(2, args.warmup // 2)):
         step_e2e()
+    torch.cuda.synchronize()
+    e2e_state["last"] = e2e_state["i"] + args.steps           # the last timed step waits for its own copy-out
     ms_e2e = timed(step_e2e, args.steps)
+    e2e_state["pending"].clear()
     # per-kernel-class device time, measured in a separate pass so the events do not sit inside the headline timing
     lib.timing(True)
     for _ in range(args.steps):

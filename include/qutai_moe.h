@@ -73,6 +73,14 @@ int qmoe_memcpy_d2h(void* dst, uint64_t src, uint64_t bytes, uint64_t stream); /
 int qmoe_memcpy_d2d(uint64_t dst, uint64_t src, uint64_t bytes, uint64_t stream);
 int qmoe_memset(uint64_t dst, int value, uint64_t bytes, uint64_t stream);
 int qmoe_stream_sync(uint64_t stream);
+/* Extra streams and events (cudaStreamNonBlocking / timing disabled) for hosts that overlap copies or
+ * exchanges with compute; the upstream runtime has a single stream (src/qutai/backends/cuda_runtime.py:326). */
+int qmoe_stream_create(uint64_t* stream);
+int qmoe_stream_destroy(uint64_t stream);
+int qmoe_event_create(uint64_t* event);
+int qmoe_event_destroy(uint64_t event);
+int qmoe_event_record(uint64_t event, uint64_t stream);
+int qmoe_stream_wait_event(uint64_t stream, uint64_t event);
 /* launches made by this library since load (the upstream runtime keeps the same counter,
  * src/qutai/backends/cuda_runtime.py:95, :327); tensor-core launches counted separately (:100). */
 int64_t qmoe_launch_count(void);
@@ -226,6 +234,16 @@ int qmoe_expert_backward(const qmoe_route_t* route, const qmoe_experts_t* expert
                          uint64_t dy_dispatched, uint64_t x_dispatched, uint64_t g, uint64_t u,
                          uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx_dispatched,
                          uint64_t d_w_gate, uint64_t d_w_up, uint64_t d_w_down, uint64_t stream);
+
+/* The same backward in two parts, for hosts that overlap an exchange with the weight gradients:
+ * QMOE_BWD_ACTIVATIONS computes dG, dU and dX (dX must then have its own buffer, not dY's),
+ * QMOE_BWD_WEIGHTS the three weight gradients.  Both bits = qmoe_expert_backward. */
+enum { QMOE_BWD_ACTIVATIONS = 1, QMOE_BWD_WEIGHTS = 2 };
+int qmoe_expert_backward_parts(const qmoe_route_t* route, const qmoe_experts_t* experts,
+                               uint64_t dy_dispatched, uint64_t x_dispatched, uint64_t g, uint64_t u,
+                               uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx_dispatched,
+                               uint64_t d_w_gate, uint64_t d_w_up, uint64_t d_w_down, int32_t parts,
+                               uint64_t stream);
 
 /* Plain (single-group) product C[M, N] = op(A) op(B) with the upstream dispatcher's meaning of
  * the arguments (src/qutai/backends/cuda.py:305-362): A is [M, K] ([K, M] when transpose_a),

@@ -157,12 +157,13 @@ struct Tile {
 };
 
 template <int MODE>
-__device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_start, int t) {
+__device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_start, const int* s_order, int t) {
     Tile tile;
     tile.valid = true;
     if (MODE == MODE_WGRAD) {
         const int per = p.m_tiles * p.n_tiles;
-        const int e = t / per, rem = t - e * per;
+        const int slot = t / per, rem = t - slot * per;
+        const int e = s_order[slot];
         tile.expert = e;
         tile.row0 = (rem % p.m_tiles) * BM;
         tile.n0 = (rem / p.m_tiles) * BN;
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_start[kMaxExperts + 1];  // first 128-row tile of each expert
+    __shared__ int s_order[kMaxExperts];      // WGRAD: experts by decreasing row count (ties by index)
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
@@ -284,6 +286,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (threadIdx.x == 0) { s_start[0] = 0; s_start[1] = (p.plain_rows + kRowPad - 1) / kRowPad; }
     } else {
         for (int i = threadIdx.x; i <= p.experts; i += NUM_THREADS) s_start[i] = p.offsets[i] / kRowPad;
+    }
+    if (MODE == MODE_WGRAD) {
+        // Tiles of large experts cost more (longer contraction).  Walking the experts from large to
+        // small and dealing tiles round-robin gives every CTA the same mix of long and short tiles.
+        for (int i = threadIdx.x; i < p.experts; i += NUM_THREADS) {
+            const int mine = p.counts[i];
+            int rank = 0;
+            for (int j = 0; j < p.experts; ++j) {
+                const int other = p.counts[j];
+                rank += (other > mine || (other == mine && j < i)) ? 1 : 0;
+            }
+            s_order[rank] = i;
+        }
     }
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -315,7 +330,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             int stage = 0;
             uint32_t phase = 0;
             for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-                const Tile tile = decode_tile<MODE>(p, s_start, t);
+                const Tile tile = decode_tile<MODE>(p, s_start, s_order, t);
                 if (!tile.valid) continue;
                 const int kb_per_seg = tile.kblocks / (MODE == MODE_WGRAD ? 1 : p.segments);
                 for (int kb = 0; kb < tile.kblocks; ++kb) {
@@ -361,7 +376,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             uint32_t phase = 0;
             int iter = 0;
             for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-                const Tile tile = decode_tile<MODE>(p, s_start, t);
+                const Tile tile = decode_tile<MODE>(p, s_start, s_order, t);
                 if (!tile.valid) continue;
                 const int acc = iter & 1;
                 const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
@@ -401,7 +416,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp converts
         int iter = 0;
         for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-            const Tile tile = decode_tile<MODE>(p, s_start, t);
+            const Tile tile = decode_tile<MODE>(p, s_start, s_order, t);
             if (!tile.valid) continue;
             const int acc = iter & 1;
             const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
@@ -459,16 +474,26 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 const __nv_bfloat16* U = (const __nv_bfloat16*)p.in1 + row0w * p.ldc + tile.n0;
                 __nv_bfloat16* dG = (__nv_bfloat16*)p.out0 + row0w * p.ldc + tile.n0;
                 __nv_bfloat16* dU = (__nv_bfloat16*)p.out1 + row0w * p.ldc + tile.n0;
+                // coalesced loads of the saved activations run one 32-column chunk ahead of their use
+                uint4 lg[4], lu[4];
+                if (p.N - (tile.n0 + 4 * half * 32) >= 32) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + 4 * half * 32 + (lane & 3) * 8;
+                        lg[j] = *reinterpret_cast<const uint4*>(G + at);
+                        lu[j] = *reinterpret_cast<const uint4*>(U + at);
+                    }
+                }
 #pragma unroll 1
                 for (int c = 4 * half; c < 4 * half + 4; ++c) {
                     const int valid = p.N - (tile.n0 + c * 32);
-                    uint4 lg[4], lu[4];
-                    if (valid >= 32) {  // coalesced loads of the saved activations, issued before waiting on TMEM
+                    uint4 ng[4], nu[4];
+                    if (c + 1 < 4 * half + 4 && valid - 32 >= 32) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + c * 32 + (lane & 3) * 8;
-                            lg[j] = *reinterpret_cast<const uint4*>(G + at);
-                            lu[j] = *reinterpret_cast<const uint4*>(U + at);
+                            const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + (c + 1) * 32 + (lane & 3) * 8;
+                            ng[j] = *reinterpret_cast<const uint4*>(G + at);
+                            nu[j] = *reinterpret_cast<const uint4*>(U + at);
                         }
                     }
                     uint32_t r[32];
@@ -489,6 +514,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         }
                         store_block32(stage, lane, og, dG + c * 32, p.ldc);
                         store_block32(stage, lane, ou, dU + c * 32, p.ldc);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { lg[j] = ng[j]; lu[j] = nu[j]; }
                     } else if (valid > 0) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)

@@ -81,27 +81,40 @@ extern "C" int qmoe_expert_forward(const qmoe_route_t* r, const qmoe_experts_t* 
     return simt_rows(r, ex, h, ex->w_down, 0, 0, y, hd, d, true, stream);
 }
 
-extern "C" int qmoe_expert_backward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t dy, uint64_t x, uint64_t g,
-                                    uint64_t u, uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx,
-                                    uint64_t d_w_gate, uint64_t d_w_up, uint64_t d_w_down, uint64_t stream_) {
+extern "C" int qmoe_expert_backward_parts(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t dy, uint64_t x, uint64_t g,
+                                          uint64_t u, uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx,
+                                          uint64_t d_w_gate, uint64_t d_w_up, uint64_t d_w_down, int32_t parts,
+                                          uint64_t stream_) {
     int engine = 0;
     if (int rc = check_experts(r, ex, &engine)) return rc;
-    if (!dy || !x || !g || !u || !h || !d_h || !d_g || !d_u || !dx || !d_w_gate || !d_w_up || !d_w_down)
-        return fail_arg("expert_backward: null buffer address");
+    if (!(parts & (QMOE_BWD_ACTIVATIONS | QMOE_BWD_WEIGHTS)) || (parts & ~(QMOE_BWD_ACTIVATIONS | QMOE_BWD_WEIGHTS)))
+        return fail_arg("expert_backward: parts must be a combination of QMOE_BWD_ACTIVATIONS and QMOE_BWD_WEIGHTS");
+    if (!dy || !x || !g || !u || !h || !d_h || !d_g || !d_u) return fail_arg("expert_backward: null buffer address");
+    if ((parts & QMOE_BWD_ACTIVATIONS) && !dx) return fail_arg("expert_backward: dx is null");
+    if ((parts & QMOE_BWD_WEIGHTS) && (!d_w_gate || !d_w_up || !d_w_down)) return fail_arg("expert_backward: null gradient address");
+    if (parts == QMOE_BWD_ACTIVATIONS && dx == dy)
+        return fail_arg("expert_backward: dx may alias dy only when both parts run in one call");
     cudaStream_t stream = (cudaStream_t)stream_;
     const long long d = ex->width, hd = ex->hidden;
     const bool tc = engine == QMOE_ENGINE_TCGEN05;
-    if (tc) {  // dG, dU straight from the accumulator of dH = dY . Wd (dH itself is never stored)
-        TimedScope timed(KC_EXPERT_GEMM, stream);
-        if (int rc = tc_dswiglu(r, ex->experts, dy, ex->w_down, g, u, d_g, d_u, d, hd, stream)) return rc;
-    } else {
-        {
+    if (parts & QMOE_BWD_ACTIVATIONS) {
+        if (tc) {  // dG, dU straight from the accumulator of dH = dY . Wd (dH itself is never stored)
             TimedScope timed(KC_EXPERT_GEMM, stream);
-            if (int rc = simt_rows(r, ex, dy, ex->w_down, 0, 0, d_h, d, hd, false, stream)) return rc;
+            if (int rc = tc_dswiglu(r, ex->experts, dy, ex->w_down, g, u, d_g, d_u, d, hd, stream)) return rc;
+        } else {
+            {
+                TimedScope timed(KC_EXPERT_GEMM, stream);
+                if (int rc = simt_rows(r, ex, dy, ex->w_down, 0, 0, d_h, d, hd, false, stream)) return rc;
+            }
+            if (int rc = launch_swiglu_backward(r, d_h, g, u, d_g, d_u, ex->dtype, hd, stream)) return rc;
         }
-        if (int rc = launch_swiglu_backward(r, d_h, g, u, d_g, d_u, ex->dtype, hd, stream)) return rc;
+        if (dx != dy) {  // dX first when it has a buffer of its own: a host can ship it while the weight gradients run
+            TimedScope timed(KC_EXPERT_GEMM, stream);
+            if (int rc = tc ? tc_rows_nn(r, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, stream)
+                            : simt_rows(r, ex, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, false, stream)) return rc;
+        }
     }
-    {   // weight gradients (dY is still intact here; dX may alias it and is written last)
+    if (parts & QMOE_BWD_WEIGHTS) {
         TimedScope timed(KC_WGRAD_GEMM, stream);
         if (int rc = tc ? tc_wgrad(r, ex->experts, dy, h, d_w_down, d, hd, stream)
                         : simt_wgrad(r, ex, dy, h, d_w_down, d, hd, stream)) return rc;
@@ -110,9 +123,19 @@ extern "C" int qmoe_expert_backward(const qmoe_route_t* r, const qmoe_experts_t*
         if (int rc = tc ? tc_wgrad(r, ex->experts, d_u, x, d_w_up, hd, d, stream)
                         : simt_wgrad(r, ex, d_u, x, d_w_up, hd, d, stream)) return rc;
     }
-    TimedScope timed(KC_EXPERT_GEMM, stream);  // dX = dG . Wg + dU . Wu
-    return tc ? tc_rows_nn(r, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, stream)
-              : simt_rows(r, ex, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, false, stream);
+    if ((parts & QMOE_BWD_ACTIVATIONS) && dx == dy) {  // dX overwrites dY: only after dY's last reader (dWd)
+        TimedScope timed(KC_EXPERT_GEMM, stream);
+        return tc ? tc_rows_nn(r, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, stream)
+                  : simt_rows(r, ex, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, false, stream);
+    }
+    return 0;
+}
+
+extern "C" int qmoe_expert_backward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t dy, uint64_t x, uint64_t g,
+                                    uint64_t u, uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx,
+                                    uint64_t d_w_gate, uint64_t d_w_up, uint64_t d_w_down, uint64_t stream) {
+    return qmoe_expert_backward_parts(r, ex, dy, x, g, u, h, d_h, d_g, d_u, dx, d_w_gate, d_w_up, d_w_down,
+                                      QMOE_BWD_ACTIVATIONS | QMOE_BWD_WEIGHTS, stream);
 }
 
 extern "C" int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtype, uint64_t c, int32_t c_dtype, int64_t m,

@@ -25,47 +25,64 @@ __device__ __forceinline__ uint4 ld16_stream(const void* p) {
     return v;
 }
 
-// ---- permute: dispatched[r] = x[token(r)], pads zero ------------------------------------------
-template <typename T, bool VEC>
+// ---- permute: dispatched[dest_row[t, s]] = x[t] for every slot, pads zero ------------------------
+// Organised by TOKEN: a warp reads one token row once and writes its k copies, so the source is
+// read T*d instead of A*d times (the k copies of a token lie far apart in the dispatched layout and
+// would miss L2).  Pad rows are zeroed afterwards by the warps that find row_source[r] < 0.
+template <typename T, bool VEC, int KMAX>
 __global__ void __launch_bounds__(kThreads)
-permute_kernel(const T* __restrict__ x, T* __restrict__ out, const int* __restrict__ row_source,
-               const int* __restrict__ meta, int k, long long width) {
+permute_kernel(const T* __restrict__ x, T* __restrict__ out, const int* __restrict__ dest_row,
+               const int* __restrict__ row_source, const int* __restrict__ meta, long long tokens, int k,
+               long long width) {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
-    const int rows = meta[0];
-    for (long long r = warp; r < rows; r += nwarps) {
-        const int a = row_source[r];
-        T* dst = out + r * width;
+    for (long long t = warp; t < tokens; t += nwarps) {
+        long long rows[KMAX];
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s) rows[s] = s < k ? dest_row[t * k + s] : 0;
+        const T* src = x + t * width;
         if constexpr (VEC) {
             constexpr int N = Vec16<T>::N;
             const int chunks = (int)(width / N);
-            if (a < 0) {
-                for (int c = lane; c < chunks; c += 32) st16(dst + (long long)c * N, make_uint4(0, 0, 0, 0));
-            } else {
-                const T* src = x + (long long)(a / k) * width;
-                int c = lane;
-                for (; c + 96 < chunks; c += 128) {
-                    uint4 v0 = ld16(src + (long long)c * N), v1 = ld16(src + (long long)(c + 32) * N);
-                    uint4 v2 = ld16(src + (long long)(c + 64) * N), v3 = ld16(src + (long long)(c + 96) * N);
-                    st16(dst + (long long)c * N, v0); st16(dst + (long long)(c + 32) * N, v1);
-                    st16(dst + (long long)(c + 64) * N, v2); st16(dst + (long long)(c + 96) * N, v3);
-                }
-                for (; c < chunks; c += 32) st16(dst + (long long)c * N, ld16(src + (long long)c * N));
+            int c = lane;
+            for (; c + 32 < chunks; c += 64) {
+                const uint4 v0 = ld16_stream(src + (long long)c * N), v1 = ld16_stream(src + (long long)(c + 32) * N);
+#pragma unroll
+                for (int s = 0; s < KMAX; ++s)
+                    if (s < k) {
+                        st16(out + rows[s] * width + (long long)c * N, v0);
+                        st16(out + rows[s] * width + (long long)(c + 32) * N, v1);
+                    }
+            }
+            for (; c < chunks; c += 32) {
+                const uint4 v0 = ld16_stream(src + (long long)c * N);
+#pragma unroll
+                for (int s = 0; s < KMAX; ++s)
+                    if (s < k) st16(out + rows[s] * width + (long long)c * N, v0);
             }
         } else {
-            if (a < 0) {
-                for (long long c = lane; c < width; c += 32) Act<T>::store(dst + c, 0.f);
-            } else {
-                const T* src = x + (long long)(a / k) * width;
-                for (long long c = lane; c < width; c += 32) dst[c] = src[c];
+            for (long long c = lane; c < width; c += 32) {
+                const T v = src[c];
+                for (int s = 0; s < k; ++s) out[rows[s] * width + c] = v;
             }
+        }
+    }
+    const int rows_used = meta[0];
+    for (long long r = warp; r < rows_used; r += nwarps) {
+        if (row_source[r] >= 0) continue;
+        T* dst = out + r * width;
+        if constexpr (VEC) {
+            constexpr int N = Vec16<T>::N;
+            for (int c = lane; c < (int)(width / N); c += 32) st16(dst + (long long)c * N, make_uint4(0, 0, 0, 0));
+        } else {
+            for (long long c = lane; c < width; c += 32) Act<T>::store(dst + c, 0.f);
         }
     }
 }
 
 // ---- combine: out[t] = sum_s w[t,s] * y[dest_row[t,s]] ----------------------------------------
-template <typename T, bool VEC>
+template <typename T, bool VEC, int KMAX>
 __global__ void __launch_bounds__(kThreads)
 combine_kernel(const T* __restrict__ y, const float* __restrict__ gate_w, const int* __restrict__ dest_row,
                T* __restrict__ out, long long tokens, int k, long long width) {
@@ -73,10 +90,10 @@ combine_kernel(const T* __restrict__ y, const float* __restrict__ gate_w, const 
     const long long warp = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
     for (long long t = warp; t < tokens; t += nwarps) {
-        int rows[kMaxTopK];
-        float w[kMaxTopK];
+        int rows[KMAX];
+        float w[KMAX];
 #pragma unroll
-        for (int s = 0; s < kMaxTopK; ++s) {
+        for (int s = 0; s < KMAX; ++s) {
             rows[s] = s < k ? dest_row[t * k + s] : 0;
             w[s] = s < k ? gate_w[t * k + s] : 0.f;
         }
@@ -85,15 +102,15 @@ combine_kernel(const T* __restrict__ y, const float* __restrict__ gate_w, const 
             constexpr int N = Vec16<T>::N;
             const int chunks = (int)(width / N);
             for (int c = lane; c < chunks; c += 32) {
-                uint4 v[kMaxTopK];
+                uint4 v[KMAX];
 #pragma unroll
-                for (int s = 0; s < kMaxTopK; ++s)
+                for (int s = 0; s < KMAX; ++s)
                     if (s < k) v[s] = ld16_stream(y + (long long)rows[s] * width + (long long)c * N);
                 float acc[N];
 #pragma unroll
                 for (int i = 0; i < N; ++i) acc[i] = 0.f;
 #pragma unroll
-                for (int s = 0; s < kMaxTopK; ++s)
+                for (int s = 0; s < KMAX; ++s)
                     if (s < k) {
                         float f[N];
                         Vec16<T>::unpack(v[s], f);
@@ -112,72 +129,78 @@ combine_kernel(const T* __restrict__ y, const float* __restrict__ gate_w, const 
     }
 }
 
-// ---- combine backward: dy[r] = g[token(r)] * w(r);  dw[a] = <g[token], y[r]> ------------------
-template <typename T, bool VEC>
+// ---- combine backward: dy[dest_row[t, s]] = g[t] * w[t, s];  dw[t, s] = <g[t], y[dest_row[t, s]]> ----
+// Organised by TOKEN like the permute: g[t] is read once for its k slots.
+template <typename T, bool VEC, int KMAX>
 __global__ void __launch_bounds__(kThreads)
 combine_backward_kernel(const T* __restrict__ g, const T* __restrict__ y, const float* __restrict__ gate_w,
-                        const int* __restrict__ row_source, const int* __restrict__ meta,
-                        T* __restrict__ dy, float* __restrict__ dw, int k, long long width) {
+                        const int* __restrict__ dest_row, const int* __restrict__ row_source,
+                        const int* __restrict__ meta, T* __restrict__ dy, float* __restrict__ dw, long long tokens,
+                        int k, long long width) {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
-    const int rows = meta[0];
-    for (long long r = warp; r < rows; r += nwarps) {
-        const int a = row_source[r];
-        T* dst = dy + r * width;
-        if (a < 0) {
-            if constexpr (VEC) {
-                constexpr int N = Vec16<T>::N;
-                for (int c = lane; c < (int)(width / N); c += 32) st16(dst + (long long)c * N, make_uint4(0, 0, 0, 0));
-            } else {
-                for (long long c = lane; c < width; c += 32) Act<T>::store(dst + c, 0.f);
-            }
-            continue;
+    for (long long t = warp; t < tokens; t += nwarps) {
+        long long rows[KMAX];
+        float w[KMAX], dot[KMAX];
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s) {
+            rows[s] = s < k ? dest_row[t * k + s] : 0;
+            w[s] = s < k ? gate_w[t * k + s] : 0.f;
+            dot[s] = 0.f;
         }
-        const float w = gate_w[a];
-        const T* gs = g + (long long)(a / k) * width;
-        const T* ys = y + r * width;
-        float dot = 0.f;
+        const T* gs = g + t * width;
         if constexpr (VEC) {
             constexpr int N = Vec16<T>::N;
             const int chunks = (int)(width / N);
-            int c = lane;
-            for (; c + 32 < chunks; c += 64) {
-                uint4 g0 = ld16(gs + (long long)c * N), g1 = ld16(gs + (long long)(c + 32) * N);
-                uint4 y0 = ld16_stream(ys + (long long)c * N), y1 = ld16_stream(ys + (long long)(c + 32) * N);
-                float fg[N], fy[N], o[N];
-                Vec16<T>::unpack(g0, fg); Vec16<T>::unpack(y0, fy);
+            for (int c = lane; c < chunks; c += 32) {
+                float fg[N];
+                Vec16<T>::unpack(ld16_stream(gs + (long long)c * N), fg);
+                uint4 v[KMAX];
 #pragma unroll
-                for (int i = 0; i < N; ++i) { dot = fmaf(fg[i], fy[i], dot); o[i] = fg[i] * w; }
-                st16(dst + (long long)c * N, Vec16<T>::pack(o));
-                Vec16<T>::unpack(g1, fg); Vec16<T>::unpack(y1, fy);
+                for (int s = 0; s < KMAX; ++s)
+                    if (s < k) v[s] = ld16_stream(y + rows[s] * width + (long long)c * N);
 #pragma unroll
-                for (int i = 0; i < N; ++i) { dot = fmaf(fg[i], fy[i], dot); o[i] = fg[i] * w; }
-                st16(dst + (long long)(c + 32) * N, Vec16<T>::pack(o));
-            }
-            for (; c < chunks; c += 32) {
-                uint4 g0 = ld16(gs + (long long)c * N);
-                uint4 y0 = ld16_stream(ys + (long long)c * N);
-                float fg[N], fy[N], o[N];
-                Vec16<T>::unpack(g0, fg); Vec16<T>::unpack(y0, fy);
+                for (int s = 0; s < KMAX; ++s)
+                    if (s < k) {
+                        float fy[N], o[N];
+                        Vec16<T>::unpack(v[s], fy);
 #pragma unroll
-                for (int i = 0; i < N; ++i) { dot = fmaf(fg[i], fy[i], dot); o[i] = fg[i] * w; }
-                st16(dst + (long long)c * N, Vec16<T>::pack(o));
+                        for (int i = 0; i < N; ++i) { dot[s] = fmaf(fg[i], fy[i], dot[s]); o[i] = fg[i] * w[s]; }
+                        st16(dy + rows[s] * width + (long long)c * N, Vec16<T>::pack(o));
+                    }
             }
         } else {
             for (long long c = lane; c < width; c += 32) {
                 const float gv = Act<T>::load(gs + c);
-                dot = fmaf(gv, Act<T>::load(ys + c), dot);
-                Act<T>::store(dst + c, gv * w);
+                for (int s = 0; s < k; ++s) {
+                    dot[s] = fmaf(gv, Act<T>::load(y + rows[s] * width + c), dot[s]);
+                    Act<T>::store(dy + rows[s] * width + c, gv * w[s]);
+                }
             }
         }
-        dot = warp_sum(dot);
-        if (lane == 0) dw[a] = dot;
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s)
+            if (s < k) {
+                const float total = warp_sum(dot[s]);
+                if (lane == 0) dw[t * k + s] = total;
+            }
+    }
+    const int rows_used = meta[0];
+    for (long long r = warp; r < rows_used; r += nwarps) {
+        if (row_source[r] >= 0) continue;
+        T* dst = dy + r * width;
+        if constexpr (VEC) {
+            constexpr int N = Vec16<T>::N;
+            for (int c = lane; c < (int)(width / N); c += 32) st16(dst + (long long)c * N, make_uint4(0, 0, 0, 0));
+        } else {
+            for (long long c = lane; c < width; c += 32) Act<T>::store(dst + c, 0.f);
+        }
     }
 }
 
 // ---- unpermute-reduce: dx[t] = sum_s d_dispatched[dest_row[t,s]] (+ extra[t]) -----------------
-template <typename T, bool VEC>
+template <typename T, bool VEC, int KMAX>
 __global__ void __launch_bounds__(kThreads)
 unpermute_kernel(const T* __restrict__ dxd, const float* __restrict__ extra, const int* __restrict__ dest_row,
                  T* __restrict__ dx, long long tokens, int k, long long width) {
@@ -185,17 +208,17 @@ unpermute_kernel(const T* __restrict__ dxd, const float* __restrict__ extra, con
     const long long warp = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
     for (long long t = warp; t < tokens; t += nwarps) {
-        int rows[kMaxTopK];
+        int rows[KMAX];
 #pragma unroll
-        for (int s = 0; s < kMaxTopK; ++s) rows[s] = s < k ? dest_row[t * k + s] : 0;
+        for (int s = 0; s < KMAX; ++s) rows[s] = s < k ? dest_row[t * k + s] : 0;
         T* dst = dx + t * width;
         if constexpr (VEC) {
             constexpr int N = Vec16<T>::N;
             const int chunks = (int)(width / N);
             for (int c = lane; c < chunks; c += 32) {
-                uint4 v[kMaxTopK];
+                uint4 v[KMAX];
 #pragma unroll
-                for (int s = 0; s < kMaxTopK; ++s)
+                for (int s = 0; s < KMAX; ++s)
                     if (s < k) v[s] = ld16_stream(dxd + (long long)rows[s] * width + (long long)c * N);
                 float acc[N];
                 if (extra) {
@@ -210,7 +233,7 @@ unpermute_kernel(const T* __restrict__ dxd, const float* __restrict__ extra, con
                     for (int i = 0; i < N; ++i) acc[i] = 0.f;
                 }
 #pragma unroll
-                for (int s = 0; s < kMaxTopK; ++s)
+                for (int s = 0; s < KMAX; ++s)
                     if (s < k) {
                         float f[N];
                         Vec16<T>::unpack(v[s], f);
@@ -385,10 +408,20 @@ extern "C" int qmoe_permute(const qmoe_route_t* r, uint64_t x, uint64_t out, int
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_PERMUTE, stream);
     const bool vec = dtype == QMOE_BF16 ? can_vec<__nv_bfloat16>(width, {x, out}) : can_vec<float>(width, {x, out});
-    const int grid = grid_for_rows(r->rows_bound);
-#define ARGS(T) <<<grid, kThreads, 0, stream>>>((const T*)x, (T*)out, (const int*)r->row_source, (const int*)r->meta, r->top_k, (long long)width)
-    if (dtype == QMOE_BF16) { if (vec) permute_kernel<__nv_bfloat16, true> ARGS(__nv_bfloat16); else permute_kernel<__nv_bfloat16, false> ARGS(__nv_bfloat16); }
-    else { if (vec) permute_kernel<float, true> ARGS(float); else permute_kernel<float, false> ARGS(float); }
+    // enough warps for the tokens and for zeroing up to experts * 127 pad rows
+    const int grid = grid_for_rows(r->tokens > (long long)r->experts * 64 ? r->tokens : (long long)r->experts * 64);
+#define ARGS(T) <<<grid, kThreads, 0, stream>>>((const T*)x, (T*)out, (const int*)r->dest_row, (const int*)r->row_source, (const int*)r->meta, (long long)r->tokens, r->top_k, (long long)width)
+#define BY_K(T, V)                                                  \
+    do {                                                            \
+        if (r->top_k <= 1) permute_kernel<T, V, 1> ARGS(T);         \
+        else if (r->top_k <= 2) permute_kernel<T, V, 2> ARGS(T);    \
+        else if (r->top_k <= 4) permute_kernel<T, V, 4> ARGS(T);    \
+        else if (r->top_k <= 6) permute_kernel<T, V, 6> ARGS(T);    \
+        else permute_kernel<T, V, 8> ARGS(T);                       \
+    } while (0)
+    if (dtype == QMOE_BF16) { if (vec) BY_K(__nv_bfloat16, true); else BY_K(__nv_bfloat16, false); }
+    else { if (vec) BY_K(float, true); else BY_K(float, false); }
+#undef BY_K
 #undef ARGS
     QMOE_LAUNCH_CHECK("permute_kernel");
     return 0;
@@ -404,8 +437,17 @@ extern "C" int qmoe_combine(const qmoe_route_t* r, uint64_t y, uint64_t out, int
     const bool vec = dtype == QMOE_BF16 ? can_vec<__nv_bfloat16>(width, {y, out}) : can_vec<float>(width, {y, out});
     const int grid = grid_for_rows(r->tokens);
 #define ARGS(T) <<<grid, kThreads, 0, stream>>>((const T*)y, (const float*)r->gate_weights, (const int*)r->dest_row, (T*)out, (long long)r->tokens, r->top_k, (long long)width)
-    if (dtype == QMOE_BF16) { if (vec) combine_kernel<__nv_bfloat16, true> ARGS(__nv_bfloat16); else combine_kernel<__nv_bfloat16, false> ARGS(__nv_bfloat16); }
-    else { if (vec) combine_kernel<float, true> ARGS(float); else combine_kernel<float, false> ARGS(float); }
+#define BY_K(T, V)                                                  \
+    do {                                                            \
+        if (r->top_k <= 1) combine_kernel<T, V, 1> ARGS(T);         \
+        else if (r->top_k <= 2) combine_kernel<T, V, 2> ARGS(T);    \
+        else if (r->top_k <= 4) combine_kernel<T, V, 4> ARGS(T);    \
+        else if (r->top_k <= 6) combine_kernel<T, V, 6> ARGS(T);    \
+        else combine_kernel<T, V, 8> ARGS(T);                       \
+    } while (0)
+    if (dtype == QMOE_BF16) { if (vec) BY_K(__nv_bfloat16, true); else BY_K(__nv_bfloat16, false); }
+    else { if (vec) BY_K(float, true); else BY_K(float, false); }
+#undef BY_K
 #undef ARGS
     QMOE_LAUNCH_CHECK("combine_kernel");
     return 0;
@@ -419,10 +461,19 @@ extern "C" int qmoe_combine_backward(const qmoe_route_t* r, uint64_t g, uint64_t
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_COMBINE_BWD, stream);
     const bool vec = dtype == QMOE_BF16 ? can_vec<__nv_bfloat16>(width, {g, y, dy}) : can_vec<float>(width, {g, y, dy});
-    const int grid = grid_for_rows(r->rows_bound);
-#define ARGS(T) <<<grid, kThreads, 0, stream>>>((const T*)g, (const T*)y, (const float*)r->gate_weights, (const int*)r->row_source, (const int*)r->meta, (T*)dy, (float*)dw, r->top_k, (long long)width)
-    if (dtype == QMOE_BF16) { if (vec) combine_backward_kernel<__nv_bfloat16, true> ARGS(__nv_bfloat16); else combine_backward_kernel<__nv_bfloat16, false> ARGS(__nv_bfloat16); }
-    else { if (vec) combine_backward_kernel<float, true> ARGS(float); else combine_backward_kernel<float, false> ARGS(float); }
+    const int grid = grid_for_rows(r->tokens > (long long)r->experts * 64 ? r->tokens : (long long)r->experts * 64);
+#define ARGS(T) <<<grid, kThreads, 0, stream>>>((const T*)g, (const T*)y, (const float*)r->gate_weights, (const int*)r->dest_row, (const int*)r->row_source, (const int*)r->meta, (T*)dy, (float*)dw, (long long)r->tokens, r->top_k, (long long)width)
+#define BY_K(T, V)                                                           \
+    do {                                                                     \
+        if (r->top_k <= 1) combine_backward_kernel<T, V, 1> ARGS(T);         \
+        else if (r->top_k <= 2) combine_backward_kernel<T, V, 2> ARGS(T);    \
+        else if (r->top_k <= 4) combine_backward_kernel<T, V, 4> ARGS(T);    \
+        else if (r->top_k <= 6) combine_backward_kernel<T, V, 6> ARGS(T);    \
+        else combine_backward_kernel<T, V, 8> ARGS(T);                       \
+    } while (0)
+    if (dtype == QMOE_BF16) { if (vec) BY_K(__nv_bfloat16, true); else BY_K(__nv_bfloat16, false); }
+    else { if (vec) BY_K(float, true); else BY_K(float, false); }
+#undef BY_K
 #undef ARGS
     QMOE_LAUNCH_CHECK("combine_backward_kernel");
     return 0;
@@ -439,8 +490,17 @@ extern "C" int qmoe_unpermute_reduce(const qmoe_route_t* r, uint64_t dxd, uint64
     if (extra && (!aligned16(extra) || (width * 4) % 16)) vec = false;
     const int grid = grid_for_rows(r->tokens);
 #define ARGS(T) <<<grid, kThreads, 0, stream>>>((const T*)dxd, (const float*)extra, (const int*)r->dest_row, (T*)dx, (long long)r->tokens, r->top_k, (long long)width)
-    if (dtype == QMOE_BF16) { if (vec) unpermute_kernel<__nv_bfloat16, true> ARGS(__nv_bfloat16); else unpermute_kernel<__nv_bfloat16, false> ARGS(__nv_bfloat16); }
-    else { if (vec) unpermute_kernel<float, true> ARGS(float); else unpermute_kernel<float, false> ARGS(float); }
+#define BY_K(T, V)                                                    \
+    do {                                                              \
+        if (r->top_k <= 1) unpermute_kernel<T, V, 1> ARGS(T);         \
+        else if (r->top_k <= 2) unpermute_kernel<T, V, 2> ARGS(T);    \
+        else if (r->top_k <= 4) unpermute_kernel<T, V, 4> ARGS(T);    \
+        else if (r->top_k <= 6) unpermute_kernel<T, V, 6> ARGS(T);    \
+        else unpermute_kernel<T, V, 8> ARGS(T);                       \
+    } while (0)
+    if (dtype == QMOE_BF16) { if (vec) BY_K(__nv_bfloat16, true); else BY_K(__nv_bfloat16, false); }
+    else { if (vec) BY_K(float, true); else BY_K(float, false); }
+#undef BY_K
 #undef ARGS
     QMOE_LAUNCH_CHECK("unpermute_kernel");
     return 0;

@@ -198,3 +198,39 @@ extern "C" int qmoe_device_status(uint64_t stream, int* status) {
     QMOE_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return 0;
 }
+
+// ---- streams and events for hosts that overlap transfers or exchanges with compute -------------
+extern "C" int qmoe_stream_create(uint64_t* stream) {
+    if (!stream) return fail_arg("stream_create: stream is null");
+    cudaStream_t s = nullptr;
+    QMOE_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = (uint64_t)s;
+    return 0;
+}
+extern "C" int qmoe_stream_destroy(uint64_t stream) {
+    if (!stream) return 0;
+    QMOE_CUDA(cudaStreamDestroy((cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qmoe_event_create(uint64_t* event) {
+    if (!event) return fail_arg("event_create: event is null");
+    cudaEvent_t e = nullptr;
+    QMOE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    *event = (uint64_t)e;
+    return 0;
+}
+extern "C" int qmoe_event_destroy(uint64_t event) {
+    if (!event) return 0;
+    QMOE_CUDA(cudaEventDestroy((cudaEvent_t)event));
+    return 0;
+}
+extern "C" int qmoe_event_record(uint64_t event, uint64_t stream) {
+    if (!event) return fail_arg("event_record: event is null");
+    QMOE_CUDA(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qmoe_stream_wait_event(uint64_t stream, uint64_t event) {
+    if (!event) return fail_arg("stream_wait_event: event is null");
+    QMOE_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+    return 0;
+}

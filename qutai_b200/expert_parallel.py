@@ -215,6 +215,7 @@ class ExpertParallelMoE:
                                   Tensor(views[2], (d, h), requires_grad=True)))
         self.experts = tuple(experts)
         self.utilization = None
+        self._side = None   # (stream, event, event) used to overlap pushes with compute
         self._work = None
         self._saved = None
 
@@ -248,6 +249,8 @@ class ExpertParallelMoE:
             d_w_down=S(L * d * h, "float32"), aux_grad=S(1, "float32"),
             ret_table=S(Rx, "int32"), dest_base=S(E, "int32"), barrier=S.zeros(1, "int32"),
         )
+        if self.transport == "p2p":
+            buf["dx_recv"] = S(Rx * d, dtype)  # dX gets its own buffer so it can travel while the weight gradients run
         if dtype == "bfloat16":
             buf.update(w_gate=S(L * h * d, "bfloat16"), w_up=S(L * h * d, "bfloat16"), w_down=S(L * d * h, "bfloat16"))
         token_route = lib.Route()
@@ -281,6 +284,12 @@ class ExpertParallelMoE:
                           host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), grad_views=grad_views)
         if self.transport == "p2p":
             self._work["peers"] = self._open_peers(buf)
+            if self._side is None:
+                side, first, second = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+                lib.call("qmoe_stream_create", ctypes.byref(side))
+                lib.call("qmoe_event_create", ctypes.byref(first))
+                lib.call("qmoe_event_create", ctypes.byref(second))
+                self._side = (side.value, first.value, second.value)
         return self._work
 
     def _open_peers(self, buf):
@@ -342,11 +351,13 @@ class ExpertParallelMoE:
         code, s = lib.DTYPE_CODES[dtype], self.stream
         w = self._workspace(tokens, dtype)
         buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
-        if dtype == "bfloat16":
-            n = L * h * d
-            lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, s)
-            lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, s)
-            lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, s)
+        def cast_weights():
+            if dtype == "bfloat16":
+                n = L * h * d
+                lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, s)
+                lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, s)
+                lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, s)
+
         lib.call("qmoe_router_forward", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr,
                  buf["router_partials"].ptr, tokens, d, E, s)
         lib.call("qmoe_route", tr, buf["scores"].ptr, s)
@@ -359,13 +370,21 @@ class ExpertParallelMoE:
         out = DeviceStorage(storage.size, dtype)
         if self.transport == "p2p":
             peers = w["peers"]
+            side, ready, done = self._side
             lib.call("qmoe_ep_dest_base", buf["stats_all"].ptr, E, L, buf["dest_base"].ptr, s)
-            lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["x_send"].ptr, ctypes.byref(peers["x_recv"]), 1, code, d, s)
+            # the rows travel on the side stream while this stream refreshes the bf16 weight copies
+            lib.call("qmoe_event_record", ready, s)
+            lib.call("qmoe_stream_wait_event", side, ready)
+            lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["x_send"].ptr, ctypes.byref(peers["x_recv"]), 1, code, d, side)
+            lib.call("qmoe_event_record", done, side)
+            cast_weights()
+            lib.call("qmoe_stream_wait_event", s, done)
             lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
             lib.call("qmoe_expert_forward", xr, ex, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr, s)
             lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["y_recv"].ptr, ctypes.byref(peers["y_send"]), code, d, s)
             lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
         else:
+            cast_weights()
             counts = self._host_counts(w)                                              # the one host wait of the step
             plan = plan_exchange(counts, self.rank, N)
             w["sends"], w["recvs"] = _segments(plan["sends"]), _segments(plan["recvs"])
@@ -406,25 +425,32 @@ class ExpertParallelMoE:
                 parameter.grad = Tensor(parameter.grad.storage.copy(s), parameter.shape)
         lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
         lib.call("qmoe_ep_zero_pad_rows", xr, buf["dy_recv"].ptr, code, d, s)
+        grads = (buf["d_w_gate"].ptr, buf["d_w_up"].ptr, buf["d_w_down"].ptr)
+        saved = (buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["d_h"].ptr, buf["d_g"].ptr, buf["d_u"].ptr)
         if self.transport == "p2p":
             peers = w["peers"]
+            side, ready, done = self._side
             lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["dy_send"].ptr, ctypes.byref(peers["dy_recv"]), 0, code, d, s)
             lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 1, s)
+            # dX goes home on the side stream while the weight gradients and the router backward run here
+            lib.call("qmoe_event_record", ready, s)
+            lib.call("qmoe_stream_wait_event", side, ready)
+            lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dx_recv"].ptr, ctypes.byref(peers["dy_send"]), code, d, side)
+            lib.call("qmoe_event_record", done, side)
+            lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 2, s)
         else:
             (sa, sn), (ra, rn) = w["sends"], w["recvs"]
             lib.call("qmoe_ep_exchange", buf["dy_send"].ptr, sa, sn, buf["dy_recv"].ptr, ra, rn, d, code, s)
-        lib.call("qmoe_expert_backward", xr, ex, buf["dy_recv"].ptr, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr,
-                 buf["d_h"].ptr, buf["d_g"].ptr, buf["d_u"].ptr, buf["dy_recv"].ptr,  # dX reuses dY's buffer
-                 buf["d_w_gate"].ptr, buf["d_w_up"].ptr, buf["d_w_down"].ptr, s)
-        if self.transport == "p2p":
-            lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dy_recv"].ptr, ctypes.byref(peers["dy_send"]), code, d, s)
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
-        else:
+            lib.call("qmoe_expert_backward", xr, ex, buf["dy_recv"].ptr, *saved, buf["dy_recv"].ptr, *grads, s)  # dX reuses dY's buffer
             lib.call("qmoe_ep_exchange", buf["dy_recv"].ptr, ra, rn, buf["dy_send"].ptr, sa, sn, d, code, s)
         lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
         lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
                  buf["dx_router"].ptr, buf["d_w_router"].ptr, buf["router_partials"].ptr, tokens, d, E, s)
         lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, s)
+        if self.transport == "p2p":
+            lib.call("qmoe_stream_wait_event", s, done)
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
         dx = DeviceStorage(x_storage.size, dtype)
         lib.call("qmoe_unpermute_reduce", tr, buf["dy_send"].ptr, buf["dx_router"].ptr, dx.ptr, code, d, s)
         _accumulate(self.router.weight, views[0], s)

@@ -76,6 +76,12 @@ SIGNATURES = {
     "qmoe_memcpy_d2d": (c_int, [_U, _U, _U, _U]),
     "qmoe_memset": (c_int, [_U, c_int, _U, _U]),
     "qmoe_stream_sync": (c_int, [_U]),
+    "qmoe_stream_create": (c_int, [POINTER(c_uint64)]),
+    "qmoe_stream_destroy": (c_int, [_U]),
+    "qmoe_event_create": (c_int, [POINTER(c_uint64)]),
+    "qmoe_event_destroy": (c_int, [_U]),
+    "qmoe_event_record": (c_int, [_U, _U]),
+    "qmoe_stream_wait_event": (c_int, [_U, _U]),
     "qmoe_launch_count": (c_int64, []),
     "qmoe_tensor_core_launch_count": (c_int64, []),
     "qmoe_timing_enable": (c_int, [c_int]),
@@ -101,6 +107,7 @@ SIGNATURES = {
     "qmoe_cast_bf16": (c_int, [_U, _U, _I64, _U]),
     "qmoe_expert_forward": (c_int, [_RP, _EP, _U, _U, _U, _U, _U, _U]),
     "qmoe_expert_backward": (c_int, [_RP, _EP] + [_U] * 13),
+    "qmoe_expert_backward_parts": (c_int, [_RP, _EP] + [_U] * 12 + [_I32, _U]),
     "qmoe_gemm": (c_int, [_U, _I32, _U, _I32, _U, _I32, _I64, _I64, _I64, _I32, _I32, _I32, _U]),
     "qmoe_silu": (c_int, [_U, _U, _U, _I32, _I64, _I32, _U]),
     "qmoe_add": (c_int, [_U, _U, _U, _I32, _I64, _U]),
