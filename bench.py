@@ -406,6 +406,15 @@ def run_gpu(args, w, rank, world):
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
+    if args.trace:  # kernel timeline of two steps (diagnosis only; nothing measured under it is reported)
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            step()
+            torch.cuda.synchronize()
+        if rank == 0:
+            prof.export_chrome_trace(args.trace)
     counts = layer.last_counts
     sampler = ClockSampler(local)
     sampler.start()
@@ -504,6 +513,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--trace", default="", help="write a chrome trace of two steps (rank 0) to this path")
     parser.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"])
     parser.add_argument("--transport", default="p2p", choices=["p2p", "nccl"],
                         help="expert-parallel exchange: direct peer-memory stores, or NCCL send/receive")

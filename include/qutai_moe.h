@@ -225,6 +225,12 @@ int qmoe_cast_bf16(uint64_t src_f32, uint64_t dst_bf16, int64_t n, uint64_t stre
  * `SwiGLU.__call__` (src/qutai/lm/layers.py:310-311: 3 gemm + lm_silu + multiply per expert). */
 int qmoe_expert_forward(const qmoe_route_t* route, const qmoe_experts_t* experts, uint64_t x_dispatched,
                         uint64_t g, uint64_t u, uint64_t h, uint64_t y_dispatched, uint64_t stream);
+/* The same forward in two parts, for hosts that pipeline it with an exchange: QMOE_FWD_UP computes
+ * G, U, H; QMOE_FWD_DOWN computes Y from H.  Both bits = qmoe_expert_forward. */
+enum { QMOE_FWD_UP = 1, QMOE_FWD_DOWN = 2 };
+int qmoe_expert_forward_parts(const qmoe_route_t* route, const qmoe_experts_t* experts, uint64_t x_dispatched,
+                              uint64_t g, uint64_t u, uint64_t h, uint64_t y_dispatched, int32_t parts,
+                              uint64_t stream);
 /* Backward of the above.  dH (scratch [rows_bound, h]), dG, dU [rows_bound, h]; dX [rows_bound, d];
  * d_w_gate, d_w_up [E, h, d] and d_w_down [E, d, h] are fp32 and are WRITTEN (not accumulated) for
  * experts that received rows and left untouched for the others (upstream such experts get no
@@ -238,7 +244,8 @@ int qmoe_expert_backward(const qmoe_route_t* route, const qmoe_experts_t* expert
 /* The same backward in two parts, for hosts that overlap an exchange with the weight gradients:
  * QMOE_BWD_ACTIVATIONS computes dG, dU and dX (dX must then have its own buffer, not dY's),
  * QMOE_BWD_WEIGHTS the three weight gradients.  Both bits = qmoe_expert_backward. */
-enum { QMOE_BWD_ACTIVATIONS = 1, QMOE_BWD_WEIGHTS = 2 };
+enum { QMOE_BWD_ACTIVATIONS = 1, QMOE_BWD_WEIGHTS = 2,
+       QMOE_BWD_NO_DX = 4 /* with ACTIVATIONS: leave dX out (the caller computes it with qmoe_ep_expert_dx_push) */ };
 int qmoe_expert_backward_parts(const qmoe_route_t* route, const qmoe_experts_t* experts,
                                uint64_t dy_dispatched, uint64_t x_dispatched, uint64_t g, uint64_t u,
                                uint64_t h, uint64_t d_h, uint64_t d_g, uint64_t d_u, uint64_t dx_dispatched,
@@ -372,14 +379,37 @@ int qmoe_ep_dest_base(uint64_t stats_all, int32_t experts, int32_t local_experts
                       uint64_t stream);
 /* Token side -> expert side: every real row of `src` (local dispatched layout of token_route) is
  * stored into the owner's buffer; with write_return_addresses the owner's return table gets
- * (source rank, source row) for each row. */
+ * (source rank, source row) for each row.  blocks_per_sm: 0 = use the whole GPU; 1 = small enough
+ * to run beside a tensor-core kernel on every SM (for pushes issued on a second stream). */
 int qmoe_ep_push_dispatch(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t src,
-                          const qmoe_ep_peers_t* peers, int32_t write_return_addresses, int32_t dtype,
-                          int64_t width, uint64_t stream);
-/* Expert side -> token side: every real row of `src` (expert-side layout) is stored at the return
- * address recorded for it. */
+                          const qmoe_ep_peers_t* peers, int32_t write_return_addresses,
+                          int32_t blocks_per_sm, int32_t dtype, int64_t width, uint64_t stream);
+/* Expert side -> token side: every real row of `src` (expert-side layout) that belongs to a local
+ * expert in [expert_begin, expert_end) is stored at the return address recorded for it. */
 int qmoe_ep_push_return(const qmoe_route_t* expert_route, uint64_t return_addresses, uint64_t src,
-                        const qmoe_ep_peers_t* peers, int32_t dtype, int64_t width, uint64_t stream);
+                        const qmoe_ep_peers_t* peers, int32_t expert_begin, int32_t expert_end,
+                        int32_t blocks_per_sm, int32_t dtype, int64_t width, uint64_t stream);
+
+/* Fused producers (no upstream counterpart): the kernel that creates a row stores it directly in the
+ * destination GPU's buffer, so dispatch and combine need no pass of their own.
+ *   qmoe_ep_permute_push            x[t] -> the k expert-side rows of token t (peers: every rank's expert-side
+ *                                   input buffer and return table); replaces qmoe_permute + qmoe_ep_push_dispatch
+ *   qmoe_ep_combine_backward_push   g[t] * w[t, s] -> the expert-side dY rows, d_gate_weights locally (y_local:
+ *                                   this rank's combine input); replaces qmoe_combine_backward + push
+ *   qmoe_ep_expert_down_push        Y = H Wd^T on the tensor cores, every output row stored at its return
+ *   qmoe_ep_expert_dx_push          dX = dG Wg + dU Wu address (peers: every rank's token-side buffer)
+ * The two tensor-core variants need bf16 activations and widths that are multiples of 8 (else
+ * QMOE_ERR_UNSUPPORTED: use the unfused entry points).  Order a qmoe_ep_barrier after each before the
+ * destination is read. */
+int qmoe_ep_permute_push(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t x,
+                         const qmoe_ep_peers_t* peers, int32_t dtype, int64_t width, uint64_t stream);
+int qmoe_ep_combine_backward_push(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t grad_out,
+                                  uint64_t y_local, const qmoe_ep_peers_t* peers, uint64_t d_gate_weights,
+                                  int32_t dtype, int64_t width, uint64_t stream);
+int qmoe_ep_expert_down_push(const qmoe_route_t* expert_route, const qmoe_experts_t* experts, uint64_t h,
+                             uint64_t return_addresses, const qmoe_ep_peers_t* peers, uint64_t stream);
+int qmoe_ep_expert_dx_push(const qmoe_route_t* expert_route, const qmoe_experts_t* experts, uint64_t d_g,
+                           uint64_t d_u, uint64_t return_addresses, const qmoe_ep_peers_t* peers, uint64_t stream);
 
 #ifdef __cplusplus
 }

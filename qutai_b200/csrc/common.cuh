@@ -144,9 +144,15 @@ int launch_swiglu_backward(const qmoe_route_t* r, uint64_t dh, uint64_t g, uint6
                            long long hidden, cudaStream_t stream);
 bool tcgen05_shape_ok(long long width, long long hidden);
 int tc_swiglu_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t x, uint64_t g, uint64_t u, uint64_t h, cudaStream_t stream);
-int tc_rows_nt(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long K, long long N, cudaStream_t stream);
+// optional "store each output row at its return address on the rank that owns it" for the bf16 row products
+struct TcScatter {
+    const int* ret;                 // [rows] rank << 26 | row
+    unsigned long long base[16];    // destination buffer of every rank
+};
+int tc_rows_nt(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long K, long long N, cudaStream_t stream,
+               const TcScatter* scatter = nullptr);
 int tc_rows_nn(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t a2, uint64_t b2, uint64_t c, long long K,
-               long long N, cudaStream_t stream);
+               long long N, cudaStream_t stream, const TcScatter* scatter = nullptr);
 int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down, uint64_t g, uint64_t u, uint64_t dg,
                uint64_t du, long long d, long long h, cudaStream_t stream);
 int tc_wgrad(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long M, long long N, cudaStream_t stream);

@@ -11,6 +11,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <initializer_list>
 #include <mutex>
 
 #include "common.cuh"
@@ -338,7 +339,7 @@ ep_dest_base_kernel(const int* __restrict__ stats_all, int world, int rank, int 
 // Token side -> expert side.  Row r of the local dispatched layout (expert e = tile_expert[r / 128],
 // index i = r - offsets[e] inside the expert, a real row when i < counts[e]) goes to rank e / E_loc,
 // row dest_base[e] + i, and its return address is recorded next to it.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 6)
 ep_push_dispatch_kernel(const uint4* __restrict__ src, long long row_vecs, const int* __restrict__ tile_expert,
                         const int* __restrict__ offsets, const int* __restrict__ counts, const int* __restrict__ meta,
                         const int* __restrict__ dest_base, int E_loc, int rank, PeerTable peers) {
@@ -367,17 +368,17 @@ ep_push_dispatch_kernel(const uint4* __restrict__ src, long long row_vecs, const
 
 // Expert side -> token side.  Row j of the local expert-side layout (a real row when it lies in
 // [offsets[x], offsets[x] + counts[x])) goes back to the rank and row recorded in ret[j].
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 6)
 ep_push_return_kernel(const uint4* __restrict__ src, long long row_vecs, const int* __restrict__ tile_expert,
                       const int* __restrict__ offsets, const int* __restrict__ counts, const int* __restrict__ meta,
-                      const int* __restrict__ ret, PeerTable peers) {
+                      const int* __restrict__ ret, int expert_begin, int expert_end, PeerTable peers) {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
     const int rows = meta[0];
     for (long long j = warp; j < rows; j += nwarps) {
         const int x = tile_expert[j / kRowPad];
-        if ((int)j - offsets[x] >= counts[x]) continue;
+        if (x < expert_begin || x >= expert_end || (int)j - offsets[x] >= counts[x]) continue;
         const int address = ret[j];
         const int q = address >> kRetRankShift;
         const long long dest = address & ((1 << kRetRankShift) - 1);
@@ -413,9 +414,11 @@ PeerTable make_table(const qmoe_ep_peers_t* peers, bool with_ret) {
     return t;
 }
 
-int push_grid(long long rows) {
+// blocks_per_sm: 0 = fill the GPU (8 blocks of 256 threads per SM); a push that is meant to run beside
+// a tensor-core kernel asks for 1, so that both fit on every SM at the same time
+int push_grid(long long rows, int blocks_per_sm) {
     long long blocks = (rows + 7) / 8;
-    const long long cap = (long long)sm_count() * 8;
+    const long long cap = (long long)sm_count() * (blocks_per_sm > 0 && blocks_per_sm < 8 ? blocks_per_sm : 8);
     return (int)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
 }
 
@@ -474,8 +477,8 @@ extern "C" int qmoe_ep_dest_base(uint64_t stats_all, int32_t experts, int32_t lo
 }
 
 extern "C" int qmoe_ep_push_dispatch(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t src,
-                                     const qmoe_ep_peers_t* peers, int32_t write_return_addresses, int32_t dtype,
-                                     int64_t width, uint64_t stream_) {
+                                     const qmoe_ep_peers_t* peers, int32_t write_return_addresses, int32_t blocks_per_sm,
+                                     int32_t dtype, int64_t width, uint64_t stream_) {
     if (int rc = route_check(token_route)) return rc;
     if (int rc = check_peers(peers, write_return_addresses != 0)) return rc;
     if (!dest_base || !src || (src & 15u)) return fail_arg("ep_push_dispatch: null or misaligned buffer");
@@ -485,7 +488,7 @@ extern "C" int qmoe_ep_push_dispatch(const qmoe_route_t* token_route, uint64_t d
     if (token_route->rows_bound >= (1ll << kRetRankShift)) return fail_arg("ep_push_dispatch: too many rows for the return-address encoding");
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_EXCHANGE, stream);
-    ep_push_dispatch_kernel<<<push_grid(token_route->rows_bound), 256, 0, stream>>>(
+    ep_push_dispatch_kernel<<<push_grid(token_route->rows_bound, blocks_per_sm), 256, 0, stream>>>(
         (const uint4*)src, row_bytes / 16, (const int*)token_route->tile_expert, (const int*)token_route->offsets,
         (const int*)token_route->counts, (const int*)token_route->meta, (const int*)dest_base,
         token_route->experts / peers->world, peers->rank, make_table(peers, write_return_addresses != 0));
@@ -494,18 +497,237 @@ extern "C" int qmoe_ep_push_dispatch(const qmoe_route_t* token_route, uint64_t d
 }
 
 extern "C" int qmoe_ep_push_return(const qmoe_route_t* expert_route, uint64_t return_addresses, uint64_t src,
-                                   const qmoe_ep_peers_t* peers, int32_t dtype, int64_t width, uint64_t stream_) {
+                                   const qmoe_ep_peers_t* peers, int32_t expert_begin, int32_t expert_end,
+                                   int32_t blocks_per_sm, int32_t dtype, int64_t width, uint64_t stream_) {
     if (int rc = route_check(expert_route)) return rc;
     if (int rc = check_peers(peers, false)) return rc;
     if (!return_addresses || !src || (src & 15u)) return fail_arg("ep_push_return: null or misaligned buffer");
+    if (expert_begin < 0 || expert_end > expert_route->experts || expert_begin > expert_end)
+        return fail_arg("ep_push_return: expert range [%d, %d) is outside [0, %d)", expert_begin, expert_end, expert_route->experts);
     const long long row_bytes = width * (dtype == QMOE_BF16 ? 2 : 4);
     if (width <= 0 || row_bytes % 16) return fail_arg("ep_push_return: rows must be multiples of 16 bytes");
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_EXCHANGE, stream);
-    ep_push_return_kernel<<<push_grid(expert_route->rows_bound), 256, 0, stream>>>(
+    ep_push_return_kernel<<<push_grid(expert_route->rows_bound, blocks_per_sm), 256, 0, stream>>>(
         (const uint4*)src, row_bytes / 16, (const int*)expert_route->tile_expert, (const int*)expert_route->offsets,
-        (const int*)expert_route->counts, (const int*)expert_route->meta, (const int*)return_addresses,
-        make_table(peers, false));
+        (const int*)expert_route->counts, (const int*)expert_route->meta, (const int*)return_addresses, expert_begin,
+        expert_end, make_table(peers, false));
     QMOE_LAUNCH_CHECK("ep_push_return_kernel");
     return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused producers: the kernels that create the rows write them straight into the destination GPU's
+// buffer, so no separate exchange pass remains — the token-side permute and combine-backward scatter
+// to the expert ranks, and the two row products of the expert FFN (down projection, dX) store their
+// tiles at the rows' return addresses from the tensor-core epilogue.
+// ---------------------------------------------------------------------------------------------
+namespace qmoe {
+namespace {
+
+__device__ __forceinline__ uint4 ldg16_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+struct SlotTarget {
+    uint4* row;   // destination row on the owning rank
+};
+
+// x[t] -> the k expert-side rows of token t, wherever they live; records the return address of each
+template <int KMAX>
+__global__ void __launch_bounds__(256)
+ep_permute_push_kernel(const uint4* __restrict__ x, long long row_vecs, const int* __restrict__ expert_index,
+                       const int* __restrict__ dest_row, const int* __restrict__ offsets, const int* __restrict__ dest_base,
+                       long long tokens, int k, int E_loc, int rank, PeerTable peers) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long t = warp; t < tokens; t += nwarps) {
+        uint4* target[KMAX];
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s) {
+            target[s] = nullptr;
+            if (s < k) {
+                const long long a = t * k + s;
+                const int e = expert_index[a], r = dest_row[a];
+                const int p = e / E_loc;
+                const long long dest = (long long)dest_base[e] + (r - offsets[e]);
+                target[s] = peers.buffer[p] + dest * row_vecs;
+                if (lane == 0) peers.ret[p][dest] = (rank << kRetRankShift) | r;
+            }
+        }
+        const uint4* src = x + t * row_vecs;
+        long long c = lane;
+        for (; c + 32 < row_vecs; c += 64) {
+            const uint4 v0 = ldg16_stream(src + c), v1 = ldg16_stream(src + c + 32);
+#pragma unroll
+            for (int s = 0; s < KMAX; ++s)
+                if (s < k) { target[s][c] = v0; target[s][c + 32] = v1; }
+        }
+        for (; c < row_vecs; c += 32) {
+            const uint4 v0 = ldg16_stream(src + c);
+#pragma unroll
+            for (int s = 0; s < KMAX; ++s)
+                if (s < k) target[s][c] = v0;
+        }
+    }
+    __threadfence_system();
+}
+
+// dY row of (t, s) = g[t] * w[t, s] -> its expert-side row; d_gate_weights[t, s] = <g[t], y_send[dest_row[t, s]]>
+template <typename T, int KMAX>
+__global__ void __launch_bounds__(256)
+ep_combine_backward_push_kernel(const T* __restrict__ g, const T* __restrict__ y, const float* __restrict__ gate_w,
+                                const int* __restrict__ expert_index, const int* __restrict__ dest_row,
+                                const int* __restrict__ offsets, const int* __restrict__ dest_base, float* __restrict__ dw,
+                                long long tokens, int k, long long width, int E_loc, PeerTable peers) {
+    constexpr int N = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    const int chunks = (int)(width / N);
+    for (long long t = warp; t < tokens; t += nwarps) {
+        T* target[KMAX];
+        long long local[KMAX];
+        float w[KMAX], dot[KMAX];
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s) {
+            target[s] = nullptr; local[s] = 0; w[s] = 0.f; dot[s] = 0.f;
+            if (s < k) {
+                const long long a = t * k + s;
+                const int e = expert_index[a], r = dest_row[a];
+                const long long dest = (long long)dest_base[e] + (r - offsets[e]);
+                target[s] = (T*)peers.buffer[e / E_loc] + dest * width;
+                local[s] = r;
+                w[s] = gate_w[a];
+            }
+        }
+        const T* gs = g + t * width;
+        for (int c = lane; c < chunks; c += 32) {
+            float fg[N];
+            Vec16<T>::unpack(ldg16_stream(gs + (long long)c * N), fg);
+            uint4 v[KMAX];
+#pragma unroll
+            for (int s = 0; s < KMAX; ++s)
+                if (s < k) v[s] = ldg16_stream(y + local[s] * width + (long long)c * N);
+#pragma unroll
+            for (int s = 0; s < KMAX; ++s)
+                if (s < k) {
+                    float fy[N], o[N];
+                    Vec16<T>::unpack(v[s], fy);
+#pragma unroll
+                    for (int i = 0; i < N; ++i) { dot[s] = fmaf(fg[i], fy[i], dot[s]); o[i] = fg[i] * w[s]; }
+                    *reinterpret_cast<uint4*>(target[s] + (long long)c * N) = Vec16<T>::pack(o);
+                }
+        }
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s)
+            if (s < k) {
+                const float total = warp_sum(dot[s]);
+                if (lane == 0) dw[t * k + s] = total;
+            }
+    }
+    __threadfence_system();
+}
+
+int check_push_rows(int dtype, long long width, std::initializer_list<uint64_t> ptrs) {
+    if (dtype != QMOE_BF16 && dtype != QMOE_F32) return fail_arg("bad dtype %d", dtype);
+    if (width <= 0 || (width * (dtype == QMOE_BF16 ? 2 : 4)) % 16) return fail_arg("rows must be multiples of 16 bytes");
+    for (uint64_t p : ptrs)
+        if (!p || (p & 15u)) return fail_arg("null or misaligned buffer");
+    return 0;
+}
+
+int token_grid(long long tokens) {
+    long long blocks = (tokens + 7) / 8;
+    const long long cap = (long long)sm_count() * 8;
+    return (int)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
+}
+
+void fill_scatter(TcScatter& s, uint64_t ret, const qmoe_ep_peers_t* peers) {
+    s.ret = (const int*)ret;
+    for (int i = 0; i < 16; ++i) s.base[i] = i < peers->world ? peers->buffer[i] : 0;
+}
+
+}  // namespace
+}  // namespace qmoe
+
+extern "C" int qmoe_ep_permute_push(const qmoe_route_t* r, uint64_t dest_base, uint64_t x, const qmoe_ep_peers_t* peers,
+                                    int32_t dtype, int64_t width, uint64_t stream_) {
+    if (int rc = route_check(r)) return rc;
+    if (int rc = check_peers(peers, true)) return rc;
+    if (int rc = check_push_rows(dtype, width, {x, dest_base})) return rc;
+    if (r->experts % peers->world) return fail_arg("ep_permute_push: experts must divide evenly over the ranks");
+    if (r->rows_bound >= (1ll << kRetRankShift)) return fail_arg("ep_permute_push: too many rows for the return-address encoding");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXCHANGE, stream);
+    const long long row_vecs = width * (dtype == QMOE_BF16 ? 2 : 4) / 16;
+    const int E_loc = r->experts / peers->world, grid = token_grid(r->tokens);
+    const PeerTable table = make_table(peers, true);
+#define LAUNCH(K) ep_permute_push_kernel<K><<<grid, 256, 0, stream>>>((const uint4*)x, row_vecs, (const int*)r->expert_index, \
+        (const int*)r->dest_row, (const int*)r->offsets, (const int*)dest_base, r->tokens, r->top_k, E_loc, peers->rank, table)
+    if (r->top_k <= 1) LAUNCH(1); else if (r->top_k <= 2) LAUNCH(2); else if (r->top_k <= 4) LAUNCH(4);
+    else if (r->top_k <= 6) LAUNCH(6); else LAUNCH(8);
+#undef LAUNCH
+    QMOE_LAUNCH_CHECK("ep_permute_push_kernel");
+    return 0;
+}
+
+extern "C" int qmoe_ep_combine_backward_push(const qmoe_route_t* r, uint64_t dest_base, uint64_t grad_out, uint64_t y_local,
+                                             const qmoe_ep_peers_t* peers, uint64_t d_gate_weights, int32_t dtype,
+                                             int64_t width, uint64_t stream_) {
+    if (int rc = route_check(r)) return rc;
+    if (int rc = check_peers(peers, false)) return rc;
+    if (int rc = check_push_rows(dtype, width, {grad_out, y_local, dest_base})) return rc;
+    if (!d_gate_weights) return fail_arg("ep_combine_backward_push: d_gate_weights is null");
+    if (r->experts % peers->world) return fail_arg("ep_combine_backward_push: experts must divide evenly over the ranks");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXCHANGE, stream);
+    const int E_loc = r->experts / peers->world, grid = token_grid(r->tokens);
+    const PeerTable table = make_table(peers, false);
+#define LAUNCH(T, K) ep_combine_backward_push_kernel<T, K><<<grid, 256, 0, stream>>>((const T*)grad_out, (const T*)y_local, \
+        (const float*)r->gate_weights, (const int*)r->expert_index, (const int*)r->dest_row, (const int*)r->offsets,            \
+        (const int*)dest_base, (float*)d_gate_weights, r->tokens, r->top_k, (long long)width, E_loc, table)
+#define BY_K(T) do { if (r->top_k <= 1) LAUNCH(T, 1); else if (r->top_k <= 2) LAUNCH(T, 2); else if (r->top_k <= 4) LAUNCH(T, 4); \
+                     else if (r->top_k <= 6) LAUNCH(T, 6); else LAUNCH(T, 8); } while (0)
+    if (dtype == QMOE_BF16) BY_K(__nv_bfloat16); else BY_K(float);
+#undef BY_K
+#undef LAUNCH
+    QMOE_LAUNCH_CHECK("ep_combine_backward_push_kernel");
+    return 0;
+}
+
+extern "C" int qmoe_ep_expert_down_push(const qmoe_route_t* expert_route, const qmoe_experts_t* ex, uint64_t h,
+                                        uint64_t return_addresses, const qmoe_ep_peers_t* peers, uint64_t stream_) {
+    if (int rc = route_check(expert_route)) return rc;
+    if (int rc = check_peers(peers, false)) return rc;
+    if (!ex || !h || !return_addresses || !ex->w_down) return fail_arg("ep_expert_down_push: null argument");
+    if (ex->dtype != QMOE_BF16 || !tcgen05_shape_ok(ex->width, ex->hidden) || ex->engine == QMOE_ENGINE_SIMT) {
+        set_error("ep_expert_down_push needs the tensor-core engine (bf16 activations, widths multiples of 8)");
+        return QMOE_ERR_UNSUPPORTED;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXPERT_GEMM, stream);
+    TcScatter scatter;
+    fill_scatter(scatter, return_addresses, peers);
+    return tc_rows_nt(expert_route, ex->experts, h, ex->w_down, peers->buffer[peers->rank], ex->hidden, ex->width, stream, &scatter);
+}
+
+extern "C" int qmoe_ep_expert_dx_push(const qmoe_route_t* expert_route, const qmoe_experts_t* ex, uint64_t d_g, uint64_t d_u,
+                                      uint64_t return_addresses, const qmoe_ep_peers_t* peers, uint64_t stream_) {
+    if (int rc = route_check(expert_route)) return rc;
+    if (int rc = check_peers(peers, false)) return rc;
+    if (!ex || !d_g || !d_u || !return_addresses || !ex->w_gate || !ex->w_up) return fail_arg("ep_expert_dx_push: null argument");
+    if (ex->dtype != QMOE_BF16 || !tcgen05_shape_ok(ex->width, ex->hidden) || ex->engine == QMOE_ENGINE_SIMT) {
+        set_error("ep_expert_dx_push needs the tensor-core engine (bf16 activations, widths multiples of 8)");
+        return QMOE_ERR_UNSUPPORTED;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXPERT_GEMM, stream);
+    TcScatter scatter;
+    fill_scatter(scatter, return_addresses, peers);
+    return tc_rows_nn(expert_route, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, peers->buffer[peers->rank], ex->hidden,
+                      ex->width, stream, &scatter);
 }

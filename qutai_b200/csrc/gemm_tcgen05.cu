@@ -67,6 +67,10 @@ struct alignas(64) GemmParams {
     int M, N, K;          // WGRAD: M, N of one expert's output; others: N = output columns, K = inner size of one segment
     int b_rows;           // rows of the stacked B operand per expert
     int segments;         // 1, or 2 when (A2, B2) is accumulated into the same tile
+    // PLAIN with scatter: row r of the output is not stored at out0 + r * ldc but sent to the rank and row
+    // recorded for it (return address = rank << 26 | row), i.e. straight into that GPU's buffer
+    const int* scatter_ret;              // [rows] return addresses, or null for a plain store
+    unsigned long long scatter_base[16]; // every rank's destination buffer (own entry: local address)
     int plain_rows;       // > 0: one group of this many rows instead of the expert groups of `offsets`
     int group_stride;     // ROUTER: accumulator columns [0,S), [S,2S), [2S,3S) hold the three bf16 terms of the weights
 };
@@ -172,14 +176,17 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_st
         tile.krow0 = s_start[e] * kRowPad;
         tile.valid = count > 0;
     } else {
-        int lo = 0, hi = p.experts;  // largest e with s_start[e] * n_tiles <= t
+        // tiles are numbered from the first group's first row (a caller may pass a sub-range of the
+        // experts, whose offsets do not start at row 0)
+        const int first = s_start[0];
+        int lo = 0, hi = p.experts;  // largest e with (s_start[e] - first) * n_tiles <= t
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if ((long long)s_start[mid] * p.n_tiles <= t) lo = mid; else hi = mid;
+            if ((long long)(s_start[mid] - first) * p.n_tiles <= t) lo = mid; else hi = mid;
         }
         const int e = lo;
         const int mt = s_start[e + 1] - s_start[e];
-        const int local = t - s_start[e] * p.n_tiles;
+        const int local = t - (s_start[e] - first) * p.n_tiles;
         tile.expert = e;
         tile.row0 = (s_start[e] + local % mt) * BM;
         tile.n0 = (local / mt) * (MODE == MODE_SWIGLU ? 128 : BN);
@@ -243,6 +250,28 @@ __device__ __forceinline__ void store_block32(uint32_t stage, int lane, const ui
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                      : "r"(stage + row * STAGE_PITCH + 16 * piece) : "memory");
         *reinterpret_cast<uint4*>(dst + (long long)row * ldc + piece * 8) = v;
+    }
+    __syncwarp();
+}
+
+// Same transpose, but every row has its own destination: `dst_row` is THIS lane's row pointer (null =
+// skip the row, e.g. a pad row); the pointer of the row a lane stores is fetched by shuffle.
+__device__ __forceinline__ void scatter_block32(uint32_t stage, int lane, const uint32_t* w, __nv_bfloat16* dst_row) {
+    const uint32_t mine = stage + lane * STAGE_PITCH;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16 * q), "r"(w[4 * q]), "r"(w[4 * q + 1]),
+                     "r"(w[4 * q + 2]), "r"(w[4 * q + 3]) : "memory");
+    __syncwarp();
+    const unsigned long long mine_ptr = (unsigned long long)dst_row;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int row = j * 8 + (lane >> 2), piece = lane & 3;
+        const unsigned long long base = __shfl_sync(0xffffffffu, mine_ptr, row);
+        uint4 v;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "r"(stage + row * STAGE_PITCH + 16 * piece) : "memory");
+        if (base) *reinterpret_cast<uint4*>((__nv_bfloat16*)base + piece * 8) = v;
     }
     __syncwarp();
 }
@@ -321,7 +350,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
     int total_tiles;
     if (MODE == MODE_WGRAD) total_tiles = p.experts * p.m_tiles * p.n_tiles;
-    else total_tiles = s_start[p.experts] * p.n_tiles;
+    else total_tiles = (s_start[p.experts] - s_start[0]) * p.n_tiles;
     volatile int* abort_flag = &s_abort;
 
     if (warp == 0) {
@@ -530,6 +559,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 }
             } else if (MODE == MODE_PLAIN) {
                 __nv_bfloat16* C = (__nv_bfloat16*)p.out0 + row0w * p.ldc + tile.n0;
+                __nv_bfloat16* remote = nullptr;  // scatter mode: where this lane's row goes (null: pad row)
+                if (p.scatter_ret) {
+                    const int index_in_expert = (int)row - s_start[tile.expert] * kRowPad;
+                    if (index_in_expert < p.counts[tile.expert]) {
+                        const int address = p.scatter_ret[row];
+                        remote = (__nv_bfloat16*)p.scatter_base[address >> 26] + (long long)(address & ((1 << 26) - 1)) * p.ldc + tile.n0;
+                    }
+                }
 #pragma unroll 1
                 for (int c = 4 * half; c < 4 * half + 4; ++c) {
                     uint32_t r[32];
@@ -540,14 +577,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         uint32_t w[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) w[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                        store_block32(stage, lane, w, C + c * 32, p.ldc);
+                        if (p.scatter_ret) scatter_block32(stage, lane, w, remote ? remote + c * 32 : nullptr);
+                        else store_block32(stage, lane, w, C + c * 32, p.ldc);
                     } else if (valid > 0) {
                         float v[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                        store_row32_bf16(C + lane * p.ldc + c * 32, v, valid);
+                        if (!p.scatter_ret) store_row32_bf16(C + lane * p.ldc + c * 32, v, valid);
+                        else if (remote) store_row32_bf16(remote + c * 32, v, valid);
                     }
                 }
+                if (p.scatter_ret) __threadfence_system();
             } else if (MODE == MODE_ROUTER) {
                 // scores = x . (W_hi + W_mid + W_lo)^T: the three partial products sit S columns apart
                 float* C = (float*)p.out0 + row * p.ldc;
@@ -699,9 +739,16 @@ int tc_swiglu_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t 
 }
 
 // C [rows, N] = A [rows, K] . B_e^T with B stacked [E*N, K]
+void set_scatter(GemmParams& p, const TcScatter* scatter) {
+    if (!scatter) return;
+    p.scatter_ret = scatter->ret;
+    for (int i = 0; i < 16; ++i) p.scatter_base[i] = scatter->base[i];
+}
+
 int tc_rows_nt(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long K, long long N,
-               cudaStream_t stream) {
+               cudaStream_t stream, const TcScatter* scatter) {
     GemmParams p = {};
+    set_scatter(p, scatter);
     if (int rc = make_map(&p.map_a, a, (uint64_t)K, (uint64_t)r->rows_bound, BM)) return rc;
     if (int rc = make_map(&p.map_b, b, (uint64_t)K, (uint64_t)experts * N, BN)) return rc;
     p.map_a2 = p.map_a; p.map_b2 = p.map_b;
@@ -713,8 +760,9 @@ int tc_rows_nt(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint6
 
 // C [rows, N] = A [rows, K] . B_e (+ A2 . B2_e) with B stacked [E*K, N]
 int tc_rows_nn(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t a2, uint64_t b2, uint64_t c,
-               long long K, long long N, cudaStream_t stream) {
+               long long K, long long N, cudaStream_t stream, const TcScatter* scatter) {
     GemmParams p = {};
+    set_scatter(p, scatter);
     if (int rc = make_map(&p.map_a, a, (uint64_t)K, (uint64_t)r->rows_bound, BM)) return rc;
     if (int rc = make_map(&p.map_b, b, (uint64_t)N, (uint64_t)experts * K, 64)) return rc;
     p.map_a2 = p.map_a; p.map_b2 = p.map_b;

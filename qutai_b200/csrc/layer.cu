@@ -59,26 +59,41 @@ int simt_wgrad(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t a, uint
 
 using namespace qmoe;
 
-extern "C" int qmoe_expert_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t x, uint64_t g, uint64_t u,
-                                   uint64_t h, uint64_t y, uint64_t stream_) {
+extern "C" int qmoe_expert_forward_parts(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t x, uint64_t g, uint64_t u,
+                                         uint64_t h, uint64_t y, int32_t parts, uint64_t stream_) {
     int engine = 0;
     if (int rc = check_experts(r, ex, &engine)) return rc;
-    if (!x || !g || !u || !h || !y) return fail_arg("expert_forward: null buffer address");
+    if (!(parts & (QMOE_FWD_UP | QMOE_FWD_DOWN)) || (parts & ~(QMOE_FWD_UP | QMOE_FWD_DOWN)))
+        return fail_arg("expert_forward: parts must be a combination of QMOE_FWD_UP and QMOE_FWD_DOWN");
+    if (!h || ((parts & QMOE_FWD_UP) && (!x || !g || !u)) || ((parts & QMOE_FWD_DOWN) && !y))
+        return fail_arg("expert_forward: null buffer address");
     cudaStream_t stream = (cudaStream_t)stream_;
     const long long d = ex->width, hd = ex->hidden;
-    if (engine == QMOE_ENGINE_TCGEN05) {
-        TimedScope timed(KC_EXPERT_GEMM, stream);
-        if (int rc = tc_swiglu_forward(r, ex, x, g, u, h, stream)) return rc;
-        return tc_rows_nt(r, ex->experts, h, ex->w_down, y, hd, d, stream);
+    const bool tc = engine == QMOE_ENGINE_TCGEN05;
+    if (parts & QMOE_FWD_UP) {
+        if (tc) {
+            TimedScope timed(KC_EXPERT_GEMM, stream);
+            if (int rc = tc_swiglu_forward(r, ex, x, g, u, h, stream)) return rc;
+        } else {
+            {
+                TimedScope timed(KC_EXPERT_GEMM, stream);
+                if (int rc = simt_rows(r, ex, x, ex->w_gate, 0, 0, g, d, hd, true, stream)) return rc;
+                if (int rc = simt_rows(r, ex, x, ex->w_up, 0, 0, u, d, hd, true, stream)) return rc;
+            }
+            if (int rc = launch_swiglu(r, g, u, h, ex->dtype, hd, stream)) return rc;
+        }
     }
-    {
+    if (parts & QMOE_FWD_DOWN) {
         TimedScope timed(KC_EXPERT_GEMM, stream);
-        if (int rc = simt_rows(r, ex, x, ex->w_gate, 0, 0, g, d, hd, true, stream)) return rc;
-        if (int rc = simt_rows(r, ex, x, ex->w_up, 0, 0, u, d, hd, true, stream)) return rc;
+        return tc ? tc_rows_nt(r, ex->experts, h, ex->w_down, y, hd, d, stream)
+                  : simt_rows(r, ex, h, ex->w_down, 0, 0, y, hd, d, true, stream);
     }
-    if (int rc = launch_swiglu(r, g, u, h, ex->dtype, hd, stream)) return rc;
-    TimedScope timed(KC_EXPERT_GEMM, stream);
-    return simt_rows(r, ex, h, ex->w_down, 0, 0, y, hd, d, true, stream);
+    return 0;
+}
+
+extern "C" int qmoe_expert_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t x, uint64_t g, uint64_t u,
+                                   uint64_t h, uint64_t y, uint64_t stream) {
+    return qmoe_expert_forward_parts(r, ex, x, g, u, h, y, QMOE_FWD_UP | QMOE_FWD_DOWN, stream);
 }
 
 extern "C" int qmoe_expert_backward_parts(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t dy, uint64_t x, uint64_t g,
@@ -87,12 +102,14 @@ extern "C" int qmoe_expert_backward_parts(const qmoe_route_t* r, const qmoe_expe
                                           uint64_t stream_) {
     int engine = 0;
     if (int rc = check_experts(r, ex, &engine)) return rc;
+    const bool skip_dx = (parts & QMOE_BWD_NO_DX) != 0;
+    parts &= ~QMOE_BWD_NO_DX;
     if (!(parts & (QMOE_BWD_ACTIVATIONS | QMOE_BWD_WEIGHTS)) || (parts & ~(QMOE_BWD_ACTIVATIONS | QMOE_BWD_WEIGHTS)))
         return fail_arg("expert_backward: parts must be a combination of QMOE_BWD_ACTIVATIONS and QMOE_BWD_WEIGHTS");
     if (!dy || !x || !g || !u || !h || !d_h || !d_g || !d_u) return fail_arg("expert_backward: null buffer address");
-    if ((parts & QMOE_BWD_ACTIVATIONS) && !dx) return fail_arg("expert_backward: dx is null");
+    if ((parts & QMOE_BWD_ACTIVATIONS) && !skip_dx && !dx) return fail_arg("expert_backward: dx is null");
     if ((parts & QMOE_BWD_WEIGHTS) && (!d_w_gate || !d_w_up || !d_w_down)) return fail_arg("expert_backward: null gradient address");
-    if (parts == QMOE_BWD_ACTIVATIONS && dx == dy)
+    if (parts == QMOE_BWD_ACTIVATIONS && !skip_dx && dx == dy)
         return fail_arg("expert_backward: dx may alias dy only when both parts run in one call");
     cudaStream_t stream = (cudaStream_t)stream_;
     const long long d = ex->width, hd = ex->hidden;
@@ -108,7 +125,7 @@ extern "C" int qmoe_expert_backward_parts(const qmoe_route_t* r, const qmoe_expe
             }
             if (int rc = launch_swiglu_backward(r, d_h, g, u, d_g, d_u, ex->dtype, hd, stream)) return rc;
         }
-        if (dx != dy) {  // dX first when it has a buffer of its own: a host can ship it while the weight gradients run
+        if (!skip_dx && dx != dy) {  // dX first when it has a buffer of its own: a host can ship it while the weight gradients run
             TimedScope timed(KC_EXPERT_GEMM, stream);
             if (int rc = tc ? tc_rows_nn(r, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, stream)
                             : simt_rows(r, ex, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, false, stream)) return rc;
@@ -123,7 +140,7 @@ extern "C" int qmoe_expert_backward_parts(const qmoe_route_t* r, const qmoe_expe
         if (int rc = tc ? tc_wgrad(r, ex->experts, d_u, x, d_w_up, hd, d, stream)
                         : simt_wgrad(r, ex, d_u, x, d_w_up, hd, d, stream)) return rc;
     }
-    if ((parts & QMOE_BWD_ACTIVATIONS) && dx == dy) {  // dX overwrites dY: only after dY's last reader (dWd)
+    if ((parts & QMOE_BWD_ACTIVATIONS) && !skip_dx && dx == dy) {  // dX overwrites dY: only after dY's last reader (dWd)
         TimedScope timed(KC_EXPERT_GEMM, stream);
         return tc ? tc_rows_nn(r, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, stream)
                   : simt_rows(r, ex, d_g, ex->w_gate, d_u, ex->w_up, dx, hd, d, false, stream);

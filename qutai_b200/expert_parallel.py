@@ -282,6 +282,10 @@ class ExpertParallelMoE:
                                Tensor(buf["d_w_down"].view(j * d * h, d * h), (d, h))))
         self._work = dict(key=(tokens, dtype), buf=buf, token_route=token_route, expert_route=expert_route, experts=ex,
                           host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), grad_views=grad_views)
+        tensor_cores = dtype == "bfloat16" and self.engine != lib.ENGINE_SIMT and d % 8 == 0 and h % 8 == 0
+        # fused: the producing kernels (permute, combine-backward, and the tensor-core epilogues of the down
+        # projection and of dX) store their rows straight into the owning GPU's buffer
+        self._work["fused"] = self.transport == "p2p" and tensor_cores
         if self.transport == "p2p":
             self._work["peers"] = self._open_peers(buf)
             if self._side is None:
@@ -351,46 +355,59 @@ class ExpertParallelMoE:
         code, s = lib.DTYPE_CODES[dtype], self.stream
         w = self._workspace(tokens, dtype)
         buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
-        def cast_weights():
+        def cast_weights(stream):
             if dtype == "bfloat16":
                 n = L * h * d
-                lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, s)
-                lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, s)
-                lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, s)
+                lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, stream)
+                lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, stream)
+                lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, stream)
 
-        lib.call("qmoe_router_forward", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr,
-                 buf["router_partials"].ptr, tokens, d, E, s)
-        lib.call("qmoe_route", tr, buf["scores"].ptr, s)
-        # the all-gather is also the point no rank passes before every rank has finished its previous step
-        lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
-                 ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
-        lib.call("qmoe_permute", tr, storage.ptr, buf["x_send"].ptr, code, d, s)
-        lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
-        lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
+        def route_and_plan():
+            lib.call("qmoe_router_forward", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr,
+                     buf["router_partials"].ptr, tokens, d, E, s)
+            lib.call("qmoe_route", tr, buf["scores"].ptr, s)
+            # the all-gather is also the point no rank passes before every rank has finished its previous step
+            lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
+                     ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
+            lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
+            lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
+
         out = DeviceStorage(storage.size, dtype)
+        acts = (buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr)
         if self.transport == "p2p":
             peers = w["peers"]
             side, ready, done = self._side
-            lib.call("qmoe_ep_dest_base", buf["stats_all"].ptr, E, L, buf["dest_base"].ptr, s)
-            # the rows travel on the side stream while this stream refreshes the bf16 weight copies
+            # the bf16 weight copies are refreshed on the side stream while this stream routes and dispatches
             lib.call("qmoe_event_record", ready, s)
             lib.call("qmoe_stream_wait_event", side, ready)
-            lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["x_send"].ptr, ctypes.byref(peers["x_recv"]), 1, code, d, side)
+            cast_weights(side)
             lib.call("qmoe_event_record", done, side)
-            cast_weights()
-            lib.call("qmoe_stream_wait_event", s, done)
+            route_and_plan()
+            lib.call("qmoe_ep_dest_base", buf["stats_all"].ptr, E, L, buf["dest_base"].ptr, s)
+            if w["fused"]:
+                lib.call("qmoe_ep_permute_push", tr, buf["dest_base"].ptr, storage.ptr, ctypes.byref(peers["x_recv"]), code, d, s)
+            else:
+                lib.call("qmoe_permute", tr, storage.ptr, buf["x_send"].ptr, code, d, s)
+                lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["x_send"].ptr, ctypes.byref(peers["x_recv"]), 1, 0, code, d, s)
             lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
-            lib.call("qmoe_expert_forward", xr, ex, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr, s)
-            lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["y_recv"].ptr, ctypes.byref(peers["y_send"]), code, d, s)
+            lib.call("qmoe_stream_wait_event", s, done)
+            if w["fused"]:
+                lib.call("qmoe_expert_forward_parts", xr, ex, *acts, 1, s)
+                lib.call("qmoe_ep_expert_down_push", xr, ex, buf["h"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["y_send"]), s)
+            else:
+                lib.call("qmoe_expert_forward", xr, ex, *acts, s)
+                lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["y_recv"].ptr, ctypes.byref(peers["y_send"]), 0, L, 0, code, d, s)
             lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
         else:
-            cast_weights()
+            cast_weights(s)
+            route_and_plan()
+            lib.call("qmoe_permute", tr, storage.ptr, buf["x_send"].ptr, code, d, s)
             counts = self._host_counts(w)                                              # the one host wait of the step
             plan = plan_exchange(counts, self.rank, N)
             w["sends"], w["recvs"] = _segments(plan["sends"]), _segments(plan["recvs"])
             (sa, sn), (ra, rn) = w["sends"], w["recvs"]
             lib.call("qmoe_ep_exchange", buf["x_send"].ptr, sa, sn, buf["x_recv"].ptr, ra, rn, d, code, s)
-            lib.call("qmoe_expert_forward", xr, ex, buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr, s)
+            lib.call("qmoe_expert_forward", xr, ex, *acts, s)
             lib.call("qmoe_ep_exchange", buf["y_recv"].ptr, ra, rn, buf["y_send"].ptr, sa, sn, d, code, s)
         lib.call("qmoe_combine", tr, buf["y_send"].ptr, out.ptr, code, d, s)
         self.utilization = Tensor(buf["utilization"], (E,))
@@ -409,50 +426,62 @@ class ExpertParallelMoE:
         tokens, dtype = x_storage.size // d, x_storage.dtype
         code, s = lib.DTYPE_CODES[dtype], self.stream
         buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
-        # which local experts received rows decides who gets a gradient: host logic on the forward's counts
-        counts = self._host_counts(w)
-        received = [sum(counts[p][self.rank * L + j] for p in range(N)) for j in range(L)]
         ga = 0
         if grad_aux is not None:
             # the routing-backward kernel scales by E / (local tokens); the loss is over all ranks' tokens
             value = float(grad_aux) / N
-            buf["aux_grad"].upload_bytes(ctypes.string_at(ctypes.byref(ctypes.c_float(value)), 4), s)
+            if w.get("aux_value") != value:  # uploaded only when it changes (the copy waits for the stream)
+                buf["aux_grad"].upload_bytes(ctypes.string_at(ctypes.byref(ctypes.c_float(value)), 4), s)
+                w["aux_value"] = value
             ga = buf["aux_grad"].ptr
         views = w["grad_views"]
         owned = {id(views[0])} | {id(t) for group in views[1:] for t in group}
         for parameter in self.parameters():
             if parameter.grad is not None and id(parameter.grad) in owned:
                 parameter.grad = Tensor(parameter.grad.storage.copy(s), parameter.shape)
-        lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
         lib.call("qmoe_ep_zero_pad_rows", xr, buf["dy_recv"].ptr, code, d, s)
         grads = (buf["d_w_gate"].ptr, buf["d_w_up"].ptr, buf["d_w_down"].ptr)
         saved = (buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["d_h"].ptr, buf["d_g"].ptr, buf["d_u"].ptr)
-        if self.transport == "p2p":
+
+        def router_backward():
+            lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
+            lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
+                     buf["dx_router"].ptr, buf["d_w_router"].ptr, buf["router_partials"].ptr, tokens, d, E, s)
+            lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, s)
+
+        if self.transport == "p2p" and w["fused"]:
             peers = w["peers"]
-            side, ready, done = self._side
-            lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["dy_send"].ptr, ctypes.byref(peers["dy_recv"]), 0, code, d, s)
+            lib.call("qmoe_ep_combine_backward_push", tr, buf["dest_base"].ptr, g.ptr, buf["y_send"].ptr,
+                     ctypes.byref(peers["dy_recv"]), buf["d_gate_weights"].ptr, code, d, s)
             lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
-            lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 1, s)
-            # dX goes home on the side stream while the weight gradients and the router backward run here
-            lib.call("qmoe_event_record", ready, s)
-            lib.call("qmoe_stream_wait_event", side, ready)
-            lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dx_recv"].ptr, ctypes.byref(peers["dy_send"]), code, d, side)
-            lib.call("qmoe_event_record", done, side)
+            lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 1 | 4, s)
+            # dX leaves from the tensor-core epilogue; it has landed long before the barrier below
+            lib.call("qmoe_ep_expert_dx_push", xr, ex, buf["d_g"].ptr, buf["d_u"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["dy_send"]), s)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 2, s)
+            router_backward()
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+        elif self.transport == "p2p":
+            peers = w["peers"]
+            lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
+            lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["dy_send"].ptr, ctypes.byref(peers["dy_recv"]), 0, 0, code, d, s)
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 3, s)
+            lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dx_recv"].ptr, ctypes.byref(peers["dy_send"]), 0, L, 0, code, d, s)
+            router_backward()
+            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
         else:
+            lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
             (sa, sn), (ra, rn) = w["sends"], w["recvs"]
             lib.call("qmoe_ep_exchange", buf["dy_send"].ptr, sa, sn, buf["dy_recv"].ptr, ra, rn, d, code, s)
             lib.call("qmoe_expert_backward", xr, ex, buf["dy_recv"].ptr, *saved, buf["dy_recv"].ptr, *grads, s)  # dX reuses dY's buffer
             lib.call("qmoe_ep_exchange", buf["dy_recv"].ptr, ra, rn, buf["dy_send"].ptr, sa, sn, d, code, s)
-        lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
-        lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
-                 buf["dx_router"].ptr, buf["d_w_router"].ptr, buf["router_partials"].ptr, tokens, d, E, s)
-        lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, s)
-        if self.transport == "p2p":
-            lib.call("qmoe_stream_wait_event", s, done)
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            router_backward()
         dx = DeviceStorage(x_storage.size, dtype)
         lib.call("qmoe_unpermute_reduce", tr, buf["dy_send"].ptr, buf["dx_router"].ptr, dx.ptr, code, d, s)
+        # which local experts received rows decides who gets a gradient object: host logic on the forward's
+        # counts, read only now so that the device never waits for the host inside the step
+        counts = self._host_counts(w)
+        received = [sum(counts[p][self.rank * L + j] for p in range(N)) for j in range(L)]
         _accumulate(self.router.weight, views[0], s)
         for j, expert in enumerate(self.experts):
             if not received[j]:

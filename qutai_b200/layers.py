@@ -240,8 +240,6 @@ class SparseMoE:
         if g.size != x_storage.size or g.dtype != x_storage.dtype:
             raise ValueError("grad_y must match the output's size and dtype")
         ga = None if grad_aux is None else (grad_aux.storage if hasattr(grad_aux, "storage") else grad_aux)
-        # which experts get a gradient is host logic: wait for the forward's counts (long done)
-        counts = self.last_counts
         views = work["grad_views"]
         owned = {id(views[0])} | {id(t) for group in views[1:] for t in group}
         for parameter in self.parameters():
@@ -251,6 +249,9 @@ class SparseMoE:
         dx = DeviceStorage(x_storage.size, x_storage.dtype)
         layer.grad_out, layer.grad_aux, layer.dx = g.ptr, 0 if ga is None else ga.ptr, dx.ptr
         lib.call("qmoe_layer_backward", ctypes.byref(layer), self.stream)
+        # which experts get a gradient object is host logic on the forward's counts; they are read only
+        # now, after the whole backward is enqueued, so the device never idles waiting for the host
+        counts = self.last_counts
         _accumulate(self.router.weight, views[0], self.stream)
         for i, expert in enumerate(self.experts):
             if not counts[i]:

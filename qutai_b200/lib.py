@@ -107,6 +107,7 @@ SIGNATURES = {
     "qmoe_cast_bf16": (c_int, [_U, _U, _I64, _U]),
     "qmoe_expert_forward": (c_int, [_RP, _EP, _U, _U, _U, _U, _U, _U]),
     "qmoe_expert_backward": (c_int, [_RP, _EP] + [_U] * 13),
+    "qmoe_expert_forward_parts": (c_int, [_RP, _EP, _U, _U, _U, _U, _U, _I32, _U]),
     "qmoe_expert_backward_parts": (c_int, [_RP, _EP] + [_U] * 12 + [_I32, _U]),
     "qmoe_gemm": (c_int, [_U, _I32, _U, _I32, _U, _I32, _I64, _I64, _I64, _I32, _I32, _I32, _U]),
     "qmoe_silu": (c_int, [_U, _U, _U, _I32, _I64, _I32, _U]),
@@ -129,8 +130,12 @@ SIGNATURES = {
     "qmoe_ep_ipc_close": (c_int, [_U]),
     "qmoe_ep_barrier": (c_int, [_U, _U]),
     "qmoe_ep_dest_base": (c_int, [_U, _I32, _I32, _U, _U]),
-    "qmoe_ep_push_dispatch": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I64, _U]),
-    "qmoe_ep_push_return": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I64, _U]),
+    "qmoe_ep_push_dispatch": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I32, _I64, _U]),
+    "qmoe_ep_permute_push": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I64, _U]),
+    "qmoe_ep_combine_backward_push": (c_int, [_RP, _U, _U, _U, POINTER(Peers), _U, _I32, _I64, _U]),
+    "qmoe_ep_expert_down_push": (c_int, [_RP, _EP, _U, _U, POINTER(Peers), _U]),
+    "qmoe_ep_expert_dx_push": (c_int, [_RP, _EP, _U, _U, _U, POINTER(Peers), _U]),
+    "qmoe_ep_push_return": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I32, _I32, _I64, _U]),
 }
 
 _lock = threading.Lock()

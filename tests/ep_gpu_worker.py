@@ -28,6 +28,9 @@ def problem():
 
 def main():
     rank, world, out_dir, transport = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+    engine = "tcgen05"
+    if transport.endswith("-simt"):  # the direct transport without the fused tensor-core producers
+        transport, engine = transport[:-5], "simt"
     from gpu_util import Config, to_device, to_host
     from qutai_b200 import lib
     from qutai_b200.expert_parallel import ExpertParallelMoE, file_all_gather, finalize_communicator, init_communicator
@@ -39,7 +42,7 @@ def main():
     p = problem()
     T, d, E, k, h = p["T"], p["d"], p["E"], p["k"], p["h"]
     init_communicator(rank, world, rendezvous_path=os.path.join(out_dir, "nccl_id"), timeout=120)
-    layer = ExpertParallelMoE(Config(d, E, k, h), rank=rank, world=world, seed=3, engine="tcgen05", transport=transport,
+    layer = ExpertParallelMoE(Config(d, E, k, h), rank=rank, world=world, seed=3, engine=engine, transport=transport,
                               gather=lambda data: file_all_gather(out_dir, "ipc", rank, world, data))
     L = E // world
     mine = slice(rank * L, (rank + 1) * L)

@@ -42,7 +42,7 @@ def run_ranks(world, out_dir, transport):
     return [np.load(os.path.join(out_dir, f"rank{rank}.npz")) for rank in range(world)]
 
 
-@pytest.mark.parametrize("transport", ["nccl", "p2p"])
+@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-simt"])
 @pytest.mark.parametrize("world", [1, 2])
 def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, transport, tmp_path):
     if gpu_count() < world:
