@@ -81,6 +81,7 @@ int qmoe_event_create(uint64_t* event);
 int qmoe_event_destroy(uint64_t event);
 int qmoe_event_record(uint64_t event, uint64_t stream);
 int qmoe_stream_wait_event(uint64_t stream, uint64_t event);
+int qmoe_event_sync(uint64_t event);                       /* host waits for the event only */
 /* launches made by this library since load (the upstream runtime keeps the same counter,
  * src/qutai/backends/cuda_runtime.py:95, :327); tensor-core launches counted separately (:100). */
 int64_t qmoe_launch_count(void);

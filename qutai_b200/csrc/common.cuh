@@ -13,8 +13,9 @@ namespace qmoe {
 constexpr int kRowPad = QMOE_ROW_PAD;
 constexpr int kMaxExperts = QMOE_MAX_EXPERTS;
 constexpr int kMaxTopK = QMOE_MAX_TOP_K;
-// Token rows handled by one block of the routing kernels (8 warps x 16 rows).
-constexpr int kRouteRowsPerBlock = 128;
+// Token rows handled by one block of the routing kernels (8 warps x 4 rows): small blocks keep all SMs
+// busy when a rank holds only a few thousand tokens.
+constexpr int kRouteRowsPerBlock = 32;
 
 // ---- error plumbing -------------------------------------------------------------------------
 void set_error(const char* fmt, ...);

@@ -15,7 +15,7 @@ namespace qmoe {
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kRowsPerWarp = kRouteRowsPerBlock / kWarps;  // 16
+constexpr int kRowsPerWarp = kRouteRowsPerBlock / kWarps;  // 4
 
 // ---- K1: softmax + top-k + per-block histogram and probability column sums --------------------
 // One warp per token row; lane l holds experts l, l+32, ... (EPL of them).  Ranking uses the raw
@@ -126,27 +126,52 @@ route_topk_kernel(const float* __restrict__ scores, float* __restrict__ probs,
 }
 
 // ---- K2: scan over blocks, padded offsets, tile map, utilisation and auxiliary loss -----------
-__global__ void __launch_bounds__(kMaxExperts)
+// One block of 1024 threads: thread (segment, expert) first totals its segment of token blocks, the
+// segments are prefixed per expert, then each thread writes the running bases of its segment.  All
+// sums run in a fixed order (column sums in double), so the results are run-to-run identical.
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads)
 route_scan_kernel(const int* __restrict__ block_counts, const float* __restrict__ block_colsum,
                   int* __restrict__ block_base, int* __restrict__ counts, int* __restrict__ offsets,
                   int* __restrict__ tile_expert, int* __restrict__ meta, float* __restrict__ util,
                   float* __restrict__ aux, int nblk, long long T, int E, int k) {
+    __shared__ int s_seg[kScanThreads];
+    __shared__ double s_segcs[kScanThreads];
     __shared__ int s_cnt[kMaxExperts];
     __shared__ int s_off[kMaxExperts + 1];
     __shared__ double s_cs[kMaxExperts];
-    const int e = threadIdx.x;
-    if (e < E) {
-        int run = 0;
+    const int nseg = kScanThreads / E;
+    const int seg = threadIdx.x / E, e = threadIdx.x - seg * E;
+    const bool active = seg < nseg;
+    const int chunk = (nblk + nseg - 1) / nseg;
+    const int b0 = seg * chunk, b1 = min(nblk, b0 + chunk);
+    if (active) {
+        int total = 0;
         double cs = 0.0;
-        for (int b = 0; b < nblk; ++b) {
+        for (int b = b0; b < b1; ++b) {
+            total += block_counts[(long long)b * E + e];
+            cs += (double)block_colsum[(long long)b * E + e];
+        }
+        s_seg[threadIdx.x] = total;
+        s_segcs[threadIdx.x] = cs;
+    }
+    __syncthreads();
+    if (active) {
+        int run = 0;
+        for (int s = 0; s < seg; ++s) run += s_seg[s * E + e];
+        for (int b = b0; b < b1; ++b) {
             const int c = block_counts[(long long)b * E + e];
             block_base[(long long)b * E + e] = run;
             run += c;
-            cs += (double)block_colsum[(long long)b * E + e];
         }
-        counts[e] = run;
-        s_cnt[e] = run;
-        s_cs[e] = cs;
+        if (seg == 0) {
+            int total = 0;
+            double cs = 0.0;
+            for (int s = 0; s < nseg; ++s) { total += s_seg[s * E + e]; cs += s_segcs[s * E + e]; }
+            counts[e] = total;
+            s_cnt[e] = total;
+            s_cs[e] = cs;
+        }
     }
     __syncthreads();
     const double A = (double)T * k;
@@ -168,9 +193,10 @@ route_scan_kernel(const int* __restrict__ block_counts, const float* __restrict_
         aux[0] = (float)((double)E * total);
     }
     __syncthreads();
-    if (e < E) {
-        util[e] = (float)((double)s_cnt[e] / A);
-        for (int t = s_off[e] / kRowPad; t < s_off[e + 1] / kRowPad; ++t) tile_expert[t] = e;
+    if (threadIdx.x < E) {
+        const int x = threadIdx.x;
+        util[x] = (float)((double)s_cnt[x] / A);
+        for (int t = s_off[x] / kRowPad; t < s_off[x + 1] / kRowPad; ++t) tile_expert[t] = x;
     }
 }
 
@@ -324,7 +350,7 @@ extern "C" int qmoe_route(const qmoe_route_t* r, uint64_t scores, uint64_t strea
     else if (epl <= 4) route_topk_kernel<4><<<nblk, kWarps * 32, 0, stream>>>(sc, probs, gw, eidx, bc, bs, T, E, k);
     else route_topk_kernel<8><<<nblk, kWarps * 32, 0, stream>>>(sc, probs, gw, eidx, bc, bs, T, E, k);
     QMOE_LAUNCH_CHECK("route_topk_kernel");
-    route_scan_kernel<<<1, kMaxExperts, 0, stream>>>(bc, bs, (int*)r->block_base, (int*)r->counts,
+    route_scan_kernel<<<1, kScanThreads, 0, stream>>>(bc, bs, (int*)r->block_base, (int*)r->counts,
                                                       (int*)r->offsets, (int*)r->tile_expert,
                                                       (int*)r->meta, (float*)r->utilization,
                                                       (float*)r->aux, nblk, T, E, k);

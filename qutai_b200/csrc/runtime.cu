@@ -234,3 +234,8 @@ extern "C" int qmoe_stream_wait_event(uint64_t stream, uint64_t event) {
     QMOE_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
     return 0;
 }
+extern "C" int qmoe_event_sync(uint64_t event) {
+    if (!event) return fail_arg("event_sync: event is null");
+    QMOE_CUDA(cudaEventSynchronize((cudaEvent_t)event));
+    return 0;
+}

@@ -273,15 +273,17 @@ class ExpertParallelMoE:
             ex.w_gate, ex.w_up, ex.w_down = buf["w_gate"].ptr, buf["w_up"].ptr, buf["w_down"].ptr
         else:
             ex.w_gate, ex.w_up, ex.w_down = self._gate.ptr, self._up.ptr, self._down.ptr
-        host = ctypes.c_void_p()
+        host, stats_event = ctypes.c_void_p(), ctypes.c_uint64()
         lib.call("qmoe_host_alloc", ctypes.byref(host), 4 * N * 2 * E)
+        lib.call("qmoe_event_create", ctypes.byref(stats_event))
         grad_views = [Tensor(buf["d_w_router"], (E, d))]
         for j in range(L):
             grad_views.append((Tensor(buf["d_w_gate"].view(j * h * d, h * d), (h, d)),
                                Tensor(buf["d_w_up"].view(j * h * d, h * d), (h, d)),
                                Tensor(buf["d_w_down"].view(j * d * h, d * h), (d, h))))
         self._work = dict(key=(tokens, dtype), buf=buf, token_route=token_route, expert_route=expert_route, experts=ex,
-                          host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), grad_views=grad_views)
+                          host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), grad_views=grad_views,
+                          stats_event=stats_event.value)
         tensor_cores = dtype == "bfloat16" and self.engine != lib.ENGINE_SIMT and d % 8 == 0 and h % 8 == 0
         # fused: the producing kernels (permute, combine-backward, and the tensor-core epilogues of the down
         # projection and of dX) store their rows straight into the owning GPU's buffer
@@ -332,8 +334,9 @@ class ExpertParallelMoE:
         return self.forward(x)
 
     def _host_counts(self, w):
-        """[world][E] counts of the last forward as Python ints (waits for the stream)."""
-        lib.call("qmoe_stream_sync", self.stream)
+        """[world][E] counts of the last forward as Python ints (waits for that forward's count exchange
+        only, not for work enqueued after it)."""
+        lib.call("qmoe_event_sync", w["stats_event"])
         stats, E = w["host_stats"], self.n_experts
         return [[stats[p * 2 * E + e] for e in range(E)] for p in range(self.world)]
 
@@ -369,6 +372,7 @@ class ExpertParallelMoE:
             # the all-gather is also the point no rank passes before every rank has finished its previous step
             lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
                      ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
+            lib.call("qmoe_event_record", w["stats_event"], s)
             lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
             lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
 

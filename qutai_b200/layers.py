@@ -141,7 +141,7 @@ class SparseMoE:
         src/qutai/backends/cuda_lm.py:432-434)."""
         if not self._counts_valid:
             return self._zero_counts
-        lib.call("qmoe_stream_sync", self.stream)
+        lib.call("qmoe_event_sync", self._counts_event)  # waits for the forward's routing only, not for later work
         return tuple(self._counts_host[i] for i in range(self.n_experts))
 
     # ------------------------------------------------------------------------------------------
@@ -192,9 +192,11 @@ class SparseMoE:
             setattr(layer, name, buf[name].ptr)
         layer.dx_dispatched = buf["dy_dispatched"].ptr  # dX reuses dY's buffer (written after its last reader)
         if self._counts_host is None:
-            host = ctypes.c_void_p()
+            host, event = ctypes.c_void_p(), ctypes.c_uint64()
             lib.call("qmoe_host_alloc", ctypes.byref(host), 4 * E)
+            lib.call("qmoe_event_create", ctypes.byref(event))
             self._counts_host = ctypes.cast(host, ctypes.POINTER(ctypes.c_int32))
+            self._counts_event = event.value
         grad_views = [Tensor(buf["d_w_router"], (E, d))]
         for i in range(E):
             grad_views.append((Tensor(buf["d_w_gate"].view(i * h * d, h * d), (h, d)),
@@ -223,6 +225,7 @@ class SparseMoE:
         lib.call("qmoe_layer_forward", ctypes.byref(layer), self.stream)
         lib.call("qmoe_memcpy_d2h", ctypes.cast(self._counts_host, ctypes.c_void_p), buf["counts"].ptr,
                  4 * self.n_experts, self.stream)
+        lib.call("qmoe_event_record", self._counts_event, self.stream)
         self._counts_valid = True
         self.utilization = Tensor(buf["utilization"], (self.n_experts,))
         self._saved = (work, storage, shape)

@@ -82,6 +82,7 @@ SIGNATURES = {
     "qmoe_event_destroy": (c_int, [_U]),
     "qmoe_event_record": (c_int, [_U, _U]),
     "qmoe_stream_wait_event": (c_int, [_U, _U]),
+    "qmoe_event_sync": (c_int, [_U]),
     "qmoe_launch_count": (c_int64, []),
     "qmoe_tensor_core_launch_count": (c_int64, []),
     "qmoe_timing_enable": (c_int, [c_int]),

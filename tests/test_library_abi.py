@@ -39,7 +39,7 @@ def test_size_helpers_need_no_device(library_path):
     assert lib.rows_bound(16384, 8, 2) == 33792            # 32768 + 8 * 127, rounded up to 128
     assert lib.rows_bound(1, 1, 1) == 128
     assert lib.rows_bound(64, 64, 6) % lib.ROW_PAD == 0 and lib.rows_bound(64, 64, 6) >= 384 + 64 * 127
-    assert lib.route_blocks(1) == 1 and lib.route_blocks(128) == 1 and lib.route_blocks(129) == 2
+    assert lib.route_blocks(1) == 1 and lib.route_blocks(32) == 1 and lib.route_blocks(33) == 2
     scratch = int(lib.load().qmoe_router_scratch_bytes(4096, 8, 1024))
     assert scratch >= 4096 * 6 * 32 * 2 + 9 * 32 * 1024 * 2      # split gradients + split weights at least
     assert int(lib.load().qmoe_router_grad_partials(4096, 8, 1024)) * 4 >= scratch

@@ -52,7 +52,7 @@ def test_static_scratch_routing_rejects_sizes_beyond_the_built_in_array():
     from gpu_util import RouteTables, to_device
     from qutai_b200 import lib
 
-    T, E = 128 * 513, 256  # 513 blocks x 256 experts > 131072 entries
+    T, E = 32 * 513, 256  # 513 blocks x 256 experts > 131072 entries
     tables = RouteTables(T, E, 2)
     scores = to_device(np.zeros((1, 1)), "float32")  # never read: the call must fail before any launch
     with pytest.raises(ValueError, match="exceed the built-in"):
