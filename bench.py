@@ -66,7 +66,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
         except Exception:
             self.proc = None
@@ -403,6 +403,8 @@ def run_gpu(args, w, rank, world):
             ms = float(worst.item())
         return ms
 
+    sampler = ClockSampler(local)   # samples clocks from the warm-up through the last timed pass: all of it is this step under load
+    sampler.start()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -416,12 +418,9 @@ def run_gpu(args, w, rank, world):
         if rank == 0:
             prof.export_chrome_trace(args.trace)
     counts = layer.last_counts
-    sampler = ClockSampler(local)
-    sampler.start()
     launches_before = lib.load().qmoe_launch_count()
     ms = timed(step, args.steps)
     launches = (lib.load().qmoe_launch_count() - launches_before) // args.steps
-    clocks = sampler.stop()
     for _ in range(max(2, args.warmup // 2)):
         step_e2e()
     torch.cuda.synchronize()
@@ -434,6 +433,7 @@ def run_gpu(args, w, rank, world):
         step()
     classes = lib.timing_read()
     lib.timing(False)
+    clocks = sampler.stop()
     status = lib.device_status(stream)
 
     peaks = load_peaks()

@@ -95,6 +95,7 @@ const char* qmoe_timing_class_name(int kernel_class);
 int qmoe_timing_read(double* milliseconds, int64_t* scopes, int capacity);
 /* status word written by kernels that check themselves; 0 = clean.  Synchronises the stream. */
 int qmoe_device_status(uint64_t stream, int* status);
+int qmoe_device_status_clear(uint64_t stream);            /* back to 0 after a reported failure was handled */
 
 /* ---------------------------------------------------------------------------------------------
  * Sizes
@@ -390,6 +391,18 @@ int qmoe_ep_push_dispatch(const qmoe_route_t* token_route, uint64_t dest_base, u
 int qmoe_ep_push_return(const qmoe_route_t* expert_route, uint64_t return_addresses, uint64_t src,
                         const qmoe_ep_peers_t* peers, int32_t expert_begin, int32_t expert_end,
                         int32_t blocks_per_sm, int32_t dtype, int64_t width, uint64_t stream);
+
+/* Barrier over peer memory for the direct transport, without NCCL: every rank writes `sequence`
+ * (positive, growing by one per barrier, the same on every rank) into its slot of every rank's flag
+ * array (`flags->buffer[p]` = i32 [world] array of rank p, zero at start) and waits, at most about a
+ * second, for all slots of its own array; a rank that never arrives shows up as a non-zero
+ * qmoe_device_status on the others, not as a hang.  With stats_local != 0 the kernel first copies this
+ * rank's stats_words words into slot `rank` of every rank's table (`stats_tables->buffer[p]` = i32
+ * [world, stats_words]): the all-gather of qmoe_ep_gather_stats without NCCL (pack the words first
+ * with qmoe_ep_pack_stats). */
+int qmoe_ep_flag_barrier(const qmoe_ep_peers_t* flags, int32_t sequence, uint64_t stats_local,
+                         int32_t stats_words, const qmoe_ep_peers_t* stats_tables, uint64_t stream);
+int qmoe_ep_pack_stats(const qmoe_route_t* route, uint64_t stats_local, uint64_t stream);
 
 /* Fused producers (no upstream counterpart): the kernel that creates a row stores it directly in the
  * destination GPU's buffer, so dispatch and combine need no pass of their own.

@@ -731,3 +731,94 @@ extern "C" int qmoe_ep_expert_dx_push(const qmoe_route_t* expert_route, const qm
     return tc_rows_nn(expert_route, ex->experts, d_g, ex->w_gate, d_u, ex->w_up, peers->buffer[peers->rank], ex->hidden,
                       ex->width, stream, &scatter);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Flag barrier over peer memory: every rank stores the barrier's sequence number into its slot of
+// every rank's flag array, then waits until all slots of its own array carry that number.  Each
+// GPU runs its own copy of the kernel; the wait is bounded (about one second), after which the
+// kernel records a code in the status word and returns, so a missing rank shows up as a status on
+// the others instead of a hang.  Sequence numbers only grow, so the flags never need resetting.
+// ---------------------------------------------------------------------------------------------
+namespace qmoe {
+namespace {
+
+constexpr int kStatusBarrierTimeout = 201;
+constexpr unsigned long long kBarrierWaitNs = 1000ull * 1000ull * 1000ull;
+
+struct FlagTable {
+    int* flags[kMaxPeers];
+};
+
+__device__ __forceinline__ unsigned long long barrier_clock_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Optionally also publishes this rank's 2E statistics words into slot `rank` of every rank's table
+// (the all-gather of the routing counts), before the flags are raised.
+__global__ void __launch_bounds__(512)
+ep_flag_barrier_kernel(FlagTable table, int rank, int world, int sequence, int* status, const int* stats_local,
+                       int stats_words, FlagTable stats_tables) {
+    if (stats_local) {
+        for (int i = threadIdx.x; i < stats_words * world; i += blockDim.x) {
+            const int p = i / stats_words, j = i - p * stats_words;
+            stats_tables.flags[p][(long long)rank * stats_words + j] = stats_local[j];
+        }
+        __threadfence_system();
+        __syncthreads();
+    }
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(table.flags[p] + rank), "r"(sequence) : "memory");
+    const int* mine = table.flags[rank] + p;
+    const unsigned long long start = barrier_clock_ns();
+    for (unsigned spin = 0;; ++spin) {
+        int seen;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if (seen - sequence >= 0) break;
+        if ((spin & 255u) == 255u && barrier_clock_ns() - start > kBarrierWaitNs) {
+            atomicExch(status, kStatusBarrierTimeout);
+            break;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace qmoe
+
+extern "C" int qmoe_ep_flag_barrier(const qmoe_ep_peers_t* flags, int32_t sequence, uint64_t stats_local,
+                                    int32_t stats_words, const qmoe_ep_peers_t* stats_tables, uint64_t stream_) {
+    if (!flags) return fail_arg("ep_flag_barrier: flags is null");
+    if (flags->world <= 0 || flags->world > kMaxPeers || flags->rank < 0 || flags->rank >= flags->world)
+        return fail_arg("ep_flag_barrier: bad world / rank");
+    if (sequence <= 0) return fail_arg("ep_flag_barrier: the sequence number must be positive and growing");
+    if (stats_local && (!stats_tables || stats_words <= 0)) return fail_arg("ep_flag_barrier: statistics tables are missing");
+    FlagTable table = {}, stats = {};
+    for (int p = 0; p < flags->world; ++p) {
+        if (!flags->buffer[p]) return fail_arg("ep_flag_barrier: flag array of rank %d is null", p);
+        table.flags[p] = (int*)flags->buffer[p];
+        if (stats_local) {
+            if (!stats_tables->buffer[p]) return fail_arg("ep_flag_barrier: statistics table of rank %d is null", p);
+            stats.flags[p] = (int*)stats_tables->buffer[p];
+        }
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_EXCHANGE, stream);
+    ep_flag_barrier_kernel<<<1, 512, 0, stream>>>(table, flags->rank, flags->world, sequence, device_status_address(),
+                                                  (const int*)stats_local, stats_words, stats);
+    QMOE_LAUNCH_CHECK("ep_flag_barrier_kernel");
+    return 0;
+}
+
+// the local half of qmoe_ep_gather_stats: pack {counts, column sums} without the NCCL all-gather
+extern "C" int qmoe_ep_pack_stats(const qmoe_route_t* r, uint64_t stats_local, uint64_t stream_) {
+    if (int rc = route_check(r)) return rc;
+    if (!stats_local) return fail_arg("ep_pack_stats: null buffer");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_OTHER, stream);
+    ep_stats_kernel<<<1, kMaxExperts, 0, stream>>>((const int*)r->counts, (const float*)r->block_colsum,
+                                                    (int)qmoe_route_blocks(r->tokens), r->experts, (int*)stats_local);
+    QMOE_LAUNCH_CHECK("ep_stats_kernel");
+    return 0;
+}

@@ -239,3 +239,9 @@ extern "C" int qmoe_event_sync(uint64_t event) {
     QMOE_CUDA(cudaEventSynchronize((cudaEvent_t)event));
     return 0;
 }
+extern "C" int qmoe_device_status_clear(uint64_t stream) {
+    int* p = device_status_address();
+    if (!p) { set_error("device status symbol is not available"); return QMOE_ERR_STATE; }
+    QMOE_CUDA(cudaMemsetAsync(p, 0, sizeof(int), (cudaStream_t)stream));
+    return 0;
+}

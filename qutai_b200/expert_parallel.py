@@ -216,6 +216,7 @@ class ExpertParallelMoE:
         self.experts = tuple(experts)
         self.utilization = None
         self._side = None   # (stream, event, event) used to overlap pushes with compute
+        self._sequence = 0  # barriers issued so far (the flag barrier's growing sequence number)
         self._work = None
         self._saved = None
 
@@ -248,6 +249,7 @@ class ExpertParallelMoE:
             d_w_router=S(E * d, "float32"), d_w_gate=S(L * h * d, "float32"), d_w_up=S(L * h * d, "float32"),
             d_w_down=S(L * d * h, "float32"), aux_grad=S(1, "float32"),
             ret_table=S(Rx, "int32"), dest_base=S(E, "int32"), barrier=S.zeros(1, "int32"),
+            flags=S.zeros(lib.EP_MAX_RANKS, "int32"),
         )
         if self.transport == "p2p":
             buf["dx_recv"] = S(Rx * d, dtype)  # dX gets its own buffer so it can travel while the weight gradients run
@@ -290,6 +292,8 @@ class ExpertParallelMoE:
         self._work["fused"] = self.transport == "p2p" and tensor_cores
         if self.transport == "p2p":
             self._work["peers"] = self._open_peers(buf)
+            # barriers and the count all-gather go through flags in peer memory unless NCCL is asked for
+            self._work["flag_barrier"] = os.environ.get("QUTAI_MOE_EP_BARRIER", "flags") != "nccl"
             if self._side is None:
                 side, first, second = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
                 lib.call("qmoe_stream_create", ctypes.byref(side))
@@ -300,7 +304,8 @@ class ExpertParallelMoE:
 
     def _open_peers(self, buf):
         """Swap CUDA IPC handles of the five buffers other ranks write into and map every peer's."""
-        names = ("x_recv", "dy_recv", "y_send", "dy_send", "ret_table")
+        names = ("x_recv", "dy_recv", "y_send", "dy_send", "ret_table", "flags", "stats_all")
+        lib.call("qmoe_stream_sync", 0)  # the zero-fill of the flag array must have run before any peer can write it
         payload = b""
         for name in names:
             handle = ctypes.create_string_buffer(64)
@@ -321,7 +326,7 @@ class ExpertParallelMoE:
                     lib.call("qmoe_ep_ipc_open", ctypes.cast(handle, ctypes.c_void_p), ctypes.byref(opened))
                     address[name][p] = opened.value
         peers = {}
-        for name in ("x_recv", "dy_recv", "y_send", "dy_send"):
+        for name in ("x_recv", "dy_recv", "y_send", "dy_send", "flags", "stats_all"):
             table = lib.Peers()
             table.world, table.rank = self.world, self.rank
             for p in range(self.world):
@@ -332,6 +337,14 @@ class ExpertParallelMoE:
 
     def __call__(self, x):
         return self.forward(x)
+
+    def _barrier(self, w):
+        """Order everything the ranks enqueued so far against what they enqueue next."""
+        if w.get("flag_barrier"):
+            self._sequence += 1
+            lib.call("qmoe_ep_flag_barrier", ctypes.byref(w["peers"]["flags"]), self._sequence, 0, 0, None, self.stream)
+        else:
+            lib.call("qmoe_ep_barrier", w["buf"]["barrier"].ptr, self.stream)
 
     def _host_counts(self, w):
         """[world][E] counts of the last forward as Python ints (waits for that forward's count exchange
@@ -370,8 +383,15 @@ class ExpertParallelMoE:
                      buf["router_partials"].ptr, tokens, d, E, s)
             lib.call("qmoe_route", tr, buf["scores"].ptr, s)
             # the all-gather is also the point no rank passes before every rank has finished its previous step
-            lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
-                     ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
+            if w.get("flag_barrier"):
+                self._sequence += 1
+                lib.call("qmoe_ep_pack_stats", tr, buf["stats_local"].ptr, s)
+                lib.call("qmoe_ep_flag_barrier", ctypes.byref(w["peers"]["flags"]), self._sequence, buf["stats_local"].ptr,
+                         2 * E, ctypes.byref(w["peers"]["stats_all"]), s)
+                lib.call("qmoe_memcpy_d2h", ctypes.cast(w["host_stats"], ctypes.c_void_p), buf["stats_all"].ptr, 4 * N * 2 * E, s)
+            else:
+                lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
+                         ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
             lib.call("qmoe_event_record", w["stats_event"], s)
             lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
             lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
@@ -393,7 +413,7 @@ class ExpertParallelMoE:
             else:
                 lib.call("qmoe_permute", tr, storage.ptr, buf["x_send"].ptr, code, d, s)
                 lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["x_send"].ptr, ctypes.byref(peers["x_recv"]), 1, 0, code, d, s)
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            self._barrier(w)
             lib.call("qmoe_stream_wait_event", s, done)
             if w["fused"]:
                 lib.call("qmoe_expert_forward_parts", xr, ex, *acts, 1, s)
@@ -401,7 +421,7 @@ class ExpertParallelMoE:
             else:
                 lib.call("qmoe_expert_forward", xr, ex, *acts, s)
                 lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["y_recv"].ptr, ctypes.byref(peers["y_send"]), 0, L, 0, code, d, s)
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            self._barrier(w)
         else:
             cast_weights(s)
             route_and_plan()
@@ -457,22 +477,22 @@ class ExpertParallelMoE:
             peers = w["peers"]
             lib.call("qmoe_ep_combine_backward_push", tr, buf["dest_base"].ptr, g.ptr, buf["y_send"].ptr,
                      ctypes.byref(peers["dy_recv"]), buf["d_gate_weights"].ptr, code, d, s)
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            self._barrier(w)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 1 | 4, s)
             # dX leaves from the tensor-core epilogue; it has landed long before the barrier below
             lib.call("qmoe_ep_expert_dx_push", xr, ex, buf["d_g"].ptr, buf["d_u"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["dy_send"]), s)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 2, s)
             router_backward()
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            self._barrier(w)
         elif self.transport == "p2p":
             peers = w["peers"]
             lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
             lib.call("qmoe_ep_push_dispatch", tr, buf["dest_base"].ptr, buf["dy_send"].ptr, ctypes.byref(peers["dy_recv"]), 0, 0, code, d, s)
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            self._barrier(w)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 3, s)
             lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dx_recv"].ptr, ctypes.byref(peers["dy_send"]), 0, L, 0, code, d, s)
             router_backward()
-            lib.call("qmoe_ep_barrier", buf["barrier"].ptr, s)
+            self._barrier(w)
         else:
             lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
             (sa, sn), (ra, rn) = w["sends"], w["recvs"]

@@ -90,6 +90,7 @@ SIGNATURES = {
     "qmoe_timing_class_name": (c_char_p, [c_int]),
     "qmoe_timing_read": (c_int, [POINTER(c_double), POINTER(c_int64), c_int]),
     "qmoe_device_status": (c_int, [_U, POINTER(c_int)]),
+    "qmoe_device_status_clear": (c_int, [_U]),
     "qmoe_rows_bound": (c_int64, [_I64, _I32, _I32]),
     "qmoe_route_blocks": (c_int64, [_I64]),
     "qmoe_router_logits": (c_int, [_U, _I32, _U, _U, _I64, _I64, _I32, _U]),
@@ -132,6 +133,8 @@ SIGNATURES = {
     "qmoe_ep_barrier": (c_int, [_U, _U]),
     "qmoe_ep_dest_base": (c_int, [_U, _I32, _I32, _U, _U]),
     "qmoe_ep_push_dispatch": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I32, _I64, _U]),
+    "qmoe_ep_flag_barrier": (c_int, [POINTER(Peers), _I32, _U, _I32, POINTER(Peers), _U]),
+    "qmoe_ep_pack_stats": (c_int, [_RP, _U, _U]),
     "qmoe_ep_permute_push": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I64, _U]),
     "qmoe_ep_combine_backward_push": (c_int, [_RP, _U, _U, _U, POINTER(Peers), _U, _I32, _I64, _U]),
     "qmoe_ep_expert_down_push": (c_int, [_RP, _EP, _U, _U, POINTER(Peers), _U]),
