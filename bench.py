@@ -313,6 +313,8 @@ def run_gpu(args, w, rank, world):
     xs, gs = Tensor(wrap(x_dev, "bfloat16"), (T, d)), Tensor(wrap(g_dev, "bfloat16"), (T, d))
     ga = wrap(aux_grad, "float32") if world == 1 else 0.01
     forward_only = args.workload == "c5"
+    if forward_only and hasattr(layer, "refresh_operands"):
+        layer.refresh_operands = False   # decode: the weights are fixed, their bf16 copies are built once
     placement = "contiguous"
     if world > 1 and args.placement == "balanced":
         # Experts are placed on ranks by measured load (one profiling forward), not by index.  With
@@ -448,6 +450,8 @@ def run_gpu(args, w, rank, world):
     gemm_launches = (classes["expert_gemm"][1] + classes["wgrad_gemm"][1]) // args.steps
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     peak = peaks["bf16_tflops_sustained"]
+    active = sum(1 for c in (counts if world == 1 else counts[rank * (w["E"] // world):(rank + 1) * (w["E"] // world)]) if c)
+    weight_bytes = active * 3 * w["d"] * w["h"] * 2     # bf16 weights of the experts that received tokens, read once
     A, h, E, k = T * w["k"], w["h"], w["E"], w["k"]
     hbm_bytes = dict(permute=T * d * 2 + A * d * 2 + A * 4, combine=A * d * 2 + 3 * A * 4 + T * d * 2,
                      combine_backward=T * d * 2 + 2 * A * d * 2 + A * 4, unpermute=A * d * 2 + T * d * 2 + A * 4,
@@ -474,6 +478,9 @@ def run_gpu(args, w, rank, world):
                       traffic=None, launches_per_step=int(gemm_launches), ms_per_step=gemm_ms,
                       algorithmic_flops_per_step=gemm_flops, whole_layer_frac=(gemm_flops + router_flops) / (ms * 1e-3) / 1e12 / peak),
         hbm_kernels=hbm,
+        decode_roofline=(dict(bound="hbm", kernel="grouped_gemm_kernel (tcgen05), weight streaming", achieved=weight_bytes / (gemm_ms * 1e-3) / 1e9,
+                              peak=peaks["hbm_gbs"], unit="GB/s", frac=weight_bytes / (gemm_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                              bytes_per_step=weight_bytes) if forward_only and gemm_ms > 0 else None),
         class_ms_per_step={name: round(v[0] / args.steps, 4) for name, v in classes.items() if v[1]},
         expert_counts=dict(max=max(counts), mean=sum(counts) / len(counts), max_over_mean=max(counts) * len(counts) / max(1, sum(counts))),
         device_status=status,
@@ -491,6 +498,17 @@ def run_gpu(args, w, rank, world):
                 note="scalar triple-loop rate of the upstream pure-Python path; tokens/s = rate / (9*k*d*h + 3*d*E) MAC per token"))
         rate = line["cpu_baseline"]["pure_python_estimate"]["mac_per_s"]
         line["cpu_baseline"]["pure_python_estimate"]["tokens_per_s"] = rate / (9.0 * k * d * h + 3.0 * d * E)
+    if forward_only:
+        # decode-shaped workload: per-call latency percentiles over 200 calls, each bracketed by its own events
+        marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
+        torch.cuda.synchronize()
+        for begin, end in marks:
+            begin.record()
+            step()
+            end.record()
+        torch.cuda.synchronize()
+        lat = sorted(b.elapsed_time(e) for b, e in marks)
+        line["latency_ms"] = dict(p50=lat[len(lat) // 2], p99=lat[int(len(lat) * 0.99)], calls=len(lat))
     if world > 1:
         line["config"]["expert_placement"] = placement
         line["config"]["transport"] = args.transport

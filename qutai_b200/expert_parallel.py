@@ -216,6 +216,7 @@ class ExpertParallelMoE:
         self.experts = tuple(experts)
         self.utilization = None
         self._side = None   # (stream, event, event) used to overlap pushes with compute
+        self.refresh_operands = True  # False: keep the bf16 weight copies of the first forward (fixed weights, serving)
         self._sequence = 0  # barriers issued so far (the flag barrier's growing sequence number)
         self._work = None
         self._saved = None
@@ -372,7 +373,8 @@ class ExpertParallelMoE:
         w = self._workspace(tokens, dtype)
         buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
         def cast_weights(stream):
-            if dtype == "bfloat16":
+            if dtype == "bfloat16" and (self.refresh_operands or not w.get("operands_built")):
+                w["operands_built"] = True
                 n = L * h * d
                 lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, stream)
                 lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, stream)

@@ -124,6 +124,10 @@ class SparseMoE:
                                   Tensor(views[2], (d, h), requires_grad=True)))
         self.experts = tuple(experts)
         self.utilization = None
+        # True (training): the bf16 operand copies of the fp32 weights are rebuilt at every forward, because an
+        # optimizer may have changed the weights.  A serving loop whose weights are fixed sets it to False after
+        # its first forward.
+        self.refresh_operands = True
         self._counts_host = None
         self._counts_valid = False
         self._zero_counts = (0,) * E
@@ -222,7 +226,12 @@ class SparseMoE:
         layer, buf = work["layer"], work["buf"]
         out = DeviceStorage(storage.size, storage.dtype)
         layer.x, layer.out = storage.ptr, out.ptr
+        masters = (layer.master_gate, layer.master_up, layer.master_down)
+        if not self.refresh_operands and work.get("operands_built"):
+            layer.master_gate = layer.master_up = layer.master_down = 0   # keep the bf16 copies of the last forward
         lib.call("qmoe_layer_forward", ctypes.byref(layer), self.stream)
+        layer.master_gate, layer.master_up, layer.master_down = masters
+        work["operands_built"] = True
         lib.call("qmoe_memcpy_d2h", ctypes.cast(self._counts_host, ctypes.c_void_p), buf["counts"].ptr,
                  4 * self.n_experts, self.stream)
         lib.call("qmoe_event_record", self._counts_event, self.stream)
