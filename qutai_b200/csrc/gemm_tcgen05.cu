@@ -35,12 +35,19 @@ namespace qmoe {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB: the 128 rows (or 128 MN columns) this CTA contributes
 constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64 x 64 bf16 TMA box (8 KiB)
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 32 * 80 /*epilogue transpose*/;
+// CTAS = 1: one CTA owns a 128 x 256 tile (A 16 KiB + B 32 KiB per stage, 4 stages).
+// CTAS = 2: a pair of CTAs (cluster of 2, tcgen05 cta_group::2) owns a 256 x 256 tile; each CTA stages its 128
+//           rows of A and HALF of B (16 + 16 KiB per stage, 6 stages), so every byte fetched from L2 feeds
+//           1.5x more math, and the issuing CTA's MMA reads both halves.
+template <int CTAS> struct Cfg {
+    static constexpr int STAGES = CTAS == 2 ? 6 : 4;
+    static constexpr int B_STAGE_BYTES = (CTAS == 2 ? BN / 2 : BN) * BK * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 32 * 80 /*epilogue transpose*/;
+};
 constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
 constexpr int EPILOGUE_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;
@@ -118,6 +125,40 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t dst
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
+// ---- cluster / CTA-pair helpers (CTAS == 2) ----------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load issued by one CTA of a pair: the data lands in this CTA's shared memory, the transaction
+// bytes are counted on the barrier of the pair's first CTA (same offset, CTA-rank bit cleared).
+__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t dst, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -149,27 +190,32 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes,
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M = 128, N = 256.
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int M>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 struct Tile {
     int expert, row0, n0, kblocks, krow0;
-    bool valid;
+    bool valid;       // false: nothing to do for the whole tile (all CTAs of the tile skip it)
+    bool rows_valid;  // CTAS == 2: false when this CTA's 128 rows lie past the end of the expert (compute, do not store)
 };
 
-template <int MODE>
-__device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_start, const int* s_order, int t) {
+// s_start[e]: first 128-row tile of expert e.  s_pair[e] (CTAS == 2): first 256-row pair-tile of expert e, an
+// expert with an odd number of 128-row tiles gets a last pair-tile whose second half is not stored.
+template <int MODE, int CTAS>
+__device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_start, const int* s_pair, const int* s_order,
+                                            int t, int cta_rank) {
     Tile tile;
     tile.valid = true;
+    tile.rows_valid = true;
     if (MODE == MODE_WGRAD) {
-        const int per = p.m_tiles * p.n_tiles;
+        const int per = p.m_tiles * p.n_tiles;  // m_tiles counts CTAS * 128-row groups of the output
         const int slot = t / per, rem = t - slot * per;
         const int e = s_order[slot];
         tile.expert = e;
-        tile.row0 = (rem % p.m_tiles) * BM;
+        tile.row0 = (rem % p.m_tiles) * (BM * CTAS) + cta_rank * BM;
         tile.n0 = (rem / p.m_tiles) * BN;
         const int count = p.counts[e];
         tile.kblocks = (count + BK - 1) / BK;
@@ -178,18 +224,21 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_st
     } else {
         // tiles are numbered from the first group's first row (a caller may pass a sub-range of the
         // experts, whose offsets do not start at row 0)
-        const int first = s_start[0];
-        int lo = 0, hi = p.experts;  // largest e with (s_start[e] - first) * n_tiles <= t
+        const int* first_of = CTAS == 2 ? s_pair : s_start;
+        const int first = first_of[0];
+        int lo = 0, hi = p.experts;  // largest e with (first_of[e] - first) * n_tiles <= t
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if ((long long)(s_start[mid] - first) * p.n_tiles <= t) lo = mid; else hi = mid;
+            if ((long long)(first_of[mid] - first) * p.n_tiles <= t) lo = mid; else hi = mid;
         }
         const int e = lo;
-        const int mt = s_start[e + 1] - s_start[e];
-        const int local = t - (s_start[e] - first) * p.n_tiles;
+        const int groups = first_of[e + 1] - first_of[e];
+        const int local = t - (first_of[e] - first) * p.n_tiles;
+        const int m_tile = (local % groups) * CTAS + cta_rank;  // 128-row tile inside the expert
         tile.expert = e;
-        tile.row0 = (s_start[e] + local % mt) * BM;
-        tile.n0 = (local / mt) * (MODE == MODE_SWIGLU ? 128 : BN);
+        tile.row0 = (s_start[e] + m_tile) * BM;
+        tile.rows_valid = m_tile < s_start[e + 1] - s_start[e];
+        tile.n0 = (local / groups) * (MODE == MODE_SWIGLU ? 128 : BN);
         tile.kblocks = ((p.K + BK - 1) / BK) * p.segments;
         tile.krow0 = 0;
     }
@@ -294,16 +343,25 @@ __device__ __forceinline__ void gather_block32(uint32_t stage, int lane, const u
     __syncwarp();
 }
 
-template <int MODE, bool A_MN, bool B_MN>
+// CTAS == 2: two CTAs of a cluster (a CTA pair on neighbouring SMs) share one 256-row x 256-column tile.
+// Each stages its own 128 rows of A and half of the B tile, the pair's first CTA issues one
+// cta_group::2 MMA per k-step that reads both halves, and each CTA converts the 128 x 256 accumulator
+// that lands in its own tensor memory.  Per SM and k-step that is 32 KiB of operands instead of 48 KiB.
+template <int MODE, bool A_MN, bool B_MN, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+    constexpr int STAGES = Cfg<CTAS>::STAGES, B_STAGE_BYTES = Cfg<CTAS>::B_STAGE_BYTES, STAGE_BYTES = Cfg<CTAS>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_start[kMaxExperts + 1];  // first 128-row tile of each expert
+    __shared__ int s_pair[kMaxExperts + 1];   // CTAS == 2: first 256-row pair-tile of each expert
     __shared__ int s_order[kMaxExperts];      // WGRAD: experts by decreasing row count (ties by index)
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cta_rank = CTAS == 2 ? (int)cluster_ctarank() : 0;
+    const int first_tile = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;  // a cluster is two consecutive blocks
+    const int tile_stride = (int)gridDim.x / CTAS;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = base + STAGES * STAGE_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -331,8 +389,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     if (threadIdx.x == 0) {
         s_abort = 0;
+        // CTAS == 2: the copies of both CTAs count on the first CTA's full barrier; the MMA issuer (first
+        // CTA) releases a stage and publishes an accumulator on the barriers of both; the epilogue warps
+        // of both hand an accumulator back on the first CTA's barrier
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPILOGUE_WARPS); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPILOGUE_WARPS * CTAS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_map(&p.map_a);
         prefetch_map(&p.map_b);
@@ -340,16 +401,32 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (p.segments == 2) prefetch_map(&p.map_a2);
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CTAS == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) {
+        // pair-tiles of the experts before e; an odd last 128-row tile takes a pair-tile of its own
+        for (int i = threadIdx.x; i <= p.experts; i += NUM_THREADS) {
+            int sum = 0;
+            for (int j = 0; j < i; ++j) sum += (s_start[j + 1] - s_start[j] + 1) >> 1;
+            s_pair[i] = sum;
+        }
+        __syncthreads();
+        cluster_sync();  // the partner's barriers exist before anything arrives on them
+    }
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
 
     int total_tiles;
     if (MODE == MODE_WGRAD) total_tiles = p.experts * p.m_tiles * p.n_tiles;
+    else if (CTAS == 2) total_tiles = s_pair[p.experts] * p.n_tiles;
     else total_tiles = (s_start[p.experts] - s_start[0]) * p.n_tiles;
     volatile int* abort_flag = &s_abort;
 
@@ -358,8 +435,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-                const Tile tile = decode_tile<MODE>(p, s_start, s_order, t);
+            for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
+                const Tile tile = decode_tile<MODE, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
                 if (!tile.valid) continue;
                 const int kb_per_seg = tile.kblocks / (MODE == MODE_WGRAD ? 1 : p.segments);
                 for (int kb = 0; kb < tile.kblocks; ++kb) {
@@ -368,29 +445,42 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         break;
                     }
                     const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
-                    const uint32_t bar = full_bar(stage);
-                    mbar_expect_tx(bar, STAGE_BYTES);
+                    // CTAS == 2: both CTAs' bytes are expected (and counted) on the first CTA's barrier
+                    const uint32_t bar = CTAS == 2 ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
+                    if (CTAS == 1) mbar_expect_tx(bar, STAGE_BYTES);
+                    else if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+                    auto load = [&](const CUtensorMap* map, uint32_t dst, int c0, int c1) {
+                        if (CTAS == 2) tma_load_2d_pair(map, dst, bar, c0, c1);
+                        else tma_load_2d(map, dst, bar, c0, c1);
+                    };
+                    constexpr int BN_MINE = BN / CTAS;       // columns of the B tile this CTA stages
+                    const int n_mine = tile.n0 + cta_rank * BN_MINE;
                     if (MODE == MODE_WGRAD) {
                         const int krow = tile.krow0 + kb * BK;
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(&p.map_a, sa + j * CHUNK_BYTES, bar, tile.row0 + 64 * j, krow);
+                        for (int j = 0; j < BM / 64; ++j) load(&p.map_a, sa + j * CHUNK_BYTES, tile.row0 + 64 * j, krow);
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(&p.map_b, sb + j * CHUNK_BYTES, bar, tile.n0 + 64 * j, krow);
+                        for (int j = 0; j < BN_MINE / 64; ++j) load(&p.map_b, sb + j * CHUNK_BYTES, n_mine + 64 * j, krow);
                     } else {
                         const int seg = kb / kb_per_seg;
                         const int k0 = (kb - seg * kb_per_seg) * BK;
                         const CUtensorMap* ma = seg ? &p.map_a2 : &p.map_a;
                         const CUtensorMap* mb = seg ? &p.map_b2 : &p.map_b;
-                        tma_load_2d(ma, sa, bar, k0, tile.row0);  // A is K-major in these modes
+                        load(ma, sa, k0, tile.row0);  // A is K-major in these modes
                         if (MODE == MODE_SWIGLU) {
-                            tma_load_2d(&p.map_b, sb, bar, k0, tile.expert * p.b_rows + tile.n0);
-                            tma_load_2d(&p.map_b2, sb + B_STAGE_BYTES / 2, bar, k0, tile.expert * p.b_rows + tile.n0);
+                            // accumulator columns [0, 128) = gate, [128, 256) = up; a pair splits them between its CTAs
+                            if (CTAS == 2) {
+                                load(cta_rank ? &p.map_b2 : &p.map_b, sb, k0, tile.expert * p.b_rows + tile.n0);
+                            } else {
+                                load(&p.map_b, sb, k0, tile.expert * p.b_rows + tile.n0);
+                                load(&p.map_b2, sb + B_STAGE_BYTES / 2, k0, tile.expert * p.b_rows + tile.n0);
+                            }
                         } else if (B_MN) {
 #pragma unroll
-                            for (int j = 0; j < BN / 64; ++j)
-                                tma_load_2d(mb, sb + j * CHUNK_BYTES, bar, tile.n0 + 64 * j, tile.expert * p.b_rows + k0);
+                            for (int j = 0; j < BN_MINE / 64; ++j)
+                                load(mb, sb + j * CHUNK_BYTES, n_mine + 64 * j, tile.expert * p.b_rows + k0);
                         } else {
-                            tma_load_2d(mb, sb, bar, k0, tile.expert * p.b_rows + tile.n0);
+                            load(mb, sb, k0, tile.expert * p.b_rows + n_mine);
                         }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -399,13 +489,18 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc<A_MN, B_MN>();
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = make_idesc<A_MN, B_MN, BM * CTAS>();
             int stage = 0;
             uint32_t phase = 0;
             int iter = 0;
-            for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-                const Tile tile = decode_tile<MODE>(p, s_start, s_order, t);
+            // one commit per CTA whose barrier has to hear about it
+            auto commit = [&](uint32_t bar) {
+                if (CTAS == 2) { umma_commit_pair(bar); umma_commit_pair(map_to_cta(bar, 1)); }
+                else umma_commit(bar);
+            };
+            for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
+                const Tile tile = decode_tile<MODE, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
                 if (!tile.valid) continue;
                 const int acc = iter & 1;
                 const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
@@ -425,16 +520,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                                     : make_desc(sa + kk * 32, 16, 1024);
                         const uint64_t bdesc = B_MN ? make_desc(sb + kk * 2048, CHUNK_BYTES, 1024)
                                                     : make_desc(sb + kk * 32, 16, 1024);
-                        umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | kk) ? 1u : 0u);
+                        if (CTAS == 2) umma_bf16_pair(tmem_d, adesc, bdesc, idesc, (kb | kk) ? 1u : 0u);
+                        else umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | kk) ? 1u : 0u);
                     }
-                    umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+                    commit(empty_bar(stage));  // the stage is free once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) {
                     if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_MMA); }
                     break;
                 }
-                umma_commit(tfull_bar(acc));
+                commit(tfull_bar(acc));
                 ++iter;
             }
         }
@@ -444,8 +540,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t stage = bars + 256u + (uint32_t)(warp - 2) * EPI_STAGE_BYTES;  // this warp's transpose buffer
         const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp converts
         int iter = 0;
-        for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-            const Tile tile = decode_tile<MODE>(p, s_start, s_order, t);
+        for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
+            const Tile tile = decode_tile<MODE, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
             if (!tile.valid) continue;
             const int acc = iter & 1;
             const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
@@ -460,7 +556,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // 32-row x 32-column bf16 block as 8 rows x 64 contiguous bytes per instruction, transposing
             // between "one thread = one row" (the TMEM read layout) and that shape through shared memory.
             const long long row0w = (long long)tile.row0 + quad * 32;
-            if (MODE == MODE_SWIGLU) {
+            if (CTAS == 2 && !tile.rows_valid) {
+                // second half of an odd pair-tile: these rows belong to nobody, nothing is stored
+            } else if (MODE == MODE_SWIGLU) {
                 __nv_bfloat16* G = (__nv_bfloat16*)p.out0 + row0w * p.ldc + tile.n0;
                 __nv_bfloat16* U = (__nv_bfloat16*)p.out1 + row0w * p.ldc + tile.n0;
                 __nv_bfloat16* H = (__nv_bfloat16*)p.out2 + row0w * p.ldc + tile.n0;
@@ -629,7 +727,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (lane == 0) {
+                if (CTAS == 2 && cta_rank) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+                else mbar_arrive(tempty_bar(acc));
+            }
             ++iter;
         }
     }
@@ -643,9 +744,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         while (global_ns() - start < 2000000ull) __nanosleep(1000);
         __syncthreads();
     }
+    // neither CTA of a pair may leave (or free tensor memory) while the other can still signal or read it
+    if (CTAS == 2) cluster_sync();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -702,20 +806,53 @@ int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uin
     return 0;
 }
 
-template <int MODE, bool A_MN, bool B_MN>
+template <int MODE, bool A_MN, bool B_MN, int CTAS = 1>
 int launch(const GemmParams& p, cudaStream_t stream) {
-    static bool configured[64] = {false};
+    static int grid_of[64] = {0};  // per device: blocks to launch (0: not configured yet)
+    constexpr int SMEM_BYTES = Cfg<CTAS>::SMEM_BYTES;
     int dev = 0;
     QMOE_CUDA(cudaGetDevice(&dev));
-    auto kernel = grouped_gemm_kernel<MODE, A_MN, B_MN>;
-    if (dev < 64 && !configured[dev]) {
-        QMOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured[dev] = true;
+    if (dev >= 64) return fail_arg("device ordinal beyond 63");
+    auto kernel = grouped_gemm_kernel<MODE, A_MN, B_MN, CTAS>;
+    cudaLaunchConfig_t config = {};
+    cudaLaunchAttribute attribute[1];
+    config.blockDim = dim3(NUM_THREADS);
+    config.dynamicSmemBytes = SMEM_BYTES;
+    config.stream = stream;
+    if (CTAS == 2) {
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = 2;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
     }
-    kernel<<<sm_count(), NUM_THREADS, SMEM_BYTES, stream>>>(p);
+    if (!grid_of[dev]) {
+        QMOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        int grid = sm_count();
+        if (CTAS == 2) {
+            // a persistent grid: launch exactly as many pairs as can be resident together (a GPC with an
+            // odd number of usable SMs leaves one without a partner)
+            int clusters = 0;
+            config.gridDim = dim3((unsigned)(grid & ~1));
+            QMOE_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &config));
+            if (clusters < 1) { set_error("no CTA pair of the tensor-core GEMM fits on this device"); return QMOE_ERR_STATE; }
+            grid = 2 * (clusters < grid / 2 ? clusters : grid / 2);
+        }
+        grid_of[dev] = grid;
+    }
+    config.gridDim = dim3((unsigned)grid_of[dev]);
+    QMOE_CUDA(cudaLaunchKernelEx(&config, kernel, p));
     count_tensor_core_launch();
     QMOE_LAUNCH_CHECK("grouped_gemm_kernel");
     return 0;
+}
+
+// CTAs per output tile of the expert GEMMs: 2 (a CTA pair per 256 x 256 tile) unless the environment
+// variable QUTAI_MOE_GEMM_CTAS is "1" (one CTA per 128 x 256 tile).  Read on every call so a process can switch.
+int gemm_ctas() {
+    const char* text = getenv("QUTAI_MOE_GEMM_CTAS");
+    return (text && text[0] == '1') ? 1 : 2;
 }
 
 }  // namespace
@@ -735,6 +872,7 @@ int tc_swiglu_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t 
     p.out0 = (void*)g; p.out1 = (void*)u; p.out2 = (void*)h;
     p.ldc = (long long)hd; p.experts = ex->experts; p.n_tiles = ceil_div((long long)hd, 128);
     p.N = (int)hd; p.K = (int)d; p.b_rows = (int)hd; p.segments = 1;
+    if (gemm_ctas() == 2) return launch<MODE_SWIGLU, false, false, 2>(p, stream);
     return launch<MODE_SWIGLU, false, false>(p, stream);
 }
 
@@ -750,11 +888,13 @@ int tc_rows_nt(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint6
     GemmParams p = {};
     set_scatter(p, scatter);
     if (int rc = make_map(&p.map_a, a, (uint64_t)K, (uint64_t)r->rows_bound, BM)) return rc;
-    if (int rc = make_map(&p.map_b, b, (uint64_t)K, (uint64_t)experts * N, BN)) return rc;
+    const int ctas = gemm_ctas();
+    if (int rc = make_map(&p.map_b, b, (uint64_t)K, (uint64_t)experts * N, BN / ctas)) return rc;
     p.map_a2 = p.map_a; p.map_b2 = p.map_b;
     p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
     p.out0 = (void*)c; p.ldc = N; p.experts = experts; p.n_tiles = ceil_div(N, BN);
     p.N = (int)N; p.K = (int)K; p.b_rows = (int)N; p.segments = 1;
+    if (ctas == 2) return launch<MODE_PLAIN, false, false, 2>(p, stream);
     return launch<MODE_PLAIN, false, false>(p, stream);
 }
 
@@ -775,6 +915,7 @@ int tc_rows_nn(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint6
     p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
     p.out0 = (void*)c; p.ldc = N; p.experts = experts; p.n_tiles = ceil_div(N, BN);
     p.N = (int)N; p.K = (int)K; p.b_rows = (int)K;
+    if (gemm_ctas() == 2) return launch<MODE_PLAIN, false, true, 2>(p, stream);
     return launch<MODE_PLAIN, false, true>(p, stream);
 }
 
@@ -790,6 +931,7 @@ int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down,
     p.out0 = (void*)dg; p.out1 = (void*)du; p.in0 = (const void*)g; p.in1 = (const void*)u;
     p.ldc = h; p.experts = experts; p.n_tiles = ceil_div(h, BN);
     p.N = (int)h; p.K = (int)d; p.b_rows = (int)d; p.segments = 1;
+    if (gemm_ctas() == 2) return launch<MODE_DSWIGLU, false, true, 2>(p, stream);
     return launch<MODE_DSWIGLU, false, true>(p, stream);
 }
 
@@ -843,8 +985,10 @@ int tc_wgrad(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_
     if (c & 15u || (N * 4) % 16) return fail_arg("weight-gradient output must be 16-byte aligned with a 16-byte row pitch");
     p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
     p.out0 = (void*)c; p.ldc = N; p.c_slab = M * N; p.experts = experts;
-    p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, BN);
+    const int ctas = gemm_ctas();
+    p.m_tiles = ceil_div(M, BM * ctas); p.n_tiles = ceil_div(N, BN);
     p.M = (int)M; p.N = (int)N; p.K = 0; p.segments = 1;
+    if (ctas == 2) return launch<MODE_WGRAD, true, true, 2>(p, stream);
     return launch<MODE_WGRAD, true, true>(p, stream);
 }
 

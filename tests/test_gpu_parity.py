@@ -208,14 +208,21 @@ LAYER_SHAPES = [
     (1000, 256, 8, 2, 512),   # several tiles, several k blocks
     (777, 128, 16, 4, 264),   # ragged counts, partial N tile
     (2048, 512, 8, 2, 1408),  # half-filled last N tile (1408 = 5.5 x 256)
+    (900, 384, 3, 1, 640),    # odd numbers of 128-row tiles per expert, d and h = 1.5 and 2.5 x 256
 ]
 
 
-@pytest.mark.parametrize("engine", ["simt", "tcgen05"])
+@pytest.mark.parametrize("engine", ["simt", "tcgen05", "tcgen05-1cta"])
 @pytest.mark.parametrize("T,d,E,k,h", LAYER_SHAPES)
-def test_layer_bf16_matches_oracle(T, d, E, k, h, engine):
+def test_layer_bf16_matches_oracle(T, d, E, k, h, engine, monkeypatch):
     from gpu_util import make_layer, run_layer
 
+    # "tcgen05" runs the expert GEMMs as CTA pairs (256-row tiles), "tcgen05-1cta" one CTA per 128-row tile
+    if engine == "tcgen05-1cta":
+        monkeypatch.setenv("QUTAI_MOE_GEMM_CTAS", "1")
+        engine = "tcgen05"
+    else:
+        monkeypatch.delenv("QUTAI_MOE_GEMM_CTAS", raising=False)
     rng = np.random.default_rng(T + d + E)
     r16 = oracle.round_bf16
     x, grad_y = r16(rng.standard_normal((T, d))), r16(rng.standard_normal((T, d)))
