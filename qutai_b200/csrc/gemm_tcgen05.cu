@@ -79,6 +79,7 @@ struct alignas(64) GemmParams {
     const int* scatter_ret;              // [rows] return addresses, or null for a plain store
     unsigned long long scatter_base[16]; // every rank's destination buffer (own entry: local address)
     int plain_rows;       // > 0: one group of this many rows instead of the expert groups of `offsets`
+    int transpose_out;    // WGRAD: store the [M, N] product of each expert as [N, M] (ldc = M)
     int group_stride;     // ROUTER: accumulator columns [0,S), [S,2S), [2S,3S) hold the three bf16 terms of the weights
 };
 
@@ -191,20 +192,21 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes,
 }
 // Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M = 128, N = 256.
 template <bool A_MN, bool B_MN, int M>
-__device__ __forceinline__ constexpr uint32_t make_idesc() {
+__device__ __forceinline__ constexpr uint32_t make_idesc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 struct Tile {
     int expert, row0, n0, kblocks, krow0;
+    int bn;           // accumulator columns of this tile: 256, or 128 for a last tile that is at most half full (B in MN-major only)
     bool valid;       // false: nothing to do for the whole tile (all CTAs of the tile skip it)
     bool rows_valid;  // CTAS == 2: false when this CTA's 128 rows lie past the end of the expert (compute, do not store)
 };
 
 // s_start[e]: first 128-row tile of expert e.  s_pair[e] (CTAS == 2): first 256-row pair-tile of expert e, an
 // expert with an odd number of 128-row tiles gets a last pair-tile whose second half is not stored.
-template <int MODE, int CTAS>
+template <int MODE, bool B_MN, int CTAS>
 __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_start, const int* s_pair, const int* s_order,
                                             int t, int cta_rank) {
     Tile tile;
@@ -242,6 +244,8 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_st
         tile.kblocks = ((p.K + BK - 1) / BK) * p.segments;
         tile.krow0 = 0;
     }
+    // MN-major B arrives in 64-column boxes, so a narrow last tile simply loads and multiplies half of them
+    tile.bn = (B_MN && MODE != MODE_SWIGLU && p.N - tile.n0 <= BN / 2) ? BN / 2 : BN;
     return tile;
 }
 
@@ -436,7 +440,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             int stage = 0;
             uint32_t phase = 0;
             for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
-                const Tile tile = decode_tile<MODE, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
+                const Tile tile = decode_tile<MODE, B_MN, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
                 if (!tile.valid) continue;
                 const int kb_per_seg = tile.kblocks / (MODE == MODE_WGRAD ? 1 : p.segments);
                 for (int kb = 0; kb < tile.kblocks; ++kb) {
@@ -447,20 +451,22 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
                     // CTAS == 2: both CTAs' bytes are expected (and counted) on the first CTA's barrier
                     const uint32_t bar = CTAS == 2 ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
-                    if (CTAS == 1) mbar_expect_tx(bar, STAGE_BYTES);
-                    else if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+                    const int bn_mine = tile.bn / CTAS;      // columns of the B tile this CTA stages
+                    const uint32_t stage_bytes = A_STAGE_BYTES + (uint32_t)bn_mine * BK * 2;
+                    if (CTAS == 1) mbar_expect_tx(bar, stage_bytes);
+                    else if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * stage_bytes);
                     auto load = [&](const CUtensorMap* map, uint32_t dst, int c0, int c1) {
                         if (CTAS == 2) tma_load_2d_pair(map, dst, bar, c0, c1);
                         else tma_load_2d(map, dst, bar, c0, c1);
                     };
-                    constexpr int BN_MINE = BN / CTAS;       // columns of the B tile this CTA stages
-                    const int n_mine = tile.n0 + cta_rank * BN_MINE;
+                    const int n_mine = tile.n0 + cta_rank * bn_mine;
                     if (MODE == MODE_WGRAD) {
                         const int krow = tile.krow0 + kb * BK;
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j) load(&p.map_a, sa + j * CHUNK_BYTES, tile.row0 + 64 * j, krow);
 #pragma unroll
-                        for (int j = 0; j < BN_MINE / 64; ++j) load(&p.map_b, sb + j * CHUNK_BYTES, n_mine + 64 * j, krow);
+                        for (int j = 0; j < BN / CTAS / 64; ++j)
+                            if (64 * j < bn_mine) load(&p.map_b, sb + j * CHUNK_BYTES, n_mine + 64 * j, krow);
                     } else {
                         const int seg = kb / kb_per_seg;
                         const int k0 = (kb - seg * kb_per_seg) * BK;
@@ -477,8 +483,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                             }
                         } else if (B_MN) {
 #pragma unroll
-                            for (int j = 0; j < BN_MINE / 64; ++j)
-                                load(mb, sb + j * CHUNK_BYTES, n_mine + 64 * j, tile.expert * p.b_rows + k0);
+                            for (int j = 0; j < BN / CTAS / 64; ++j)
+                                if (64 * j < bn_mine) load(mb, sb + j * CHUNK_BYTES, n_mine + 64 * j, tile.expert * p.b_rows + k0);
                         } else {
                             load(mb, sb, k0, tile.expert * p.b_rows + n_mine);
                         }
@@ -490,7 +496,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc = make_idesc<A_MN, B_MN, BM * CTAS>();
             int stage = 0;
             uint32_t phase = 0;
             int iter = 0;
@@ -500,13 +505,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 else umma_commit(bar);
             };
             for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
-                const Tile tile = decode_tile<MODE, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
+                const Tile tile = decode_tile<MODE, B_MN, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
                 if (!tile.valid) continue;
                 const int acc = iter & 1;
                 const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
                 bool ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
+                const uint32_t idesc = make_idesc<A_MN, B_MN, BM * CTAS>(tile.bn);
                 for (int kb = 0; ok && kb < tile.kblocks; ++kb) {
                     ok = mbar_wait(full_bar(stage), phase, abort_flag);
                     if (!ok) break;
@@ -541,7 +547,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp converts
         int iter = 0;
         for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
-            const Tile tile = decode_tile<MODE, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
+            const Tile tile = decode_tile<MODE, B_MN, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
             if (!tile.valid) continue;
             const int acc = iter & 1;
             const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
@@ -556,6 +562,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // 32-row x 32-column bf16 block as 8 rows x 64 contiguous bytes per instruction, transposing
             // between "one thread = one row" (the TMEM read layout) and that shape through shared memory.
             const long long row0w = (long long)tile.row0 + quad * 32;
+            // 32-column chunks of this warp: its half of the tile's columns (4 of 8, or 2 of 4 in a narrow tile)
+            const int c_begin = half * (tile.bn / 64), c_end = c_begin + tile.bn / 64;
             if (CTAS == 2 && !tile.rows_valid) {
                 // second half of an odd pair-tile: these rows belong to nobody, nothing is stored
             } else if (MODE == MODE_SWIGLU) {
@@ -603,19 +611,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 __nv_bfloat16* dU = (__nv_bfloat16*)p.out1 + row0w * p.ldc + tile.n0;
                 // coalesced loads of the saved activations run one 32-column chunk ahead of their use
                 uint4 lg[4], lu[4];
-                if (p.N - (tile.n0 + 4 * half * 32) >= 32) {
+                if (p.N - (tile.n0 + c_begin * 32) >= 32) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + 4 * half * 32 + (lane & 3) * 8;
+                        const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + c_begin * 32 + (lane & 3) * 8;
                         lg[j] = *reinterpret_cast<const uint4*>(G + at);
                         lu[j] = *reinterpret_cast<const uint4*>(U + at);
                     }
                 }
 #pragma unroll 1
-                for (int c = 4 * half; c < 4 * half + 4; ++c) {
+                for (int c = c_begin; c < c_end; ++c) {
                     const int valid = p.N - (tile.n0 + c * 32);
                     uint4 ng[4], nu[4];
-                    if (c + 1 < 4 * half + 4 && valid - 32 >= 32) {
+                    if (c + 1 < c_end && valid - 32 >= 32) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + (c + 1) * 32 + (lane & 3) * 8;
@@ -666,7 +674,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     }
                 }
 #pragma unroll 1
-                for (int c = 4 * half; c < 4 * half + 4; ++c) {
+                for (int c = c_begin; c < c_end; ++c) {
                     uint32_t r[32];
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
@@ -705,11 +713,28 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                 C[c * 32 + i] = (__uint_as_float(r2[i]) + __uint_as_float(r1[i])) + __uint_as_float(r0[i]);
                     }
                 }
+            } else if (MODE == MODE_WGRAD && p.transpose_out) {
+                // the product is stored transposed, out[e][n][m]: the 32 lanes of a warp hold consecutive m,
+                // so each store instruction writes one 128-byte line
+                float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + (long long)tile.n0 * p.ldc + row;
+                const bool row_ok = row < p.M;
+#pragma unroll 1
+                for (int c = c_begin; c < c_end; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    const int valid = p.N - (tile.n0 + c * 32);
+                    if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) C[(long long)(c * 32 + i) * p.ldc] = __uint_as_float(r[i]);
+                    }
+                }
             } else {
                 float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
                 const bool row_ok = row < p.M;  // WGRAD: rows of one expert's output; PLAIN_F32: rows of the single group
 #pragma unroll 1
-                for (int c = 4 * half; c < 4 * half + 4; ++c) {
+                for (int c = c_begin; c < c_end; ++c) {
                     uint32_t r[32];
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
@@ -975,19 +1000,24 @@ int tc_split_wgrad(uint64_t a, long long a_pitch, uint64_t b, uint64_t partial, 
     return launch<MODE_WGRAD, true, true>(p, stream);
 }
 
-// C_e [M, N] (fp32) = A_e^T . B_e, A [rows, M], B [rows, N], contraction over the rows of expert e
+// C_e [M, N] (fp32) = A_e^T . B_e, A [rows, M], B [rows, N], contraction over the rows of expert e.
+// Tiles are 128 * ctas rows x 256 (or a last 128) columns, so when M is the dimension that leaves a partly
+// empty last tile, the kernel computes B_e^T . A_e instead and stores it transposed.
 int tc_wgrad(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long M, long long N,
              cudaStream_t stream) {
     GemmParams p = {};
-    if (int rc = make_map(&p.map_a, a, (uint64_t)M, (uint64_t)r->rows_bound, 64)) return rc;
-    if (int rc = make_map(&p.map_b, b, (uint64_t)N, (uint64_t)r->rows_bound, 64)) return rc;
-    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
     if (c & 15u || (N * 4) % 16) return fail_arg("weight-gradient output must be 16-byte aligned with a 16-byte row pitch");
-    p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
-    p.out0 = (void*)c; p.ldc = N; p.c_slab = M * N; p.experts = experts;
     const int ctas = gemm_ctas();
-    p.m_tiles = ceil_div(M, BM * ctas); p.n_tiles = ceil_div(N, BN);
-    p.M = (int)M; p.N = (int)N; p.K = 0; p.segments = 1;
+    auto padded = [&](long long m, long long n) { return ceil_div(m, BM * ctas) * (BM * ctas) * ceil_div(n, BN / 2) * (BN / 2); };
+    const bool swap = padded(N, M) < padded(M, N);
+    const long long m = swap ? N : M, n = swap ? M : N;  // the kernel's own M (tile rows) and N (tile columns)
+    if (int rc = make_map(&p.map_a, swap ? b : a, (uint64_t)m, (uint64_t)r->rows_bound, 64)) return rc;
+    if (int rc = make_map(&p.map_b, swap ? a : b, (uint64_t)n, (uint64_t)r->rows_bound, 64)) return rc;
+    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
+    p.out0 = (void*)c; p.ldc = N; p.c_slab = M * N; p.experts = experts; p.transpose_out = swap ? 1 : 0;
+    p.m_tiles = ceil_div(m, BM * ctas); p.n_tiles = ceil_div(n, BN);
+    p.M = (int)m; p.N = (int)n; p.K = 0; p.segments = 1;
     if (ctas == 2) return launch<MODE_WGRAD, true, true, 2>(p, stream);
     return launch<MODE_WGRAD, true, true>(p, stream);
 }
