@@ -78,6 +78,7 @@ struct alignas(64) GemmParams {
     // recorded for it (return address = rank << 26 | row), i.e. straight into that GPU's buffer
     const int* scatter_ret;              // [rows] return addresses, or null for a plain store
     unsigned long long scatter_base[16]; // every rank's destination buffer (own entry: local address)
+    int scatter_wide;     // scatter in 256-byte row pieces (0: 64-byte pieces)
     int plain_rows;       // > 0: one group of this many rows instead of the expert groups of `offsets`
     int transpose_out;    // WGRAD: store the [M, N] product of each expert as [N, M] (ldc = M)
     int group_stride;     // ROUTER: accumulator columns [0,S), [S,2S), [2S,3S) hold the three bf16 terms of the weights
@@ -327,6 +328,36 @@ __device__ __forceinline__ void scatter_block32(uint32_t stage, int lane, const 
         if (base) *reinterpret_cast<uint4*>((__nv_bfloat16*)base + piece * 8) = v;
     }
     __syncwarp();
+}
+
+// Scatter of 128 columns: thread `lane` holds 128 consecutive bf16 (64 packed words) of row `lane`, every row
+// has its own destination (`dst_row`, null = skip).  Rows that live on another GPU cross NVLink, where a
+// store of 64 contiguous bytes per row costs about twice the time per byte of a long one, so the block goes
+// through the staging buffer 8 rows at a time and every store instruction covers 2 rows x 256 contiguous bytes.
+__device__ __forceinline__ void scatter_rows256(uint32_t stage, int lane, const uint32_t* w, __nv_bfloat16* dst_row) {
+    constexpr int PITCH = 272;  // 8 rows x 272 B fit the 32 x 80 B buffer; 68 words per row keep the v4 accesses conflict-free
+    const unsigned long long mine_ptr = (unsigned long long)dst_row;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        if ((lane >> 3) == pass) {
+            const uint32_t mine = stage + (lane & 7) * PITCH;
+#pragma unroll
+            for (int q = 0; q < 16; ++q)
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16 * q), "r"(w[4 * q]), "r"(w[4 * q + 1]),
+                             "r"(w[4 * q + 2]), "r"(w[4 * q + 3]) : "memory");
+        }
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int row = it * 2 + (lane >> 4), piece = lane & 15;
+            const unsigned long long base = __shfl_sync(0xffffffffu, mine_ptr, pass * 8 + row);
+            uint4 v;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(stage + row * PITCH + 16 * piece) : "memory");
+            if (base) *reinterpret_cast<uint4*>((__nv_bfloat16*)base + piece * 8) = v;
+        }
+        __syncwarp();
+    }
 }
 
 // The inverse: `v[j]` was loaded by this lane from row j * 8 + lane / 4, piece lane % 4 (the coalesced
@@ -673,8 +704,22 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         remote = (__nv_bfloat16*)p.scatter_base[address >> 26] + (long long)(address & ((1 << 26) - 1)) * p.ldc + tile.n0;
                     }
                 }
+                const bool wide = p.scatter_ret && p.scatter_wide && c_end - c_begin == 4 && p.N - (tile.n0 + c_begin * 32) >= 128;
+                if (wide) {  // this warp's 128 columns are all there: scatter them as 256-byte row pieces
+                    uint32_t w[64];
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + (c_begin + cc) * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            w[cc * 16 + j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    }
+                    scatter_rows256(stage, lane, w, remote ? remote + c_begin * 32 : nullptr);
+                }
 #pragma unroll 1
-                for (int c = c_begin; c < c_end; ++c) {
+                for (int c = wide ? c_end : c_begin; c < c_end; ++c) {
                     uint32_t r[32];
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
@@ -693,7 +738,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         else if (remote) store_row32_bf16(remote + c * 32, v, valid);
                     }
                 }
-                if (p.scatter_ret) __threadfence_system();
             } else if (MODE == MODE_ROUTER) {
                 // scores = x . (W_hi + W_mid + W_lo)^T: the three partial products sit S columns apart
                 float* C = (float*)p.out0 + row * p.ldc;
@@ -758,6 +802,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
             ++iter;
         }
+        // rows stored into other GPUs' memory: one system-scope fence per thread after its last tile (the
+        // kernel's completion orders them before whatever the stream signals next; a fence per tile only
+        // made the accumulator wait for an NVLink round trip)
+        if (MODE == MODE_PLAIN && p.scatter_ret) __threadfence_system();
     }
 
     // ------------------------------ teardown ---------------------------------------
@@ -905,6 +953,8 @@ int tc_swiglu_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t 
 void set_scatter(GemmParams& p, const TcScatter* scatter) {
     if (!scatter) return;
     p.scatter_ret = scatter->ret;
+    const char* pieces = getenv("QUTAI_MOE_SCATTER_BYTES");  // "64": the narrow store pattern, for comparison
+    p.scatter_wide = !(pieces && pieces[0] == '6');
     for (int i = 0; i < 16; ++i) p.scatter_base[i] = scatter->base[i];
 }
 

@@ -215,7 +215,7 @@ class ExpertParallelMoE:
                                   Tensor(views[2], (d, h), requires_grad=True)))
         self.experts = tuple(experts)
         self.utilization = None
-        self._side = None   # (stream, event, event) used to overlap pushes with compute
+        self._side = None   # second stream and its events: work that nothing on the main stream waits for soon
         self.refresh_operands = True  # False: keep the bf16 weight copies of the first forward (fixed weights, serving)
         self._sequence = 0  # barriers issued so far (the flag barrier's growing sequence number)
         self._work = None
@@ -296,11 +296,13 @@ class ExpertParallelMoE:
             # barriers and the count all-gather go through flags in peer memory unless NCCL is asked for
             self._work["flag_barrier"] = os.environ.get("QUTAI_MOE_EP_BARRIER", "flags") != "nccl"
             if self._side is None:
-                side, first, second = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+                side = ctypes.c_uint64()
                 lib.call("qmoe_stream_create", ctypes.byref(side))
-                lib.call("qmoe_event_create", ctypes.byref(first))
-                lib.call("qmoe_event_create", ctypes.byref(second))
-                self._side = (side.value, first.value, second.value)
+                self._side = {"stream": side.value}
+                for name in ("ready", "done", "stats", "grads", "reduced"):
+                    event = ctypes.c_uint64()
+                    lib.call("qmoe_event_create", ctypes.byref(event))
+                    self._side[name] = event.value
         return self._work
 
     def _open_peers(self, buf):
@@ -390,11 +392,17 @@ class ExpertParallelMoE:
                 lib.call("qmoe_ep_pack_stats", tr, buf["stats_local"].ptr, s)
                 lib.call("qmoe_ep_flag_barrier", ctypes.byref(w["peers"]["flags"]), self._sequence, buf["stats_local"].ptr,
                          2 * E, ctypes.byref(w["peers"]["stats_all"]), s)
-                lib.call("qmoe_memcpy_d2h", ctypes.cast(w["host_stats"], ctypes.c_void_p), buf["stats_all"].ptr, 4 * N * 2 * E, s)
+                # the host's copy of the counts is only read when gradients are handed out: it leaves on the side stream
+                side = self._side
+                lib.call("qmoe_event_record", side["stats"], s)
+                lib.call("qmoe_stream_wait_event", side["stream"], side["stats"])
+                lib.call("qmoe_memcpy_d2h", ctypes.cast(w["host_stats"], ctypes.c_void_p), buf["stats_all"].ptr, 4 * N * 2 * E,
+                         side["stream"])
+                lib.call("qmoe_event_record", w["stats_event"], side["stream"])
             else:
                 lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
                          ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
-            lib.call("qmoe_event_record", w["stats_event"], s)
+                lib.call("qmoe_event_record", w["stats_event"], s)
             lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
             lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
 
@@ -402,7 +410,7 @@ class ExpertParallelMoE:
         acts = (buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr)
         if self.transport == "p2p":
             peers = w["peers"]
-            side, ready, done = self._side
+            side, ready, done = self._side["stream"], self._side["ready"], self._side["done"]
             # the bf16 weight copies are refreshed on the side stream while this stream routes and dispatches
             lib.call("qmoe_event_record", ready, s)
             lib.call("qmoe_stream_wait_event", side, ready)
@@ -473,7 +481,16 @@ class ExpertParallelMoE:
             lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
             lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
                      buf["dx_router"].ptr, buf["d_w_router"].ptr, buf["router_partials"].ptr, tokens, d, E, s)
-            lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, s)
+            if w.get("flag_barrier"):
+                # no other NCCL call in the step: the all-reduce runs on the side stream, beside the last barrier
+                # and the un-permute, and is waited for where the router gradient is handed out
+                side = self._side
+                lib.call("qmoe_event_record", side["grads"], s)
+                lib.call("qmoe_stream_wait_event", side["stream"], side["grads"])
+                lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, side["stream"])
+                lib.call("qmoe_event_record", side["reduced"], side["stream"])
+            else:
+                lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, s)
 
         if self.transport == "p2p" and w["fused"]:
             peers = w["peers"]
@@ -485,6 +502,8 @@ class ExpertParallelMoE:
             lib.call("qmoe_ep_expert_dx_push", xr, ex, buf["d_g"].ptr, buf["d_u"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["dy_send"]), s)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 2, s)
             router_backward()
+            if w.get("flag_barrier"):  # peers overwrite the gathered counts after this barrier: the host's copy has left by then
+                lib.call("qmoe_stream_wait_event", s, w["stats_event"])
             self._barrier(w)
         elif self.transport == "p2p":
             peers = w["peers"]
@@ -494,6 +513,8 @@ class ExpertParallelMoE:
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 3, s)
             lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dx_recv"].ptr, ctypes.byref(peers["dy_send"]), 0, L, 0, code, d, s)
             router_backward()
+            if w.get("flag_barrier"):
+                lib.call("qmoe_stream_wait_event", s, w["stats_event"])
             self._barrier(w)
         else:
             lib.call("qmoe_combine_backward", tr, g.ptr, buf["y_send"].ptr, buf["dy_send"].ptr, buf["d_gate_weights"].ptr, code, d, s)
@@ -508,6 +529,8 @@ class ExpertParallelMoE:
         # counts, read only now so that the device never waits for the host inside the step
         counts = self._host_counts(w)
         received = [sum(counts[p][self.rank * L + j] for p in range(N)) for j in range(L)]
+        if w.get("flag_barrier"):
+            lib.call("qmoe_stream_wait_event", s, self._side["reduced"])
         _accumulate(self.router.weight, views[0], s)
         for j, expert in enumerate(self.experts):
             if not received[j]:
