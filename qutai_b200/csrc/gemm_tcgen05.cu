@@ -330,6 +330,32 @@ __device__ __forceinline__ void scatter_block32(uint32_t stage, int lane, const 
     __syncwarp();
 }
 
+// Thread `lane` holds the 32 fp32 values r[0..31] of row `lane` (the TMEM read layout).  Redistribute the
+// 32 x 32 block to the coalesced layout: on return out[j][0..7] are the values of row j * 8 + lane / 4,
+// columns (lane % 4) * 8 .. + 8, i.e. exactly what one 16-byte bf16 access of that lane covers.  Two passes
+// of 16 columns each fit the 32 x 80 B staging buffer (pass s moves columns 8q + 4s .. + 4 of every row).
+__device__ __forceinline__ void spread_block32(uint32_t stage, int lane, const uint32_t* r, float (*out)[8]) {
+    const uint32_t mine = stage + lane * STAGE_PITCH;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16 * q), "r"(r[8 * q + 4 * s]),
+                         "r"(r[8 * q + 4 * s + 1]), "r"(r[8 * q + 4 * s + 2]), "r"(r[8 * q + 4 * s + 3]) : "memory");
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int row = j * 8 + (lane >> 2), piece = lane & 3;
+            uint32_t a, b, c, d;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+                         : "r"(stage + row * STAGE_PITCH + 16 * piece) : "memory");
+            out[j][4 * s] = __uint_as_float(a); out[j][4 * s + 1] = __uint_as_float(b);
+            out[j][4 * s + 2] = __uint_as_float(c); out[j][4 * s + 3] = __uint_as_float(d);
+        }
+        __syncwarp();
+    }
+}
+
 // Scatter of 128 columns: thread `lane` holds 128 consecutive bf16 (64 packed words) of row `lane`, every row
 // has its own destination (`dst_row`, null = skip).  Rows that live on another GPU cross NVLink, where a
 // store of 64 contiguous bytes per row costs about twice the time per byte of a long one, so the block goes
@@ -358,24 +384,6 @@ __device__ __forceinline__ void scatter_rows256(uint32_t stage, int lane, const 
         }
         __syncwarp();
     }
-}
-
-// The inverse: `v[j]` was loaded by this lane from row j * 8 + lane / 4, piece lane % 4 (the coalesced
-// pattern); return the 16 packed words of row `lane`.
-__device__ __forceinline__ void gather_block32(uint32_t stage, int lane, const uint4* v, uint32_t* w) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int row = j * 8 + (lane >> 2), piece = lane & 3;
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + row * STAGE_PITCH + 16 * piece), "r"(v[j].x),
-                     "r"(v[j].y), "r"(v[j].z), "r"(v[j].w) : "memory");
-    }
-    __syncwarp();
-    const uint32_t mine = stage + lane * STAGE_PITCH;
-#pragma unroll
-    for (int q = 0; q < 4; ++q)
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4 * q]), "=r"(w[4 * q + 1]), "=r"(w[4 * q + 2]),
-                     "=r"(w[4 * q + 3]) : "r"(mine + 16 * q) : "memory");
-    __syncwarp();
 }
 
 // CTAS == 2: two CTAs of a cluster (a CTA pair on neighbouring SMs) share one 256-row x 256-column tile.
@@ -666,20 +674,28 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
                     if (valid >= 32) {
-                        uint32_t gw[16], uw[16], og[16], ou[16];
-                        gather_block32(stage, lane, lg, gw);
-                        gather_block32(stage, lane, lu, uw);
+                        // one fp32 transpose of dH into the layout G and U were loaded in; the products are
+                        // formed and stored there (16-byte accesses, 8 rows x 64 contiguous bytes per instruction)
+                        float dh[4][8];
+                        spread_block32(stage, lane, r, dh);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
-                            const float u0 = bf16_lo(uw[j]), u1 = bf16_hi(uw[j]);
-                            const float s0 = fast_sigmoid(g0), s1 = fast_sigmoid(g1);
-                            const float h0 = __uint_as_float(r[2 * j]), h1 = __uint_as_float(r[2 * j + 1]);
-                            ou[j] = pack_bf16(h0 * g0 * s0, h1 * g1 * s1);
-                            og[j] = pack_bf16(h0 * u0 * s0 * (1.f + g0 * (1.f - s0)), h1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t gw[4] = {lg[j].x, lg[j].y, lg[j].z, lg[j].w};
+                            const uint32_t uw[4] = {lu[j].x, lu[j].y, lu[j].z, lu[j].w};
+                            uint32_t og[4], ou[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float g0 = bf16_lo(gw[i]), g1 = bf16_hi(gw[i]);
+                                const float u0 = bf16_lo(uw[i]), u1 = bf16_hi(uw[i]);
+                                const float s0 = fast_sigmoid(g0), s1 = fast_sigmoid(g1);
+                                const float h0 = dh[j][2 * i], h1 = dh[j][2 * i + 1];
+                                ou[i] = pack_bf16(h0 * g0 * s0, h1 * g1 * s1);
+                                og[i] = pack_bf16(h0 * u0 * s0 * (1.f + g0 * (1.f - s0)), h1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
+                            }
+                            const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + c * 32 + (lane & 3) * 8;
+                            *reinterpret_cast<uint4*>(dG + at) = make_uint4(og[0], og[1], og[2], og[3]);
+                            *reinterpret_cast<uint4*>(dU + at) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
                         }
-                        store_block32(stage, lane, og, dG + c * 32, p.ldc);
-                        store_block32(stage, lane, ou, dU + c * 32, p.ldc);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) { lg[j] = ng[j]; lu[j] = nu[j]; }
                     } else if (valid > 0) {

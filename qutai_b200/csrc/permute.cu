@@ -15,7 +15,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarpsPerBlock = kThreads / 32;
 
-__device__ __forceinline__ uint4 ld16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ void st16(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
 // streaming variants: data that is read or written once should not displace reusable lines in L2
 __device__ __forceinline__ uint4 ld16_stream(const void* p) {
