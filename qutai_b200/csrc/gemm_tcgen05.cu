@@ -58,6 +58,7 @@ enum { STATUS_WAIT_PRODUCER = 101, STATUS_WAIT_MMA = 102, STATUS_WAIT_EPILOGUE =
 
 struct alignas(64) GemmParams {
     CUtensorMap map_a, map_b, map_a2, map_b2;
+    CUtensorMap map_a3, map_b3;  // WGRAD with three problems in one launch: operands of problems 0, 1, 2 = (a, b), (a2, b2), (a3, b3)
     const int* offsets;   // [E + 1] first dispatched row of each expert
     const int* counts;    // [E]
     int* status;
@@ -80,7 +81,8 @@ struct alignas(64) GemmParams {
     unsigned long long scatter_base[16]; // every rank's destination buffer (own entry: local address)
     int scatter_wide;     // scatter in 256-byte row pieces (0: 64-byte pieces)
     int plain_rows;       // > 0: one group of this many rows instead of the expert groups of `offsets`
-    int transpose_out;    // WGRAD: store the [M, N] product of each expert as [N, M] (ldc = M)
+    int transpose_out;    // WGRAD: bit i set = problem i stores the [M, N] product of each expert as [N, M]
+    int problems;         // WGRAD: 1, or 3 products of the same shape (outputs out0, out1, out2) sharing the tile queue
     int group_stride;     // ROUTER: accumulator columns [0,S), [S,2S), [2S,3S) hold the three bf16 terms of the weights
 };
 
@@ -200,6 +202,7 @@ __device__ __forceinline__ constexpr uint32_t make_idesc(int n) {
 
 struct Tile {
     int expert, row0, n0, kblocks, krow0;
+    int problem;      // WGRAD: which of the launch's products this tile belongs to
     int bn;           // accumulator columns of this tile: 256, or 128 for a last tile that is at most half full (B in MN-major only)
     bool valid;       // false: nothing to do for the whole tile (all CTAs of the tile skip it)
     bool rows_valid;  // CTAS == 2: false when this CTA's 128 rows lie past the end of the expert (compute, do not store)
@@ -213,9 +216,15 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_st
     Tile tile;
     tile.valid = true;
     tile.rows_valid = true;
+    tile.problem = 0;
     if (MODE == MODE_WGRAD) {
-        const int per = p.m_tiles * p.n_tiles;  // m_tiles counts CTAS * 128-row groups of the output
-        const int slot = t / per, rem = t - slot * per;
+        // m_tiles counts CTAS * 128-row groups of the output.  Tiles of the launch's products alternate, so the
+        // operand two of them share (the layer input for dWg and dWu) is fetched by neighbouring CTAs together.
+        const int per = p.m_tiles * p.n_tiles * p.problems;
+        const int slot = t / per;
+        int rem = t - slot * per;
+        tile.problem = rem % p.problems;
+        rem /= p.problems;
         const int e = s_order[slot];
         tile.expert = e;
         tile.row0 = (rem % p.m_tiles) * (BM * CTAS) + cta_rank * BM;
@@ -468,7 +477,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t tmem_base = s_tmem_base;
 
     int total_tiles;
-    if (MODE == MODE_WGRAD) total_tiles = p.experts * p.m_tiles * p.n_tiles;
+    if (MODE == MODE_WGRAD) total_tiles = p.experts * p.m_tiles * p.n_tiles * p.problems;
     else if (CTAS == 2) total_tiles = s_pair[p.experts] * p.n_tiles;
     else total_tiles = (s_start[p.experts] - s_start[0]) * p.n_tiles;
     volatile int* abort_flag = &s_abort;
@@ -501,11 +510,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     const int n_mine = tile.n0 + cta_rank * bn_mine;
                     if (MODE == MODE_WGRAD) {
                         const int krow = tile.krow0 + kb * BK;
+                        const CUtensorMap* ma = tile.problem == 0 ? &p.map_a : tile.problem == 1 ? &p.map_a2 : &p.map_a3;
+                        const CUtensorMap* mb = tile.problem == 0 ? &p.map_b : tile.problem == 1 ? &p.map_b2 : &p.map_b3;
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) load(&p.map_a, sa + j * CHUNK_BYTES, tile.row0 + 64 * j, krow);
+                        for (int j = 0; j < BM / 64; ++j) load(ma, sa + j * CHUNK_BYTES, tile.row0 + 64 * j, krow);
 #pragma unroll
                         for (int j = 0; j < BN / CTAS / 64; ++j)
-                            if (64 * j < bn_mine) load(&p.map_b, sb + j * CHUNK_BYTES, n_mine + 64 * j, krow);
+                            if (64 * j < bn_mine) load(mb, sb + j * CHUNK_BYTES, n_mine + 64 * j, krow);
                     } else {
                         const int seg = kb / kb_per_seg;
                         const int k0 = (kb - seg * kb_per_seg) * BK;
@@ -773,10 +784,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                 C[c * 32 + i] = (__uint_as_float(r2[i]) + __uint_as_float(r1[i])) + __uint_as_float(r0[i]);
                     }
                 }
-            } else if (MODE == MODE_WGRAD && p.transpose_out) {
-                // the product is stored transposed, out[e][n][m]: the 32 lanes of a warp hold consecutive m,
-                // so each store instruction writes one 128-byte line
-                float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + (long long)tile.n0 * p.ldc + row;
+            } else if (MODE == MODE_WGRAD && ((p.transpose_out >> tile.problem) & 1)) {
+                // the product is stored transposed, out[e][n][m] (row pitch M): the 32 lanes of a warp hold
+                // consecutive m, so each store instruction writes one 128-byte line
+                float* out = (float*)(tile.problem == 0 ? p.out0 : tile.problem == 1 ? p.out1 : p.out2);
+                const long long ldc = p.M;
+                float* C = out + (long long)tile.expert * p.c_slab + (long long)tile.n0 * ldc + row;
                 const bool row_ok = row < p.M;
 #pragma unroll 1
                 for (int c = c_begin; c < c_end; ++c) {
@@ -787,11 +800,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     if (row_ok) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (i < valid) C[(long long)(c * 32 + i) * p.ldc] = __uint_as_float(r[i]);
+                            if (i < valid) C[(long long)(c * 32 + i) * ldc] = __uint_as_float(r[i]);
                     }
                 }
             } else {
-                float* C = (float*)p.out0 + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
+                float* out = (float*)(MODE != MODE_WGRAD || tile.problem == 0 ? p.out0 : tile.problem == 1 ? p.out1 : p.out2);
+                float* C = out + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
                 const bool row_ok = row < p.M;  // WGRAD: rows of one expert's output; PLAIN_F32: rows of the single group
 #pragma unroll 1
                 for (int c = c_begin; c < c_end; ++c) {
@@ -1062,28 +1076,53 @@ int tc_split_wgrad(uint64_t a, long long a_pitch, uint64_t b, uint64_t partial, 
     p.offsets = offsets; p.counts = counts; p.status = device_status_address();
     p.out0 = (void*)partial; p.ldc = N; p.c_slab = M * N; p.experts = splits;
     p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, BN);
-    p.M = (int)M; p.N = (int)N; p.K = 0; p.segments = 1;
+    p.M = (int)M; p.N = (int)N; p.K = 0; p.segments = 1; p.problems = 1;
     return launch<MODE_WGRAD, true, true>(p, stream);
 }
 
-// C_e [M, N] (fp32) = A_e^T . B_e, A [rows, M], B [rows, N], contraction over the rows of expert e.
-// Tiles are 128 * ctas rows x 256 (or a last 128) columns, so when M is the dimension that leaves a partly
-// empty last tile, the kernel computes B_e^T . A_e instead and stores it transposed.
-int tc_wgrad(const qmoe_route_t* r, int experts, uint64_t a, uint64_t b, uint64_t c, long long M, long long N,
-             cudaStream_t stream) {
+// The three weight gradients of an expert FFN in one launch (one tile queue: fewer, fuller rounds of the
+// persistent grid than three launches, and dWg / dWu tiles that share the layer input run side by side):
+// dWd [d, h] = dY^T . H, dWg [h, d] = dG^T . X, dWu [h, d] = dU^T . X per expert, fp32, the contraction running
+// over the expert's dispatched rows.  Tiles are 128 * ctas rows x 256 (or a last 128) columns, so all three
+// run in the orientation (rows x columns = d x h or h x d) that leaves less padding; those stored the other
+// way round are written transposed.
+int tc_wgrad3(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t h_act, uint64_t x, uint64_t dg, uint64_t du,
+              uint64_t d_w_down, uint64_t d_w_gate, uint64_t d_w_up, long long d, long long h, cudaStream_t stream) {
     GemmParams p = {};
-    if (c & 15u || (N * 4) % 16) return fail_arg("weight-gradient output must be 16-byte aligned with a 16-byte row pitch");
+    if ((d_w_down | d_w_gate | d_w_up) & 15u || (d * 4) % 16 || (h * 4) % 16)
+        return fail_arg("weight-gradient output must be 16-byte aligned with a 16-byte row pitch");
     const int ctas = gemm_ctas();
     auto padded = [&](long long m, long long n) { return ceil_div(m, BM * ctas) * (BM * ctas) * ceil_div(n, BN / 2) * (BN / 2); };
-    const bool swap = padded(N, M) < padded(M, N);
-    const long long m = swap ? N : M, n = swap ? M : N;  // the kernel's own M (tile rows) and N (tile columns)
-    if (int rc = make_map(&p.map_a, swap ? b : a, (uint64_t)m, (uint64_t)r->rows_bound, 64)) return rc;
-    if (int rc = make_map(&p.map_b, swap ? a : b, (uint64_t)n, (uint64_t)r->rows_bound, 64)) return rc;
-    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    const bool rows_are_d = padded(d, h) <= padded(h, d);
+    const long long m = rows_are_d ? d : h, n = rows_are_d ? h : d;
+    const uint64_t rows = (uint64_t)r->rows_bound;
+    // kernel A = the operand with m columns, B = the one with n columns
+    const uint64_t a_of[3] = {rows_are_d ? dy : h_act, rows_are_d ? x : dg, rows_are_d ? x : du};
+    const uint64_t b_of[3] = {rows_are_d ? h_act : dy, rows_are_d ? dg : x, rows_are_d ? du : x};
+    CUtensorMap* ma[3] = {&p.map_a, &p.map_a2, &p.map_a3};
+    CUtensorMap* mb[3] = {&p.map_b, &p.map_b2, &p.map_b3};
+    for (int i = 0; i < 3; ++i) {
+        if (int rc = make_map(ma[i], a_of[i], (uint64_t)m, rows, 64)) return rc;
+        if (int rc = make_map(mb[i], b_of[i], (uint64_t)n, rows, 64)) return rc;
+    }
     p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
-    p.out0 = (void*)c; p.ldc = N; p.c_slab = M * N; p.experts = experts; p.transpose_out = swap ? 1 : 0;
+    p.out0 = (void*)d_w_down; p.out1 = (void*)d_w_gate; p.out2 = (void*)d_w_up;
+    // dWd is [d, h]: natural when the kernel's rows are d; dWg, dWu are [h, d]: natural when they are h
+    p.transpose_out = rows_are_d ? 0b110 : 0b001;
+    p.ldc = n; p.c_slab = d * h; p.experts = experts; p.problems = 3;
     p.m_tiles = ceil_div(m, BM * ctas); p.n_tiles = ceil_div(n, BN);
     p.M = (int)m; p.N = (int)n; p.K = 0; p.segments = 1;
+    const char* together = getenv("QUTAI_MOE_WGRAD_LAUNCHES");  // "3": one launch per product, for comparison
+    if (together && together[0] == '3') {
+        void* const outs[3] = {p.out0, p.out1, p.out2};
+        const int transposed = p.transpose_out;
+        for (int i = 0; i < 3; ++i) {
+            GemmParams q = p;
+            q.map_a = *ma[i]; q.map_b = *mb[i]; q.out0 = outs[i]; q.transpose_out = (transposed >> i) & 1; q.problems = 1;
+            if (int rc = ctas == 2 ? launch<MODE_WGRAD, true, true, 2>(q, stream) : launch<MODE_WGRAD, true, true>(q, stream)) return rc;
+        }
+        return 0;
+    }
     if (ctas == 2) return launch<MODE_WGRAD, true, true, 2>(p, stream);
     return launch<MODE_WGRAD, true, true>(p, stream);
 }

@@ -133,12 +133,13 @@ extern "C" int qmoe_expert_backward_parts(const qmoe_route_t* r, const qmoe_expe
     }
     if (parts & QMOE_BWD_WEIGHTS) {
         TimedScope timed(KC_WGRAD_GEMM, stream);
-        if (int rc = tc ? tc_wgrad(r, ex->experts, dy, h, d_w_down, d, hd, stream)
-                        : simt_wgrad(r, ex, dy, h, d_w_down, d, hd, stream)) return rc;
-        if (int rc = tc ? tc_wgrad(r, ex->experts, d_g, x, d_w_gate, hd, d, stream)
-                        : simt_wgrad(r, ex, d_g, x, d_w_gate, hd, d, stream)) return rc;
-        if (int rc = tc ? tc_wgrad(r, ex->experts, d_u, x, d_w_up, hd, d, stream)
-                        : simt_wgrad(r, ex, d_u, x, d_w_up, hd, d, stream)) return rc;
+        if (tc) {  // all three in one launch
+            if (int rc = tc_wgrad3(r, ex->experts, dy, h, x, d_g, d_u, d_w_down, d_w_gate, d_w_up, d, hd, stream)) return rc;
+        } else {
+            if (int rc = simt_wgrad(r, ex, dy, h, d_w_down, d, hd, stream)) return rc;
+            if (int rc = simt_wgrad(r, ex, d_g, x, d_w_gate, hd, d, stream)) return rc;
+            if (int rc = simt_wgrad(r, ex, d_u, x, d_w_up, hd, d, stream)) return rc;
+        }
     }
     if ((parts & QMOE_BWD_ACTIVATIONS) && !skip_dx && dx == dy) {  // dX overwrites dY: only after dY's last reader (dWd)
         TimedScope timed(KC_EXPERT_GEMM, stream);
