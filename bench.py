@@ -31,6 +31,8 @@ WORKLOADS = {
     "c2": dict(tokens=16384, d=1024, E=8, k=2, h=2816, router_std=0.01, bias_std=0.0),
     "c3": dict(tokens=32768, d=2048, E=64, k=6, h=1408, router_std=0.02, bias_std=0.5),
     "c4layer": dict(tokens=65536, d=1024, E=16, k=2, h=2048, router_std=0.02, bias_std=0.0),
+    # c3 cut to a quarter of the tokens and experts (same rows per expert, same tile shapes): small enough for a profiler capture
+    "c3s": dict(tokens=8192, d=2048, E=16, k=6, h=1408, router_std=0.02, bias_std=0.5),
     "c5": dict(tokens=64, d=2048, E=64, k=6, h=1408, router_std=0.02, bias_std=0.5),
 }
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)

@@ -105,7 +105,8 @@ def test_permute_combine_and_backwards(T, E, k, d, dtype):
 
     xd = DeviceStorage(R * d, dtype)
     lib.call("qmoe_memset", xd.ptr, 0x7f, xd.nbytes, 0)  # stale data must not survive in pad rows
-    lib.call("qmoe_permute", tables.ref, to_device(x, dtype).ptr, xd.ptr, code, d, 0)
+    x_dev = to_device(x, dtype)  # kept alive by name: a temporary would be released before the call is made
+    lib.call("qmoe_permute", tables.ref, x_dev.ptr, xd.ptr, code, d, 0)
     xh = to_host(xd, (R, d))
     for e in range(E):
         assert np.array_equal(xh[offsets[e]: offsets[e] + counts[e]], oracle.route_gather(x, route, e))
@@ -127,7 +128,8 @@ def test_permute_combine_and_backwards(T, E, k, d, dtype):
 
     dy, dw = DeviceStorage(R * d, dtype), DeviceStorage(T * k, "float32")
     lib.call("qmoe_memset", dy.ptr, 0x7f, dy.nbytes, 0)
-    lib.call("qmoe_combine_backward", tables.ref, to_device(gout, dtype).ptr, yd.ptr, dy.ptr, dw.ptr, code, d, 0)
+    gout_dev = to_device(gout, dtype)
+    lib.call("qmoe_combine_backward", tables.ref, gout_dev.ptr, yd.ptr, dy.ptr, dw.ptr, code, d, 0)
     want_dy, want_dw = oracle.combine_backward(gout, outputs, weights, route_w)
     dyh = to_host(dy, (R, d))
     for (e, _), want in zip(outputs, want_dy):
@@ -138,7 +140,8 @@ def test_permute_combine_and_backwards(T, E, k, d, dtype):
     # unpermute-reduce == sum over experts of route_gather_backward, plus the optional fp32 addend
     extra = rng.standard_normal((T, d)).astype(np.float32)
     dx = DeviceStorage(T * d, dtype)
-    lib.call("qmoe_unpermute_reduce", tables.ref, yd.ptr, to_device(extra, "float32").ptr, dx.ptr, code, d, 0)
+    extra_dev = to_device(extra, "float32")
+    lib.call("qmoe_unpermute_reduce", tables.ref, yd.ptr, extra_dev.ptr, dx.ptr, code, d, 0)
     want = extra.astype(np.float64)
     for e, ye in outputs:
         want = want + oracle.route_gather_backward(ye, route, e)
@@ -328,3 +331,26 @@ def test_router_forward_backward_fp32_semantics(T, d, E, dtype):
     lib.call("qmoe_router_backward", dsd.ptr, xd.ptr, code, wd.ptr, dxr.ptr, dwr.ptr, scratch.ptr, T, d, E, 0)
     assert np.array_equal(first, to_host(dwr, (E, d)))  # fixed reduction order: bit-identical
     assert lib.device_status() == 0
+
+
+def test_launch_variants_of_the_weight_gradients_agree_bit_for_bit(monkeypatch):
+    """One launch for the three weight gradients (default) against one launch each
+    (QUTAI_MOE_WGRAD_LAUNCHES=3): the same tiles in a different order give the same bits."""
+    from gpu_util import make_layer, run_layer
+
+    T, d, E, k, h = 1100, 384, 5, 2, 1408
+    rng = np.random.default_rng(11)
+    x, grad_y = oracle.round_bf16(rng.standard_normal((T, d))), oracle.round_bf16(rng.standard_normal((T, d)))
+    router = rng.standard_normal((E, d)).astype(np.float32) * 0.05
+    gate = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    up = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    down = rng.standard_normal((E, d, h)).astype(np.float32) / np.sqrt(h)
+    results = []
+    for launches in ("1", "3"):
+        monkeypatch.setenv("QUTAI_MOE_WGRAD_LAUNCHES", launches)
+        layer = make_layer(x.shape, router, gate, up, down, k, engine="tcgen05")
+        results.append(run_layer(layer, x, grad_y, None, "bfloat16"))
+    a, b = results
+    for e in range(E):
+        for key in ("d_gate", "d_up", "d_down"):
+            assert np.array_equal(a[key][e], b[key][e]), (key, e)

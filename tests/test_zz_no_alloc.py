@@ -28,7 +28,8 @@ def _run(entry, scores, top_k, with_scratch):
         tables.struct.block_counts = tables.struct.block_base = tables.struct.block_colsum = 0
     for name in ("tile_expert", "row_source"):  # entries past the used range are never written: make them comparable
         lib.call("qmoe_memset", tables.buf[name].ptr, 0, tables.buf[name].nbytes, 0)
-    lib.call(entry, tables.ref, to_device(scores, "float32").ptr, 0)
+    scores_dev = to_device(scores, "float32")  # kept alive by name until the call has been made
+    lib.call(entry, tables.ref, scores_dev.ptr, 0)
     return {name: tables.host(name) for name in TABLES}
 
 
