@@ -35,6 +35,10 @@ WORKLOADS = {
     "c3s": dict(tokens=8192, d=2048, E=16, k=6, h=1408, router_std=0.02, bias_std=0.5),
     "c5": dict(tokens=64, d=2048, E=64, k=6, h=1408, router_std=0.02, bias_std=0.5),
 }
+# DRAM bytes (read + written) of the five expert tensor-core launches of one step, from profiler captures of the
+# same command (profiles/grouped_gemm_c2_ncu_full.md, profiles/grouped_gemm_c3s_ncu_full.md); c3 is too large to
+# capture and has exactly four times c3s's experts and tokens at the same rows per expert: 4 x the c3s figure
+GEMM_DRAM_BYTES_PER_STEP = {"c2": 3.74e9, "c3s": 4.70e9, "c3": 4 * 4.70e9}
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
 
@@ -477,7 +481,9 @@ def run_gpu(args, w, rank, world):
         gpu_launches=int(launches), clocks=clocks,
         roofline=dict(bound="tensor", kernel="grouped_gemm_kernel (tcgen05)", achieved=achieved, peak=peak,
                       unit="TFLOP/s", frac=achieved / peak, peak_source=peaks["source"] + " (sustained cuBLAS bf16)",
-                      traffic=None, launches_per_step=int(gemm_launches), ms_per_step=gemm_ms,
+                      traffic=(GEMM_DRAM_BYTES_PER_STEP.get(args.workload) if world == 1 else None),
+                      traffic_unit="DRAM bytes per step over the same launches (profiler capture, see profiles/)",
+                      launches_per_step=int(gemm_launches), ms_per_step=gemm_ms,
                       algorithmic_flops_per_step=gemm_flops, whole_layer_frac=(gemm_flops + router_flops) / (ms * 1e-3) / 1e12 / peak),
         hbm_kernels=hbm,
         decode_roofline=(dict(bound="hbm", kernel="grouped_gemm_kernel (tcgen05), weight streaming", achieved=weight_bytes / (gemm_ms * 1e-3) / 1e9,
