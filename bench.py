@@ -506,6 +506,28 @@ def run_gpu(args, w, rank, world):
                 note="scalar triple-loop rate of the upstream pure-Python path; tokens/s = rate / (9*k*d*h + 3*d*E) MAC per token"))
         rate = line["cpu_baseline"]["pure_python_estimate"]["mac_per_s"]
         line["cpu_baseline"]["pure_python_estimate"]["tokens_per_s"] = rate / (9.0 * k * d * h + 3.0 * d * E)
+    if world == 1 and not forward_only and any(p.grad is not None for p in layer.parameters()):
+        # the optimizer step either side of the layer (not part of `value`): AdamW over every parameter that has a
+        # gradient, one launch, refreshing the bf16 operand copies in the same pass; HBM-bound at 30 bytes per element
+        from qutai_b200.optim import AdamW
+
+        optimizer = AdamW(layer.parameters(), learning_rate=1e-5, shadows=layer.operand_shadows(), stream=stream)
+        updated = sum(p.storage.size for p in layer.parameters() if p.grad is not None)
+        shadowed = sum(p.storage.size for p in layer.parameters() if p.grad is not None and p in optimizer.shadows)
+        optimizer.step()                       # allocates the moments
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(3):
+            optimizer.step()
+        end.record()
+        torch.cuda.synchronize()
+        adam_ms = begin.elapsed_time(end) / 3
+        adam_bytes = 28 * updated + 2 * shadowed
+        line["optimizer_step"] = dict(kernel="adamw_multi_kernel", ms=adam_ms, parameters=updated, launches=1,
+                                      bytes=adam_bytes, achieved_gbs=adam_bytes / (adam_ms * 1e-3) / 1e9,
+                                      frac=adam_bytes / (adam_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], bound="hbm")
+        del optimizer
     if forward_only:
         # decode-shaped workload: per-call latency percentiles over 200 calls, each bracketed by its own events
         marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]

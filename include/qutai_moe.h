@@ -425,6 +425,43 @@ int qmoe_ep_expert_down_push(const qmoe_route_t* expert_route, const qmoe_expert
 int qmoe_ep_expert_dx_push(const qmoe_route_t* expert_route, const qmoe_experts_t* experts, uint64_t d_g,
                            uint64_t d_u, uint64_t return_addresses, const qmoe_ep_peers_t* peers, uint64_t stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * The optimizer step either side of the layer: AdamW and the global gradient-norm clip over many
+ * parameter tensors in one launch.  Upstream loops over the parameters and launches one element-wise
+ * kernel per tensor for AdamW (src/qutai/nn/optimizers.py:136-153 -> adamw_step_into,
+ * src/qutai/backends/cuda.py:449-452, kernel src/qutai/backends/cuda/tensor.cu:101-104) and two
+ * reductions plus one scaling per tensor for the clip (src/qutai/nn/optimizers.py:19-31 ->
+ * global_norm src/qutai/backends/cuda.py:425-437, scale_into :150-154).
+ *
+ * The caller lists the tensors that have a gradient (upstream skips `parameter.grad is None`) in a host
+ * array of items and passes a device buffer of qmoe_optim_table_bytes(count) bytes the array is copied
+ * into; `first_chunk` is filled in by the library.  fp32 parameters, gradients and moments.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qmoe_optim_item {
+    uint64_t values;      /* [size] fp32 parameter, updated in place */
+    uint64_t grad;        /* [size] fp32 gradient */
+    uint64_t exp_avg;     /* [size] fp32 first moment, updated in place (zeros before the first step) */
+    uint64_t exp_avg_sq;  /* [size] fp32 second moment, updated in place */
+    uint64_t shadow;      /* [size] bf16 copy of the updated parameter (the tensor-core operand), or 0 */
+    int64_t size;
+    int64_t first_chunk;  /* set by the library */
+    float c1, c2;         /* bias corrections 1 - beta1^step, 1 - beta2^step of THIS tensor's step count */
+} qmoe_optim_item_t;
+int64_t qmoe_optim_table_bytes(int32_t count);
+/* m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  p = p (1 - lr wd) - lr (m / c1) / (sqrt(v / c2) + eps), in
+ * fp32 in exactly this order (the upstream kernel's); shadow = bf16(p) when given.  `items` may be
+ * modified (first_chunk).  Negative settings or betas outside [0, 1) are argument errors, as upstream. */
+int qmoe_adamw_multi(qmoe_optim_item_t* items, int32_t count, uint64_t table, float learning_rate, float beta1,
+                     float beta2, float eps, float weight_decay, uint64_t stream);
+/* L2 norm of all listed gradients (sum of squares in double, fixed order: run-to-run identical) and, when
+ * it exceeds max_norm, every gradient scaled by max_norm / norm.  scratch: qmoe_clip_scratch_bytes() bytes;
+ * afterwards scratch[0] (double) holds the norm before clipping and scratch[1] the factor applied.  Only
+ * `grad` and `size` of the items are read.  Upstream raises for a non-finite norm after reading it back;
+ * here a non-finite norm leaves the gradients unscaled and the host decides when it reads scratch[0]. */
+int64_t qmoe_clip_scratch_bytes(void);
+int qmoe_clip_grad_norm(qmoe_optim_item_t* items, int32_t count, uint64_t table, double max_norm, uint64_t scratch,
+                        uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,7 +25,7 @@ struct Scope { int kc; cudaEvent_t start, stop; };
 std::vector<Scope> g_scopes;
 const char* kClassNames[KC_COUNT] = {"router_gemm", "route", "permute", "expert_gemm", "swiglu", "combine",
                                      "combine_backward", "wgrad_gemm", "unpermute", "route_backward",
-                                     "cast", "other", "exchange"};
+                                     "cast", "other", "exchange", "optimizer"};
 __device__ int g_device_status;
 }  // namespace
 

@@ -138,6 +138,24 @@ class SparseMoE:
     def parameters(self):
         return (*self.router.parameters(), *(p for expert in self.experts for p in expert.parameters()))
 
+    def operand_shadows(self, tokens=None):
+        """``{parameter: bf16 storage}`` of the tensor-core operand copies of the expert weights (those of the
+        last bf16 forward, or of the workspace for ``tokens``).  An optimizer that writes the rounded weights
+        there (``qutai_b200.optim.AdamW(shadows=...)``) makes the per-forward conversion unnecessary: set
+        ``refresh_operands = False`` once the first forward has built them."""
+        works = [w for (t, dtype), w in self._work.items() if dtype == "bfloat16" and (tokens is None or t == tokens)]
+        if self._saved is not None and any(w is self._saved[0] for w in works):
+            works = [self._saved[0]]
+        if not works:
+            raise RuntimeError("no bfloat16 forward has run yet")
+        buf, h, d = works[-1]["buf"], self.d_expert, self.d_model
+        shadows = {}
+        for i, expert in enumerate(self.experts):
+            shadows[expert.gate.weight] = buf["w_gate"].view(i * h * d, h * d)
+            shadows[expert.up.weight] = buf["w_up"].view(i * h * d, h * d)
+            shadows[expert.down.weight] = buf["w_down"].view(i * d * h, d * h)
+        return shadows
+
     @property
     def last_counts(self):
         """Tokens routed to each expert in the last forward, as Python ints.  Reading it is the

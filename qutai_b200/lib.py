@@ -10,7 +10,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_int, c_int32, c_int64,
+from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_float, c_int, c_int32, c_int64,
                     c_uint64, c_void_p)
 
 QMOE_F32, QMOE_BF16 = 0, 1
@@ -47,6 +47,12 @@ class Peers(Structure):
     """``qmoe_ep_peers_t``."""
     _fields_ = [("world", c_int32), ("rank", c_int32), ("buffer", c_uint64 * EP_MAX_RANKS),
                 ("ret", c_uint64 * EP_MAX_RANKS)]
+
+
+class OptimItem(Structure):
+    """``qmoe_optim_item_t``."""
+    _fields_ = [("values", c_uint64), ("grad", c_uint64), ("exp_avg", c_uint64), ("exp_avg_sq", c_uint64),
+                ("shadow", c_uint64), ("size", c_int64), ("first_chunk", c_int64), ("c1", c_float), ("c2", c_float)]
 
 
 class Layer(Structure):
@@ -140,6 +146,10 @@ SIGNATURES = {
     "qmoe_ep_expert_down_push": (c_int, [_RP, _EP, _U, _U, POINTER(Peers), _U]),
     "qmoe_ep_expert_dx_push": (c_int, [_RP, _EP, _U, _U, _U, POINTER(Peers), _U]),
     "qmoe_ep_push_return": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I32, _I32, _I64, _U]),
+    "qmoe_optim_table_bytes": (c_int64, [_I32]),
+    "qmoe_clip_scratch_bytes": (c_int64, []),
+    "qmoe_adamw_multi": (c_int, [POINTER(OptimItem), _I32, _U, c_float, c_float, c_float, c_float, c_float, _U]),
+    "qmoe_clip_grad_norm": (c_int, [POINTER(OptimItem), _I32, _U, c_double, _U, _U]),
 }
 
 _lock = threading.Lock()
