@@ -365,6 +365,31 @@ __device__ __forceinline__ void spread_block32(uint32_t stage, int lane, const u
     }
 }
 
+// Thread `lane` holds the 32 fp32 values of row `lane`; store the 32 x 32 block to `dst` (first element of the
+// block, row pitch ldc floats, rows >= rows_left skipped) so that every store instruction covers 8 rows x 64
+// contiguous bytes.  Two passes of 16 columns through the 32 x 80 B staging buffer.
+__device__ __forceinline__ void store_block32_f32(uint32_t stage, int lane, const uint32_t* r, float* dst, long long ldc,
+                                                  long long rows_left) {
+    const uint32_t mine = stage + lane * STAGE_PITCH;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16 * q), "r"(r[16 * s + 4 * q]),
+                         "r"(r[16 * s + 4 * q + 1]), "r"(r[16 * s + 4 * q + 2]), "r"(r[16 * s + 4 * q + 3]) : "memory");
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int row = j * 8 + (lane >> 2), piece = lane & 3;
+            uint4 v;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(stage + row * STAGE_PITCH + 16 * piece) : "memory");
+            if (row < rows_left) *reinterpret_cast<uint4*>(dst + (long long)row * ldc + 16 * s + 4 * piece) = v;
+        }
+        __syncwarp();
+    }
+}
+
 // Scatter of 128 columns: thread `lane` holds 128 consecutive bf16 (64 packed words) of row `lane`, every row
 // has its own destination (`dst_row`, null = skip).  Rows that live on another GPU cross NVLink, where a
 // store of 64 contiguous bytes per row costs about twice the time per byte of a long one, so the block goes
@@ -806,6 +831,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             } else {
                 float* out = (float*)(MODE != MODE_WGRAD || tile.problem == 0 ? p.out0 : tile.problem == 1 ? p.out1 : p.out2);
                 float* C = out + (long long)tile.expert * p.c_slab + row * p.ldc + tile.n0;
+                float* Cw = out + (long long)tile.expert * p.c_slab + row0w * p.ldc + tile.n0;  // this warp's first row
                 const bool row_ok = row < p.M;  // WGRAD: rows of one expert's output; PLAIN_F32: rows of the single group
 #pragma unroll 1
                 for (int c = c_begin; c < c_end; ++c) {
@@ -813,10 +839,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
                     const int valid = p.N - (tile.n0 + c * 32);
-                    if (row_ok && valid >= 32) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            *reinterpret_cast<uint4*>(C + c * 32 + 4 * q) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    if (valid >= 32) {
+                        store_block32_f32(stage, lane, r, Cw + c * 32, p.ldc, (long long)p.M - row0w);
                     } else if (row_ok) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
