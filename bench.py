@@ -419,9 +419,13 @@ def run_gpu(args, w, rank, world):
     if args.trace:  # kernel timeline of two steps (diagnosis only; nothing measured under it is reported)
         from torch.profiler import ProfilerActivity, profile
 
+        traced = step_e2e if os.environ.get("QUTAI_BENCH_TRACE_E2E") else step   # which arm's timeline to look at
+        for _ in range(4):
+            traced()
+        torch.cuda.synchronize()
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            step()
-            step()
+            for _ in range(3):
+                traced()
             torch.cuda.synchronize()
         if rank == 0:
             prof.export_chrome_trace(args.trace)
@@ -429,12 +433,38 @@ def run_gpu(args, w, rank, world):
     launches_before = lib.load().qmoe_launch_count()
     ms = timed(step, args.steps)
     launches = (lib.load().qmoe_launch_count() - launches_before) // args.steps
-    for _ in range(max(2, args.warmup // 2)):
+    for _ in range(max(4, args.warmup)):  # until the output buffers of the steps in flight all come from the cache
         step_e2e()
     torch.cuda.synchronize()
     e2e_state["last"] = e2e_state["i"] + args.steps           # the last timed step waits for its own copy-out
     ms_e2e = timed(step_e2e, args.steps)
     e2e_state["pending"].clear()
+
+    # the floor of the end-to-end arm: the same host<->device copies on the same streams with no compute between
+    def copies_only():
+        with torch.cuda.stream(copy_in):
+            x_buf[1].copy_(x_host, non_blocking=True)
+            if not forward_only:
+                g_buf[1].copy_(g_host, non_blocking=True)
+        with torch.cuda.stream(copy_out):
+            lib.call("qmoe_memcpy_d2h", y_host.data_ptr(), x_buf[0].data_ptr(), x_buf[0].numel() * 2, copy_out.cuda_stream)
+            if not forward_only:
+                lib.call("qmoe_memcpy_d2h", dx_host.data_ptr(), g_buf[0].data_ptr(), g_buf[0].numel() * 2, copy_out.cuda_stream)
+
+    def timed_copies(steps):
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        for _ in range(steps):
+            copies_only()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - begin) * 1e3 / steps
+
+    timed_copies(2)
+    ms_copies = timed_copies(max(3, args.steps // 2))
+    if world > 1:
+        worst = torch.tensor([ms_copies], dtype=torch.float64, device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        ms_copies = float(worst.item())
     # per-kernel-class device time, measured in a separate pass so the events do not sit inside the headline timing
     lib.timing(True)
     for _ in range(args.steps):
@@ -477,7 +507,8 @@ def run_gpu(args, w, rank, world):
         higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
         config=workload_config(args.workload, w, world),
         e2e=dict(value=T_global / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=bytes_in,
-                 d2h_bytes_per_step=bytes_out),
+                 d2h_bytes_per_step=bytes_out, copies_alone_ms_per_step=ms_copies,
+                 note="copies_alone = the same pinned-host copies, both directions at once, without the layer: the floor this box's host link sets"),
         gpu_launches=int(launches), clocks=clocks,
         roofline=dict(bound="tensor", kernel="grouped_gemm_kernel (tcgen05)", achieved=achieved, peak=peak,
                       unit="TFLOP/s", frac=achieved / peak, peak_source=peaks["source"] + " (sustained cuBLAS bf16)",

@@ -214,11 +214,13 @@ class SparseMoE:
             setattr(layer, name, buf[name].ptr)
         layer.dx_dispatched = buf["dy_dispatched"].ptr  # dX reuses dY's buffer (written after its last reader)
         if self._counts_host is None:
-            host, event = ctypes.c_void_p(), ctypes.c_uint64()
+            host, event, routed, side = ctypes.c_void_p(), ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
             lib.call("qmoe_host_alloc", ctypes.byref(host), 4 * E)
             lib.call("qmoe_event_create", ctypes.byref(event))
+            lib.call("qmoe_event_create", ctypes.byref(routed))
+            lib.call("qmoe_stream_create", ctypes.byref(side))
             self._counts_host = ctypes.cast(host, ctypes.POINTER(ctypes.c_int32))
-            self._counts_event = event.value
+            self._counts_event, self._routed_event, self._copy_stream = event.value, routed.value, side.value
         grad_views = [Tensor(buf["d_w_router"], (E, d))]
         for i in range(E):
             grad_views.append((Tensor(buf["d_w_gate"].view(i * h * d, h * d), (h, d)),
@@ -247,12 +249,19 @@ class SparseMoE:
         masters = (layer.master_gate, layer.master_up, layer.master_down)
         if not self.refresh_operands and work.get("operands_built"):
             layer.master_gate = layer.master_up = layer.master_down = 0   # keep the bf16 copies of the last forward
+        if self._counts_valid:  # the previous forward's counts have left before routing overwrites them
+            lib.call("qmoe_stream_wait_event", self.stream, self._counts_event)
         lib.call("qmoe_layer_forward", ctypes.byref(layer), self.stream)
         layer.master_gate, layer.master_up, layer.master_down = masters
         work["operands_built"] = True
+        # The host's copy of the counts travels on a stream of its own: a device-to-host copy queued on the
+        # caller's stream would wait behind whatever large copy-out the caller has in flight on the same copy
+        # engine, and every kernel after it would wait too.
+        lib.call("qmoe_event_record", self._routed_event, self.stream)
+        lib.call("qmoe_stream_wait_event", self._copy_stream, self._routed_event)
         lib.call("qmoe_memcpy_d2h", ctypes.cast(self._counts_host, ctypes.c_void_p), buf["counts"].ptr,
-                 4 * self.n_experts, self.stream)
-        lib.call("qmoe_event_record", self._counts_event, self.stream)
+                 4 * self.n_experts, self._copy_stream)
+        lib.call("qmoe_event_record", self._counts_event, self._copy_stream)
         self._counts_valid = True
         self.utilization = Tensor(buf["utilization"], (self.n_experts,))
         self._saved = (work, storage, shape)

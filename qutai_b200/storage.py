@@ -10,6 +10,7 @@ upstream ``CUDAStorage``, a ``torch`` tensor's ``data_ptr()``), or is a view int
 from __future__ import annotations
 
 import ctypes
+import os
 import struct
 from array import array
 
@@ -18,7 +19,10 @@ from . import lib
 _FORMATS = {"float32": "f", "float64": "d", "int32": "i", "int64": "q"}
 _cache: dict[int, list[int]] = {}
 _cached_bytes = 0
-CACHE_LIMIT_BYTES = 1 << 30
+# Freed blocks are kept for reuse up to this many bytes (a B200 has 180 GB; activations of the benchmark
+# shapes are hundreds of MB each, and a block that is really freed costs a device-wide synchronisation);
+# QUTAI_MOE_CACHE_BYTES overrides it.
+CACHE_LIMIT_BYTES = int(os.environ.get("QUTAI_MOE_CACHE_BYTES", 16 << 30))
 
 
 def _bucket(nbytes):
