@@ -106,7 +106,9 @@ class _Finder(importlib.abc.MetaPathFinder):
 
 def reference_root():
     """Directory holding the upstream ``src/qutai`` tree, or None when it is not mounted."""
-    root = os.environ.get("QUTAI_REFERENCE_SRC", "/root/reference/src")
+    # QUTAI_REFERENCE_SRC, else a checkout named "reference" next to this repository
+    beside = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "src")
+    root = os.environ.get("QUTAI_REFERENCE_SRC", beside)
     return root if os.path.isfile(os.path.join(root, "qutai", "__init__.py")) else None
 
 
