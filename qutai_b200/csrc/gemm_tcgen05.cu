@@ -2,10 +2,14 @@
 // operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast),
 // fp32 accumulators in tensor memory (TMEM), read back with tcgen05.ld for the epilogue.
 //
-// One persistent kernel, one CTA per SM, 10 warps:
-//   warp 0      TMA producer (one lane): fills a 4-stage ring of {A 128x64, B 256x64} bf16 tiles
-//   warp 1      MMA issuer (one lane): 4 x tcgen05.mma (128x256x16) per stage, commits free the stage;
-//               also allocates / frees the 512 TMEM columns (two 128x256 fp32 accumulators)
+// One persistent kernel, one CTA per SM, 10 warps; the expert products run as CTA PAIRS (CTAS = 2: the two
+// CTAs of a cluster share one 256 x 256 tile, tcgen05.mma.cta_group::2), the small router products with one
+// CTA per 128 x 256 tile:
+//   warp 0      TMA producer (one lane): fills a ring of {A 128x64, B 256x64 or this CTA's 128x64 half} bf16
+//               tiles (4 stages of 48 KiB, or 6 stages of 32 KiB per CTA of a pair)
+//   warp 1      MMA issuer (one lane, in a pair only the first CTA's): 4 x tcgen05.mma (K = 16 each) per
+//               stage, commits free the stage in both CTAs; also allocates / frees the 512 TMEM columns
+//               (two 128x256 fp32 accumulators per CTA)
 //   warps 2-9   epilogue: two warps per 32-lane TMEM quadrant (= 32 tile rows), each taking half of
 //               the columns; they convert and store to HBM while the MMA warp already works on the
 //               next tile in the other accumulator
@@ -19,10 +23,12 @@
 //   MODE_DSWIGLU dH = dY Wd_e (never stored): dU = dH * silu(G), dG = dH * U * silu'(G), bf16.
 //   MODE_WGRAD   C_e[M, N] (fp32) = A_e^T . B_e, contraction over the rows of expert e (both
 //                operands MN-major); experts without rows are skipped and their slab is not written.
+//                Up to three such products of one shape share a launch (dWd, dWg, dWu).
+//   MODE_ROUTER / MODE_PLAIN_F32: the router's products (fp32 results from bf16 terms), one row group.
 //
 // Every wait on an mbarrier is bounded (about one second of %globaltimer); when one runs out the
 // CTA records a code in the status word, stops issuing work, waits a bounded time for copies in
-// flight, frees its TMEM and returns.
+// flight, meets its partner CTA at the cluster barrier (pairs), frees its TMEM and returns.
 #include <cuda.h>
 
 #include <map>
