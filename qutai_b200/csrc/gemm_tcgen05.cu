@@ -553,7 +553,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         const int k0 = (kb - seg * kb_per_seg) * BK;
                         const CUtensorMap* ma = seg ? &p.map_a2 : &p.map_a;
                         const CUtensorMap* mb = seg ? &p.map_b2 : &p.map_b;
-                        load(ma, sa, k0, tile.row0);  // A is K-major in these modes
+                        // A is K-major in these modes.  The unused half of an odd pair-tile reads past the end of
+                        // the matrix: TMA fills zeros without touching memory, and a tensor core fed zeros draws
+                        // far less power than one fed another expert's rows (the result is discarded either way).
+                        load(ma, sa, k0, (CTAS == 2 && !tile.rows_valid) ? 0x3fffff00 : tile.row0);
                         if (MODE == MODE_SWIGLU) {
                             // accumulator columns [0, 128) = gate, [128, 256) = up; a pair splits them between its CTAs
                             if (CTAS == 2) {
