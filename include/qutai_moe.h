@@ -82,6 +82,16 @@ int qmoe_event_destroy(uint64_t event);
 int qmoe_event_record(uint64_t event, uint64_t stream);
 int qmoe_stream_wait_event(uint64_t stream, uint64_t event);
 int qmoe_event_sync(uint64_t event);                       /* host waits for the event only */
+/* CUDA graphs (no upstream counterpart: its runtime launches kernel by kernel,
+ * src/qutai/backends/cuda_runtime.py:299-328).  Between qmoe_graph_begin and qmoe_graph_end every call of this
+ * library on `stream` (a stream from qmoe_stream_create, not 0) is recorded instead of run; qmoe_graph_launch
+ * replays the recording with the same addresses.  Run the same calls once without capture first (the first call
+ * of a kernel configures it).  After an error inside a capture call qmoe_graph_abandon. */
+int qmoe_graph_begin(uint64_t stream);
+int qmoe_graph_end(uint64_t stream, uint64_t* graph);
+int qmoe_graph_abandon(uint64_t stream);
+int qmoe_graph_launch(uint64_t graph, uint64_t stream);
+int qmoe_graph_destroy(uint64_t graph);
 /* launches made by this library since load (the upstream runtime keeps the same counter,
  * src/qutai/backends/cuda_runtime.py:95, :327); tensor-core launches counted separately (:100). */
 int64_t qmoe_launch_count(void);

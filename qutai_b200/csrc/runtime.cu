@@ -1,6 +1,7 @@
 // Process-wide plumbing of libqutai_moe.so: error text, launch counters, per-kernel-class event
 // timing, the device status word, and the small memory/stream helpers of the C ABI.
 #include <atomic>
+#include <map>
 #include <mutex>
 #include <stdarg.h>
 #include <stdio.h>
@@ -239,6 +240,64 @@ extern "C" int qmoe_event_sync(uint64_t event) {
     QMOE_CUDA(cudaEventSynchronize((cudaEvent_t)event));
     return 0;
 }
+// ---- CUDA graphs: a launch-bound sequence (the decode-shaped forward: about ten short kernels) recorded
+// once and replayed with one call -----------------------------------------------------------------------
+namespace {
+std::mutex g_graph_mutex;
+std::map<uint64_t, long long> g_graph_kernels;        // kernels recorded in each instantiated graph
+thread_local long long g_capture_started_at = 0;      // launch counter when this thread's capture began
+}  // namespace
+
+extern "C" int qmoe_graph_begin(uint64_t stream) {
+    if (!stream) return fail_arg("graph_begin: capture needs a stream of its own, not the default stream");
+    if (g_sync_each_launch) { set_error("graph capture is not possible with QUTAI_MOE_SYNC=1"); return QMOE_ERR_STATE; }
+    QMOE_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    g_capture_started_at = g_launches.load();
+    return 0;
+}
+extern "C" int qmoe_graph_end(uint64_t stream, uint64_t* graph) {
+    if (!graph) return fail_arg("graph_end: graph is null");
+    *graph = 0;
+    cudaGraph_t recorded = nullptr;
+    QMOE_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &recorded));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t code = cudaGraphInstantiate(&exec, recorded, 0);
+    cudaGraphDestroy(recorded);
+    QMOE_CUDA(code);
+    *graph = (uint64_t)exec;
+    const long long recorded_kernels = g_launches.load() - g_capture_started_at;
+    g_launches.fetch_sub(recorded_kernels, std::memory_order_relaxed);  // they were recorded, not run
+    std::lock_guard<std::mutex> lock(g_graph_mutex);
+    g_graph_kernels[*graph] = recorded_kernels;
+    return 0;
+}
+extern "C" int qmoe_graph_abandon(uint64_t stream) {  // after a failed call during capture: end it, drop the result
+    cudaGraph_t recorded = nullptr;
+    cudaStreamEndCapture((cudaStream_t)stream, &recorded);
+    if (recorded) cudaGraphDestroy(recorded);
+    cudaGetLastError();
+    return 0;
+}
+extern "C" int qmoe_graph_launch(uint64_t graph, uint64_t stream) {
+    if (!graph) return fail_arg("graph_launch: graph is null");
+    QMOE_CUDA(cudaGraphLaunch((cudaGraphExec_t)graph, (cudaStream_t)stream));
+    long long kernels = 1;
+    {
+        std::lock_guard<std::mutex> lock(g_graph_mutex);
+        auto it = g_graph_kernels.find(graph);
+        if (it != g_graph_kernels.end()) kernels = it->second;
+    }
+    g_launches.fetch_add(kernels, std::memory_order_relaxed);  // the launch counter counts kernels that ran
+    return 0;
+}
+extern "C" int qmoe_graph_destroy(uint64_t graph) {
+    if (!graph) return 0;
+    QMOE_CUDA(cudaGraphExecDestroy((cudaGraphExec_t)graph));
+    std::lock_guard<std::mutex> lock(g_graph_mutex);
+    g_graph_kernels.erase(graph);
+    return 0;
+}
+
 extern "C" int qmoe_device_status_clear(uint64_t stream) {
     int* p = device_status_address();
     if (!p) { set_error("device status symbol is not available"); return QMOE_ERR_STATE; }

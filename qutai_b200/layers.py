@@ -53,6 +53,30 @@ class Tensor:
         self.grad = None
 
 
+class ForwardGraph:
+    """A recorded forward of one ``SparseMoE`` on one input buffer (``SparseMoE.capture_forward``).  Keeps the
+    workspace, the input and the output alive; a forward with another token count in between does not disturb it."""
+
+    def __init__(self, layer, graph, work, x_storage, shape, y, aux):
+        self.layer, self.graph, self.work, self.x_storage, self.shape, self.y, self.aux = layer, graph, work, x_storage, shape, y, aux
+
+    def replay(self):
+        layer = self.layer
+        lib.call("qmoe_graph_launch", self.graph, layer.stream)
+        layer._counts_valid = "stream"
+        layer.utilization = Tensor(self.work["buf"]["utilization"], (layer.n_experts,))
+        layer._saved = (self.work, self.x_storage, self.shape)
+        return self.y, self.aux
+
+    def __del__(self):
+        graph, self.graph = getattr(self, "graph", 0), 0
+        if graph:
+            try:
+                lib.load().qmoe_graph_destroy(graph)
+            except Exception:
+                pass
+
+
 class Projection:
     """Bias-free linear map with ``weight`` of shape (outputs, inputs) (src/qutai/lm/layers.py:260-272)."""
 
@@ -163,7 +187,10 @@ class SparseMoE:
         src/qutai/backends/cuda_lm.py:432-434)."""
         if not self._counts_valid:
             return self._zero_counts
-        lib.call("qmoe_event_sync", self._counts_event)  # waits for the forward's routing only, not for later work
+        if self._counts_valid == "stream":  # the last forward was a graph replay: its copy is a node of the graph
+            lib.call("qmoe_stream_sync", self.stream)
+        else:
+            lib.call("qmoe_event_sync", self._counts_event)  # waits for the forward's routing only, not for later work
         return tuple(self._counts_host[i] for i in range(self.n_experts))
 
     # ------------------------------------------------------------------------------------------
@@ -249,7 +276,7 @@ class SparseMoE:
         masters = (layer.master_gate, layer.master_up, layer.master_down)
         if not self.refresh_operands and work.get("operands_built"):
             layer.master_gate = layer.master_up = layer.master_down = 0   # keep the bf16 copies of the last forward
-        if self._counts_valid:  # the previous forward's counts have left before routing overwrites them
+        if self._counts_valid is True:  # the previous forward's counts have left before routing overwrites them
             lib.call("qmoe_stream_wait_event", self.stream, self._counts_event)
         lib.call("qmoe_layer_forward", ctypes.byref(layer), self.stream)
         layer.master_gate, layer.master_up, layer.master_down = masters
@@ -266,6 +293,37 @@ class SparseMoE:
         self.utilization = Tensor(buf["utilization"], (self.n_experts,))
         self._saved = (work, storage, shape)
         return Tensor(out, shape), Tensor(buf["aux"], ())
+
+    def capture_forward(self, x):
+        """Record the forward on ``x``'s buffer as a CUDA graph (the decode-shaped call is a dozen short kernels:
+        one graph launch replaces their launches).  Returns a ``ForwardGraph``; ``replay()`` reruns the forward on
+        whatever ``x`` holds then and returns the same ``(y, aux)`` tensors every time.  The layer must run on a
+        stream of its own (``stream != 0``); ``refresh_operands`` is recorded as it is now."""
+        if not self.stream:
+            raise ValueError("capture needs a layer whose stream is not the default stream")
+        self.forward(x)                                    # once without capture: workspace, kernel attributes
+        storage = x.storage if hasattr(x, "storage") else x
+        work, _, shape = self._saved
+        layer, buf = work["layer"], work["buf"]
+        out = DeviceStorage(storage.size, storage.dtype)   # allocated before the capture starts
+        lib.call("qmoe_event_sync", self._counts_event)
+        layer.x, layer.out = storage.ptr, out.ptr
+        masters = (layer.master_gate, layer.master_up, layer.master_down)
+        if not self.refresh_operands:
+            layer.master_gate = layer.master_up = layer.master_down = 0
+        graph = ctypes.c_uint64()
+        lib.call("qmoe_graph_begin", self.stream)
+        try:
+            lib.call("qmoe_layer_forward", ctypes.byref(layer), self.stream)
+            lib.call("qmoe_memcpy_d2h", ctypes.cast(self._counts_host, ctypes.c_void_p), buf["counts"].ptr,
+                     4 * self.n_experts, self.stream)
+        except Exception:
+            lib.load().qmoe_graph_abandon(self.stream)
+            raise
+        finally:
+            layer.master_gate, layer.master_up, layer.master_down = masters
+        lib.call("qmoe_graph_end", self.stream, ctypes.byref(graph))
+        return ForwardGraph(self, graph.value, work, storage, shape, Tensor(out, shape), Tensor(buf["aux"], ()))
 
     def backward(self, grad_y, grad_aux=None):
         """Propagate ``grad_y`` (shaped like the output) and optionally ``grad_aux`` (float32

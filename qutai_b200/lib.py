@@ -146,6 +146,11 @@ SIGNATURES = {
     "qmoe_ep_expert_down_push": (c_int, [_RP, _EP, _U, _U, POINTER(Peers), _U]),
     "qmoe_ep_expert_dx_push": (c_int, [_RP, _EP, _U, _U, _U, POINTER(Peers), _U]),
     "qmoe_ep_push_return": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I32, _I32, _I64, _U]),
+    "qmoe_graph_begin": (c_int, [_U]),
+    "qmoe_graph_end": (c_int, [_U, POINTER(c_uint64)]),
+    "qmoe_graph_abandon": (c_int, [_U]),
+    "qmoe_graph_launch": (c_int, [_U, _U]),
+    "qmoe_graph_destroy": (c_int, [_U]),
     "qmoe_optim_table_bytes": (c_int64, [_I32]),
     "qmoe_clip_scratch_bytes": (c_int64, []),
     "qmoe_adamw_multi": (c_int, [POINTER(OptimItem), _I32, _U, c_float, c_float, c_float, c_float, c_float, _U]),
