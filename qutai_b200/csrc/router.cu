@@ -108,6 +108,55 @@ router_reduce_dw_kernel(const float* __restrict__ partial, float* __restrict__ d
     }
 }
 
+// Few tokens (decode): one block per token, a warp per expert in turn, fp32 dot products with the lanes
+// striding over the width and a fixed shuffle tree, so the logits are run-to-run identical.  A tile kernel
+// would put the whole product on one or two SMs and walk the width serially.
+constexpr long long kSmallRouterTokens = 512;
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                       __uint_as_float(v.y & 0xffff0000u));
+}
+// grid (tokens, ceil(E / 8)): warp w of block (t, g) computes scores[t, 8 g + w].  Four 16-byte loads of the weight
+// row and of the token row are in flight per lane and iteration, so the few round trips to L2 overlap.
+template <typename T>
+__global__ void __launch_bounds__(256)
+router_small_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ scores, int E, long long d) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * 8 + warp;
+    if (e >= E) return;
+    const T* row = x + (long long)blockIdx.x * d;
+    const float* we = w + (long long)e * d;
+    const bool vec = (d & 3) == 0 && (((uintptr_t)row | (uintptr_t)we) & 15u) == 0;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (vec) {
+        for (long long j = (long long)lane * 4; j < d; j += 512) {
+            float4 wv[4], xv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long at = j + 128 * u;
+                const bool in = at < d;
+                wv[u] = in ? load4(we + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+                xv[u] = in ? load4(row + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {   // fixed order: the sums do not depend on timing
+                a0 = fmaf(xv[u].x, wv[u].x, a0);
+                a1 = fmaf(xv[u].y, wv[u].y, a1);
+                a2 = fmaf(xv[u].z, wv[u].z, a2);
+                a3 = fmaf(xv[u].w, wv[u].w, a3);
+            }
+        }
+    } else {
+        for (long long j = lane; j < d; j += 32) a0 = fmaf(Act<T>::load(row + j), we[j], a0);
+    }
+    float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, step);
+    if (lane == 0) scores[(long long)blockIdx.x * E + e] = acc;
+}
+
 int elem_grid(long long n) {
     long long blocks = (n + 255) / 256;
     const long long cap = (long long)sm_count() * 8;
@@ -135,6 +184,17 @@ extern "C" int qmoe_router_forward(uint64_t x, int32_t x_dtype, uint64_t w_route
     if (tokens <= 0 || width <= 0 || experts <= 0) return fail_arg("router_forward: sizes must be positive");
     if (x_dtype != QMOE_F32 && x_dtype != QMOE_BF16) return fail_arg("router_forward: bad dtype %d", x_dtype);
     cudaStream_t stream = (cudaStream_t)stream_;
+    if (tokens <= kSmallRouterTokens) {
+        TimedScope timed(KC_ROUTER_GEMM, stream);
+        if (x_dtype == QMOE_BF16)
+            router_small_kernel<__nv_bfloat16><<<dim3((unsigned)tokens, (unsigned)((experts + 7) / 8)), 256, 0, stream>>>((const __nv_bfloat16*)x, (const float*)w_router,
+                                                                                   (float*)scores, experts, width);
+        else
+            router_small_kernel<float><<<dim3((unsigned)tokens, (unsigned)((experts + 7) / 8)), 256, 0, stream>>>((const float*)x, (const float*)w_router,
+                                                                             (float*)scores, experts, width);
+        QMOE_LAUNCH_CHECK("router_small_kernel");
+        return 0;
+    }
     if (!tc_router_ok(x_dtype, experts, width, x, scratch))
         return simt_router_logits(x, x_dtype, w_router, scores, tokens, width, experts, stream);
     TimedScope timed(KC_ROUTER_GEMM, stream);
