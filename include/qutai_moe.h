@@ -106,6 +106,20 @@ int qmoe_timing_read(double* milliseconds, int64_t* scopes, int capacity);
 /* status word written by kernels that check themselves; 0 = clean.  Synchronises the stream. */
 int qmoe_device_status(uint64_t stream, int* status);
 int qmoe_device_status_clear(uint64_t stream);            /* back to 0 after a reported failure was handled */
+/* The same word copied to (pinned) host memory in stream order, without waiting: a host that already waits
+ * for an event later on that stream reads it then. */
+int qmoe_device_status_async(uint64_t stream, void* host_status);
+
+/* Test hook (no upstream counterpart): selects, process-wide, the comparison form of a kernel that the
+ * parity tests run against the default form.  value 0 = default, 1 = comparison form.  Not for production
+ * hosts: the defaults are the measured-faster forms. */
+enum {
+    QMOE_VARIANT_SINGLE_CTA_GEMM = 0,   /* expert GEMMs with one CTA per 128 x 256 tile instead of a CTA pair per 256 x 256 */
+    QMOE_VARIANT_WGRAD_PER_PRODUCT = 1, /* one launch per weight-gradient product instead of one for all three */
+    QMOE_VARIANT_NARROW_SCATTER = 2,    /* 64-byte instead of 256-byte row pieces in the peer-memory scatter epilogues */
+    QMOE_VARIANT_COUNT = 3
+};
+int qmoe_test_select_variant(int32_t which, int32_t value);
 
 /* ---------------------------------------------------------------------------------------------
  * Sizes
@@ -173,6 +187,9 @@ int qmoe_route(const qmoe_route_t* route, uint64_t scores, uint64_t stream);
  * experts <= 131072, otherwise an argument error.  Allocates nothing.  The array is shared by all
  * calls on a device, so calls that overlap on the GPU race: use one stream at a time.  The first
  * call on a device resolves the array's address and should be made before any stream capture.
+ * The filled route can be handed to every other entry point with the three scratch fields left 0
+ * (only qmoe_route itself needs them); qmoe_ep_pack_stats / qmoe_ep_gather_stats, which read the
+ * column sums out of block_colsum, reject such a route.
  * This entry point has no counterpart in the upstream project. */
 int qmoe_route_static(const qmoe_route_t* route, uint64_t scores, uint64_t stream);
 /* The same tables in the upstream layout, for hosts that keep the upstream `route` dict
@@ -278,6 +295,12 @@ int qmoe_silu(uint64_t values, uint64_t gradient, uint64_t out, int32_t dtype, i
 /* out = a + b element-wise (the sum autograd applies when a tensor receives several gradient
  * contributions, src/qutai/core/grad.py:62, and when a leaf accumulates, src/qutai/core/tensor.py:207-209). */
 int qmoe_add(uint64_t a, uint64_t b, uint64_t out, int32_t dtype, int64_t n, uint64_t stream);
+/* dst[i, :] = src[index[i], :] for i < rows (index: i32 on the device, entries in [0, src_rows); row_bytes a
+ * multiple of 4).  Used for the small expert-indexed tables (router weight rows, their gradient, utilisation)
+ * when the expert-parallel layer places experts on ranks by a map instead of by contiguous blocks; upstream
+ * has one device and no such map. */
+int qmoe_gather_rows(uint64_t src, uint64_t dst, uint64_t index, int32_t rows, int32_t src_rows, int64_t row_bytes,
+                     uint64_t stream);
 /* Fill n values with N(mean, std) from a counter-based generator keyed by (seed, index).  Plays
  * the role of `normal` (src/qutai/backends/cuda_lm.py:27-28, normal_fill
  * src/qutai/backends/cuda/gemm.cu:146-161); like upstream, the stream differs from the CPU
@@ -369,8 +392,9 @@ int qmoe_ep_all_reduce_f32(uint64_t buffer, int64_t n, uint64_t stream);
  * computed on the device from the gathered counts, so the host does not read them.  Buffers that
  * other ranks write into must come from one cudaMalloc each (qmoe_malloc), are exported with
  * qmoe_ep_ipc_export, and opened by every other rank with qmoe_ep_ipc_open (all GPUs of the job
- * must be visible to every process).  After a push, qmoe_ep_barrier orders it against the readers
- * on every rank.  No kernel waits on another GPU. */
+ * must be visible to every process).  After a push, qmoe_ep_barrier (NCCL) or qmoe_ep_flag_barrier
+ * (flags in peer memory; the one kernel that waits on another GPU, for a bounded time) orders it against
+ * the readers on every rank. */
 #define QMOE_EP_MAX_RANKS 16
 typedef struct qmoe_ep_peers {
     int32_t world;
@@ -404,8 +428,8 @@ int qmoe_ep_push_return(const qmoe_route_t* expert_route, uint64_t return_addres
 
 /* Barrier over peer memory for the direct transport, without NCCL: every rank writes `sequence`
  * (positive, growing by one per barrier, the same on every rank) into its slot of every rank's flag
- * array (`flags->buffer[p]` = i32 [world] array of rank p, zero at start) and waits, at most about a
- * second, for all slots of its own array; a rank that never arrives shows up as a non-zero
+ * array (`flags->buffer[p]` = i32 [world] array of rank p, zero at start) and waits, for a bounded time
+ * (qmoe_ep_set_barrier_timeout_ms), for all slots of its own array; a rank that never arrives shows up as a non-zero
  * qmoe_device_status on the others, not as a hang.  With stats_local != 0 the kernel first copies this
  * rank's stats_words words into slot `rank` of every rank's table (`stats_tables->buffer[p]` = i32
  * [world, stats_words]): the all-gather of qmoe_ep_gather_stats without NCCL (pack the words first
@@ -413,6 +437,9 @@ int qmoe_ep_push_return(const qmoe_route_t* expert_route, uint64_t return_addres
 int qmoe_ep_flag_barrier(const qmoe_ep_peers_t* flags, int32_t sequence, uint64_t stats_local,
                          int32_t stats_words, const qmoe_ep_peers_t* stats_tables, uint64_t stream);
 int qmoe_ep_pack_stats(const qmoe_route_t* route, uint64_t stats_local, uint64_t stream);
+/* How long qmoe_ep_flag_barrier waits for the other ranks before it gives up (default 10 000 ms: seconds of
+ * skew between the hosts of a training job are normal); applies to barriers enqueued afterwards. */
+int qmoe_ep_set_barrier_timeout_ms(int64_t milliseconds);
 
 /* Fused producers (no upstream counterpart): the kernel that creates a row stores it directly in the
  * destination GPU's buffer, so dispatch and combine need no pass of their own.

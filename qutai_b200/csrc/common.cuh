@@ -170,6 +170,7 @@ int simt_router_backward(uint64_t d_scores, uint64_t x, int32_t x_dtype, uint64_
 long long simt_router_partials(int64_t tokens, int32_t experts, int64_t width);
 int launch_reduce_partials(const float* partials, float* out, long long n, int splits, cudaStream_t stream);
 void count_tensor_core_launch();
+int kernel_variant(int which);  // 0 = default form, 1 = the comparison form selected by qmoe_test_select_variant
 int* device_status_address();
 
 }  // namespace qmoe

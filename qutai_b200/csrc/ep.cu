@@ -6,11 +6,13 @@
 // (src/qutai/backends/cuda/lm.cu:353-383).
 //
 // NCCL is opened at run time (dlopen of libnccl.so.2): when the host process already carries an
-// NCCL (e.g. the one bundled with torch) the same library instance is used.  Nothing here waits on
-// flags of its own: all cross-GPU ordering comes from NCCL's stream semantics.
+// NCCL (e.g. the one bundled with torch) the same library instance is used.  With the NCCL transport all
+// cross-GPU ordering comes from NCCL's stream semantics; the direct transport orders the ranks with
+// ep_flag_barrier_kernel, whose wait on the peers' flags is bounded and reports a status instead of hanging.
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <atomic>
 #include <initializer_list>
 #include <mutex>
 
@@ -195,6 +197,7 @@ extern "C" int qmoe_ep_gather_stats(const qmoe_route_t* r, uint64_t stats_local,
     if (int rc = route_check(r)) return rc;
     if (int rc = need_comm()) return rc;
     if (!stats_local || !stats_all) return fail_arg("ep_gather_stats: null buffer");
+    if (!r->block_colsum) return fail_arg("ep_gather_stats: route.block_colsum is null (a route filled by qmoe_route_static keeps its column sums inside the library)");
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_OTHER, stream);
     const int E = r->experts;
@@ -303,9 +306,9 @@ extern "C" int qmoe_ep_all_reduce_f32(uint64_t buf, int64_t n, uint64_t stream_)
 // ---------------------------------------------------------------------------------------------
 // Direct transport: rows are pushed into the destination GPU's buffer with plain 16-byte stores
 // over NVLink (peer memory mapped through CUDA IPC), one warp per row.  Sizes and destinations are
-// computed on the device from the gathered counts, so the host never has to read them; the only
-// cross-GPU ordering is a tiny NCCL collective after each push (qmoe_ep_barrier).  No kernel here
-// waits on another GPU.
+// computed on the device from the gathered counts, so the host never has to read them.  Cross-GPU
+// ordering after each push is either a tiny NCCL collective (qmoe_ep_barrier) or the flag barrier further
+// down (qmoe_ep_flag_barrier), the only kernel here that waits on another GPU, for a bounded time.
 // ---------------------------------------------------------------------------------------------
 namespace qmoe {
 namespace {
@@ -735,7 +738,7 @@ extern "C" int qmoe_ep_expert_dx_push(const qmoe_route_t* expert_route, const qm
 // ---------------------------------------------------------------------------------------------
 // Flag barrier over peer memory: every rank stores the barrier's sequence number into its slot of
 // every rank's flag array, then waits until all slots of its own array carry that number.  Each
-// GPU runs its own copy of the kernel; the wait is bounded (about one second), after which the
+// GPU runs its own copy of the kernel; the wait is bounded (ten seconds unless set otherwise), after which the
 // kernel records a code in the status word and returns, so a missing rank shows up as a status on
 // the others instead of a hang.  Sequence numbers only grow, so the flags never need resetting.
 // ---------------------------------------------------------------------------------------------
@@ -743,7 +746,10 @@ namespace qmoe {
 namespace {
 
 constexpr int kStatusBarrierTimeout = 201;
-constexpr unsigned long long kBarrierWaitNs = 1000ull * 1000ull * 1000ull;
+// How long a rank waits for the others before it gives up.  Seconds of skew between the hosts of a training
+// job are normal (a checkpoint write, a data-loader stall, logging on one rank), so the default is generous;
+// qmoe_ep_set_barrier_timeout_ms changes it (the failure-detection test asks for a fraction of a second).
+std::atomic<long long> g_barrier_wait_ns{10ll * 1000 * 1000 * 1000};
 
 struct FlagTable {
     int* flags[kMaxPeers];
@@ -759,7 +765,7 @@ __device__ __forceinline__ unsigned long long barrier_clock_ns() {
 // (the all-gather of the routing counts), before the flags are raised.
 __global__ void __launch_bounds__(512)
 ep_flag_barrier_kernel(FlagTable table, int rank, int world, int sequence, int* status, const int* stats_local,
-                       int stats_words, FlagTable stats_tables) {
+                       int stats_words, FlagTable stats_tables, unsigned long long wait_ns) {
     if (stats_local) {
         for (int i = threadIdx.x; i < stats_words * world; i += blockDim.x) {
             const int p = i / stats_words, j = i - p * stats_words;
@@ -777,7 +783,7 @@ ep_flag_barrier_kernel(FlagTable table, int rank, int world, int sequence, int* 
         int seen;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
         if (seen - sequence >= 0) break;
-        if ((spin & 255u) == 255u && barrier_clock_ns() - start > kBarrierWaitNs) {
+        if ((spin & 255u) == 255u && barrier_clock_ns() - start > wait_ns) {
             atomicExch(status, kStatusBarrierTimeout);
             break;
         }
@@ -806,8 +812,15 @@ extern "C" int qmoe_ep_flag_barrier(const qmoe_ep_peers_t* flags, int32_t sequen
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_EXCHANGE, stream);
     ep_flag_barrier_kernel<<<1, 512, 0, stream>>>(table, flags->rank, flags->world, sequence, device_status_address(),
-                                                  (const int*)stats_local, stats_words, stats);
+                                                  (const int*)stats_local, stats_words, stats,
+                                                  (unsigned long long)g_barrier_wait_ns.load());
     QMOE_LAUNCH_CHECK("ep_flag_barrier_kernel");
+    return 0;
+}
+
+extern "C" int qmoe_ep_set_barrier_timeout_ms(int64_t milliseconds) {
+    if (milliseconds <= 0 || milliseconds > 600000) return fail_arg("ep_set_barrier_timeout_ms: need 1 .. 600000 ms");
+    g_barrier_wait_ns.store((long long)milliseconds * 1000000ll);
     return 0;
 }
 
@@ -815,6 +828,7 @@ extern "C" int qmoe_ep_flag_barrier(const qmoe_ep_peers_t* flags, int32_t sequen
 extern "C" int qmoe_ep_pack_stats(const qmoe_route_t* r, uint64_t stats_local, uint64_t stream_) {
     if (int rc = route_check(r)) return rc;
     if (!stats_local) return fail_arg("ep_pack_stats: null buffer");
+    if (!r->block_colsum) return fail_arg("ep_pack_stats: route.block_colsum is null (a route filled by qmoe_route_static keeps its column sums inside the library)");
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_OTHER, stream);
     ep_stats_kernel<<<1, kMaxExperts, 0, stream>>>((const int*)r->counts, (const float*)r->block_colsum,

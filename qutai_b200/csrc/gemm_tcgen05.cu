@@ -984,12 +984,9 @@ int launch(const GemmParams& p, cudaStream_t stream) {
     return 0;
 }
 
-// CTAs per output tile of the expert GEMMs: 2 (a CTA pair per 256 x 256 tile) unless the environment
-// variable QUTAI_MOE_GEMM_CTAS is "1" (one CTA per 128 x 256 tile).  Read on every call so a process can switch.
-int gemm_ctas() {
-    const char* text = getenv("QUTAI_MOE_GEMM_CTAS");
-    return (text && text[0] == '1') ? 1 : 2;
-}
+// CTAs per output tile of the expert GEMMs: 2 (a CTA pair per 256 x 256 tile); the one-CTA kernel
+// (128 x 256 tiles) stays reachable for the parity tests through qmoe_test_select_variant.
+int gemm_ctas() { return kernel_variant(QMOE_VARIANT_SINGLE_CTA_GEMM) ? 1 : 2; }
 
 }  // namespace
 
@@ -1016,8 +1013,7 @@ int tc_swiglu_forward(const qmoe_route_t* r, const qmoe_experts_t* ex, uint64_t 
 void set_scatter(GemmParams& p, const TcScatter* scatter) {
     if (!scatter) return;
     p.scatter_ret = scatter->ret;
-    const char* pieces = getenv("QUTAI_MOE_SCATTER_BYTES");  // "64": the narrow store pattern, for comparison
-    p.scatter_wide = !(pieces && pieces[0] == '6');
+    p.scatter_wide = !kernel_variant(QMOE_VARIANT_NARROW_SCATTER);
     for (int i = 0; i < 16; ++i) p.scatter_base[i] = scatter->base[i];
 }
 
@@ -1145,8 +1141,7 @@ int tc_wgrad3(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t h_act, u
     p.ldc = n; p.c_slab = d * h; p.experts = experts; p.problems = 3;
     p.m_tiles = ceil_div(m, BM * ctas); p.n_tiles = ceil_div(n, BN);
     p.M = (int)m; p.N = (int)n; p.K = 0; p.segments = 1;
-    const char* together = getenv("QUTAI_MOE_WGRAD_LAUNCHES");  // "3": one launch per product, for comparison
-    if (together && together[0] == '3') {
+    if (kernel_variant(QMOE_VARIANT_WGRAD_PER_PRODUCT)) {  // one launch per product, for comparison
         void* const outs[3] = {p.out0, p.out1, p.out2};
         const int transposed = p.transpose_out;
         for (int i = 0; i < 3; ++i) {

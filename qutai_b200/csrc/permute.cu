@@ -563,3 +563,51 @@ extern "C" int qmoe_normal_fill(uint64_t out, int32_t dtype, int64_t n, double m
     QMOE_LAUNCH_CHECK("normal_fill_kernel");
     return 0;
 }
+
+// ---- row gather: dst[i, :] = src[index[i], :] (16-byte pieces; expert-indexed tables of a few hundred KB) ----
+namespace qmoe {
+namespace {
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int* __restrict__ index, int rows,
+                   long long row_vecs, int src_rows) {
+    const long long total = (long long)rows * row_vecs;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / row_vecs);
+        const int from = index[row];
+        if (from < 0 || from >= src_rows) continue;  // a bad table never becomes a bad address
+        dst[i] = src[(long long)from * row_vecs + (i - (long long)row * row_vecs)];
+    }
+}
+__global__ void __launch_bounds__(256)
+gather_words_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, const int* __restrict__ index, int rows,
+                    long long row_words, int src_rows) {
+    const long long total = (long long)rows * row_words;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / row_words);
+        const int from = index[row];
+        if (from < 0 || from >= src_rows) continue;
+        dst[i] = src[(long long)from * row_words + (i - (long long)row * row_words)];
+    }
+}
+}  // namespace
+}  // namespace qmoe
+
+extern "C" int qmoe_gather_rows(uint64_t src, uint64_t dst, uint64_t index, int32_t rows, int32_t src_rows, int64_t row_bytes,
+                                uint64_t stream_) {
+    if (!src || !dst || !index) return fail_arg("gather_rows: null address");
+    if (src == dst) return fail_arg("gather_rows: the output must not alias the input");
+    if (rows <= 0 || src_rows <= 0 || row_bytes <= 0 || row_bytes % 4) return fail_arg("gather_rows: rows must be positive and a multiple of 4 bytes");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_OTHER, stream);
+    if (row_bytes % 16 == 0 && !((src | dst) & 15u)) {
+        const long long total = (long long)rows * (row_bytes / 16);
+        gather_rows_kernel<<<(int)((total + 255) / 256 > 1184 ? 1184 : (total + 255) / 256), 256, 0, stream>>>(
+            (const uint4*)src, (uint4*)dst, (const int*)index, rows, row_bytes / 16, src_rows);
+    } else {
+        const long long total = (long long)rows * (row_bytes / 4);
+        gather_words_kernel<<<(int)((total + 255) / 256 > 1184 ? 1184 : (total + 255) / 256), 256, 0, stream>>>(
+            (const uint32_t*)src, (uint32_t*)dst, (const int*)index, rows, row_bytes / 4, src_rows);
+    }
+    QMOE_LAUNCH_CHECK("gather_rows_kernel");
+    return 0;
+}

@@ -295,7 +295,9 @@ route_backward_kernel(const float* __restrict__ probs, const float* __restrict__
     }
 }
 
-int check_route(const qmoe_route_t* r) {
+// need_scratch: the three block tables are only used while the routing itself runs (qmoe_route); every
+// consumer of a finished route accepts null there, so a route filled by qmoe_route_static can be passed on.
+int check_route(const qmoe_route_t* r, bool need_scratch) {
     if (!r) return fail_arg("route is null");
     if (r->tokens <= 0) return fail_arg("tokens must be positive (got %lld)", (long long)r->tokens);
     if (r->experts <= 0 || r->experts > kMaxExperts)
@@ -306,15 +308,16 @@ int check_route(const qmoe_route_t* r) {
     if (r->rows_bound < qmoe_rows_bound(r->tokens, r->experts, r->top_k))
         return fail_arg("rows_bound %lld is smaller than qmoe_rows_bound()", (long long)r->rows_bound);
     if (!r->probs || !r->gate_weights || !r->expert_index || !r->dest_row || !r->row_source ||
-        !r->counts || !r->offsets || !r->tile_expert || !r->meta || !r->utilization || !r->aux ||
-        !r->block_counts || !r->block_base || !r->block_colsum)
+        !r->counts || !r->offsets || !r->tile_expert || !r->meta || !r->utilization || !r->aux)
         return fail_arg("route has a null table address");
+    if (need_scratch && (!r->block_counts || !r->block_base || !r->block_colsum))
+        return fail_arg("route has a null scratch table address (block_counts / block_base / block_colsum)");
     return 0;
 }
 
 }  // namespace
 
-int route_check(const qmoe_route_t* r) { return check_route(r); }
+int route_check(const qmoe_route_t* r) { return check_route(r, false); }
 
 }  // namespace qmoe
 
@@ -330,7 +333,7 @@ extern "C" int64_t qmoe_route_blocks(int64_t tokens) {
 }
 
 extern "C" int qmoe_route(const qmoe_route_t* r, uint64_t scores, uint64_t stream_) {
-    if (int rc = check_route(r)) return rc;
+    if (int rc = check_route(r, true)) return rc;
     if (!scores) return fail_arg("scores is null");
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_ROUTE, stream);
@@ -365,7 +368,7 @@ extern "C" int qmoe_route(const qmoe_route_t* r, uint64_t scores, uint64_t strea
 extern "C" int qmoe_route_export_i64(const qmoe_route_t* r, uint64_t indices, uint64_t ids, uint64_t slots,
                                      uint64_t locations, uint64_t counts, int64_t capacity,
                                      uint64_t stream_) {
-    if (int rc = check_route(r)) return rc;
+    if (int rc = check_route(r, false)) return rc;
     const long long A = r->tokens * r->top_k;
     if ((ids || slots) && capacity < A) return fail_arg("capacity %lld is smaller than tokens*top_k", (long long)capacity);
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -381,7 +384,7 @@ extern "C" int qmoe_route_export_i64(const qmoe_route_t* r, uint64_t indices, ui
 
 extern "C" int qmoe_route_backward(const qmoe_route_t* r, uint64_t grad_weights, uint64_t grad_aux,
                                    uint64_t d_scores, uint64_t stream_) {
-    if (int rc = check_route(r)) return rc;
+    if (int rc = check_route(r, false)) return rc;
     if (!d_scores) return fail_arg("d_scores is null");
     cudaStream_t stream = (cudaStream_t)stream_;
     TimedScope timed(KC_ROUTE_BWD, stream);
@@ -419,7 +422,8 @@ extern "C" int qmoe_route_backward(const qmoe_route_t* r, uint64_t grad_weights,
 //
 // The first call on a device looks up the array's device address (cudaGetSymbolAddress, checked)
 // with that device current, and remembers it; make that first call before starting any stream
-// capture.  No cudaMalloc, cudaFree or allocating library routine is called on any path.
+// capture.  The remembered address is written without a lock: two host threads that make the first
+// call at the same moment both look the address up and store the same value.  No cudaMalloc, cudaFree or allocating library routine is called on any path.
 namespace {
 constexpr long long kStaticRouteEntries = 131072;  // entries per table (blocks * experts)
 static __device__ __align__(256) unsigned char g_route_scratch[3 * kStaticRouteEntries * 4];

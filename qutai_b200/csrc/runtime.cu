@@ -28,7 +28,10 @@ const char* kClassNames[KC_COUNT] = {"router_gemm", "route", "permute", "expert_
                                      "combine_backward", "wgrad_gemm", "unpermute", "route_backward",
                                      "cast", "other", "exchange", "optimizer"};
 __device__ int g_device_status;
+std::atomic<int> g_variants[QMOE_VARIANT_COUNT];  // zero-initialised: every kernel in its default form
 }  // namespace
+
+int kernel_variant(int which) { return g_variants[which].load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
     va_list ap;
@@ -61,6 +64,17 @@ int after_launch(const char* name) {
 }
 
 void count_tensor_core_launch() { g_tc_launches.fetch_add(1, std::memory_order_relaxed); }
+
+}  // namespace qmoe
+
+extern "C" int qmoe_test_select_variant(int32_t which, int32_t value) {
+    if (which < 0 || which >= QMOE_VARIANT_COUNT) return qmoe::fail_arg("test_select_variant: unknown selector %d", which);
+    if (value < 0 || value > 1) return qmoe::fail_arg("test_select_variant: value must be 0 (default) or 1");
+    qmoe::g_variants[which].store(value, std::memory_order_relaxed);
+    return 0;
+}
+
+namespace qmoe {
 
 int* device_status_address() {
     int* p = nullptr;
@@ -197,6 +211,14 @@ extern "C" int qmoe_device_status(uint64_t stream, int* status) {
     if (!p) { set_error("device status symbol is not available"); return QMOE_ERR_STATE; }
     QMOE_CUDA(cudaMemcpyAsync(status, p, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     QMOE_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return 0;
+}
+
+extern "C" int qmoe_device_status_async(uint64_t stream, void* host_status) {
+    if (!host_status) return fail_arg("device_status_async: host_status is null");
+    int* p = device_status_address();
+    if (!p) { set_error("device status symbol is not available"); return QMOE_ERR_STATE; }
+    QMOE_CUDA(cudaMemcpyAsync(host_status, p, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     return 0;
 }
 

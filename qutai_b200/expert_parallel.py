@@ -1,6 +1,6 @@
 """Expert-parallel ``SparseMoE``: one process per GPU, tokens sharded by rank (contiguous shards of
-equal size), experts sharded by rank (contiguous blocks of E / world), NCCL all-to-all for dispatch
-and combine.
+equal size), experts sharded by rank (E / world each; contiguous blocks unless a placement map says
+otherwise), rows exchanged by direct stores into peer memory over NVLink or by NCCL send/receive.
 
 The upstream project is single-GPU; this module keeps its layer semantics across ranks: routing is
 decided per token exactly as on one GPU, an expert's rows arrive ordered by source rank — with
@@ -9,9 +9,16 @@ contiguous token shards that is the upstream global (token, slot) order
 tokens (src/qutai/backends/cpu_lm.py:221-229).  Host code is standard-library Python; the NCCL id
 travels through a small file rendezvous (or any callable the caller supplies).
 
-Per step the host waits once for the device: to read the [world, E] matrix of counts that sizes
-the exchanges (the upstream layer also reads its counts in every forward,
-src/qutai/backends/cuda_lm.py:432-434).
+With the NCCL transport the host waits once per step for the device, to read the [world, E] matrix of
+counts that sizes the exchanges (the upstream layer also reads its counts in every forward,
+src/qutai/backends/cuda_lm.py:432-434); with the direct transport it waits for nothing inside a step.
+
+Expert placement.  ``placement[e]`` names the rank that owns expert ``e``.  Inside the layer experts are
+numbered physically — rank ``p`` owns physical experts ``p * L .. p * L + L - 1``, its logical experts in
+ascending order — and every kernel works on physical numbers; only the small expert-indexed tables
+(router weight rows, their gradient, utilisation, counts) are permuted at the layer's boundary, so
+``router.weight``, ``utilization``, ``last_counts`` and the parameter names (``expert_ids``) keep the
+model's own expert numbering (src/qutai/lm/decoder.py:57-68).
 """
 from __future__ import annotations
 
@@ -129,6 +136,70 @@ def file_all_gather(directory, tag, rank, world, payload, timeout=120.0, poll=0.
         time.sleep(poll)
 
 
+class FileExchange:
+    """Repeated all-gathers between the ranks of one job through files in one directory.  Every exchange
+    uses a tag of its own (``<name>_<n>``, n counted the same way on every rank), so a rank that is one
+    exchange ahead can never be handed a file a slower rank wrote for the previous one; the rank's own
+    files are removed by ``close()``, after which the directory can be reused."""
+
+    def __init__(self, directory, name, rank, world, timeout=120.0):
+        self.directory, self.name, self.rank, self.world, self.timeout = directory, name, rank, world, timeout
+        self.exchanges = 0
+
+    def all_gather(self, payload):
+        self.exchanges += 1
+        return file_all_gather(self.directory, f"{self.name}_{self.exchanges}", self.rank, self.world, payload, self.timeout)
+
+    def close(self):
+        for n in range(1, self.exchanges + 1):
+            try:
+                os.remove(os.path.join(self.directory, f"{self.name}_{n}.{self.rank}"))
+            except OSError:
+                pass
+        self.exchanges = 0
+
+
+def contiguous_placement(experts, world):
+    """Expert ``e`` on rank ``e // (experts / world)``."""
+    if experts % world:
+        raise ValueError("the number of experts must be a multiple of the number of ranks")
+    return [e // (experts // world) for e in range(experts)]
+
+
+def balanced_placement(counts, world):
+    """Load-aware placement from per-expert row counts: longest-processing-time greedy (experts by falling
+    count, each to the least loaded rank that still has a free slot).  Returns ``placement[e] = rank``."""
+    experts = len(counts)
+    if experts % world:
+        raise ValueError("the number of experts must be a multiple of the number of ranks")
+    slots = experts // world
+    loads, filled, placement = [0] * world, [0] * world, [0] * experts
+    for e in sorted(range(experts), key=lambda i: (-counts[i], i)):
+        p = min((r for r in range(world) if filled[r] < slots), key=lambda r: (loads[r], r))
+        placement[e] = p
+        loads[p] += counts[e]
+        filled[p] += 1
+    return placement
+
+
+def physical_numbering(placement, world):
+    """``(physical_of_logical, logical_of_physical)`` for a placement: rank ``p`` owns physical experts
+    ``p * L + j`` where ``j`` counts its logical experts in ascending order.  Raises when a rank does not
+    own exactly E / world experts."""
+    experts = len(placement)
+    if experts % world:
+        raise ValueError("the number of experts must be a multiple of the number of ranks")
+    slots = experts // world
+    owned = [[e for e in range(experts) if placement[e] == p] for p in range(world)]
+    if any(not 0 <= p < world for p in placement) or any(len(o) != slots for o in owned):
+        raise ValueError(f"every rank must own exactly {slots} experts")
+    logical_of_physical = [e for p in range(world) for e in owned[p]]
+    physical_of_logical = [0] * experts
+    for physical, e in enumerate(logical_of_physical):
+        physical_of_logical[e] = physical
+    return physical_of_logical, logical_of_physical
+
+
 def init_communicator(rank, world, share=None, rendezvous_path=None, timeout=60.0):
     """Create the process' NCCL communicator.  ``share(payload_or_None) -> bytes`` broadcasts rank
     0's 128-byte id (rank 0 passes it, the others pass None); without it a file rendezvous at
@@ -154,6 +225,9 @@ def init_communicator(rank, world, share=None, rendezvous_path=None, timeout=60.
 
 def finalize_communicator(abort=False):
     lib.call("qmoe_ep_finalize", 1 if abort else 0)
+    for exchange in _IPC_EXCHANGES.values():   # this process' rendezvous files of the job
+        exchange.close()
+    _IPC_EXCHANGES.clear()
 
 
 def _segments(triples):
@@ -166,25 +240,33 @@ def _segments(triples):
 # ------------------------------------------------------------------------------------------------
 # the layer
 # ------------------------------------------------------------------------------------------------
+_IPC_EXCHANGES = {}   # job token -> FileExchange of this process (the default channel for swapping IPC handles)
+
+
 class ExpertParallelMoE:
     """``SparseMoE`` over ``world`` GPUs.  Same constructor fields as the single-GPU layer plus
-    ``rank`` / ``world``; ``experts`` holds only this rank's E / world experts (global expert
-    ``rank * E_loc + j``), ``router`` is replicated and its gradient is summed over ranks."""
+    ``rank`` / ``world``; ``experts`` holds only this rank's E / world experts (``expert_ids[j]`` is the
+    model's number of ``experts[j]``), ``router`` is replicated and its gradient is summed over ranks."""
 
     def __init__(self, config, *, rank, world, device="cuda", dtype="float32", seed=None, engine="auto", stream=0,
-                 transport="nccl", gather=None):
-        """``transport``: "nccl" = grouped NCCL send/receive sized by counts the host reads once per
-        step; "p2p" = rows pushed straight into the peers' buffers over NVLink (CUDA IPC mappings,
-        destinations computed on the device, no host read in the forward).  ``gather(payload) ->
-        [payload of rank 0, ...]`` all-gathers a bytes object between the ranks (needed once for
-        "p2p" to swap the IPC handles); without it a directory rendezvous is used."""
+                 transport="p2p", barrier="flags", placement=None, gather=None):
+        """``transport``: "p2p" (default) = rows pushed straight into the peers' buffers over NVLink (CUDA IPC
+        mappings, destinations computed on the device, no host read in the forward); "nccl" = grouped NCCL
+        send/receive sized by counts the host reads once per step.  ``barrier`` (p2p only): "flags" = the
+        bounded flag barrier over peer memory, which also carries the count all-gather; "nccl" = NCCL
+        collectives instead.  ``placement[e]`` = rank owning expert ``e`` (default: contiguous blocks); every
+        rank passes the same list.  ``gather(payload) -> [payload of rank 0, ...]`` all-gathers a bytes object
+        between the ranks (needed for "p2p" to swap the IPC handles); without it files in a per-job directory
+        are used."""
         if device != "cuda" or dtype != "float32":
             raise ValueError("parameters are float32 on device='cuda'")
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' or 'p2p'")
+        if barrier not in ("flags", "nccl"):
+            raise ValueError("barrier must be 'flags' or 'nccl'")
         if world > lib.EP_MAX_RANKS:
             raise ValueError(f"at most {lib.EP_MAX_RANKS} ranks")
-        self.transport, self._gather = transport, gather
+        self.transport, self.barrier, self._gather = transport, barrier, gather
         d, E, h = config.d_model, config.n_experts, config.d_expert
         if E % world:
             raise ValueError("n_experts must be a multiple of the number of ranks")
@@ -192,42 +274,116 @@ class ExpertParallelMoE:
         self.top_k, self.n_experts, self.d_model, self.d_expert = config.top_k, E, d, h
         self.local_experts = L = E // world
         self.engine = {"auto": lib.ENGINE_AUTO, "simt": lib.ENGINE_SIMT, "tcgen05": lib.ENGINE_TCGEN05}[engine]
+        self._down_std = 0.02 / sqrt(2 * config.n_layers)
+        router = DeviceStorage(E * d, "float32")
+        router.fill_normal(0.0, 0.02, 0x5EED if seed is None else seed, stream)
+        self.router = Projection(Tensor(router, (E, d), requires_grad=True))
+        self._set_placement(contiguous_placement(E, world) if placement is None else list(placement))
         self._gate = DeviceStorage(L * h * d, "float32")
         self._up = DeviceStorage(L * h * d, "float32")
         self._down = DeviceStorage(L * d * h, "float32")
-        router = DeviceStorage(E * d, "float32")
-
-        def fill(storage, std, key):
-            lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std,
-                     (0x5EED if key is None else key) & (2 ** 64 - 1), stream)
-
-        fill(router, 0.02, seed)
-        self.router = Projection(Tensor(router, (E, d), requires_grad=True))
-        experts = []
-        for j in range(L):
-            i = rank * L + j  # global expert index decides the generator key, as on one GPU
-            views = (self._gate.view(j * h * d, h * d), self._up.view(j * h * d, h * d), self._down.view(j * d * h, d * h))
+        self._make_experts()
+        for j, i in enumerate(self.expert_ids):   # the model's expert number decides the generator key, as on one GPU
             base = None if seed is None else seed + 1 + 3 * i
-            fill(views[0], 0.02, base)
-            fill(views[1], 0.02, None if base is None else base + 1)
-            fill(views[2], 0.02 / sqrt(2 * config.n_layers), None if base is None else base + 2)
-            experts.append(SwiGLU(Tensor(views[0], (h, d), requires_grad=True), Tensor(views[1], (h, d), requires_grad=True),
-                                  Tensor(views[2], (d, h), requires_grad=True)))
-        self.experts = tuple(experts)
+            expert = self.experts[j]
+            expert.gate.weight.storage.fill_normal(0.0, 0.02, 0x5EED if base is None else base, stream)
+            expert.up.weight.storage.fill_normal(0.0, 0.02, 0x5EED if base is None else base + 1, stream)
+            expert.down.weight.storage.fill_normal(0.0, self._down_std, 0x5EED if base is None else base + 2, stream)
         self.utilization = None
         self._side = None   # second stream and its events: work that nothing on the main stream waits for soon
-        self.refresh_operands = True  # False: keep the bf16 weight copies of the first forward (fixed weights, serving)
+        # "auto": rebuild the bf16 weight copies only after a weight storage was written (DeviceStorage.generation);
+        # True: at every forward; False: never after the first forward
+        self.refresh_operands = "auto"
         self._sequence = 0  # barriers issued so far (the flag barrier's growing sequence number)
         self._work = None
         self._saved = None
 
+    # ------------------------------------------------------------------------------------------
+    def _set_placement(self, placement):
+        E = self.n_experts
+        if len(placement) != E:
+            raise ValueError("placement needs one rank per expert")
+        self._physical_of_logical, self._logical_of_physical = physical_numbering(placement, self.world)
+        self.placement = tuple(placement)
+        L = self.local_experts
+        self.expert_ids = tuple(self._logical_of_physical[self.rank * L:(self.rank + 1) * L])
+        self._identity = self._logical_of_physical == list(range(E))
+        if not self._identity:
+            ints = lambda values: DeviceStorage.from_bytes(b"".join(int(v).to_bytes(4, "little") for v in values), "int32")
+            self._to_physical = ints(self._logical_of_physical)   # gather index: physical row p <- logical row
+            self._to_logical = ints(self._physical_of_logical)    # gather index: logical row e <- physical row
+            self._router_physical = DeviceStorage(E * self.d_model, "float32")
+
+    def _make_experts(self):
+        L, h, d = self.local_experts, self.d_expert, self.d_model
+        experts = []
+        for j in range(L):
+            views = (self._gate.view(j * h * d, h * d), self._up.view(j * h * d, h * d), self._down.view(j * d * h, d * h))
+            experts.append(SwiGLU(Tensor(views[0], (h, d), requires_grad=True), Tensor(views[1], (h, d), requires_grad=True),
+                                  Tensor(views[2], (d, h), requires_grad=True)))
+        self.experts = tuple(experts)
+
     def parameters(self):
         return (*self.router.parameters(), *(p for expert in self.experts for p in expert.parameters()))
 
+    def named_expert_parameters(self, prefix="experts"):
+        """``(name, parameter)`` pairs of this rank's expert weights under the model's expert numbers
+        (``experts.{e}.gate.weight`` ..., the names src/qutai/lm/decoder.py:57-68 gives them on one GPU)."""
+        for j, e in enumerate(self.expert_ids):
+            expert = self.experts[j]
+            yield f"{prefix}.{e}.gate.weight", expert.gate.weight
+            yield f"{prefix}.{e}.up.weight", expert.up.weight
+            yield f"{prefix}.{e}.down.weight", expert.down.weight
+
+    def rebalance(self, counts=None, placement=None):
+        """Move the expert weights to a new placement: ``placement`` if given, else the load-balanced one for
+        the per-expert ``counts`` (default: the counts of the last forward).  Every rank calls it with the same
+        arguments; the weights travel through one grouped NCCL exchange per kind.  ``experts`` and
+        ``expert_ids`` are rebuilt (new parameter objects over the moved weights), gradients are dropped:
+        call it before an optimizer is created, or move the optimizer's moments the same way with
+        ``move_expert_tensors``.  Returns the new placement."""
+        if placement is None:
+            placement = balanced_placement(list(self.last_counts if counts is None else counts), self.world)
+        old_ids = self.expert_ids
+        old_owner = dict(zip(range(self.n_experts), self.placement))
+        self._set_placement(list(placement))
+        h, d = self.d_expert, self.d_model
+        moved = [self.move_expert_tensors(storage, rows, width, old_ids, old_owner)
+                 for storage, rows, width in ((self._gate, h, d), (self._up, h, d), (self._down, d, h))]
+        self._gate, self._up, self._down = moved
+        self._make_experts()
+        self.router.weight.grad = None
+        self._work, self._saved = self._close_workspace(), None
+        return self.placement
+
+    def move_expert_tensors(self, stacked, rows, width, old_ids, old_owner):
+        """One stacked fp32 buffer of per-expert blocks (``rows`` x ``width`` each, in the slot order of
+        ``old_ids``) re-sharded to the layer's current placement; returns the new stacked storage."""
+        s = self.stream
+        out = DeviceStorage(stacked.size, "float32")
+        sends = [(self.placement[e], j * rows, rows) for j, e in enumerate(old_ids)]
+        recvs = [(old_owner[e], j * rows, rows) for j, e in enumerate(self.expert_ids)]
+        (sa, sn), (ra, rn) = _segments(sends), _segments(recvs)
+        lib.call("qmoe_ep_exchange", stacked.ptr, sa, sn, out.ptr, ra, rn, width, lib.QMOE_F32, s)
+        lib.call("qmoe_stream_sync", s)   # the old buffer may be released once the exchange has run
+        out.touch()
+        return out
+
     # ------------------------------------------------------------------------------------------
+    def _close_workspace(self):
+        """Unmap the peers' buffers of the workspace that is being replaced."""
+        work = self._work
+        if work is not None and work.get("opened"):
+            lib.call("qmoe_stream_sync", self.stream)
+            for address in work["opened"]:
+                lib.load().qmoe_ep_ipc_close(address)
+            work["opened"] = []
+        return None
+
     def _workspace(self, tokens, dtype):
         if self._work is not None and self._work["key"] == (tokens, dtype):
             return self._work
+        self._work = self._close_workspace()
         E, L, k, d, h, N = self.n_experts, self.local_experts, self.top_k, self.d_model, self.d_expert, self.world
         A = tokens * k
         Rt = lib.rows_bound(tokens, E, k)
@@ -252,6 +408,8 @@ class ExpertParallelMoE:
             ret_table=S(Rx, "int32"), dest_base=S(E, "int32"), barrier=S.zeros(1, "int32"),
             flags=S.zeros(lib.EP_MAX_RANKS, "int32"),
         )
+        if not self._identity:   # the expert-indexed outputs in the model's numbering
+            buf.update(utilization_logical=S(E, "float32"), d_w_router_logical=S(E * d, "float32"))
         if self.transport == "p2p":
             buf["dx_recv"] = S(Rx * d, dtype)  # dX gets its own buffer so it can travel while the weight gradients run
         if dtype == "bfloat16":
@@ -276,37 +434,41 @@ class ExpertParallelMoE:
             ex.w_gate, ex.w_up, ex.w_down = buf["w_gate"].ptr, buf["w_up"].ptr, buf["w_down"].ptr
         else:
             ex.w_gate, ex.w_up, ex.w_down = self._gate.ptr, self._up.ptr, self._down.ptr
-        host, stats_event = ctypes.c_void_p(), ctypes.c_uint64()
+        host, status, stats_event = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_uint64()
         lib.call("qmoe_host_alloc", ctypes.byref(host), 4 * N * 2 * E)
+        lib.call("qmoe_host_alloc", ctypes.byref(status), 8)
         lib.call("qmoe_event_create", ctypes.byref(stats_event))
-        grad_views = [Tensor(buf["d_w_router"], (E, d))]
+        host_status = ctypes.cast(status, ctypes.POINTER(ctypes.c_int32))
+        host_status[0] = host_status[1] = 0
+        router_grad = buf["d_w_router"] if self._identity else buf["d_w_router_logical"]
+        grad_views = [Tensor(router_grad, (E, d))]
         for j in range(L):
             grad_views.append((Tensor(buf["d_w_gate"].view(j * h * d, h * d), (h, d)),
                                Tensor(buf["d_w_up"].view(j * h * d, h * d), (h, d)),
                                Tensor(buf["d_w_down"].view(j * d * h, d * h), (d, h))))
         self._work = dict(key=(tokens, dtype), buf=buf, token_route=token_route, expert_route=expert_route, experts=ex,
-                          host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), grad_views=grad_views,
-                          stats_event=stats_event.value)
+                          host_stats=ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), host_status=host_status,
+                          grad_views=grad_views, stats_event=stats_event.value, opened=[])
         tensor_cores = dtype == "bfloat16" and self.engine != lib.ENGINE_SIMT and d % 8 == 0 and h % 8 == 0
         # fused: the producing kernels (permute, combine-backward, and the tensor-core epilogues of the down
         # projection and of dX) store their rows straight into the owning GPU's buffer
         self._work["fused"] = self.transport == "p2p" and tensor_cores
+        if self._side is None:
+            side = ctypes.c_uint64()
+            lib.call("qmoe_stream_create", ctypes.byref(side))
+            self._side = {"stream": side.value}
+            for name in ("ready", "done", "stats", "grads", "reduced", "ended"):
+                event = ctypes.c_uint64()
+                lib.call("qmoe_event_create", ctypes.byref(event))
+                self._side[name] = event.value
         if self.transport == "p2p":
-            self._work["peers"] = self._open_peers(buf)
+            self._work["peers"] = self._open_peers(buf, self._work["opened"])
             # barriers and the count all-gather go through flags in peer memory unless NCCL is asked for
-            self._work["flag_barrier"] = os.environ.get("QUTAI_MOE_EP_BARRIER", "flags") != "nccl"
-            if self._side is None:
-                side = ctypes.c_uint64()
-                lib.call("qmoe_stream_create", ctypes.byref(side))
-                self._side = {"stream": side.value}
-                for name in ("ready", "done", "stats", "grads", "reduced"):
-                    event = ctypes.c_uint64()
-                    lib.call("qmoe_event_create", ctypes.byref(event))
-                    self._side[name] = event.value
+            self._work["flag_barrier"] = self.barrier == "flags"
         return self._work
 
-    def _open_peers(self, buf):
-        """Swap CUDA IPC handles of the five buffers other ranks write into and map every peer's."""
+    def _open_peers(self, buf, opened):
+        """Swap CUDA IPC handles of the buffers other ranks write into and map every peer's."""
         names = ("x_recv", "dy_recv", "y_send", "dy_send", "ret_table", "flags", "stats_all")
         lib.call("qmoe_stream_sync", 0)  # the zero-fill of the flag array must have run before any peer can write it
         payload = b""
@@ -314,7 +476,14 @@ class ExpertParallelMoE:
             handle = ctypes.create_string_buffer(64)
             lib.call("qmoe_ep_ipc_export", buf[name].ptr, ctypes.cast(handle, ctypes.c_void_p))
             payload += handle.raw
-        gather = self._gather or (lambda data: file_all_gather(default_rendezvous_dir(), "ipc_" + _JOB["token"], self.rank, self.world, data))
+        gather = self._gather
+        if gather is None:
+            # one exchange object per job and process: every exchange (a second layer of the model, a workspace
+            # rebuilt for another token count) gets a tag of its own, counted alike on all ranks
+            token = _JOB["token"]
+            if token not in _IPC_EXCHANGES:
+                _IPC_EXCHANGES[token] = FileExchange(default_rendezvous_dir(), "ipc_" + token, self.rank, self.world)
+            gather = _IPC_EXCHANGES[token].all_gather
         everyone = gather(payload)
         if len(everyone) != self.world or any(len(item) != 64 * len(names) for item in everyone):
             raise ValueError("the IPC handle all-gather returned a wrong shape")
@@ -324,10 +493,11 @@ class ExpertParallelMoE:
                 if p == self.rank:
                     address[name][p] = buf[name].ptr
                 else:
-                    opened = ctypes.c_uint64()
+                    mapped = ctypes.c_uint64()
                     handle = ctypes.create_string_buffer(everyone[p][64 * i: 64 * (i + 1)], 64)
-                    lib.call("qmoe_ep_ipc_open", ctypes.cast(handle, ctypes.c_void_p), ctypes.byref(opened))
-                    address[name][p] = opened.value
+                    lib.call("qmoe_ep_ipc_open", ctypes.cast(handle, ctypes.c_void_p), ctypes.byref(mapped))
+                    address[name][p] = mapped.value
+                    opened.append(mapped.value)
         peers = {}
         for name in ("x_recv", "dy_recv", "y_send", "dy_send", "flags", "stats_all"):
             table = lib.Peers()
@@ -349,20 +519,46 @@ class ExpertParallelMoE:
         else:
             lib.call("qmoe_ep_barrier", w["buf"]["barrier"].ptr, self.stream)
 
+    def _raise_on_status(self, code):
+        if code:
+            what = ("a rank did not arrive at an expert-parallel barrier within the time limit" if code == 201
+                    else "a kernel gave up a bounded wait")
+            raise RuntimeError(f"{what} (device status {code}): the results of the steps in flight are invalid; "
+                               "qmoe_device_status_clear after the cause has been dealt with")
+
     def _host_counts(self, w):
-        """[world][E] counts of the last forward as Python ints (waits for that forward's count exchange
-        only, not for work enqueued after it)."""
+        """[world][E] counts (physical expert numbers) of the last forward as Python ints.  Waits for that
+        forward's count exchange only, not for work enqueued after it, and raises if a kernel up to that point
+        (or in the step before) reported a failed bounded wait."""
         lib.call("qmoe_event_sync", w["stats_event"])
+        self._raise_on_status(w["host_status"][0] or w["host_status"][1])
         stats, E = w["host_stats"], self.n_experts
         return [[stats[p * 2 * E + e] for e in range(E)] for p in range(self.world)]
 
+    def check_status(self):
+        """Wait for everything enqueued on the layer's stream and raise if any kernel reported a failed bounded
+        wait (a rank missing at a barrier): the way to be certain about a step's results before using them."""
+        self._raise_on_status(lib.device_status(self.stream))
+
     @property
     def last_counts(self):
-        """Global per-expert counts (all ranks' tokens) of the last forward."""
+        """Global per-expert counts (all ranks' tokens, the model's expert numbers) of the last forward."""
         if self._saved is None:
             return (0,) * self.n_experts
         counts = self._host_counts(self._saved[0])
-        return tuple(sum(counts[p][e] for p in range(self.world)) for e in range(self.n_experts))
+        physical = [sum(counts[p][e] for p in range(self.world)) for e in range(self.n_experts)]
+        return tuple(physical[self._physical_of_logical[e]] for e in range(self.n_experts))
+
+    def _router_operand(self, s):
+        """Address of the router weight with rows in physical expert order."""
+        weight = self.router.weight.storage
+        if self._identity:
+            return weight.ptr
+        if not self._router_physical.is_derived_from(weight):
+            E, d = self.n_experts, self.d_model
+            lib.call("qmoe_gather_rows", weight.ptr, self._router_physical.ptr, self._to_physical.ptr, E, E, 4 * d, s)
+            self._router_physical.mark_derived_from(weight)
+        return self._router_physical.ptr
 
     def forward(self, x):
         """``x``: this rank's (T / world, d) shard.  Returns ``(y, aux)``; ``aux`` is the global
@@ -374,16 +570,22 @@ class ExpertParallelMoE:
         code, s = lib.DTYPE_CODES[dtype], self.stream
         w = self._workspace(tokens, dtype)
         buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
+        side = self._side
+
         def cast_weights(stream):
-            if dtype == "bfloat16" and (self.refresh_operands or not w.get("operands_built")):
-                w["operands_built"] = True
-                n = L * h * d
-                lib.call("qmoe_cast_bf16", self._gate.ptr, buf["w_gate"].ptr, n, stream)
-                lib.call("qmoe_cast_bf16", self._up.ptr, buf["w_up"].ptr, n, stream)
-                lib.call("qmoe_cast_bf16", self._down.ptr, buf["w_down"].ptr, n, stream)
+            if dtype != "bfloat16":
+                return
+            pairs = ((self._gate, buf["w_gate"]), (self._up, buf["w_up"]), (self._down, buf["w_down"]))
+            if w.get("operands_built") and self.refresh_operands is not True:
+                if self.refresh_operands is False or all(copy.is_derived_from(master) for master, copy in pairs):
+                    return
+            w["operands_built"] = True
+            for master, copy in pairs:
+                lib.call("qmoe_cast_bf16", master.ptr, copy.ptr, master.size, stream)
+                copy.mark_derived_from(master)
 
         def route_and_plan():
-            lib.call("qmoe_router_forward", storage.ptr, code, self.router.weight.storage.ptr, buf["scores"].ptr,
+            lib.call("qmoe_router_forward", storage.ptr, code, self._router_operand(s), buf["scores"].ptr,
                      buf["router_partials"].ptr, tokens, d, E, s)
             lib.call("qmoe_route", tr, buf["scores"].ptr, s)
             # the all-gather is also the point no rank passes before every rank has finished its previous step
@@ -392,16 +594,18 @@ class ExpertParallelMoE:
                 lib.call("qmoe_ep_pack_stats", tr, buf["stats_local"].ptr, s)
                 lib.call("qmoe_ep_flag_barrier", ctypes.byref(w["peers"]["flags"]), self._sequence, buf["stats_local"].ptr,
                          2 * E, ctypes.byref(w["peers"]["stats_all"]), s)
-                # the host's copy of the counts is only read when gradients are handed out: it leaves on the side stream
-                side = self._side
+                # the host's copy of the counts is only read when gradients are handed out: it leaves on the side
+                # stream, together with the status word the barrier kernels report a missing rank in
                 lib.call("qmoe_event_record", side["stats"], s)
                 lib.call("qmoe_stream_wait_event", side["stream"], side["stats"])
                 lib.call("qmoe_memcpy_d2h", ctypes.cast(w["host_stats"], ctypes.c_void_p), buf["stats_all"].ptr, 4 * N * 2 * E,
                          side["stream"])
+                lib.call("qmoe_device_status_async", side["stream"], ctypes.cast(w["host_status"], ctypes.c_void_p))
                 lib.call("qmoe_event_record", w["stats_event"], side["stream"])
             else:
                 lib.call("qmoe_ep_gather_stats", tr, buf["stats_local"].ptr, buf["stats_all"].ptr,
                          ctypes.cast(w["host_stats"], ctypes.c_void_p), s)
+                lib.call("qmoe_device_status_async", s, ctypes.cast(w["host_status"], ctypes.c_void_p))
                 lib.call("qmoe_event_record", w["stats_event"], s)
             lib.call("qmoe_ep_plan", buf["stats_all"].ptr, tr, xr, tokens * N, s)
             lib.call("qmoe_ep_zero_pad_rows", xr, buf["x_recv"].ptr, code, d, s)
@@ -410,12 +614,12 @@ class ExpertParallelMoE:
         acts = (buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["y_recv"].ptr)
         if self.transport == "p2p":
             peers = w["peers"]
-            side, ready, done = self._side["stream"], self._side["ready"], self._side["done"]
+            ready, done = side["ready"], side["done"]
             # the bf16 weight copies are refreshed on the side stream while this stream routes and dispatches
             lib.call("qmoe_event_record", ready, s)
-            lib.call("qmoe_stream_wait_event", side, ready)
-            cast_weights(side)
-            lib.call("qmoe_event_record", done, side)
+            lib.call("qmoe_stream_wait_event", side["stream"], ready)
+            cast_weights(side["stream"])
+            lib.call("qmoe_event_record", done, side["stream"])
             route_and_plan()
             lib.call("qmoe_ep_dest_base", buf["stats_all"].ptr, E, L, buf["dest_base"].ptr, s)
             if w["fused"]:
@@ -444,7 +648,11 @@ class ExpertParallelMoE:
             lib.call("qmoe_expert_forward", xr, ex, *acts, s)
             lib.call("qmoe_ep_exchange", buf["y_recv"].ptr, ra, rn, buf["y_send"].ptr, sa, sn, d, code, s)
         lib.call("qmoe_combine", tr, buf["y_send"].ptr, out.ptr, code, d, s)
-        self.utilization = Tensor(buf["utilization"], (E,))
+        if self._identity:
+            self.utilization = Tensor(buf["utilization"], (E,))
+        else:
+            lib.call("qmoe_gather_rows", buf["utilization"].ptr, buf["utilization_logical"].ptr, self._to_logical.ptr, E, E, 4, s)
+            self.utilization = Tensor(buf["utilization_logical"], (E,))
         self._saved = (w, storage, shape)
         return Tensor(out, shape), Tensor(buf["aux"], ())
 
@@ -460,6 +668,7 @@ class ExpertParallelMoE:
         tokens, dtype = x_storage.size // d, x_storage.dtype
         code, s = lib.DTYPE_CODES[dtype], self.stream
         buf, tr, xr, ex = w["buf"], ctypes.byref(w["token_route"]), ctypes.byref(w["expert_route"]), ctypes.byref(w["experts"])
+        side = self._side
         ga = 0
         if grad_aux is not None:
             # the routing-backward kernel scales by E / (local tokens); the loss is over all ranks' tokens
@@ -476,21 +685,24 @@ class ExpertParallelMoE:
         lib.call("qmoe_ep_zero_pad_rows", xr, buf["dy_recv"].ptr, code, d, s)
         grads = (buf["d_w_gate"].ptr, buf["d_w_up"].ptr, buf["d_w_down"].ptr)
         saved = (buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["d_h"].ptr, buf["d_g"].ptr, buf["d_u"].ptr)
+        overlapped = bool(w.get("flag_barrier"))   # no other NCCL call in the step: the all-reduce can leave the main stream
 
         def router_backward():
             lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
-            lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
+            lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self._router_operand(s),
                      buf["dx_router"].ptr, buf["d_w_router"].ptr, buf["router_partials"].ptr, tokens, d, E, s)
-            if w.get("flag_barrier"):
-                # no other NCCL call in the step: the all-reduce runs on the side stream, beside the last barrier
-                # and the un-permute, and is waited for where the router gradient is handed out
-                side = self._side
+            # overlapped: the all-reduce runs on the side stream, beside the last barrier and the un-permute, and
+            # is waited for where the router gradient is handed out
+            stream = side["stream"] if overlapped else s
+            if overlapped:
                 lib.call("qmoe_event_record", side["grads"], s)
-                lib.call("qmoe_stream_wait_event", side["stream"], side["grads"])
-                lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, side["stream"])
-                lib.call("qmoe_event_record", side["reduced"], side["stream"])
-            else:
-                lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, s)
+                lib.call("qmoe_stream_wait_event", stream, side["grads"])
+            lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, stream)
+            if not self._identity:   # rows back into the model's expert order
+                lib.call("qmoe_gather_rows", buf["d_w_router"].ptr, buf["d_w_router_logical"].ptr, self._to_logical.ptr,
+                         E, E, 4 * d, stream)
+            if overlapped:
+                lib.call("qmoe_event_record", side["reduced"], stream)
 
         if self.transport == "p2p" and w["fused"]:
             peers = w["peers"]
@@ -502,7 +714,7 @@ class ExpertParallelMoE:
             lib.call("qmoe_ep_expert_dx_push", xr, ex, buf["d_g"].ptr, buf["d_u"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["dy_send"]), s)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 2, s)
             router_backward()
-            if w.get("flag_barrier"):  # peers overwrite the gathered counts after this barrier: the host's copy has left by then
+            if overlapped:  # peers overwrite the gathered counts after this barrier: the host's copy has left by then
                 lib.call("qmoe_stream_wait_event", s, w["stats_event"])
             self._barrier(w)
         elif self.transport == "p2p":
@@ -513,7 +725,7 @@ class ExpertParallelMoE:
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 3, s)
             lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dx_recv"].ptr, ctypes.byref(peers["dy_send"]), 0, L, 0, code, d, s)
             router_backward()
-            if w.get("flag_barrier"):
+            if overlapped:
                 lib.call("qmoe_stream_wait_event", s, w["stats_event"])
             self._barrier(w)
         else:
@@ -525,12 +737,17 @@ class ExpertParallelMoE:
             router_backward()
         dx = DeviceStorage(x_storage.size, dtype)
         lib.call("qmoe_unpermute_reduce", tr, buf["dy_send"].ptr, buf["dx_router"].ptr, dx.ptr, code, d, s)
+        # the status word at the end of the step leaves on the side stream; it is looked at together with the next
+        # step's counts (or by check_status), so the host still waits for nothing here
+        lib.call("qmoe_event_record", side["ended"], s)
+        lib.call("qmoe_stream_wait_event", side["stream"], side["ended"])
+        lib.call("qmoe_device_status_async", side["stream"], ctypes.cast(ctypes.addressof(w["host_status"].contents) + 4, ctypes.c_void_p))
         # which local experts received rows decides who gets a gradient object: host logic on the forward's
         # counts, read only now so that the device never waits for the host inside the step
         counts = self._host_counts(w)
         received = [sum(counts[p][self.rank * L + j] for p in range(N)) for j in range(L)]
-        if w.get("flag_barrier"):
-            lib.call("qmoe_stream_wait_event", s, self._side["reduced"])
+        if overlapped:
+            lib.call("qmoe_stream_wait_event", s, side["reduced"])
         _accumulate(self.router.weight, views[0], s)
         for j, expert in enumerate(self.experts):
             if not received[j]:

@@ -131,8 +131,7 @@ class SparseMoE:
         def fill(storage, std, tensor_seed):
             # one generator stream per parameter tensor, keyed like upstream: router seed, expert i
             # gate seed+1+3i, up +1, down +2 (src/qutai/lm/layers.py:355-371, :292-308)
-            key = 0x5EED if tensor_seed is None else tensor_seed
-            lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std, key & (2 ** 64 - 1), stream)
+            storage.fill_normal(0.0, std, 0x5EED if tensor_seed is None else tensor_seed, stream)
 
         fill(router, 0.02, seed)
         self.router = Projection(Tensor(router, (E, d), requires_grad=True))
@@ -148,10 +147,11 @@ class SparseMoE:
                                   Tensor(views[2], (d, h), requires_grad=True)))
         self.experts = tuple(experts)
         self.utilization = None
-        # True (training): the bf16 operand copies of the fp32 weights are rebuilt at every forward, because an
-        # optimizer may have changed the weights.  A serving loop whose weights are fixed sets it to False after
-        # its first forward.
-        self.refresh_operands = True
+        # "auto": the bf16 operand copies of the fp32 weights are rebuilt by a forward only when a weight storage
+        # was written since they were made (``DeviceStorage.generation``; upstream pays nothing either, it rounds
+        # while staging tiles, src/qutai/backends/cuda/gemm.cu:122-127).  True rebuilds at every forward (for
+        # weights that are written through raw addresses), False never after the first forward.
+        self.refresh_operands = "auto"
         self._counts_host = None
         self._counts_valid = False
         self._zero_counts = (0,) * E
@@ -165,8 +165,8 @@ class SparseMoE:
     def operand_shadows(self, tokens=None):
         """``{parameter: bf16 storage}`` of the tensor-core operand copies of the expert weights (those of the
         last bf16 forward, or of the workspace for ``tokens``).  An optimizer that writes the rounded weights
-        there (``qutai_b200.optim.AdamW(shadows=...)``) makes the per-forward conversion unnecessary: set
-        ``refresh_operands = False`` once the first forward has built them."""
+        there (``qutai_b200.optim.AdamW(shadows=...)``) keeps them current across its steps, so the forward
+        after a step converts nothing (with ``refresh_operands`` left at "auto")."""
         works = [w for (t, dtype), w in self._work.items() if dtype == "bfloat16" and (tokens is None or t == tokens)]
         if self._saved is not None and any(w is self._saved[0] for w in works):
             works = [self._saved[0]]
@@ -257,6 +257,25 @@ class SparseMoE:
         self._work = {key: work}  # one token count at a time keeps memory bounded
         return work
 
+    def _operands_current(self, work):
+        """True when this forward can keep the bf16 operand copies it finds in the workspace."""
+        buf = work["buf"]
+        if "w_gate" not in buf or not work.get("operands_built") or self.refresh_operands is True:
+            return False
+        if self.refresh_operands is False:
+            return True
+        return (buf["w_gate"].is_derived_from(self._gate) and buf["w_up"].is_derived_from(self._up)
+                and buf["w_down"].is_derived_from(self._down))
+
+    def _operands_made(self, work):
+        """A forward that converted the weights has been enqueued: the copies follow the weights as they are now."""
+        buf = work["buf"]
+        work["operands_built"] = True
+        if "w_gate" in buf:
+            buf["w_gate"].mark_derived_from(self._gate)
+            buf["w_up"].mark_derived_from(self._up)
+            buf["w_down"].mark_derived_from(self._down)
+
     def __call__(self, x):
         return self.forward(x)
 
@@ -274,13 +293,15 @@ class SparseMoE:
         out = DeviceStorage(storage.size, storage.dtype)
         layer.x, layer.out = storage.ptr, out.ptr
         masters = (layer.master_gate, layer.master_up, layer.master_down)
-        if not self.refresh_operands and work.get("operands_built"):
+        keep = self._operands_current(work)
+        if keep:
             layer.master_gate = layer.master_up = layer.master_down = 0   # keep the bf16 copies of the last forward
         if self._counts_valid is True:  # the previous forward's counts have left before routing overwrites them
             lib.call("qmoe_stream_wait_event", self.stream, self._counts_event)
         lib.call("qmoe_layer_forward", ctypes.byref(layer), self.stream)
         layer.master_gate, layer.master_up, layer.master_down = masters
-        work["operands_built"] = True
+        if not keep:
+            self._operands_made(work)
         # The host's copy of the counts travels on a stream of its own: a device-to-host copy queued on the
         # caller's stream would wait behind whatever large copy-out the caller has in flight on the same copy
         # engine, and every kernel after it would wait too.
@@ -298,7 +319,9 @@ class SparseMoE:
         """Record the forward on ``x``'s buffer as a CUDA graph (the decode-shaped call is a dozen short kernels:
         one graph launch replaces their launches).  Returns a ``ForwardGraph``; ``replay()`` reruns the forward on
         whatever ``x`` holds then and returns the same ``(y, aux)`` tensors every time.  The layer must run on a
-        stream of its own (``stream != 0``); ``refresh_operands`` is recorded as it is now."""
+        stream of its own (``stream != 0``).  Unless ``refresh_operands`` is True the recording keeps the bf16
+        operand copies as they are at capture time: after a weight update run one plain ``forward`` (which
+        rebuilds them) before the next replay."""
         if not self.stream:
             raise ValueError("capture needs a layer whose stream is not the default stream")
         self.forward(x)                                    # once without capture: workspace, kernel attributes
@@ -309,7 +332,7 @@ class SparseMoE:
         lib.call("qmoe_event_sync", self._counts_event)
         layer.x, layer.out = storage.ptr, out.ptr
         masters = (layer.master_gate, layer.master_up, layer.master_down)
-        if not self.refresh_operands:
+        if self.refresh_operands is not True:   # the forward above has just built them
             layer.master_gate = layer.master_up = layer.master_down = 0
         graph = ctypes.c_uint64()
         lib.call("qmoe_graph_begin", self.stream)

@@ -15,6 +15,7 @@ from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_float, c_in
 
 QMOE_F32, QMOE_BF16 = 0, 1
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05 = 0, 1, 2
+VARIANT_SINGLE_CTA_GEMM, VARIANT_WGRAD_PER_PRODUCT, VARIANT_NARROW_SCATTER = 0, 1, 2
 ROW_PAD, MAX_EXPERTS, MAX_TOP_K = 128, 256, 8
 DTYPE_CODES = {"float32": QMOE_F32, "bfloat16": QMOE_BF16}
 ITEM_BYTES = {"float32": 4, "bfloat16": 2, "int32": 4, "int64": 8, "float64": 8}
@@ -97,6 +98,10 @@ SIGNATURES = {
     "qmoe_timing_read": (c_int, [POINTER(c_double), POINTER(c_int64), c_int]),
     "qmoe_device_status": (c_int, [_U, POINTER(c_int)]),
     "qmoe_device_status_clear": (c_int, [_U]),
+    "qmoe_device_status_async": (c_int, [_U, c_void_p]),
+    "qmoe_gather_rows": (c_int, [_U, _U, _U, _I32, _I32, _I64, _U]),
+    "qmoe_ep_set_barrier_timeout_ms": (c_int, [_I64]),
+    "qmoe_test_select_variant": (c_int, [_I32, _I32]),
     "qmoe_rows_bound": (c_int64, [_I64, _I32, _I32]),
     "qmoe_route_blocks": (c_int64, [_I64]),
     "qmoe_router_logits": (c_int, [_U, _I32, _U, _U, _I64, _I64, _I32, _U]),

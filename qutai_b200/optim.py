@@ -88,7 +88,7 @@ class AdamW:
 
     def step(self):
         beta1, beta2 = self.betas
-        rows = []
+        rows, updated = [], []
         for parameter in self.parameters:
             gradient = parameter.grad
             if gradient is None:
@@ -106,8 +106,26 @@ class AdamW:
                          self.square_averages[parameter].ptr, shadow.ptr if shadow is not None else 0,
                          parameter.storage.size, 1 - beta1 ** step, 1 - beta2 ** step))
             self.steps[parameter] = step
+            updated.append((parameter.storage, shadow))
         if not rows:
             return
         items, count, device = self._table.fill(rows)
+        # Change tracking (storage.py): the parameters' generation grows.  A bf16 copy that was current before the
+        # step and whose every updated part was rewritten by this launch is current afterwards as well; a copy of
+        # an allocation in which some updated parameter had no shadow is left stale for its owner to rebuild.
+        groups = {}
+        for master, shadow in updated:
+            group = groups.setdefault(id(master._root), dict(master=master, shadows={}, complete=True))
+            if shadow is None:
+                group["complete"] = False
+            else:
+                group["shadows"][id(shadow._root)] = shadow
+        for group in groups.values():
+            group["current"] = [s for s in group["shadows"].values() if group["complete"] and len(group["shadows"]) == 1
+                                and s.is_derived_from(group["master"])]
         lib.call("qmoe_adamw_multi", items, count, device, self.learning_rate, beta1, beta2, self.eps, self.weight_decay,
                  self.stream)
+        for group in groups.values():
+            group["master"].touch()
+            for shadow in group["current"]:
+                shadow.mark_derived_from(group["master"])

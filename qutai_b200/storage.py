@@ -6,6 +6,12 @@
 either owns an allocation made through the library, or wraps memory owned by someone else (an
 upstream ``CUDAStorage``, a ``torch`` tensor's ``data_ptr()``), or is a view into another storage
 (how the stacked expert weights are handed out as separate parameters).
+
+Every storage carries a ``generation`` counter that the host-visible write paths of this package bump
+(``upload_bytes``, ``fill_zero``, ``fill_normal``, ``copy_from``, the optimizer step); a view shares its
+parent's counter.  A reader that keeps something derived from the contents (the layer's bf16 operand
+copies of the fp32 weights) compares generations instead of rebuilding it on every use.  Code that
+writes through the raw ``ptr`` calls ``touch()`` afterwards.
 """
 from __future__ import annotations
 
@@ -85,6 +91,9 @@ class DeviceStorage:
         self.nbytes = self.size * lib.ITEM_BYTES[dtype]
         self._owner = owner
         self._block = None
+        self._root = self          # a view shares the generation counter of the storage it was cut from
+        self._generation = 0
+        self._synced = {}          # id(source root) -> generation of the source this storage was last derived from
         if ptr is None:
             self.ptr, self._block = _allocate(max(self.nbytes, 1))
         else:
@@ -108,7 +117,27 @@ class DeviceStorage:
         """Elements [start, start + size) of this storage as a storage of their own."""
         if start < 0 or size < 0 or start + size > self.size:
             raise ValueError("view exceeds the storage")
-        return DeviceStorage(size, self.dtype, ptr=self.ptr + start * lib.ITEM_BYTES[self.dtype], owner=self)
+        out = DeviceStorage(size, self.dtype, ptr=self.ptr + start * lib.ITEM_BYTES[self.dtype], owner=self)
+        out._root = self._root
+        return out
+
+    # -- change tracking ------------------------------------------------------------------
+    @property
+    def generation(self):
+        """Grows with every write made through this package (shared by all views of one allocation)."""
+        return self._root._generation
+
+    def touch(self):
+        """Declare the contents changed (for writers that went through the raw address)."""
+        self._root._generation += 1
+
+    def mark_derived_from(self, source):
+        """Record that this storage now holds what was computed from ``source`` as it is now."""
+        self._root._synced[id(source._root)] = source.generation
+
+    def is_derived_from(self, source):
+        """True while ``source`` has not been written since the last ``mark_derived_from(source)``."""
+        return self._root._synced.get(id(source._root)) == source.generation
 
     @classmethod
     def zeros(cls, size, dtype="float32", stream=0):
@@ -137,6 +166,19 @@ class DeviceStorage:
     # -- transfers ------------------------------------------------------------------------
     def fill_zero(self, stream=0):
         lib.call("qmoe_memset", self.ptr, 0, self.nbytes, stream)
+        self.touch()
+
+    def fill_normal(self, mean, std, seed, stream=0):
+        """N(mean, std) draws of the library's counter-based generator keyed by ``seed``."""
+        lib.call("qmoe_normal_fill", self.ptr, lib.DTYPE_CODES[self.dtype], self.size, float(mean), float(std),
+                 int(seed) & (2 ** 64 - 1), stream)
+        self.touch()
+
+    def copy_from(self, other, stream=0):
+        if other.dtype != self.dtype or other.size != self.size:
+            raise ValueError("copy_from needs a storage of the same dtype and size")
+        lib.call("qmoe_memcpy_d2d", self.ptr, other.ptr, self.nbytes, stream)
+        self.touch()
 
     def upload_bytes(self, data, stream=0):
         if len(data) != self.nbytes:
@@ -145,6 +187,7 @@ class DeviceStorage:
         if buffer is not None:
             lib.call("qmoe_memcpy_h2d", self.ptr, ctypes.cast(buffer, ctypes.c_void_p), self.nbytes, stream)
             lib.call("qmoe_stream_sync", stream)  # the staging buffer dies with this call
+            self.touch()
 
     def tobytes(self, stream=0):
         buffer = ctypes.create_string_buffer(self.nbytes)

@@ -25,3 +25,20 @@ def library_path():
     from qutai_b200 import build
 
     return build.ensure_built()
+
+
+@pytest.fixture
+def kernel_variant():
+    """``kernel_variant(which)`` switches one kernel to its comparison form (``qmoe_test_select_variant``) for the
+    rest of the test; every selector is back at its default afterwards."""
+    from qutai_b200 import lib
+
+    chosen = []
+
+    def select(which):
+        lib.call("qmoe_test_select_variant", which, 1)
+        chosen.append(which)
+
+    yield select
+    for which in chosen:
+        lib.call("qmoe_test_select_variant", which, 0)

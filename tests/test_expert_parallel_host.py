@@ -94,3 +94,57 @@ def test_rendezvous_times_out_when_rank_zero_never_arrives(tmp_path):
     path = str(tmp_path / "id")
     assert file_rendezvous(path, 0, b"x" * 128) == b"x" * 128
     assert file_rendezvous(path, 1, timeout=1.0) == b"x" * 128
+
+
+def test_repeated_file_exchanges_never_hand_back_an_older_payload(tmp_path):
+    """Two all-gathers in a row through the same directory, one rank lagging a whole exchange behind: the fast
+    rank's second gather must wait for the slow rank's SECOND payload, not pick up its first one again."""
+    import threading
+
+    from qutai_b200.expert_parallel import FileExchange
+
+    world, results = 3, {}
+
+    def rank_main(rank):
+        exchange = FileExchange(str(tmp_path), "ipc_job", rank, world, timeout=20.0)
+        got = []
+        for round_number in (1, 2):
+            if rank == 2:
+                time.sleep(0.4)            # always late: the others finish a round long before it publishes
+            got.append(exchange.all_gather(f"rank{rank}-round{round_number}".encode()))
+        results[rank] = (got, exchange)
+
+    threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=60)
+    for rank in range(world):
+        got, _ = results[rank]
+        for round_number, payloads in zip((1, 2), got):
+            assert payloads == [f"rank{p}-round{round_number}".encode() for p in range(world)]
+    for rank in range(world):
+        results[rank][1].close()
+    assert not [name for name in os.listdir(tmp_path) if name.startswith("ipc_job")]   # every rank removed its own files
+
+
+def test_placement_maps_and_parameter_names():
+    from qutai_b200.expert_parallel import balanced_placement, contiguous_placement, physical_numbering
+
+    assert contiguous_placement(8, 4) == [0, 0, 1, 1, 2, 2, 3, 3]
+    counts = [900, 100, 800, 200, 700, 300, 600, 400]
+    placement = balanced_placement(counts, 4)
+    loads = [sum(c for c, p in zip(counts, placement) if p == r) for r in range(4)]
+    assert sorted(placement) == [0, 0, 1, 1, 2, 2, 3, 3] and loads == [1000] * 4     # LPT pairs large with small
+    physical_of_logical, logical_of_physical = physical_numbering(placement, 4)
+    assert sorted(logical_of_physical) == list(range(8))
+    for physical, e in enumerate(logical_of_physical):
+        assert physical_of_logical[e] == physical and placement[e] == physical // 2    # rank p owns slots 2p, 2p + 1
+    for rank in range(4):                                                              # ascending inside a rank
+        mine = logical_of_physical[2 * rank: 2 * rank + 2]
+        assert mine == sorted(mine)
+    assert physical_numbering(contiguous_placement(8, 2), 2)[1] == list(range(8))      # contiguous blocks = identity
+    with pytest.raises(ValueError):
+        physical_numbering([0, 0, 0, 1], 2)          # a rank with three experts
+    with pytest.raises(ValueError):
+        balanced_placement([1, 2, 3], 2)

@@ -16,6 +16,7 @@ def test_flag_barrier_gives_up_when_a_rank_never_arrives():
     from qutai_b200.storage import DeviceStorage
 
     assert lib.device_status() == 0
+    lib.call("qmoe_ep_set_barrier_timeout_ms", 1000)             # the default (10 s) is sized for training jobs
     mine, absent = DeviceStorage.zeros(16, "int32"), DeviceStorage.zeros(16, "int32")
     flags = lib.Peers()
     flags.world, flags.rank = 2, 0
@@ -35,3 +36,20 @@ def test_flag_barrier_gives_up_when_a_rank_never_arrives():
     start = time.monotonic()
     lib.call("qmoe_ep_flag_barrier", ctypes.byref(flags), 2, 0, 0, None, 0)
     assert lib.device_status() == 0 and time.monotonic() - start < 0.5
+    lib.call("qmoe_ep_set_barrier_timeout_ms", 10000)
+
+
+def test_layer_raises_when_a_barrier_of_its_step_timed_out(tmp_path):
+    """The expert-parallel layer surfaces the barrier's status: a step during which a rank never arrived raises
+    instead of handing back rows that were read before their owners wrote them (child process: the layer needs
+    a communicator of its own)."""
+    import os
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    proc = subprocess.run([sys.executable, os.path.join(here, "ep_timeout_worker.py"), str(tmp_path)],
+                          capture_output=True, text=True, timeout=240)
+    out = proc.stdout + proc.stderr
+    assert proc.returncode == 0, out[-3000:]
+    assert "raised in backward" in out and "raised in check_status" in out and "timeout worker done" in out, out[-3000:]

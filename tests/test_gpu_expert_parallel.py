@@ -1,7 +1,7 @@
 """Expert-parallel layer on real GPUs: every rank is a child process that sees one GPU.  world = 1
-runs on any box (all exchanges are self-sends through NCCL); world = 2 needs two GPUs.  The parent
-assembles the ranks' results and checks them against the oracle run on the whole problem with the
-devices' own fp32 logits."""
+runs on any box (all exchanges are self-sends); world = 2, 4, 8 need that many GPUs and are skipped on a
+smaller box.  The parent assembles the ranks' results and checks them against the oracle run on the whole
+problem with the devices' own fp32 logits, in the model's expert numbering whatever the placement."""
 import os
 import subprocess
 import sys
@@ -24,13 +24,13 @@ def gpu_count():
         return 0
 
 
-def run_ranks(world, out_dir, transport):
+def run_ranks(world, out_dir, transport, placement="contiguous"):
     procs = []
     for rank in range(world):
         env = dict(os.environ, NCCL_DEBUG="WARN")
         if transport == "nccl":  # one visible GPU per process, the upstream runtime's "device 0" assumption
             env["CUDA_VISIBLE_DEVICES"] = str(rank)
-        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "ep_gpu_worker.py"), str(rank), str(world), out_dir, transport],
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "ep_gpu_worker.py"), str(rank), str(world), out_dir, transport, placement],
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env))
     for rank, proc in enumerate(procs):
         try:
@@ -42,9 +42,15 @@ def run_ranks(world, out_dir, transport):
     return [np.load(os.path.join(out_dir, f"rank{rank}.npz")) for rank in range(world)]
 
 
-@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-simt"])
-@pytest.mark.parametrize("world", [1, 2])
-def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, transport, tmp_path):
+CASES = [(1, "nccl", "contiguous"), (1, "p2p", "contiguous"), (1, "p2p-simt", "contiguous"),
+         (2, "nccl", "contiguous"), (2, "p2p", "contiguous"), (2, "p2p-simt", "contiguous"),
+         (2, "p2p", "interleaved"), (2, "p2p", "rebalanced"), (2, "nccl", "interleaved"),
+         (4, "p2p", "contiguous"), (4, "p2p", "interleaved"),
+         (8, "p2p", "contiguous"), (8, "p2p", "rebalanced")]
+
+
+@pytest.mark.parametrize("world,transport,placement", CASES)
+def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, transport, placement, tmp_path):
     if gpu_count() < world:
         pytest.skip(f"needs {world} GPUs")
     sys.path.insert(0, HERE)
@@ -52,14 +58,14 @@ def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, transpor
 
     p = problem()
     T, E, k = p["T"], p["E"], p["k"]
-    ranks = run_ranks(world, str(tmp_path), transport)
+    ranks = run_ranks(world, str(tmp_path), transport, placement)
     scores = np.concatenate([r["scores"] for r in ranks])
     assert oracle.max_rel_err(scores, p["x"] @ p["router"].astype(np.float64).T) <= 1e-4
     r16 = oracle.round_bf16
     y, aux, ctx = oracle.moe_forward(p["x"], p["router"], r16(p["gate"]), r16(p["up"]), r16(p["down"]), k, scores=scores)
     grads = oracle.moe_backward(ctx, p["grad"], p["grad_aux"])
     route = ctx["route"]
-    L = E // world
+    owners = [e // (E // world) for e in range(E)] if placement == "contiguous" else [e % world for e in range(E)]
     for rank, r in enumerate(ranks):
         shard = slice(rank * T // world, (rank + 1) * T // world)
         assert tuple(r["counts"].tolist()) == route["counts"]            # global counts, bit-exact, on every rank
@@ -68,11 +74,11 @@ def test_expert_parallel_matches_the_oracle_on_the_whole_problem(world, transpor
         assert oracle.max_rel_err(r["y"], y[shard]) <= BF16_TOL
         assert oracle.max_rel_err(r["dx"], grads["x"][shard]) <= BF16_TOL
         assert oracle.max_rel_err(r["d_router"], grads["router"]) <= BF16_TOL   # summed over ranks
-        for j in range(L):
-            e = rank * L + j
+        assert r["expert_ids"].tolist() == [e for e in range(E) if owners[e] == rank]
+        for j, e in enumerate(r["expert_ids"].tolist()):
             assert bool(r["has_grad"][j]) == (route["counts"][e] > 0)
             if route["counts"][e]:
                 for key in ("gate", "up", "down"):
-                    assert oracle.max_rel_err(r[f"d_{key}_{j}"], grads[key][e]) <= BF16_TOL
-    if world > 1:  # the router gradient is identical on every rank after the all-reduce
-        assert np.array_equal(ranks[0]["d_router"], ranks[1]["d_router"])
+                    assert oracle.max_rel_err(r[f"d_{key}_{e}"], grads[key][e]) <= BF16_TOL
+    for other in ranks[1:]:  # the router gradient is identical on every rank after the all-reduce
+        assert np.array_equal(ranks[0]["d_router"], other["d_router"])

@@ -164,3 +164,60 @@ def test_optimizer_keeps_the_layer_operands_current():
         y, _ = layer(xs)
         outputs.append(y.storage.tobytes())
     assert outputs[0] == outputs[1]
+
+
+def test_operand_copies_are_rebuilt_only_after_a_weight_was_written():
+    """``refresh_operands = "auto"`` (the default): a forward converts the fp32 weights to their bf16 operand
+    copies only when a weight storage was written since the copies were made (optimizer step, upload).  The bits
+    are those of a layer that converts at every forward, and a forward on unchanged weights launches three
+    kernels fewer (the three conversions)."""
+    from gpu_util import make_layer, to_device
+    from qutai_b200 import lib
+    from qutai_b200.layers import Tensor
+    from qutai_b200.optim import AdamW
+
+    T, d, E, k, h = 300, 64, 4, 2, 128
+    rng = np.random.default_rng(17)
+    x, grad_y = moe_oracle.round_bf16(rng.standard_normal((T, d))), moe_oracle.round_bf16(rng.standard_normal((T, d)))
+    router = rng.standard_normal((E, d)).astype(np.float32) * 0.05
+    gate = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    up = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
+    down = rng.standard_normal((E, d, h)).astype(np.float32) / np.sqrt(h)
+    new_up = (rng.standard_normal((h, d)) / np.sqrt(d)).astype(np.float32)
+    count = lib.load().qmoe_launch_count
+    outputs, launches = [], []
+    for mode in (True, "auto"):
+        layer = make_layer((T, d), router, gate, up, down, k, engine="tcgen05")
+        assert layer.refresh_operands == "auto"
+        layer.refresh_operands = mode
+        xs, gs = Tensor(to_device(x, "bfloat16"), (T, d)), Tensor(to_device(grad_y, "bfloat16"), (T, d))
+        seen, per_forward = [], []
+
+        def forward():
+            before = count()
+            y, _ = layer(xs)
+            per_forward.append(count() - before)
+            seen.append(y.storage.tobytes())
+
+        forward()                                             # builds the copies
+        forward()                                             # nothing was written in between
+        optimizer = AdamW(layer.parameters(), learning_rate=1e-2)   # no shadows: the step only writes the fp32 weights
+        optimizer.zero_grad()
+        layer.backward(gs, None)
+        optimizer.step()
+        forward()                                             # after an optimizer step
+        forward()
+        layer.experts[1].up.weight.storage.upload_bytes(new_up.tobytes())   # through a view of the stacked buffer
+        forward()                                             # after an upload
+        shadowed = AdamW(layer.parameters(), learning_rate=1e-2, shadows=layer.operand_shadows())
+        shadowed.zero_grad()
+        layer.backward(gs, None)
+        shadowed.step()                                       # writes weights and copies together
+        forward()
+        outputs.append(seen)
+        launches.append(per_forward)
+    assert outputs[0] == outputs[1]
+    always, auto = launches
+    assert len(set(always)) == 1                              # the forced layer converts every time
+    full = always[0]
+    assert auto == [full, full - 3, full, full - 3, full, full - 3], (always, auto)

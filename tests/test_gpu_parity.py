@@ -217,15 +217,14 @@ LAYER_SHAPES = [
 
 @pytest.mark.parametrize("engine", ["simt", "tcgen05", "tcgen05-1cta"])
 @pytest.mark.parametrize("T,d,E,k,h", LAYER_SHAPES)
-def test_layer_bf16_matches_oracle(T, d, E, k, h, engine, monkeypatch):
+def test_layer_bf16_matches_oracle(T, d, E, k, h, engine, kernel_variant):
     from gpu_util import make_layer, run_layer
+    from qutai_b200 import lib
 
     # "tcgen05" runs the expert GEMMs as CTA pairs (256-row tiles), "tcgen05-1cta" one CTA per 128-row tile
     if engine == "tcgen05-1cta":
-        monkeypatch.setenv("QUTAI_MOE_GEMM_CTAS", "1")
+        kernel_variant(lib.VARIANT_SINGLE_CTA_GEMM)
         engine = "tcgen05"
-    else:
-        monkeypatch.delenv("QUTAI_MOE_GEMM_CTAS", raising=False)
     rng = np.random.default_rng(T + d + E)
     r16 = oracle.round_bf16
     x, grad_y = r16(rng.standard_normal((T, d))), r16(rng.standard_normal((T, d)))
@@ -333,10 +332,11 @@ def test_router_forward_backward_fp32_semantics(T, d, E, dtype):
     assert lib.device_status() == 0
 
 
-def test_launch_variants_of_the_weight_gradients_agree_bit_for_bit(monkeypatch):
-    """One launch for the three weight gradients (default) against one launch each
-    (QUTAI_MOE_WGRAD_LAUNCHES=3): the same tiles in a different order give the same bits."""
+def test_launch_variants_of_the_weight_gradients_agree_bit_for_bit(kernel_variant):
+    """One launch for the three weight gradients (default) against one launch each (the comparison form of
+    ``qmoe_test_select_variant``): the same tiles in a different order give the same bits."""
     from gpu_util import make_layer, run_layer
+    from qutai_b200 import lib
 
     T, d, E, k, h = 1100, 384, 5, 2, 1408
     rng = np.random.default_rng(11)
@@ -346,8 +346,9 @@ def test_launch_variants_of_the_weight_gradients_agree_bit_for_bit(monkeypatch):
     up = rng.standard_normal((E, h, d)).astype(np.float32) / np.sqrt(d)
     down = rng.standard_normal((E, d, h)).astype(np.float32) / np.sqrt(h)
     results = []
-    for launches in ("1", "3"):
-        monkeypatch.setenv("QUTAI_MOE_WGRAD_LAUNCHES", launches)
+    for per_product in (False, True):
+        if per_product:
+            kernel_variant(lib.VARIANT_WGRAD_PER_PRODUCT)
         layer = make_layer(x.shape, router, gate, up, down, k, engine="tcgen05")
         results.append(run_layer(layer, x, grad_y, None, "bfloat16"))
     a, b = results

@@ -58,3 +58,41 @@ def test_static_scratch_routing_rejects_sizes_beyond_the_built_in_array():
     scores = to_device(np.zeros((1, 1)), "float32")  # never read: the call must fail before any launch
     with pytest.raises(ValueError, match="exceed the built-in"):
         lib.call("qmoe_route_static", tables.ref, scores.ptr, 0)
+
+
+def test_a_route_filled_without_caller_scratch_feeds_the_other_entry_points():
+    """A host that could not allocate the scratch tables still has to permute, combine and run the routing
+    backward with the struct the static variant filled: those calls must accept the three scratch fields left
+    at 0 and give the bits they give for a route filled by ``qmoe_route``."""
+    from gpu_util import RouteTables, to_device, to_host
+    from qutai_b200 import lib
+    from qutai_b200.storage import DeviceStorage
+
+    rng = np.random.default_rng(7)
+    T, E, k, d = 500, 8, 2, 64
+    scores = to_device(rng.standard_normal((T, E)).astype(np.float32), "float32")
+    x = to_device(rng.standard_normal((T, d)).astype(np.float32), "float32")
+    grad_w = to_device(rng.standard_normal((T, k)).astype(np.float32), "float32")
+    results = []
+    for entry, with_scratch in (("qmoe_route_static", False), ("qmoe_route", True)):
+        tables = RouteTables(T, E, k)
+        if not with_scratch:
+            tables.struct.block_counts = tables.struct.block_base = tables.struct.block_colsum = 0
+        lib.call(entry, tables.ref, scores.ptr, 0)
+        R = tables.rows_bound
+        dispatched, out = DeviceStorage(R * d, "float32"), DeviceStorage(T * d, "float32")
+        dy, dw = DeviceStorage(R * d, "float32"), DeviceStorage(T * k, "float32")
+        back, d_scores = DeviceStorage(T * d, "float32"), DeviceStorage(T * E, "float32")
+        lib.call("qmoe_permute", tables.ref, x.ptr, dispatched.ptr, lib.QMOE_F32, d, 0)
+        lib.call("qmoe_combine", tables.ref, dispatched.ptr, out.ptr, lib.QMOE_F32, d, 0)
+        lib.call("qmoe_combine_backward", tables.ref, x.ptr, dispatched.ptr, dy.ptr, dw.ptr, lib.QMOE_F32, d, 0)
+        lib.call("qmoe_unpermute_reduce", tables.ref, dy.ptr, 0, back.ptr, lib.QMOE_F32, d, 0)
+        lib.call("qmoe_route_backward", tables.ref, grad_w.ptr, 0, d_scores.ptr, 0)
+        results.append([to_host(s) for s in (dispatched, out, dy, dw, back, d_scores)])
+        if not with_scratch:  # the statistics packer reads the column sums out of the scratch: it has to say so
+            stats = DeviceStorage(2 * E, "int32")
+            with pytest.raises(ValueError, match="block_colsum"):
+                lib.call("qmoe_ep_pack_stats", tables.ref, stats.ptr, 0)
+    for got, want in zip(*results):
+        assert np.array_equal(got, want)
+    assert lib.device_status() == 0
