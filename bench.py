@@ -6,7 +6,10 @@ Prints ONE JSON line (rank 0).  ``value`` is whole-job tokens/s with inputs resi
 ``e2e`` is the same metric through the public layer with HOST buffers (pinned inputs copied in,
 outputs copied back, inside the timed region); ``roofline`` describes the dominant kernel (the
 tcgen05 grouped GEMM) against the measured bf16 peak; ``cpu_baseline`` is the CPU oracle timed on
-this host on a bounded token sample.  ``--impl reference`` times that CPU implementation alone.
+this host on a bounded token sample; ``ep_check`` compares the values the timed path produces with the
+CPU oracle (routing counts bit-exact over all ranks' tokens, sampled outputs and gradients at the bf16
+bar) and the process exits non-zero when it fails; ``decode`` is the decode-shaped forward latency (c5).
+``--impl reference`` times the CPU implementation alone.
 
 Workloads are the synthetic shapes of the upstream project's MoE layer study: c2 = 16384 tokens,
 d 1024, 8 experts top-2, hidden 2816; c3 = 32768 tokens, d 2048, 64 experts top-6, hidden 1408,
@@ -17,12 +20,27 @@ c5 = c3's layer on 64 tokens (decode latency, forward only).
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
 import sys
 import threading
 import time
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+# The CPU oracle (numpy) runs on rank 0 only: it gets all the host's cores, whatever the launcher put into
+# OMP_NUM_THREADS (torch.distributed.run sets 1).  Must happen before numpy is first imported.
+if int(os.environ.get("RANK", "0")) == 0:
+    for _name in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_name] = str(host_cores())
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -35,11 +53,10 @@ WORKLOADS = {
     "c3s": dict(tokens=8192, d=2048, E=16, k=6, h=1408, router_std=0.02, bias_std=0.5),
     "c5": dict(tokens=64, d=2048, E=64, k=6, h=1408, router_std=0.02, bias_std=0.5),
 }
-# DRAM bytes (read + written) of the five expert tensor-core launches of one step, from profiler captures of the
-# same command (profiles/grouped_gemm_c2_ncu_full.md, profiles/grouped_gemm_c3s_ncu_full.md); c3 is too large to
-# capture and has exactly four times c3s's experts and tokens at the same rows per expert: 4 x the c3s figure
-GEMM_DRAM_BYTES_PER_STEP = {"c2": 3.74e9, "c3s": 4.70e9, "c3": 4 * 4.70e9}
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+BF16_TOL = 2e-2          # max |a - b| / max |b| of outputs and gradients, bf16 activations
+AUX_GRAD = 0.01          # upstream gradient of the auxiliary loss used by every step
+EXPERT_SEED = 100        # expert e's weights are drawn with keys EXPERT_SEED + 3 e (+0 gate, +1 up, +2 down)
 
 
 def load_peaks():
@@ -54,6 +71,28 @@ def load_peaks():
         return dict(FALLBACK_PEAKS, source="fallback")
 
 
+def load_gemm_traffic(workload):
+    """DRAM bytes (read + written) of the expert tensor-core launches of one step, from the profiler summary
+    ``profiles/grouped_gemm_dram_bytes.txt`` (lines ``workload  launch  bytes``; the file says which capture
+    made it).  c3 is too large to capture and has exactly four times c3s's experts and tokens at the same rows
+    per expert, so its traffic is taken as four times c3s's.  None when the file has no line for the workload."""
+    path = os.path.join(ROOT, "profiles", "grouped_gemm_dram_bytes.txt")
+    per_workload = {}
+    try:
+        with open(path) as handle:
+            for line in handle:
+                parts = line.split()
+                if len(parts) == 3 and not line.startswith("#"):
+                    per_workload.setdefault(parts[0], {})[parts[1]] = float(parts[2])
+    except OSError:
+        return None
+    scale = 1.0
+    if workload == "c3" and "c3" not in per_workload:
+        workload, scale = "c3s", 4.0
+    launches = per_workload.get(workload)
+    return scale * sum(launches.values()) if launches else None
+
+
 def layer_flops(w, tokens=None):
     """Algorithmic FLOPs of one forward + backward: expert GEMMs 18*A*d*h, router 6*T*d*E."""
     T = w["tokens"] if tokens is None else tokens
@@ -61,50 +100,67 @@ def layer_flops(w, tokens=None):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """Samples SM clock, power and throttle reasons with nvidia-smi while the benchmark runs; ``begin()`` /
+    ``end()`` bracket the timed region, and only samples taken inside it are summarised."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.lines, self.proc = index, [], None
+        self.index, self.lines, self.proc, self.t0, self.t1 = index, [], None, None, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "20", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
         except Exception:
             self.proc = None
 
+    def begin(self):
+        self.t0 = datetime.datetime.now()
+
+    def end(self):
+        self.t1 = datetime.datetime.now()
+
     def stop(self):
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        clocks, max_clock, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        parsed, max_clock = [], None
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
-                clocks.append(float(parts[1]))
-                max_clock = float(parts[2])
+                clock, max_clock, power = float(parts[1]), float(parts[2]), float(parts[3])
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[5:9]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        clocks.sort()
-        # samples under load: the upper half (the sampler also sees the idle edges of the region)
-        busy = clocks[len(clocks) // 2:] if clocks else []
-        median = busy[len(busy) // 2] if busy else None
-        return dict(sm_mhz=median, sm_max_mhz=max_clock, samples=len(clocks), reasons=sorted(reasons))
+            try:
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+            except ValueError:
+                stamp = None
+            parsed.append((stamp, clock, power, [name for name, flag in zip(names, parts[5:9]) if flag.lower().startswith("active")]))
+        inside = [p for p in parsed if p[0] is not None and self.t0 is not None and self.t0 <= p[0] <= (self.t1 or p[0])]
+        window = "samples inside the timed regions only"
+        if not inside:   # no usable time stamps: fall back to every sample of the run (the power filter below still applies)
+            inside, window = parsed, "all samples of the run (time stamps unusable)"
+        if not inside:
+            return dict(sm_mhz=None, sm_max_mhz=max_clock, samples=0, reasons=[])
+        samples = [(clock, power) for _, clock, power, _ in inside]
+        reasons = {name for item in inside for name in item[3]}
+        # under load = the samples whose power draw is within 60 % of the region's maximum (under a power cap the
+        # loaded samples are the ones with the LOW clocks; idle edges draw little)
+        top = max(power for _, power in samples)
+        loaded = sorted(clock for clock, power in samples if power >= 0.6 * top)
+        return dict(sm_mhz=loaded[len(loaded) // 2], sm_min_mhz=loaded[0], sm_max_mhz=max_clock, samples=len(samples),
+                    samples_under_load=len(loaded), power_w_max=top, reasons=sorted(reasons), window=window)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -134,21 +190,38 @@ def cpu_step(w, inputs):
 
     x, router, gate, up, down, grad = inputs
     y, aux, ctx = oracle.moe_forward(x, router, gate, up, down, w["k"])
-    oracle.moe_backward(ctx, grad, 0.01)
+    oracle.moe_backward(ctx, grad, AUX_GRAD)
     return y
 
 
-def pure_python_rate():
-    """Multiply-accumulates per second of the scalar triple loop the upstream CPU path runs
-    (measured on a small product; the upstream layer is that loop almost entirely)."""
+def pure_python_layer(max_seconds=6.0):
+    """The scalar-loop restatement of the upstream pure-Python layer (the code path ``device="cpu"`` runs
+    upstream), forward + backward, timed at the shape of the tiny CPU configuration's MoE layer (d 64, 4 experts
+    top-2, hidden 128; that configuration has 128 tokens per layer) on a token sample sized to stay within
+    ``max_seconds``.  Returns measured tokens/s on one core and multiply-accumulates per second."""
+    import random
     from array import array
+
     from oracle import moe_pure
 
-    n = 48
-    a = array("d", [0.5] * (n * n))
-    start = time.perf_counter()
-    moe_pure.gemm(a, a, n, n, n, transpose_right=True)
-    return n ** 3 / (time.perf_counter() - start)
+    d, E, k, h = 64, 4, 2, 128
+    rng = random.Random(0)
+    draw = lambda n, std: array("d", (rng.gauss(0.0, std) for _ in range(n)))
+    router = draw(E * d, 0.02)
+    gate, up, down = [draw(h * d, 0.02) for _ in range(E)], [draw(h * d, 0.02) for _ in range(E)], [draw(d * h, 0.01) for _ in range(E)]
+    mac_per_token = 9 * k * d * h + 3 * d * E
+    tokens, seconds = 4, 0.0
+    while True:
+        x, grad = draw(tokens * d, 1.0), draw(tokens * d, 1.0)
+        start = time.perf_counter()
+        moe_pure.moe_forward_backward(x, router, gate, up, down, tokens, d, h, k, grad, AUX_GRAD)
+        seconds = time.perf_counter() - start
+        if tokens >= 128 or seconds * 4 > max_seconds:
+            break
+        tokens *= 4
+    return dict(tokens_per_s=tokens / seconds, mac_per_s=tokens * mac_per_token / seconds, seconds=seconds, cores=1,
+                sample=f"{tokens} of 128 tokens of the tiny CPU configuration's MoE layer (d 64, 4 experts top-2, hidden 128), "
+                       "float64 scalar loops, forward + backward")
 
 
 def time_cpu(w, steps, warmup, sample_tokens):
@@ -160,13 +233,6 @@ def time_cpu(w, steps, warmup, sample_tokens):
         cpu_step(w, inputs)
     seconds = (time.perf_counter() - start) / steps
     return sample_tokens / seconds, seconds
-
-
-def host_cores():
-    try:
-        return len(os.sched_getaffinity(0))
-    except Exception:
-        return os.cpu_count() or 1
 
 
 def cpu_sample_tokens(w):
@@ -204,65 +270,47 @@ def workload_config(name, w, gpus):
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
-def build_layer(w, torch, device, seed=0):
+class Cfg:
+    def __init__(self, w):
+        self.d_model, self.n_experts, self.top_k, self.d_expert, self.n_layers = w["d"], w["E"], w["k"], w["h"], 1
+
+
+def router_weights(w, seed=0):
     import numpy as np
 
-    from qutai_b200 import lib
+    rng = np.random.default_rng(seed)   # the same draws on every rank: the router is replicated
+    router = (rng.standard_normal((w["E"], w["d"])) * w["router_std"]).astype(np.float32)
+    if w["bias_std"]:
+        router[:, w["d"] - 1] = (rng.standard_normal(w["E"]) * w["bias_std"]).astype(np.float32)
+    return router
+
+
+def fill_experts(layer, w, expert_ids):
+    """Synthetic expert weights N(0, 1/sqrt(fan_in)), keyed by the model's expert number: the layer computes the
+    same function however its experts are spread over ranks."""
+    d, h = w["d"], w["h"]
+    for expert, e in zip(layer.experts, expert_ids):
+        expert.gate.weight.storage.fill_normal(0.0, d ** -0.5, EXPERT_SEED + 3 * e)
+        expert.up.weight.storage.fill_normal(0.0, d ** -0.5, EXPERT_SEED + 3 * e + 1)
+        expert.down.weight.storage.fill_normal(0.0, h ** -0.5, EXPERT_SEED + 3 * e + 2)
+
+
+def build_layer(w, seed=0):
     from qutai_b200.layers import SparseMoE
 
-    class Cfg:
-        d_model, n_experts, top_k, d_expert, n_layers = w["d"], w["E"], w["k"], w["h"], 1
-
-    layer = SparseMoE(Cfg, device="cuda", dtype="float32", seed=seed)
-    d, E, h = w["d"], w["E"], w["h"]
-    fill = lambda storage, std, key: lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std, key, 0)
-    fill(layer._gate, d ** -0.5, 101)
-    fill(layer._up, d ** -0.5, 102)
-    fill(layer._down, h ** -0.5, 103)
-    rng = np.random.default_rng(seed)
-    router = (rng.standard_normal((E, d)) * w["router_std"]).astype(np.float32)
-    if w["bias_std"]:
-        router[:, d - 1] = (rng.standard_normal(E) * w["bias_std"]).astype(np.float32)
-    layer.router.weight.storage.upload_bytes(router.tobytes())
+    layer = SparseMoE(Cfg(w), device="cuda", dtype="float32", seed=seed)
+    fill_experts(layer, w, range(w["E"]))
+    layer.router.weight.storage.upload_bytes(router_weights(w, seed).tobytes())
     return layer
 
 
 def build_ep_layer(w, rank, world, seed=0, transport="p2p", gather=None):
-    import numpy as np
-
-    from qutai_b200 import lib
     from qutai_b200.expert_parallel import ExpertParallelMoE
 
-    class Cfg:
-        d_model, n_experts, top_k, d_expert, n_layers = w["d"], w["E"], w["k"], w["h"], 1
-
-    layer = ExpertParallelMoE(Cfg, rank=rank, world=world, seed=seed, transport=transport, gather=gather)
-    d, E, h = w["d"], w["E"], w["h"]
-    fill = lambda storage, std, key: lib.call("qmoe_normal_fill", storage.ptr, lib.QMOE_F32, storage.size, 0.0, std, key, 0)
-    fill(layer._gate, d ** -0.5, 101 + 10 * rank)
-    fill(layer._up, d ** -0.5, 102 + 10 * rank)
-    fill(layer._down, h ** -0.5, 103 + 10 * rank)
-    rng = np.random.default_rng(seed)   # the replicated router: same draws on every rank
-    router = (rng.standard_normal((E, d)) * w["router_std"]).astype(np.float32)
-    if w["bias_std"]:
-        router[:, d - 1] = (rng.standard_normal(E) * w["bias_std"]).astype(np.float32)
-    layer.router.weight.storage.upload_bytes(router.tobytes())
-    layer.router_host = router
+    layer = ExpertParallelMoE(Cfg(w), rank=rank, world=world, seed=seed, transport=transport, gather=gather)
+    fill_experts(layer, w, layer.expert_ids)
+    layer.router.weight.storage.upload_bytes(router_weights(w, seed).tobytes())
     return layer
-
-
-def balanced_placement(counts, world):
-    """Static load-aware expert placement: longest-processing-time greedy.  Returns ``order`` with
-    ``order[new_index] = old_index`` such that rank p owns new indices [p*L, (p+1)*L) and the rows
-    per rank are as even as the per-expert loads allow."""
-    E = len(counts)
-    L = E // world
-    loads, members = [0] * world, [[] for _ in range(world)]
-    for e in sorted(range(E), key=lambda i: (-counts[i], i)):
-        p = min((r for r in range(world) if len(members[r]) < L), key=lambda r: (loads[r], r))
-        members[p].append(e)
-        loads[p] += counts[e]
-    return [e for p in range(world) for e in sorted(members[p])]
 
 
 def host_inputs(w, torch, seed=0):
@@ -274,7 +322,12 @@ def host_inputs(w, torch, seed=0):
     return x.to(torch.bfloat16).pin_memory(), g.to(torch.bfloat16).pin_memory()
 
 
+def percentile(sorted_values, fraction):
+    return sorted_values[min(len(sorted_values) - 1, int(len(sorted_values) * fraction))]
+
+
 def run_gpu(args, w, rank, world):
+    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -285,10 +338,10 @@ def run_gpu(args, w, rank, world):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if args.workload == "c5" and world == 1:
-        # the decode-shaped forward is replayed from a CUDA graph, which needs a stream other than the default one
-        torch.cuda.set_stream(torch.cuda.Stream())
+    # a stream of the benchmark's own: the decode-shaped forward is replayed from a CUDA graph, which the default stream cannot record
+    torch.cuda.set_stream(torch.cuda.Stream())
     stream = torch.cuda.current_stream().cuda_stream
+    gather = None
     if world > 1:
         from qutai_b200.expert_parallel import init_communicator
 
@@ -307,39 +360,28 @@ def run_gpu(args, w, rank, world):
         init_communicator(rank, world, share=share)
         layer = build_ep_layer(w, rank, world, transport=args.transport, gather=gather)
     else:
-        layer = build_layer(w, torch, device)
+        layer = build_layer(w)
     layer.stream = stream
     x_host, g_host = host_inputs(w, torch)
-    T_global, d = w["tokens"], w["d"]
+    T_global, d, E, k, h = w["tokens"], w["d"], w["E"], w["k"], w["h"]
     T = T_global // world                      # tokens of this rank (contiguous shard)
+    L = E // world                             # experts of this rank
     x_host = x_host[rank * T:(rank + 1) * T].clone().pin_memory()
     g_host = g_host[rank * T:(rank + 1) * T].clone().pin_memory()
     x_dev, g_dev = x_host.to(device), g_host.to(device)
-    aux_grad = torch.full((1,), 0.01, dtype=torch.float32, device=device)
+    aux_grad = torch.full((1,), AUX_GRAD, dtype=torch.float32, device=device)
     y_host = torch.empty_like(x_host).pin_memory()
     dx_host = torch.empty_like(x_host).pin_memory()
     wrap = lambda t, dtype: DeviceStorage.wrap(t.data_ptr(), t.numel(), dtype, owner=t)
     xs, gs = Tensor(wrap(x_dev, "bfloat16"), (T, d)), Tensor(wrap(g_dev, "bfloat16"), (T, d))
-    ga = wrap(aux_grad, "float32") if world == 1 else 0.01
+    ga = wrap(aux_grad, "float32") if world == 1 else AUX_GRAD
     forward_only = args.workload == "c5"
-    if forward_only and hasattr(layer, "refresh_operands"):
-        layer.refresh_operands = False   # decode: the weights are fixed, their bf16 copies are built once
-    placement = "contiguous"
-    if world > 1 and args.placement == "balanced":
-        # Experts are placed on ranks by measured load (one profiling forward), not by index.  With
-        # synthetic iid expert weights this is a relabelling of the experts, i.e. of the router rows.
-        layer(xs)
-        order = balanced_placement(layer.last_counts, world)
-        layer.router.weight.storage.upload_bytes(layer.router_host[order].copy().tobytes())
-        placement = "balanced (LPT greedy on the counts of a profiling forward)"
-
     parameters = layer.parameters()
-
     graphs, graph_mode = {}, {"on": True}
 
     def forward(x):
         """The layer's forward; for the decode shape on one GPU, a replay of its recorded graph (one per input buffer)."""
-        if not (graph_mode["on"] and forward_only and world == 1 and stream):
+        if not (graph_mode["on"] and forward_only and world == 1):
             return layer(x)
         key = x.storage.ptr
         if key not in graphs:
@@ -353,10 +395,88 @@ def run_gpu(args, w, rank, world):
         dx = None if forward_only else layer.backward(gs, ga)
         return y, aux, dx
 
-    # End-to-end arm: every step's inputs come from pinned host memory and every step's outputs (y, dx,
-    # aux) go back to pinned host memory.  The copies run on their own streams, double-buffered, so the
-    # H2D of step i+1 and the D2H of step i-1 overlap the compute of step i — the way a host that feeds
-    # the layer from its own buffers would drive it.
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler.begin() if sampler.t0 is None else None
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        sampler.end()
+        ms = start.elapsed_time(stop) / steps
+        if world > 1:  # the job is as slow as its slowest rank
+            worst = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = float(worst.item())
+        return ms
+
+    def preroll(seconds):
+        """Back-to-back steps until the GPU has worked for ``seconds``: the timed steps then sit at the operating
+        point a long job sees under the power cap, whatever --warmup says."""
+        done = 0
+        begin = time.perf_counter()
+        while True:
+            for _ in range(10):
+                step()
+            done += 10
+            torch.cuda.synchronize()
+            elapsed = torch.tensor([time.perf_counter() - begin], dtype=torch.float64, device=device)
+            if world > 1:   # every rank must leave the loop after the same number of steps
+                dist.all_reduce(elapsed, op=dist.ReduceOp.MIN)
+            if float(elapsed.item()) >= seconds:
+                return done
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    contiguous = None
+    if world > 1:
+        placement_label = "contiguous blocks of E / N experts per rank"
+        if args.placement == "balanced":
+            # the contiguous placement first (device time only), then the experts move to the load-balanced one
+            preroll(args.preroll / 2)
+            ms_contiguous = timed(step, args.steps)
+            rows = [sum(layer.last_counts[p * L + j] for j in range(L)) for p in range(world)]
+            contiguous = dict(ms_per_step=ms_contiguous, value=T_global / (ms_contiguous * 1e-3), unit="tokens/s",
+                              per_rank_rows=rows, placement=placement_label)
+            sampler.t0 = None   # the clock summary covers the headline placement's timed regions
+            layer.rebalance()   # LPT greedy on the counts of the last forward; the weights travel over NCCL
+            parameters = layer.parameters()
+            placement_label = "balanced: longest-processing-time greedy on measured per-expert counts (ExpertParallelMoE.rebalance)"
+            for _ in range(args.warmup):
+                step()
+    if args.trace:  # kernel timeline of a few steps (diagnosis only; nothing measured under it is reported)
+        from torch.profiler import ProfilerActivity, profile
+
+        for _ in range(4):
+            step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+        if rank == 0:
+            prof.export_chrome_trace(args.trace)
+    prerolled = preroll(args.preroll)
+    logical_counts = layer.last_counts
+    physical = getattr(layer, "_logical_of_physical", list(range(E)))
+    counts = [logical_counts[e] for e in physical]          # in the layer's internal (rank-major) expert order
+    launches_before = lib.load().qmoe_launch_count()
+    ms = timed(step, args.steps)
+    launches = (lib.load().qmoe_launch_count() - launches_before) // args.steps
+
+    # ---- end-to-end arm: every step's inputs come from pinned host memory and every step's outputs (y, dx, aux)
+    # go back to pinned host memory.  The copies run on their own streams, double-buffered, so the H2D of step
+    # i+1 and the D2H of step i-1 overlap the compute of step i — the way a host that feeds the layer from its
+    # own buffers would drive it.
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
     main = torch.cuda.current_stream()
     x_buf = [x_dev, torch.empty_like(x_dev)]
@@ -409,47 +529,6 @@ def run_gpu(args, w, rank, world):
         main.wait_event(copied) if i + 1 == e2e_state.get("last", -1) else None
         e2e_state["i"] = i + 1
 
-    def timed(fn, steps):
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            fn()
-        stop.record()
-        torch.cuda.synchronize()
-        ms = start.elapsed_time(stop) / steps
-        if world > 1:  # the job is as slow as its slowest rank
-            worst = torch.tensor([ms], dtype=torch.float64, device=device)
-            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-            dist.barrier()
-            ms = float(worst.item())
-        return ms
-
-    sampler = ClockSampler(local)   # samples clocks from the warm-up through the last timed pass: all of it is this step under load
-    sampler.start()
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
-    if args.trace:  # kernel timeline of two steps (diagnosis only; nothing measured under it is reported)
-        from torch.profiler import ProfilerActivity, profile
-
-        traced = step_e2e if os.environ.get("QUTAI_BENCH_TRACE_E2E") else step   # which arm's timeline to look at
-        for _ in range(4):
-            traced()
-        torch.cuda.synchronize()
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            for _ in range(3):
-                traced()
-            torch.cuda.synchronize()
-        if rank == 0:
-            prof.export_chrome_trace(args.trace)
-    counts = layer.last_counts
-    launches_before = lib.load().qmoe_launch_count()
-    ms = timed(step, args.steps)
-    launches = (lib.load().qmoe_launch_count() - launches_before) // args.steps
     for _ in range(max(4, args.warmup)):  # until the output buffers of the steps in flight all come from the cache
         step_e2e()
     torch.cuda.synchronize()
@@ -484,11 +563,15 @@ def run_gpu(args, w, rank, world):
         ms_copies = float(worst.item())
     # per-kernel-class device time, measured in a separate pass so the events do not sit inside the headline timing
     graph_mode["on"] = False   # the recorded graph holds no timing events: this pass runs launch by launch
+    for _ in range(5):
+        step()
     lib.timing(True)
+    sampler_end = sampler.t1
     for _ in range(args.steps):
         step()
     classes = lib.timing_read()
     lib.timing(False)
+    sampler.t1 = sampler_end
     graph_mode["on"] = True
     clocks = sampler.stop()
     status = lib.device_status(stream)
@@ -496,8 +579,7 @@ def run_gpu(args, w, rank, world):
     peaks = load_peaks()
     gemm_flops, router_flops = layer_flops(w)
     if world > 1:  # this rank's share: the rows its experts received, its own tokens for the router
-        L = w["E"] // world
-        gemm_flops = 18.0 * sum(counts[rank * L:(rank + 1) * L]) * w["d"] * w["h"]
+        gemm_flops = 18.0 * sum(counts[rank * L:(rank + 1) * L]) * d * h
         router_flops /= world
     if forward_only:
         gemm_flops, router_flops = gemm_flops / 3, router_flops / 3
@@ -505,9 +587,9 @@ def run_gpu(args, w, rank, world):
     gemm_launches = (classes["expert_gemm"][1] + classes["wgrad_gemm"][1]) // args.steps
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     peak = peaks["bf16_tflops_sustained"]
-    active = sum(1 for c in (counts if world == 1 else counts[rank * (w["E"] // world):(rank + 1) * (w["E"] // world)]) if c)
-    weight_bytes = active * 3 * w["d"] * w["h"] * 2     # bf16 weights of the experts that received tokens, read once
-    A, h, E, k = T * w["k"], w["h"], w["E"], w["k"]
+    active = sum(1 for c in counts[rank * L:(rank + 1) * L] if c)
+    weight_bytes = active * 3 * d * h * 2     # bf16 weights of the experts that received tokens, read once
+    A = T * k
     hbm_bytes = dict(permute=T * d * 2 + A * d * 2 + A * 4, combine=A * d * 2 + 3 * A * 4 + T * d * 2,
                      combine_backward=T * d * 2 + 2 * A * d * 2 + A * 4, unpermute=A * d * 2 + T * d * 2 + A * 4,
                      route=2 * T * E * 4 + 2 * A * 4)
@@ -520,6 +602,7 @@ def run_gpu(args, w, rank, world):
     tokens_per_s = T_global / (ms * 1e-3)
     bytes_in = x_host.numel() * 2 * (1 if forward_only else 2)
     bytes_out = x_host.numel() * 2 * (1 if forward_only else 2) + 4
+    mhz = clocks.get("sm_mhz")
     line = dict(
         metric="moe_layer_fwd_bwd_tokens_per_s" if not forward_only else "moe_layer_fwd_tokens_per_s",
         value=tokens_per_s, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
@@ -529,10 +612,13 @@ def run_gpu(args, w, rank, world):
                  d2h_bytes_per_step=bytes_out, copies_alone_ms_per_step=ms_copies,
                  note="copies_alone = the same pinned-host copies, both directions at once, without the layer: the floor this box's host link sets"),
         gpu_launches=int(launches), clocks=clocks,
+        steady_state=dict(preroll_steps=prerolled, preroll_seconds=args.preroll,
+                          ms_x_mhz=(ms * mhz if mhz else None), gemm_ms_x_mhz=(gemm_ms * mhz if mhz else None),
+                          note="back-to-back steps ran for preroll_seconds before the timed ones; ms_x_mhz = ms_per_step x median SM MHz under load, comparable across boxes"),
         roofline=dict(bound="tensor", kernel="grouped_gemm_kernel (tcgen05)", achieved=achieved, peak=peak,
                       unit="TFLOP/s", frac=achieved / peak, peak_source=peaks["source"] + " (sustained cuBLAS bf16)",
-                      traffic=(GEMM_DRAM_BYTES_PER_STEP.get(args.workload) if world == 1 else None),
-                      traffic_unit="DRAM bytes per step over the same launches (profiler capture, see profiles/)",
+                      traffic=(load_gemm_traffic(args.workload) if world == 1 else None),
+                      traffic_unit="DRAM bytes per step over the same launches (profiler capture, profiles/grouped_gemm_dram_bytes.txt)",
                       launches_per_step=int(gemm_launches), ms_per_step=gemm_ms,
                       algorithmic_flops_per_step=gemm_flops, whole_layer_frac=(gemm_flops + router_flops) / (ms * 1e-3) / 1e12 / peak),
         hbm_kernels=hbm,
@@ -543,19 +629,26 @@ def run_gpu(args, w, rank, world):
         expert_counts=dict(max=max(counts), mean=sum(counts) / len(counts), max_over_mean=max(counts) * len(counts) / max(1, sum(counts))),
         device_status=status,
     )
+    if world > 1:
+        line["expert_parallel"] = dict(placement=placement_label, transport=args.transport,
+                                       per_rank_rows=[sum(counts[p * L:(p + 1) * L]) for p in range(world)],
+                                       contiguous=contiguous)
+
+    # ---- value check of the timed path against the CPU oracle (outside every timed region) ----------------
+    check = ep_check(layer, w, rank, world, step, x_dev, g_dev, counts, physical, torch, dist, np)
+    line["ep_check"] = check
+
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample = cpu_sample_tokens(w)
         value, seconds = time_cpu(w, 2, 1, sample)
         cores = host_cores()
+        pure = pure_python_layer()
+        pure["scaled_to_this_workload_tokens_per_s"] = pure["mac_per_s"] / (9.0 * k * d * h + 3.0 * d * E)
         line["cpu_baseline"] = dict(
             value=value, unit="tokens/s", cores=cores, kind="port",
             sample=f"{sample} of {T_global} tokens, full d/E/k/h, numpy float64 restatement of the upstream CPU path on "
                    f"{cores} threads, {seconds:.2f} s per forward+backward",
-            pure_python_estimate=dict(
-                mac_per_s=pure_python_rate(), cores=1,
-                note="scalar triple-loop rate of the upstream pure-Python path; tokens/s = rate / (9*k*d*h + 3*d*E) MAC per token"))
-        rate = line["cpu_baseline"]["pure_python_estimate"]["mac_per_s"]
-        line["cpu_baseline"]["pure_python_estimate"]["tokens_per_s"] = rate / (9.0 * k * d * h + 3.0 * d * E)
+            pure_python=pure)
     if world == 1 and not forward_only and any(p.grad is not None for p in layer.parameters()):
         # the optimizer step either side of the layer (not part of `value`): AdamW over every parameter that has a
         # gradient, one launch, refreshing the bf16 operand copies in the same pass; HBM-bound at 30 bytes per element
@@ -579,20 +672,11 @@ def run_gpu(args, w, rank, world):
                                       frac=adam_bytes / (adam_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], bound="hbm")
         del optimizer
     if forward_only:
-        # decode-shaped workload: per-call latency percentiles over 200 calls, each bracketed by its own events
-        marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
-        torch.cuda.synchronize()
-        for begin, end in marks:
-            begin.record()
-            step()
-            end.record()
-        torch.cuda.synchronize()
-        lat = sorted(b.elapsed_time(e) for b, e in marks)
-        line["latency_ms"] = dict(p50=lat[len(lat) // 2], p99=lat[int(len(lat) * 0.99)], calls=len(lat))
-    if world > 1:
-        line["config"]["expert_placement"] = placement
-        line["config"]["transport"] = args.transport
-        line["per_rank_rows"] = [sum(counts[p * (w["E"] // world):(p + 1) * (w["E"] // world)]) for p in range(world)]
+        line["latency_ms"] = call_latency(step, torch, dist, world, device)
+    elif args.workload == "c3" and not args.no_decode:
+        # the decode-shaped configuration (c3's layer on 64 tokens, forward only): per-call latency of 200 calls
+        line["decode"] = decode_latency(layer, w, rank, world, torch, dist, device, Tensor, wrap, peaks)
+    ok = bool(check["ok"])
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -601,6 +685,153 @@ def run_gpu(args, w, rank, world):
         dist.barrier()
         finalize_communicator()
         dist.destroy_process_group()
+    if not ok:
+        sys.exit(1)
+
+
+def call_latency(call, torch, dist, world, device, calls=200):
+    """p50 / p99 of ``calls`` single calls, each bracketed by its own pair of events (max over ranks per call)."""
+    marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(calls)]
+    for _ in range(10):
+        call()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    for begin, end in marks:
+        begin.record()
+        call()
+        end.record()
+    torch.cuda.synchronize()
+    times = torch.tensor([b.elapsed_time(e) for b, e in marks], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    lat = sorted(times.tolist())
+    return dict(p50=percentile(lat, 0.5), p99=percentile(lat, 0.99), calls=calls)
+
+
+def decode_latency(layer, w, rank, world, torch, dist, device, Tensor, wrap, peaks):
+    """Forward latency of the same layer on 64 tokens (64 sequences x 1 step): a replayed CUDA graph on one GPU,
+    the expert-parallel forward (8 tokens per rank at 8 GPUs) on several."""
+    tokens_global, d = 64, w["d"]
+    tokens = tokens_global // world
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(tokens_global, d, generator=gen, dtype=torch.float32)
+    if w["bias_std"]:
+        x[:, d - 1] = 1.0
+    x_dev = x[rank * tokens:(rank + 1) * tokens].to(torch.bfloat16).to(device)
+    xs = Tensor(wrap(x_dev, "bfloat16"), (tokens, d))
+    layer.refresh_operands = False           # decode: the weights are fixed, their bf16 copies are built once
+    if world == 1:
+        graph = layer.capture_forward(xs)
+        call, how = graph.replay, "CUDA graph replay of the forward (one launch per call)"
+    else:
+        call, how = (lambda: layer(xs)), "expert-parallel forward, launched call by call"
+    out = call_latency(call, torch, dist, world, device)
+    active = sum(1 for c in layer.last_counts if c)
+    weight_bytes = active * 3 * d * w["h"] * 2 / world   # bf16 weights of the experts that received tokens, per GPU
+    out.update(workload=f"c5: {tokens_global} tokens, d_model {d}, experts {w['E']}, top_k {w['k']}, d_expert {w['h']}, forward only",
+               how=how, unit="ms per layer call", tokens_per_s=tokens_global / (out["p50"] * 1e-3),
+               weight_bytes_per_gpu=weight_bytes, weight_stream_gbs_at_p50=weight_bytes / (out["p50"] * 1e-3) / 1e9,
+               weight_stream_frac_of_hbm_peak=weight_bytes / (out["p50"] * 1e-3) / 1e9 / peaks["hbm_gbs"])
+    return out
+
+
+class StackedWeights:
+    """Per-expert view of a gathered [experts, rows, columns] bf16 tensor on the device; an expert's block
+    crosses to the host only when the oracle asks for it."""
+
+    def __init__(self, tensor):
+        self.tensor = tensor
+
+    def __len__(self):
+        return self.tensor.shape[0]
+
+    def __getitem__(self, e):
+        return self.tensor[e].float().cpu().numpy()
+
+
+def ep_check(layer, w, rank, world, step, x_dev, g_dev, counts, logical_of_physical, torch, dist, np):
+    """One more step, its results compared with the CPU oracle: the per-expert counts over all ranks' tokens
+    (bit-exact, from the devices' own fp32 logits) and the auxiliary loss; y and dx of 48 tokens per rank; the
+    three weight gradients of one expert of rank 0.  Expert numbers are the layer's internal (rank-major) ones.
+    Every rank takes part in the gathers; rank 0 computes and shares the verdict."""
+    T_global, d, E, k, h = w["tokens"], w["d"], w["E"], w["k"], w["h"]
+    T, L = T_global // world, E // world
+    device = x_dev.device
+    y, aux, dx = step()
+    torch.cuda.synchronize()
+    buf = layer._saved[0]["buf"]
+
+    def as_tensor(storage, shape, dtype):
+        from qutai_b200 import lib
+
+        out = torch.empty(shape, dtype=dtype, device=device)
+        lib.call("qmoe_memcpy_d2d", out.data_ptr(), storage.ptr, storage.nbytes, torch.cuda.current_stream().cuda_stream)
+        return out
+
+    def gathered(tensor):
+        if world == 1:
+            return tensor
+        out = torch.empty((world * tensor.shape[0], *tensor.shape[1:]), dtype=tensor.dtype, device=device)
+        dist.all_gather_into_tensor(out, tensor.contiguous())
+        return out
+
+    rng = np.random.default_rng(1234)
+    sample_local = torch.from_numpy(np.sort(rng.choice(T, size=min(48, T), replace=False))).to(device)
+    scores = gathered(as_tensor(buf["scores"], (T, E), torch.float32))
+    x_all, g_all = gathered(x_dev), gathered(g_dev)
+    y_s = gathered(as_tensor(y.storage, (T, d), torch.bfloat16)[sample_local])
+    forward_only = dx is None
+    dx_s = None if forward_only else gathered(as_tensor(dx.storage, (T, d), torch.bfloat16)[sample_local])
+    aux_value = as_tensor(aux.storage, (1,), torch.float32)
+    shape = {"w_gate": (L, h, d), "w_up": (L, h, d), "w_down": (L, d, h)}
+    weights = {name: StackedWeights(gathered(as_tensor(buf[name], shape[name], torch.bfloat16))) for name in shape}
+    torch.cuda.synchronize()
+    verdict = None
+    if rank == 0:
+        from oracle import moe_oracle as oracle
+
+        router = router_weights(w)[logical_of_physical].astype(np.float64)     # rows in the layer's internal order
+        scores_host = scores.cpu().numpy().astype(np.float64)
+        route = oracle.routing(scores_host, k)
+        counts_exact = tuple(counts) == route["counts"] and sum(route["counts"]) == T_global * k
+        aux_err = abs(float(aux_value.item()) - route["aux"])
+        sample = torch.cat([sample_local + p * T for p in range(world)])
+        idx = sample.cpu().numpy()
+        xs_host = x_all[sample].float().cpu().numpy().astype(np.float64)
+        ys, _, ctx = oracle.moe_forward(xs_host, router, weights["w_gate"], weights["w_up"], weights["w_down"], k,
+                                        scores=scores_host[idx])
+        y_err = oracle.max_rel_err(y_s.float().cpu().numpy(), ys)
+        dx_err = dw_err = None
+        if not forward_only:
+            gs_host = g_all[sample].float().cpu().numpy().astype(np.float64)
+            grads = oracle.moe_backward(ctx, gs_host, 0.0)
+            # the auxiliary-loss path needs the utilisation over ALL tokens (src/qutai/backends/cpu_lm.py:262-275)
+            probs, util = route["probs"][idx], route["utilization"]
+            d_scores_aux = AUX_GRAD * E / T_global * probs * (util[None, :] - (probs @ util)[:, None])
+            dx_err = oracle.max_rel_err(dx_s.float().cpu().numpy(), grads["x"] + d_scores_aux @ router)
+            # one expert of rank 0 (the one whose row count is the median of the rank's): all its rows, whichever rank sent them
+            local = sorted(range(L), key=lambda j: (counts[j], j))
+            e = local[len(local) // 2]
+            members = torch.from_numpy(route["ids"][e]).to(device)
+            gate_w = route["weights"][route["ids"][e], route["slots"][e]]
+            xe = x_all[members].float().cpu().numpy().astype(np.float64)
+            dy = g_all[members].float().cpu().numpy().astype(np.float64) * gate_w[:, None]
+            _, saved = oracle.expert_forward(xe, weights["w_gate"][e], weights["w_up"][e], weights["w_down"][e])
+            want = oracle.expert_backward(saved, dy, weights["w_gate"][e], weights["w_up"][e], weights["w_down"][e])[:3]
+            expert = layer.experts[e]
+            got = [as_tensor(p.grad.storage, shape, torch.float32).cpu().numpy() for p, shape in
+                   ((expert.gate.weight, (h, d)), (expert.up.weight, (h, d)), (expert.down.weight, (d, h)))]
+            dw_err = max(oracle.max_rel_err(a, b) for a, b in zip(got, want))
+        ok = counts_exact and aux_err <= 1e-5 and y_err <= BF16_TOL and (forward_only or (dx_err <= BF16_TOL and dw_err <= BF16_TOL))
+        verdict = dict(ok=bool(ok), counts_exact=bool(counts_exact), aux_abs_err=aux_err, y=y_err, dx=dx_err, dw=dw_err,
+                       tolerance=BF16_TOL, sampled_tokens=int(idx.size),
+                       how="CPU float64 oracle on the devices' own fp32 logits; max |a - b| / max |b|; counts over all ranks' tokens")
+    if world > 1:
+        box = [verdict]
+        dist.broadcast_object_list(box, src=0)
+        verdict = box[0]
+    return verdict
 
 
 def main():
@@ -611,8 +842,12 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--trace", default="", help="write a chrome trace of two steps (rank 0) to this path")
-    parser.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"])
+    parser.add_argument("--no-decode", action="store_true", help="leave the decode-shaped latency block out of the c3 line")
+    parser.add_argument("--preroll", type=float, default=2.0,
+                        help="seconds of back-to-back steps before the timed ones (the power-capped operating point)")
+    parser.add_argument("--trace", default="", help="write a chrome trace of a few steps (rank 0) to this path")
+    parser.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
+                        help="N > 1: 'balanced' times the contiguous placement first and reports it beside the headline")
     parser.add_argument("--transport", default="p2p", choices=["p2p", "nccl"],
                         help="expert-parallel exchange: direct peer-memory stores, or NCCL send/receive")
     args = parser.parse_args()

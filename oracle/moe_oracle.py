@@ -174,6 +174,34 @@ def combine_backward(gradient, outputs, weights, route):
 
 
 # --------------------------------------------------------------------------------------
+# one expert
+# --------------------------------------------------------------------------------------
+def expert_forward(xe, w_gate, w_up, w_down):
+    """``down(silu(gate(x)) * up(x))`` of one expert on its rows ``xe`` (c_e, d); the expert body of
+    src/qutai/lm/layers.py:310-311 with the bias-free linear maps of src/qutai/lm/layers.py:35-48.
+    Returns ``(ye, saved)`` with ``saved = (xe, g, u, hidden)`` for the backward."""
+    xe = np.asarray(xe, dtype=np.float64)
+    g = xe @ np.asarray(w_gate, dtype=np.float64).T
+    u = xe @ np.asarray(w_up, dtype=np.float64).T
+    hidden = silu(g) * u
+    return hidden @ np.asarray(w_down, dtype=np.float64).T, (xe, g, u, hidden)
+
+
+def expert_backward(saved, dy, w_gate, w_up, w_down):
+    """Backward of ``expert_forward`` for the upstream gradient ``dy`` (c_e, d): the closures of
+    src/qutai/lm/layers.py:50-70 (linear), :99-105 (silu) and
+    src/qutai/core/operations/elementwise.py:40-51 (multiply).  Returns
+    ``(d_w_gate, d_w_up, d_w_down, dxe)``."""
+    xe, g, u, hidden = saved
+    dy = np.asarray(dy, dtype=np.float64)
+    wg, wu, wd = (np.asarray(w, dtype=np.float64) for w in (w_gate, w_up, w_down))
+    d_hidden = dy @ wd
+    d_up = d_hidden * silu(g)
+    d_gate = silu_backward(d_hidden * u, g)
+    return d_gate.T @ xe, d_up.T @ xe, dy.T @ hidden, d_gate @ wg + d_up @ wu
+
+
+# --------------------------------------------------------------------------------------
 # the layer
 # --------------------------------------------------------------------------------------
 def moe_forward(x, router, gate, up, down, top_k, scores=None):
@@ -194,12 +222,7 @@ def moe_forward(x, router, gate, up, down, top_k, scores=None):
     for e in range(route["experts"]):
         if not route["counts"][e]:
             continue
-        xe = route_gather(x, route, e)
-        g = xe @ np.asarray(gate[e], dtype=np.float64).T
-        u = xe @ np.asarray(up[e], dtype=np.float64).T
-        hidden = silu(g) * u
-        ye = hidden @ np.asarray(down[e], dtype=np.float64).T
-        saved[e] = (xe, g, u, hidden)
+        ye, saved[e] = expert_forward(route_gather(x, route, e), gate[e], up[e], down[e])
         outputs.append((e, ye))
     y = combine(outputs, route["weights"], route)
     ctx = dict(x=x, router=router, gate=gate, up=up, down=down, route=route, saved=saved,
@@ -226,15 +249,9 @@ def moe_backward(ctx, grad_y, grad_aux=0.0):
     dx = np.zeros_like(x)
     grads = dict(gate=[None] * experts, up=[None] * experts, down=[None] * experts)
     for (e, _), dy in zip(ctx["outputs"], dys):
-        xe, g, u, hidden = ctx["saved"][e]
-        wg, wu, wd = (np.asarray(ctx[name][e], dtype=np.float64) for name in ("gate", "up", "down"))
-        d_hidden = dy @ wd
-        grads["down"][e] = dy.T @ hidden
-        d_up = d_hidden * silu(g)
-        d_gate = silu_backward(d_hidden * u, g)
-        grads["gate"][e] = d_gate.T @ xe
-        grads["up"][e] = d_up.T @ xe
-        dx += route_gather_backward(d_gate @ wg + d_up @ wu, route, e)
+        grads["gate"][e], grads["up"][e], grads["down"][e], dxe = expert_backward(
+            ctx["saved"][e], dy, ctx["gate"][e], ctx["up"][e], ctx["down"][e])
+        dx += route_gather_backward(dxe, route, e)
     d_scores = routing_backward(dw, route)
     if grad_aux:
         d_scores = d_scores + routing_backward([grad_aux], route, True)
@@ -254,6 +271,19 @@ def round_bf16(a):
     bits = a32.view(np.uint32).astype(np.uint64)
     rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
     return rounded.view(np.float32).astype(np.float64).reshape(a32.shape)
+
+
+def elementwise_err(actual, expected, bf16=False):
+    """Element-wise error in the form of the upstream GPU-against-CPU checks: ``max |a - b| / (1 + |b|)``
+    (``|x - y| <= tol * (1 + |y|)``, tests/test_lm_moe.py:105-138) or, with ``bf16``,
+    ``max |a - b| / max(1, |b|)`` (``tol * max(1, |y|)``, tests/test_lm_bfloat16.py:129-167).  Unlike
+    ``max_rel_err`` a small entry cannot hide behind the largest one of its tensor."""
+    actual = np.asarray(actual, dtype=np.float64)
+    expected = np.asarray(expected, dtype=np.float64)
+    if not expected.size:
+        return 0.0
+    scale = np.maximum(1.0, np.abs(expected)) if bf16 else 1.0 + np.abs(expected)
+    return float((np.abs(actual - expected) / scale).max())
 
 
 def max_rel_err(actual, expected):

@@ -29,6 +29,7 @@ class Tensor:
     (src/qutai/core/tensor.py:14-33); just enough for parameters and activations of this layer."""
 
     def __init__(self, storage, shape=None, requires_grad=False):
+        self.parents, self.backward_rule = (), None     # the fields upstream's ``record`` fills in
         self.storage = storage
         self.shape = tuple(shape) if shape is not None else (storage.size,)
         if prod(self.shape) != storage.size:
@@ -348,10 +349,13 @@ class SparseMoE:
         lib.call("qmoe_graph_end", self.stream, ctypes.byref(graph))
         return ForwardGraph(self, graph.value, work, storage, shape, Tensor(out, shape), Tensor(buf["aux"], ()))
 
-    def backward(self, grad_y, grad_aux=None):
-        """Propagate ``grad_y`` (shaped like the output) and optionally ``grad_aux`` (float32
-        scalar storage/tensor) through the last forward.  Accumulates into ``parameter.grad`` and
-        returns the gradient of the input as a Tensor."""
+    def backward_contributions(self, grad_y, grad_aux=None):
+        """The backward of the last forward as autograd sees it: returns ``(dx, d_router, experts)`` where
+        ``experts[i]`` is ``None`` for an expert that received no token (upstream never calls such an expert, so
+        its parameters get no contribution, src/qutai/lm/layers.py:396) and else the ``(d_gate, d_up, d_down)``
+        tensors.  ``parameter.grad`` is not touched.  The weight contributions are views of the layer's stacked
+        gradient buffers and stay valid until the next backward of this layer; a ``parameter.grad`` that still
+        aliases them is copied out first."""
         if self._saved is None:
             raise RuntimeError("backward called before forward")
         work, x_storage, shape = self._saved
@@ -361,23 +365,53 @@ class SparseMoE:
             raise ValueError("grad_y must match the output's size and dtype")
         ga = None if grad_aux is None else (grad_aux.storage if hasattr(grad_aux, "storage") else grad_aux)
         views = work["grad_views"]
-        owned = {id(views[0])} | {id(t) for group in views[1:] for t in group}
+        owned = {id(views[0].storage)} | {id(t.storage) for group in views[1:] for t in group}
         for parameter in self.parameters():
             # a gradient that still aliases the buffers about to be overwritten is copied out first
-            if parameter.grad is not None and id(parameter.grad) in owned:
-                parameter.grad = Tensor(parameter.grad.storage.copy(self.stream), parameter.shape)
+            if parameter.grad is not None and id(parameter.grad.storage) in owned:
+                parameter.grad = type(parameter.grad)(parameter.grad.storage.copy(self.stream), shape=parameter.shape)
         dx = DeviceStorage(x_storage.size, x_storage.dtype)
         layer.grad_out, layer.grad_aux, layer.dx = g.ptr, 0 if ga is None else ga.ptr, dx.ptr
         lib.call("qmoe_layer_backward", ctypes.byref(layer), self.stream)
         # which experts get a gradient object is host logic on the forward's counts; they are read only
         # now, after the whole backward is enqueued, so the device never idles waiting for the host
         counts = self.last_counts
-        _accumulate(self.router.weight, views[0], self.stream)
-        for i, expert in enumerate(self.experts):
-            if not counts[i]:
+        return Tensor(dx, shape), views[0], [views[1 + i] if counts[i] else None for i in range(self.n_experts)]
+
+    def backward_aux(self, grad_aux):
+        """The auxiliary loss' own path through the last forward (upstream records it as a node of its own,
+        src/qutai/lm/layers.py:387-391): returns ``(dx, d_router)`` for the float32 scalar ``grad_aux`` in fresh
+        storages; touches neither ``parameter.grad`` nor the buffers of ``backward_contributions``."""
+        if self._saved is None:
+            raise RuntimeError("backward_aux called before forward")
+        work, x_storage, shape = self._saved
+        layer, buf = work["layer"], work["buf"]
+        ga = grad_aux.storage if hasattr(grad_aux, "storage") else grad_aux
+        tokens, d, E = x_storage.size // self.d_model, self.d_model, self.n_experts
+        code = lib.DTYPE_CODES[x_storage.dtype]
+        d_router = DeviceStorage(E * d, "float32")
+        dx32 = DeviceStorage(tokens * d, "float32")
+        lib.call("qmoe_route_backward", ctypes.byref(layer.route), 0, ga.ptr, buf["d_scores"].ptr, self.stream)
+        lib.call("qmoe_router_backward", buf["d_scores"].ptr, x_storage.ptr, code, self.router.weight.storage.ptr,
+                 dx32.ptr, d_router.ptr, buf["router_partials"].ptr, tokens, d, E, self.stream)
+        if x_storage.dtype == "bfloat16":
+            dx = DeviceStorage(tokens * d, "bfloat16")
+            lib.call("qmoe_cast_bf16", dx32.ptr, dx.ptr, tokens * d, self.stream)
+        else:
+            dx = dx32
+        return Tensor(dx, shape), Tensor(d_router, (E, d))
+
+    def backward(self, grad_y, grad_aux=None):
+        """Propagate ``grad_y`` (shaped like the output) and optionally ``grad_aux`` (float32
+        scalar storage/tensor) through the last forward.  Accumulates into ``parameter.grad`` and
+        returns the gradient of the input as a Tensor."""
+        dx, d_router, experts = self.backward_contributions(grad_y, grad_aux)
+        _accumulate(self.router.weight, d_router, self.stream)
+        for expert, contribution in zip(self.experts, experts):
+            if contribution is None:
                 continue
-            gate, up, down = views[1 + i]
+            gate, up, down = contribution
             _accumulate(expert.gate.weight, gate, self.stream)
             _accumulate(expert.up.weight, up, self.stream)
             _accumulate(expert.down.weight, down, self.stream)
-        return Tensor(dx, shape)
+        return dx
