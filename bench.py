@@ -218,7 +218,7 @@ def pure_python_layer(max_seconds=6.0):
         seconds = time.perf_counter() - start
         if tokens >= 128 or seconds * 4 > max_seconds:
             break
-        tokens *= 4
+        tokens = min(128, tokens * 4)
     return dict(tokens_per_s=tokens / seconds, mac_per_s=tokens * mac_per_token / seconds, seconds=seconds, cores=1,
                 sample=f"{tokens} of 128 tokens of the tiny CPU configuration's MoE layer (d 64, 4 experts top-2, hidden 128), "
                        "float64 scalar loops, forward + backward")

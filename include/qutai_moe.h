@@ -342,6 +342,55 @@ int qmoe_layer_forward(const qmoe_layer_t* layer, uint64_t stream);
 int qmoe_layer_backward(const qmoe_layer_t* layer, uint64_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The step either side of the layer inside a decoder block, fused into the layer's first read and last write:
+ *     out = x + MoE(rms_norm(x, w))
+ * Upstream: Block.__call__ (src/qutai/lm/layers.py:430-437) = residual_add(x, ffn(ffn_norm(x))), rms_norm
+ * src/qutai/lm/layers.py:88-96, kernels lm_rms / lm_rms_dx / lm_rms_dw src/qutai/backends/cuda/lm.cu:40-53 (launched
+ * from src/qutai/backends/cuda_lm.py:124-178; the norm's output is an fp32 copy of the activations there), CPU
+ * statement src/qutai/backends/cpu_lm.py:84-117.  rms_norm(x, w)[t, j] = x[t, j] * inverse[t] * w[j] with
+ * inverse[t] = 1 / sqrt(mean_j x[t, j]^2 + eps); w is f32 [d].
+ * ------------------------------------------------------------------------------------------- */
+/* inverse[t] (f32 [T]) of every token row: the statistic half of lm_rms; the normalised activations themselves
+ * are never written. */
+int qmoe_rms_inverse(uint64_t x, int32_t dtype, uint64_t inverse, int64_t tokens, int64_t width, double eps,
+                     uint64_t stream);
+/* out[r, c] = in[r, c] * row_scale[r] * col_scale[c] (f32; either scale may be 0 = none; in place allowed).  Folds
+ * the norm weight into the router weight (columns), applies inverse[t] to the logits of the raw activations (rows),
+ * and the reverse for the router's gradients. */
+int qmoe_scale_f32(uint64_t in, uint64_t out, uint64_t row_scale, uint64_t col_scale, int64_t rows, int64_t cols,
+                   uint64_t stream);
+/* qmoe_permute with the norm applied to the row it copies: dispatched[r, :] = round(x[token(r), :] * inverse[token] * w). */
+int qmoe_permute_norm(const qmoe_route_t* route, uint64_t x, uint64_t inverse, uint64_t norm_weight, uint64_t dispatched,
+                      int32_t dtype, int64_t width, uint64_t stream);
+/* qmoe_combine with the residual added before the single rounding: out[t, :] = round(residual[t, :] + sum_s w y). */
+int qmoe_combine_residual(const qmoe_route_t* route, uint64_t y_dispatched, uint64_t residual, uint64_t out, int32_t dtype,
+                          int64_t width, uint64_t stream);
+/* qmoe_unpermute_reduce with the norm's backward (lm_rms_dx, lm_rms_dw) and the residual's gradient folded in.  With
+ * d_n[t] = sum_s d_dispatched[dest_row(t, s)] + extra_f32[t] (gradient of the normalised input; extra may be 0):
+ *   dx[t, j] = round(grad_out[t, j] + inverse[t] * (d_n[j] w[j] - x[t, j] inverse[t]^2 mean_j(d_n[j] w[j] x[t, j])))
+ *   d_norm_weight[j] (f32 [d], written) = sum_t d_n[t, j] x[t, j] inverse[t], reduced in a fixed order.
+ * partials: scratch of qmoe_norm_backward_partials(T, d) floats.  width <= 4096, else QMOE_ERR_UNSUPPORTED. */
+int64_t qmoe_norm_backward_partials(int64_t tokens, int64_t width);
+int qmoe_unpermute_norm_backward(const qmoe_route_t* route, uint64_t d_dispatched, uint64_t extra_f32, uint64_t x,
+                                 uint64_t inverse, uint64_t norm_weight, uint64_t grad_out, uint64_t dx,
+                                 uint64_t d_norm_weight, uint64_t partials, int32_t dtype, int64_t width, uint64_t stream);
+/* The whole feed-forward half of a block in one call per direction: layer.out = layer.x + MoE(rms_norm(layer.x)),
+ * and its backward (layer.dx = gradient of layer.x including the residual's, d_norm_weight written).  `layer` is
+ * filled as for qmoe_layer_forward / qmoe_layer_backward; layer.out must not alias layer.x. */
+typedef struct qmoe_block {
+    qmoe_layer_t layer;
+    uint64_t norm_weight;      /* f32 [d] */
+    uint64_t inverse;          /* f32 [T]      written by the forward, read by the backward */
+    uint64_t w_router_folded;  /* f32 [E, d]   scratch: router weight times the norm weight */
+    uint64_t d_norm_weight;    /* f32 [d]      backward output */
+    uint64_t norm_partials;    /* f32 [qmoe_norm_backward_partials(T, d)] scratch */
+    uint64_t d_scores_scaled;  /* f32 [T, E]   scratch */
+    double norm_eps;
+} qmoe_block_t;
+int qmoe_block_forward(const qmoe_block_t* block, uint64_t stream);
+int qmoe_block_backward(const qmoe_block_t* block, uint64_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Expert parallelism (one process per GPU, NCCL over NVLink / NVSwitch).  The upstream project is
  * single-GPU (src/qutai/backends/cuda_runtime.py:82, :105), so these entry points have no upstream
  * counterpart; they keep the layer's semantics when tokens are sharded T/N per rank (contiguous

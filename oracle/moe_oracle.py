@@ -263,6 +263,53 @@ def moe_backward(ctx, grad_y, grad_aux=0.0):
 
 
 # --------------------------------------------------------------------------------------
+# the step either side of the layer inside a block: RMS norm before, residual after
+# --------------------------------------------------------------------------------------
+def rms_norm(x, weight, eps):
+    """``out[t, j] = x[t, j] * inverse[t] * weight[j]`` with ``inverse[t] = 1 / sqrt(mean_j x[t, j]^2 + eps)``;
+    src/qutai/backends/cpu_lm.py:84-97.  Returns ``(out, inverse)``."""
+    x = np.asarray(x, dtype=np.float64)
+    weight = np.asarray(weight, dtype=np.float64)
+    inverse = 1.0 / np.sqrt((x * x).sum(axis=1) / x.shape[1] + eps)
+    return x * inverse[:, None] * weight[None, :], inverse
+
+
+def rms_norm_backward(gradient, x, weight, inverse):
+    """``dx[t, j] = inverse * (g[t, j] w[j] - x[t, j] inverse^2 projected[t])`` with
+    ``projected[t] = mean_j g[t, j] w[j] x[t, j]``, and ``dw[j] = sum_t g[t, j] x[t, j] inverse[t]``;
+    src/qutai/backends/cpu_lm.py:100-117.  Returns ``(dx, dw)``."""
+    g = np.asarray(gradient, dtype=np.float64)
+    x = np.asarray(x, dtype=np.float64)
+    weight = np.asarray(weight, dtype=np.float64)
+    projected = (g * weight[None, :] * x).sum(axis=1) / x.shape[1]
+    dx = inverse[:, None] * (g * weight[None, :] - x * (inverse * inverse * projected)[:, None])
+    dw = (g * x * inverse[:, None]).sum(axis=0)
+    return dx, dw
+
+
+def block_ffn_forward(x, norm_weight, eps, router, gate, up, down, top_k, scores=None):
+    """The feed-forward half of ``Block.__call__`` for a mixture-of-experts block,
+    src/qutai/lm/layers.py:430-437: ``(x + ffn(ffn_norm(x)), aux)``.  ``scores`` overrides the router product
+    (identical fp32 logits).  Returns ``(out, aux, ctx)``."""
+    x = np.asarray(x, dtype=np.float64)
+    normed, inverse = rms_norm(x, norm_weight, eps)
+    y, aux, ctx = moe_forward(normed, router, gate, up, down, top_k, scores=scores)
+    return x + y, aux, dict(moe=ctx, x=x, norm_weight=np.asarray(norm_weight, dtype=np.float64), inverse=inverse)
+
+
+def block_ffn_backward(ctx, grad_out, grad_aux=0.0):
+    """Backward of ``block_ffn_forward``: the layer's gradients (as ``moe_backward`` returns them, ``x`` being
+    the gradient of the block's input, residual included) plus ``norm_weight``."""
+    grad_out = np.asarray(grad_out, dtype=np.float64).reshape(ctx["x"].shape)
+    grads = moe_backward(ctx["moe"], grad_out, grad_aux)
+    dx, dw = rms_norm_backward(grads["x"], ctx["x"], ctx["norm_weight"], ctx["inverse"])
+    grads["normed"] = grads["x"]
+    grads["x"] = grad_out + dx
+    grads["norm_weight"] = dw
+    return grads
+
+
+# --------------------------------------------------------------------------------------
 # helpers used by tests and by the benchmark's CPU leg
 # --------------------------------------------------------------------------------------
 def round_bf16(a):
@@ -273,17 +320,35 @@ def round_bf16(a):
     return rounded.view(np.float32).astype(np.float64).reshape(a32.shape)
 
 
-def elementwise_err(actual, expected, bf16=False):
-    """Element-wise error in the form of the upstream GPU-against-CPU checks: ``max |a - b| / (1 + |b|)``
+def elementwise_err(actual, expected, bf16=False, unit=1.0):
+    """Element-wise error in the form of the upstream GPU-against-CPU checks: ``max |a - b| / (unit + |b|)``
     (``|x - y| <= tol * (1 + |y|)``, tests/test_lm_moe.py:105-138) or, with ``bf16``,
-    ``max |a - b| / max(1, |b|)`` (``tol * max(1, |y|)``, tests/test_lm_bfloat16.py:129-167).  Unlike
-    ``max_rel_err`` a small entry cannot hide behind the largest one of its tensor."""
+    ``max |a - b| / max(unit, |b|)`` (``tol * max(1, |y|)``, tests/test_lm_bfloat16.py:129-167).  Upstream's
+    test data are of order one, hence its ``1``; ``unit`` is that scale (pass the tensor's root mean square for
+    data of another magnitude).  Unlike ``max_rel_err`` an entry cannot hide behind the largest one of its tensor."""
     actual = np.asarray(actual, dtype=np.float64)
     expected = np.asarray(expected, dtype=np.float64)
     if not expected.size:
         return 0.0
-    scale = np.maximum(1.0, np.abs(expected)) if bf16 else 1.0 + np.abs(expected)
+    scale = np.maximum(unit, np.abs(expected)) if bf16 else unit + np.abs(expected)
     return float((np.abs(actual - expected) / scale).max())
+
+
+def rms(values):
+    values = np.asarray(values, dtype=np.float64)
+    return float(np.sqrt(np.mean(values * values))) if values.size else 0.0
+
+
+def rowwise_rel_err(actual, expected):
+    """``max over rows of (max |a - b| over the row / max |b| over the row)`` for 2-D arrays: every row (an
+    expert's router gradient, a token's output) is held to the relative bar on its own scale."""
+    actual = np.asarray(actual, dtype=np.float64)
+    expected = np.asarray(expected, dtype=np.float64)
+    if not expected.size:
+        return 0.0
+    scale = np.abs(expected).max(axis=1)
+    error = np.abs(actual - expected).max(axis=1)
+    return float((error[scale > 0] / scale[scale > 0]).max()) if np.any(scale > 0) else float(error.max())
 
 
 def max_rel_err(actual, expected):

@@ -6,7 +6,8 @@
 // CTAs of a cluster share one 256 x 256 tile, tcgen05.mma.cta_group::2), the small router products with one
 // CTA per 128 x 256 tile:
 //   warp 0      TMA producer (one lane): fills a ring of {A 128x64, B 256x64 or this CTA's 128x64 half} bf16
-//               tiles (4 stages of 48 KiB, or 6 stages of 32 KiB per CTA of a pair)
+//               tiles (4 stages of 48 KiB, or 6 stages of 32 KiB per CTA of a pair; two fewer in dSwiGLU, whose
+//               epilogue stages its own operands in shared memory)
 //   warp 1      MMA issuer (one lane, in a pair only the first CTA's): 4 x tcgen05.mma (K = 16 each) per
 //               stage, commits free the stage in both CTAs; also allocates / frees the 512 TMEM columns
 //               (two 128x256 fp32 accumulators per CTA)
@@ -20,7 +21,8 @@
 //                "x W^T") or [E*K, N] (MN-major, "g W").
 //   MODE_SWIGLU  G = X Wg_e^T, U = X Wu_e^T (128 + 128 accumulator columns), H = silu(G) * U, all
 //                three stored as bf16.
-//   MODE_DSWIGLU dH = dY Wd_e (never stored): dU = dH * silu(G), dG = dH * U * silu'(G), bf16.
+//   MODE_DSWIGLU dH = dY Wd_e (never stored): dU = dH * silu(G), dG = dH * U * silu'(G), bf16; G and U are
+//                fetched and dG and dU written by TMA in the layout the accumulator is read in.
 //   MODE_WGRAD   C_e[M, N] (fp32) = A_e^T . B_e, contraction over the rows of expert e (both
 //                operands MN-major); experts without rows are skipped and their slab is not written.
 //                Up to three such products of one shape share a launch (dWd, dWg, dWu).
@@ -48,18 +50,27 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64 x 64 bf16 TMA box (8 KiB)
 // CTAS = 2: a pair of CTAs (cluster of 2, tcgen05 cta_group::2) owns a 256 x 256 tile; each CTA stages its 128
 //           rows of A and HALF of B (16 + 16 KiB per stage, 6 stages), so every byte fetched from L2 feeds
 //           1.5x more math, and the issuing CTA's MMA reads both halves.
-template <int CTAS> struct Cfg {
-    static constexpr int STAGES = CTAS == 2 ? 6 : 4;
+// Shared memory of a CTA: [operand ring][epilogue staging, one slice per epilogue warp][mbarriers].  The dSwiGLU
+// epilogue keeps two {G, U} boxes of 32 rows x 32 columns per warp in its slice (fetched and written back by TMA),
+// which costs the ring two stages; the other modes only need a small transpose buffer per warp.
+constexpr int EPILOGUE_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * EPILOGUE_WARPS;  // TMA warp + MMA warp + epilogue warps
+constexpr int MODE_DSWIGLU_ID = 3;
+constexpr int BOX_BYTES = 32 * 32 * 2;            // one 32 x 32 bf16 box of the dSwiGLU epilogue (2 KiB, 64-byte rows)
+constexpr int BARRIER_BYTES = 512;
+template <int CTAS, int MODE> struct Cfg {
+    static constexpr bool STAGED = MODE == MODE_DSWIGLU_ID;
+    static constexpr int STAGES = CTAS == 2 ? (STAGED ? 4 : 6) : (STAGED ? 3 : 4);
     static constexpr int B_STAGE_BYTES = (CTAS == 2 ? BN / 2 : BN) * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 32 * 80 /*epilogue transpose*/;
+    static constexpr int EPI_WARP_BYTES = STAGED ? 4 * BOX_BYTES : 32 * 80;   // per epilogue warp
+    static constexpr int EPI_BYTES = EPILOGUE_WARPS * EPI_WARP_BYTES;        // a multiple of 1 KiB either way
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + EPI_BYTES + BARRIER_BYTES;
 };
-constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
-constexpr int EPILOGUE_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
-enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2, MODE_DSWIGLU = 3, MODE_ROUTER = 4, MODE_PLAIN_F32 = 5 };
+enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2, MODE_DSWIGLU = MODE_DSWIGLU_ID, MODE_ROUTER = 4, MODE_PLAIN_F32 = 5 };
 enum { STATUS_WAIT_PRODUCER = 101, STATUS_WAIT_MMA = 102, STATUS_WAIT_EPILOGUE = 103 };
 
 struct alignas(64) GemmParams {
@@ -132,6 +143,17 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t dst
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+// TMA store of one box from this CTA's shared memory (bulk async group of the issuing thread)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's bulk stores have finished READING shared memory (all of them / all but the newest group)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// writes made with ordinary stores become visible to the TMA unit (async proxy)
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -345,32 +367,6 @@ __device__ __forceinline__ void scatter_block32(uint32_t stage, int lane, const 
     __syncwarp();
 }
 
-// Thread `lane` holds the 32 fp32 values r[0..31] of row `lane` (the TMEM read layout).  Redistribute the
-// 32 x 32 block to the coalesced layout: on return out[j][0..7] are the values of row j * 8 + lane / 4,
-// columns (lane % 4) * 8 .. + 8, i.e. exactly what one 16-byte bf16 access of that lane covers.  Two passes
-// of 16 columns each fit the 32 x 80 B staging buffer (pass s moves columns 8q + 4s .. + 4 of every row).
-__device__ __forceinline__ void spread_block32(uint32_t stage, int lane, const uint32_t* r, float (*out)[8]) {
-    const uint32_t mine = stage + lane * STAGE_PITCH;
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16 * q), "r"(r[8 * q + 4 * s]),
-                         "r"(r[8 * q + 4 * s + 1]), "r"(r[8 * q + 4 * s + 2]), "r"(r[8 * q + 4 * s + 3]) : "memory");
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int row = j * 8 + (lane >> 2), piece = lane & 3;
-            uint32_t a, b, c, d;
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
-                         : "r"(stage + row * STAGE_PITCH + 16 * piece) : "memory");
-            out[j][4 * s] = __uint_as_float(a); out[j][4 * s + 1] = __uint_as_float(b);
-            out[j][4 * s + 2] = __uint_as_float(c); out[j][4 * s + 3] = __uint_as_float(d);
-        }
-        __syncwarp();
-    }
-}
-
 // Thread `lane` holds the 32 fp32 values of row `lane`; store the 32 x 32 block to `dst` (first element of the
 // block, row pitch ldc floats, rows >= rows_left skipped) so that every store instruction covers 8 rows x 64
 // contiguous bytes.  Two passes of 16 columns through the 32 x 80 B staging buffer.
@@ -433,7 +429,8 @@ __device__ __forceinline__ void scatter_rows256(uint32_t stage, int lane, const 
 template <int MODE, bool A_MN, bool B_MN, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
-    constexpr int STAGES = Cfg<CTAS>::STAGES, B_STAGE_BYTES = Cfg<CTAS>::B_STAGE_BYTES, STAGE_BYTES = Cfg<CTAS>::STAGE_BYTES;
+    using Config = Cfg<CTAS, MODE>;
+    constexpr int STAGES = Config::STAGES, B_STAGE_BYTES = Config::B_STAGE_BYTES, STAGE_BYTES = Config::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_start[kMaxExperts + 1];  // first 128-row tile of each expert
     __shared__ int s_pair[kMaxExperts + 1];   // CTAS == 2: first 256-row pair-tile of each expert
@@ -446,7 +443,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const int first_tile = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;  // a cluster is two consecutive blocks
     const int tile_stride = (int)gridDim.x / CTAS;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    const uint32_t epi0 = base + STAGES * STAGE_BYTES;   // epilogue staging, 1 KiB aligned
+    const uint32_t bars = epi0 + Config::EPI_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
@@ -477,11 +475,15 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         // of both hand an accumulator back on the first CTA's barrier
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPILOGUE_WARPS * CTAS); }
+        if (MODE == MODE_DSWIGLU) {  // per epilogue warp: one barrier per {G, U} box pair
+            for (int i = 0; i < 2 * EPILOGUE_WARPS; ++i) mbar_init(bars + 8u * (2 * STAGES + 4 + i), 1);
+            prefetch_map(&p.map_a2); prefetch_map(&p.map_b2); prefetch_map(&p.map_a3); prefetch_map(&p.map_b3);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_map(&p.map_a);
         prefetch_map(&p.map_b);
-        if (MODE == MODE_SWIGLU || p.segments == 2) prefetch_map(&p.map_b2);
-        if (p.segments == 2) prefetch_map(&p.map_a2);
+        if (MODE == MODE_SWIGLU || (MODE != MODE_DSWIGLU && p.segments == 2)) prefetch_map(&p.map_b2);
+        if (MODE != MODE_DSWIGLU && p.segments == 2) prefetch_map(&p.map_a2);
     }
     if (warp == 1) {
         if (CTAS == 2) {
@@ -624,10 +626,127 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 ++iter;
             }
         }
+    } else if (MODE == MODE_DSWIGLU) {
+        // ------------------------------ epilogue of dSwiGLU -------------------------
+        // dG = dH . U . silu'(G), dU = dH . silu(G), with dH only ever in tensor memory.  G and U arrive, and dG and
+        // dU leave, through TMA in boxes of 32 rows x 32 columns laid out like the accumulator is read (one thread =
+        // one row, 64-byte swizzle so the 32 rows of a warp do not collide on the banks): no transposes and no
+        // per-thread global accesses.  Each warp owns two {G, U} buffers; while it works on one chunk the boxes of its
+        // next chunk (of this tile or of its next tile) are already on their way, and results overwrite their inputs
+        // in place before the store.
+        const int warp_e = warp - 2, quad = warp & 3, half = warp_e >> 2;
+        const uint32_t slice = epi0 + (uint32_t)warp_e * Config::EPI_WARP_BYTES;
+        auto load_bar = [&](uint32_t n) { return bars + 8u * (2 * STAGES + 4 + warp_e * 2 + (n & 1u)); };
+        auto buffer = [&](uint32_t n) { return slice + (n & 1u) * 2u * BOX_BYTES; };
+        // chunks [c, c_last) of 32 columns this warp converts in `tile` (none when its rows lie past the expert's end)
+        auto chunks_of = [&](const Tile& tile, int& c, int& c_last) {
+            c = c_last = 0;
+            if (!tile.valid || (CTAS == 2 && !tile.rows_valid)) return;
+            const int per = tile.bn / 64, in_range = (p.N - tile.n0 + 31) / 32;
+            c = half * per;
+            c_last = c + per < in_range ? c + per : in_range;
+            if (c_last < c) c_last = c;
+        };
+        auto issue_load = [&](const Tile& tile, int c, uint32_t n) {  // one lane: boxes of chunk c into buffer n & 1
+            const uint32_t bar = load_bar(n), dst = buffer(n);
+            const int col = tile.n0 + c * 32, row = tile.row0 + quad * 32;
+            mbar_expect_tx(bar, 2 * BOX_BYTES);
+            tma_load_2d(&p.map_a2, dst, bar, col, row);
+            tma_load_2d(&p.map_b2, dst + BOX_BYTES, bar, col, row);
+        };
+        uint32_t n = 0;            // chunks this warp has consumed: buffer n & 1, barrier phase (n >> 1) & 1
+        bool on_its_way = false;   // the boxes of chunk number n have been asked for
+        int iter = 0;
+        bool gave_up = false;
+        for (int t = first_tile; t < total_tiles && !*abort_flag && !gave_up; t += tile_stride) {
+            const Tile tile = decode_tile<MODE, B_MN, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
+            if (!tile.valid) continue;
+            int c_begin, c_end;
+            chunks_of(tile, c_begin, c_end);
+            if (c_begin < c_end && !on_its_way) {  // only the first chunk of the kernel is not prefetched
+                if (lane == 0) issue_load(tile, c_begin, n);
+                on_its_way = true;
+            }
+            const int acc = iter & 1;
+            const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+                if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_EPILOGUE); }
+                break;
+            }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; ++c) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 32, r);
+                // the chunk after this one: the next of this tile, else the first of this warp's next tile with work
+                {
+                    Tile next_tile = tile;
+                    int next_c = c + 1, next_last = c_end;
+                    if (next_c >= c_end) {
+                        next_c = next_last = 0;
+                        for (int u = t + tile_stride; u < total_tiles; u += tile_stride) {
+                            next_tile = decode_tile<MODE, B_MN, CTAS>(p, s_start, s_pair, s_order, u, cta_rank);
+                            chunks_of(next_tile, next_c, next_last);
+                            if (next_c < next_last) break;
+                        }
+                    }
+                    on_its_way = next_c < next_last;
+                    if (on_its_way && lane == 0) {
+                        bulk_wait_read_all();   // the store that last used that buffer (chunk n - 1) has read it
+                        issue_load(next_tile, next_c, n + 1);
+                    }
+                }
+                tmem_ld_wait();
+                if (!mbar_wait(load_bar(n), (n >> 1) & 1u, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_EPILOGUE); }
+                    gave_up = true;
+                    break;
+                }
+                const uint32_t row_g = buffer(n) + (uint32_t)lane * 64u, row_u = row_g + BOX_BYTES;
+                const uint32_t twist = ((uint32_t)lane >> 1) & 3u;   // 64-byte swizzle: 16-byte piece j of row r sits at j ^ ((r >> 1) & 3)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t at = ((uint32_t)j ^ twist) * 16u;
+                    uint32_t gw[4], uw[4], og[4], ou[4];
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(gw[0]), "=r"(gw[1]), "=r"(gw[2]), "=r"(gw[3]) : "r"(row_g + at) : "memory");
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(uw[0]), "=r"(uw[1]), "=r"(uw[2]), "=r"(uw[3]) : "r"(row_u + at) : "memory");
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float g0 = bf16_lo(gw[i]), g1 = bf16_hi(gw[i]);
+                        const float u0 = bf16_lo(uw[i]), u1 = bf16_hi(uw[i]);
+                        const float s0 = fast_sigmoid(g0), s1 = fast_sigmoid(g1);
+                        const float h0 = __uint_as_float(r[8 * j + 2 * i]), h1 = __uint_as_float(r[8 * j + 2 * i + 1]);
+                        ou[i] = pack_bf16(h0 * g0 * s0, h1 * g1 * s1);
+                        og[i] = pack_bf16(h0 * u0 * s0 * (1.f + g0 * (1.f - s0)), h1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
+                    }
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_g + at), "r"(og[0]), "r"(og[1]), "r"(og[2]), "r"(og[3]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_u + at), "r"(ou[0]), "r"(ou[1]), "r"(ou[2]), "r"(ou[3]) : "memory");
+                }
+                fence_async_shared();
+                __syncwarp();
+                if (lane == 0) {
+                    const int col = tile.n0 + c * 32, row = tile.row0 + quad * 32;
+                    tma_store_2d(&p.map_a3, buffer(n), col, row);
+                    tma_store_2d(&p.map_b3, buffer(n) + BOX_BYTES, col, row);
+                    bulk_commit();
+                }
+                ++n;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (CTAS == 2 && cta_rank) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+                else mbar_arrive(tempty_bar(acc));
+            }
+            ++iter;
+        }
+        if (lane == 0) bulk_wait_all();   // shared memory stays until the last store has left it
+        __syncwarp();
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int quad = warp & 3;         // TMEM lanes [32 * quad, 32 * quad + 32) belong to this warp
-        const uint32_t stage = bars + 256u + (uint32_t)(warp - 2) * EPI_STAGE_BYTES;  // this warp's transpose buffer
+        const uint32_t stage = epi0 + (uint32_t)(warp - 2) * Config::EPI_WARP_BYTES;  // this warp's transpose buffer
         const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp converts
         int iter = 0;
         for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
@@ -685,73 +804,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                 G[lane * p.ldc + c * 32 + i] = gb;
                                 U[lane * p.ldc + c * 32 + i] = ub;
                                 H[lane * p.ldc + c * 32 + i] = __float2bfloat16_rn(g * fast_sigmoid(g) * __bfloat162float(ub));
-                            }
-                    }
-                }
-            } else if (MODE == MODE_DSWIGLU) {
-                const __nv_bfloat16* G = (const __nv_bfloat16*)p.in0 + row0w * p.ldc + tile.n0;
-                const __nv_bfloat16* U = (const __nv_bfloat16*)p.in1 + row0w * p.ldc + tile.n0;
-                __nv_bfloat16* dG = (__nv_bfloat16*)p.out0 + row0w * p.ldc + tile.n0;
-                __nv_bfloat16* dU = (__nv_bfloat16*)p.out1 + row0w * p.ldc + tile.n0;
-                // coalesced loads of the saved activations run one 32-column chunk ahead of their use
-                uint4 lg[4], lu[4];
-                if (p.N - (tile.n0 + c_begin * 32) >= 32) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + c_begin * 32 + (lane & 3) * 8;
-                        lg[j] = *reinterpret_cast<const uint4*>(G + at);
-                        lu[j] = *reinterpret_cast<const uint4*>(U + at);
-                    }
-                }
-#pragma unroll 1
-                for (int c = c_begin; c < c_end; ++c) {
-                    const int valid = p.N - (tile.n0 + c * 32);
-                    uint4 ng[4], nu[4];
-                    if (c + 1 < c_end && valid - 32 >= 32) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + (c + 1) * 32 + (lane & 3) * 8;
-                            ng[j] = *reinterpret_cast<const uint4*>(G + at);
-                            nu[j] = *reinterpret_cast<const uint4*>(U + at);
-                        }
-                    }
-                    uint32_t r[32];
-                    tmem_ld32(taddr + c * 32, r);
-                    tmem_ld_wait();
-                    if (valid >= 32) {
-                        // one fp32 transpose of dH into the layout G and U were loaded in; the products are
-                        // formed and stored there (16-byte accesses, 8 rows x 64 contiguous bytes per instruction)
-                        float dh[4][8];
-                        spread_block32(stage, lane, r, dh);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t gw[4] = {lg[j].x, lg[j].y, lg[j].z, lg[j].w};
-                            const uint32_t uw[4] = {lu[j].x, lu[j].y, lu[j].z, lu[j].w};
-                            uint32_t og[4], ou[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float g0 = bf16_lo(gw[i]), g1 = bf16_hi(gw[i]);
-                                const float u0 = bf16_lo(uw[i]), u1 = bf16_hi(uw[i]);
-                                const float s0 = fast_sigmoid(g0), s1 = fast_sigmoid(g1);
-                                const float h0 = dh[j][2 * i], h1 = dh[j][2 * i + 1];
-                                ou[i] = pack_bf16(h0 * g0 * s0, h1 * g1 * s1);
-                                og[i] = pack_bf16(h0 * u0 * s0 * (1.f + g0 * (1.f - s0)), h1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
-                            }
-                            const long long at = (long long)(j * 8 + (lane >> 2)) * p.ldc + c * 32 + (lane & 3) * 8;
-                            *reinterpret_cast<uint4*>(dG + at) = make_uint4(og[0], og[1], og[2], og[3]);
-                            *reinterpret_cast<uint4*>(dU + at) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) { lg[j] = ng[j]; lu[j] = nu[j]; }
-                    } else if (valid > 0) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (i < valid) {
-                                const long long at = lane * p.ldc + c * 32 + i;
-                                const float g = __bfloat162float(G[at]), u = __bfloat162float(U[at]);
-                                const float sg = fast_sigmoid(g), dh = __uint_as_float(r[i]);
-                                dU[at] = __float2bfloat16_rn(dh * g * sg);
-                                dG[at] = __float2bfloat16_rn(dh * u * sg * (1.f + g * (1.f - sg)));
                             }
                     }
                 }
@@ -910,9 +962,10 @@ EncodeTiledFn encode_fn() {
 std::mutex g_map_mutex;
 std::map<std::tuple<uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> g_maps;
 
-// 2-D bf16 row-major matrix [outer, inner], box {box_inner = 64, box_outer}, 128-byte swizzle.
-int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uint32_t box_outer, uint64_t pitch = 0) {
-    const uint32_t box_inner = 64;
+// 2-D bf16 row-major matrix [outer, inner], box {box_inner, box_outer}: 64 columns with the 128-byte swizzle (the
+// operand tiles), or 32 columns with the 64-byte swizzle (the epilogue boxes of dSwiGLU).
+int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uint32_t box_outer, uint64_t pitch = 0,
+             uint32_t box_inner = 64) {
     if (!pitch) pitch = inner;  // elements between consecutive rows
     auto key = std::make_tuple(ptr, inner | (pitch << 32), outer, box_inner, box_outer);
     {
@@ -929,7 +982,8 @@ int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uin
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner %llu, outer %llu, box %u x %u)", (int)rc,
@@ -945,7 +999,7 @@ int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uin
 template <int MODE, bool A_MN, bool B_MN, int CTAS = 1>
 int launch(const GemmParams& p, cudaStream_t stream) {
     static int grid_of[64] = {0};  // per device: blocks to launch (0: not configured yet)
-    constexpr int SMEM_BYTES = Cfg<CTAS>::SMEM_BYTES;
+    constexpr int SMEM_BYTES = Cfg<CTAS, MODE>::SMEM_BYTES;
     int dev = 0;
     QMOE_CUDA(cudaGetDevice(&dev));
     if (dev >= 64) return fail_arg("device ordinal beyond 63");
@@ -1060,7 +1114,12 @@ int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down,
     GemmParams p = {};
     if (int rc = make_map(&p.map_a, dy, (uint64_t)d, (uint64_t)r->rows_bound, BM)) return rc;
     if (int rc = make_map(&p.map_b, w_down, (uint64_t)h, (uint64_t)experts * d, 64)) return rc;
-    p.map_a2 = p.map_a; p.map_b2 = p.map_b;
+    // the epilogue's boxes: G and U in, dG and dU out, 32 rows x 32 columns each
+    const uint64_t rows = (uint64_t)r->rows_bound;
+    if (int rc = make_map(&p.map_a2, g, (uint64_t)h, rows, 32, 0, 32)) return rc;
+    if (int rc = make_map(&p.map_b2, u, (uint64_t)h, rows, 32, 0, 32)) return rc;
+    if (int rc = make_map(&p.map_a3, dg, (uint64_t)h, rows, 32, 0, 32)) return rc;
+    if (int rc = make_map(&p.map_b3, du, (uint64_t)h, rows, 32, 0, 32)) return rc;
     p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
     p.out0 = (void*)dg; p.out1 = (void*)du; p.in0 = (const void*)g; p.in1 = (const void*)u;
     p.ldc = h; p.experts = experts; p.n_tiles = ceil_div(h, BN);

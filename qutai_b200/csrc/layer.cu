@@ -214,3 +214,69 @@ extern "C" int qmoe_layer_backward(const qmoe_layer_t* L, uint64_t stream) {
                                       L->router_partials, r->tokens, d, r->experts, stream)) return rc;
     return qmoe_unpermute_reduce(r, L->dx_dispatched, L->dx_router, L->dx, ex->dtype, d, stream);
 }
+
+// ---- the block's feed-forward half with the norm and the residual fused in -------------------------------
+namespace {
+int check_block(const qmoe_block_t* B) {
+    if (!B) return fail_arg("block is null");
+    if (!B->norm_weight || !B->inverse || !B->w_router_folded) return fail_arg("block: null norm weight / inverse / folded router address");
+    if (!(B->norm_eps >= 0)) return fail_arg("block: norm_eps must not be negative");
+    return 0;
+}
+}  // namespace
+
+extern "C" int qmoe_block_forward(const qmoe_block_t* B, uint64_t stream) {
+    if (int rc = check_block(B)) return rc;
+    const qmoe_layer_t* L = &B->layer;
+    const qmoe_route_t* r = &L->route;
+    const qmoe_experts_t* ex = &L->experts;
+    int engine = 0;
+    if (int rc = check_experts(r, ex, &engine)) return rc;
+    if (!L->x || !L->w_router || !L->scores || !L->x_dispatched || !L->g || !L->u || !L->h || !L->y_dispatched || !L->out)
+        return fail_arg("block_forward: null buffer address");
+    if (L->out == L->x) return fail_arg("block_forward: the output must not alias the input (the backward re-reads it)");
+    const long long d = ex->width, hd = ex->hidden, E = ex->experts;
+    if (ex->dtype == QMOE_BF16 && L->master_gate) {
+        if (!L->master_up || !L->master_down) return fail_arg("block_forward: master weights must be given together");
+        if (int rc = qmoe_cast_bf16(L->master_gate, ex->w_gate, E * hd * d, stream)) return rc;
+        if (int rc = qmoe_cast_bf16(L->master_up, ex->w_up, E * hd * d, stream)) return rc;
+        if (int rc = qmoe_cast_bf16(L->master_down, ex->w_down, E * hd * d, stream)) return rc;
+    }
+    // scores = rms_norm(x) . W_r^T = inverse[t] * (x . (W_r * w)^T): the product reads the raw activations
+    if (int rc = qmoe_rms_inverse(L->x, ex->dtype, B->inverse, r->tokens, d, B->norm_eps, stream)) return rc;
+    if (int rc = qmoe_scale_f32(L->w_router, B->w_router_folded, 0, B->norm_weight, E, d, stream)) return rc;
+    if (int rc = qmoe_router_forward(L->x, ex->dtype, B->w_router_folded, L->scores, L->router_partials, r->tokens, d, r->experts, stream)) return rc;
+    if (int rc = qmoe_scale_f32(L->scores, L->scores, B->inverse, 0, r->tokens, E, stream)) return rc;
+    if (int rc = qmoe_route(r, L->scores, stream)) return rc;
+    if (int rc = qmoe_permute_norm(r, L->x, B->inverse, B->norm_weight, L->x_dispatched, ex->dtype, d, stream)) return rc;
+    if (int rc = qmoe_expert_forward(r, ex, L->x_dispatched, L->g, L->u, L->h, L->y_dispatched, stream)) return rc;
+    return qmoe_combine_residual(r, L->y_dispatched, L->x, L->out, ex->dtype, d, stream);
+}
+
+extern "C" int qmoe_block_backward(const qmoe_block_t* B, uint64_t stream) {
+    if (int rc = check_block(B)) return rc;
+    const qmoe_layer_t* L = &B->layer;
+    const qmoe_route_t* r = &L->route;
+    const qmoe_experts_t* ex = &L->experts;
+    int engine = 0;
+    if (int rc = check_experts(r, ex, &engine)) return rc;
+    if (!L->grad_out || !L->dy_dispatched || !L->d_h || !L->d_g || !L->d_u || !L->dx_dispatched || !L->d_gate_weights ||
+        !L->d_scores || !L->dx_router || !L->router_partials || !L->dx || !L->d_w_router || !B->d_norm_weight ||
+        !B->norm_partials || !B->d_scores_scaled)
+        return fail_arg("block_backward: null buffer address");
+    const long long d = ex->width, E = ex->experts;
+    if (int rc = qmoe_combine_backward(r, L->grad_out, L->y_dispatched, L->dy_dispatched, L->d_gate_weights, ex->dtype, d, stream)) return rc;
+    if (int rc = qmoe_expert_backward(r, ex, L->dy_dispatched, L->x_dispatched, L->g, L->u, L->h, L->d_h, L->d_g, L->d_u,
+                                      L->dx_dispatched, L->d_w_gate, L->d_w_up, L->d_w_down, stream)) return rc;
+    if (int rc = qmoe_route_backward(r, L->d_gate_weights, L->grad_aux, L->d_scores, stream)) return rc;
+    // router: the gradient of the NORMALISED input is d_scores . W_r; the weight gradient is d_scores^T . rms_norm(x)
+    // = ((inverse * d_scores)^T . x) * w, again from the raw activations
+    if (int rc = qmoe_router_backward(L->d_scores, L->x, ex->dtype, L->w_router, L->dx_router, 0, L->router_partials,
+                                      r->tokens, d, r->experts, stream)) return rc;
+    if (int rc = qmoe_scale_f32(L->d_scores, B->d_scores_scaled, B->inverse, 0, r->tokens, E, stream)) return rc;
+    if (int rc = qmoe_router_backward(B->d_scores_scaled, L->x, ex->dtype, L->w_router, 0, L->d_w_router, L->router_partials,
+                                      r->tokens, d, r->experts, stream)) return rc;
+    if (int rc = qmoe_scale_f32(L->d_w_router, L->d_w_router, 0, B->norm_weight, E, d, stream)) return rc;
+    return qmoe_unpermute_norm_backward(r, L->dx_dispatched, L->dx_router, L->x, B->inverse, B->norm_weight, L->grad_out,
+                                        L->dx, B->d_norm_weight, B->norm_partials, ex->dtype, d, stream);
+}

@@ -303,18 +303,29 @@ class SparseMoE:
         layer.master_gate, layer.master_up, layer.master_down = masters
         if not keep:
             self._operands_made(work)
-        # The host's copy of the counts travels on a stream of its own: a device-to-host copy queued on the
-        # caller's stream would wait behind whatever large copy-out the caller has in flight on the same copy
-        # engine, and every kernel after it would wait too.
+        self._publish_counts(buf)
+        self.utilization = Tensor(buf["utilization"], (self.n_experts,))
+        self._saved = (work, storage, shape)
+        return Tensor(out, shape), Tensor(buf["aux"], ())
+
+    def _publish_counts(self, buf):
+        """Start the host's copy of the counts of the forward just enqueued.  It travels on a stream of its own: a
+        device-to-host copy queued on the caller's stream would wait behind whatever large copy-out the caller
+        has in flight on the same copy engine, and every kernel after it would wait too."""
         lib.call("qmoe_event_record", self._routed_event, self.stream)
         lib.call("qmoe_stream_wait_event", self._copy_stream, self._routed_event)
         lib.call("qmoe_memcpy_d2h", ctypes.cast(self._counts_host, ctypes.c_void_p), buf["counts"].ptr,
                  4 * self.n_experts, self._copy_stream)
         lib.call("qmoe_event_record", self._counts_event, self._copy_stream)
         self._counts_valid = True
-        self.utilization = Tensor(buf["utilization"], (self.n_experts,))
-        self._saved = (work, storage, shape)
-        return Tensor(out, shape), Tensor(buf["aux"], ())
+
+    def _release_aliased_gradients(self, work):
+        """A ``parameter.grad`` that still aliases the stacked gradient buffers about to be overwritten is copied out."""
+        views = work["grad_views"]
+        owned = {id(views[0].storage)} | {id(t.storage) for group in views[1:] for t in group}
+        for parameter in self.parameters():
+            if parameter.grad is not None and id(parameter.grad.storage) in owned:
+                parameter.grad = type(parameter.grad)(parameter.grad.storage.copy(self.stream), shape=parameter.shape)
 
     def capture_forward(self, x):
         """Record the forward on ``x``'s buffer as a CUDA graph (the decode-shaped call is a dozen short kernels:
@@ -365,11 +376,7 @@ class SparseMoE:
             raise ValueError("grad_y must match the output's size and dtype")
         ga = None if grad_aux is None else (grad_aux.storage if hasattr(grad_aux, "storage") else grad_aux)
         views = work["grad_views"]
-        owned = {id(views[0].storage)} | {id(t.storage) for group in views[1:] for t in group}
-        for parameter in self.parameters():
-            # a gradient that still aliases the buffers about to be overwritten is copied out first
-            if parameter.grad is not None and id(parameter.grad.storage) in owned:
-                parameter.grad = type(parameter.grad)(parameter.grad.storage.copy(self.stream), shape=parameter.shape)
+        self._release_aliased_gradients(work)
         dx = DeviceStorage(x_storage.size, x_storage.dtype)
         layer.grad_out, layer.grad_aux, layer.dx = g.ptr, 0 if ga is None else ga.ptr, dx.ptr
         lib.call("qmoe_layer_backward", ctypes.byref(layer), self.stream)
@@ -415,3 +422,119 @@ class SparseMoE:
             _accumulate(expert.up.weight, up, self.stream)
             _accumulate(expert.down.weight, down, self.stream)
         return dx
+
+
+class RMSNorm:
+    """Holder of the norm's weight and epsilon, with upstream's constructor (src/qutai/lm/layers.py:275-288):
+    ``weight`` of shape (width,), ones, float32.  The arithmetic runs inside ``MoEFeedForward``."""
+
+    def __init__(self, width, eps, *, device="cuda", dtype="float32", stream=0):
+        if device != "cuda" or dtype != "float32":
+            raise ValueError("the norm weight is float32 on device='cuda'")
+        storage = DeviceStorage.from_values([1.0] * width, "float32", stream)
+        self.weight = Tensor(storage, (width,), requires_grad=True)
+        self.eps = float(eps)
+
+    def parameters(self):
+        return (self.weight,)
+
+
+class MoEFeedForward:
+    """The feed-forward half of upstream's ``Block.__call__`` for a mixture-of-experts block
+    (src/qutai/lm/layers.py:430-437): ``(x + ffn(ffn_norm(x)), aux)``, with the norm and the residual fused into
+    the layer's first read and last write (``qmoe_block_forward`` / ``qmoe_block_backward``): no normalised copy of
+    the activations is written, the expert input is normalised while it is gathered, the residual is added
+    before the combine's single rounding, and in the backward the gather-sum of the input gradient applies the
+    norm's backward and adds the residual's gradient.  ``ffn_norm`` and ``ffn`` carry upstream's attribute names."""
+
+    def __init__(self, ffn_norm, ffn):
+        if ffn_norm.weight.size != ffn.d_model:
+            raise ValueError("the norm's width must be the layer's d_model")
+        self.ffn_norm, self.ffn = ffn_norm, ffn
+        self._blocks = {}
+
+    def parameters(self):
+        return (*self.ffn_norm.parameters(), *self.ffn.parameters())
+
+    def _block(self, work, tokens):
+        block = self._blocks.get(id(work))
+        if block is None:
+            moe = self.ffn
+            E, d = moe.n_experts, moe.d_model
+            S = DeviceStorage
+            extra = dict(inverse=S(tokens, "float32"), w_router_folded=S(E * d, "float32"), d_norm_weight=S(d, "float32"),
+                         norm_partials=S(int(lib.load().qmoe_norm_backward_partials(tokens, d)), "float32"),
+                         d_scores_scaled=S(tokens * E, "float32"))
+            block = dict(struct=lib.Block(), extra=extra, work=work)
+            for name, storage in extra.items():
+                setattr(block["struct"], name, storage.ptr)
+            self._blocks = {id(work): block}   # follows the layer's one-workspace-at-a-time rule
+        return block
+
+    def __call__(self, x):
+        return self.forward(x)
+
+    def forward(self, x):
+        """``x``: (..., d_model) float32 or bfloat16.  Returns ``(x + ffn(ffn_norm(x)), aux)``."""
+        moe = self.ffn
+        storage = x.storage if hasattr(x, "storage") else x
+        shape = tuple(x.shape) if hasattr(x, "shape") and not hasattr(x, "ptr") else (storage.size // moe.d_model, moe.d_model)
+        if shape[-1] != moe.d_model or storage.dtype not in lib.DTYPE_CODES:
+            raise ValueError("input must be (..., d_model) float32 or bfloat16")
+        tokens = storage.size // moe.d_model
+        work = moe._workspace(tokens, storage.dtype)
+        block = self._block(work, tokens)
+        layer, buf, struct = work["layer"], work["buf"], block["struct"]
+        out = DeviceStorage(storage.size, storage.dtype)
+        layer.x, layer.out = storage.ptr, out.ptr
+        masters = (layer.master_gate, layer.master_up, layer.master_down)
+        keep = moe._operands_current(work)
+        if keep:
+            layer.master_gate = layer.master_up = layer.master_down = 0
+        struct.layer = layer
+        struct.norm_weight, struct.norm_eps = self.ffn_norm.weight.storage.ptr, self.ffn_norm.eps
+        if moe._counts_valid is True:
+            lib.call("qmoe_stream_wait_event", moe.stream, moe._counts_event)
+        lib.call("qmoe_block_forward", ctypes.byref(struct), moe.stream)
+        layer.master_gate, layer.master_up, layer.master_down = masters
+        if not keep:
+            moe._operands_made(work)
+        moe._publish_counts(buf)
+        moe.utilization = Tensor(buf["utilization"], (moe.n_experts,))
+        moe._saved = (work, storage, shape)
+        return Tensor(out, shape), Tensor(buf["aux"], ())
+
+    def backward(self, grad_out, grad_aux=None):
+        """Gradient of the block's input for ``grad_out`` (shaped like the output; it also flows through the
+        residual) and the optional float32 scalar ``grad_aux``; accumulates into every ``parameter.grad``."""
+        moe = self.ffn
+        if moe._saved is None:
+            raise RuntimeError("backward called before forward")
+        work, x_storage, shape = moe._saved
+        block = self._blocks.get(id(work))
+        if block is None:
+            raise RuntimeError("the last forward of the layer did not go through this block")
+        layer, struct = work["layer"], block["struct"]
+        g = grad_out.storage if hasattr(grad_out, "storage") else grad_out
+        if g.size != x_storage.size or g.dtype != x_storage.dtype:
+            raise ValueError("grad_out must match the output's size and dtype")
+        ga = None if grad_aux is None else (grad_aux.storage if hasattr(grad_aux, "storage") else grad_aux)
+        moe._release_aliased_gradients(work)
+        dx = DeviceStorage(x_storage.size, x_storage.dtype)
+        layer.x, layer.grad_out, layer.grad_aux, layer.dx = x_storage.ptr, g.ptr, 0 if ga is None else ga.ptr, dx.ptr
+        struct.layer = layer
+        struct.norm_weight, struct.norm_eps = self.ffn_norm.weight.storage.ptr, self.ffn_norm.eps
+        lib.call("qmoe_block_backward", ctypes.byref(struct), moe.stream)
+        views = work["grad_views"]
+        counts = moe.last_counts
+        d_norm = Tensor(block["extra"]["d_norm_weight"].copy(moe.stream), (moe.d_model,))   # the buffer is reused by the next backward
+        _accumulate(self.ffn_norm.weight, d_norm, moe.stream)
+        _accumulate(moe.router.weight, views[0], moe.stream)
+        for i, expert in enumerate(moe.experts):
+            if not counts[i]:
+                continue
+            gate, up, down = views[1 + i]
+            _accumulate(expert.gate.weight, gate, moe.stream)
+            _accumulate(expert.up.weight, up, moe.stream)
+            _accumulate(expert.down.weight, down, moe.stream)
+        return Tensor(dx, shape)

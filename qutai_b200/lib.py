@@ -66,6 +66,12 @@ class Layer(Structure):
             "d_w_gate", "d_w_up", "d_w_down", "master_gate", "master_up", "master_down")]
 
 
+class Block(Structure):
+    """``qmoe_block_t``."""
+    _fields_ = [("layer", Layer)] + [(name, c_uint64) for name in (
+        "norm_weight", "inverse", "w_router_folded", "d_norm_weight", "norm_partials", "d_scores_scaled")] + [("norm_eps", c_double)]
+
+
 _U, _I32, _I64 = c_uint64, c_int32, c_int64
 _RP, _EP, _LP, _SP = POINTER(Route), POINTER(Experts), POINTER(Layer), POINTER(Segment)
 
@@ -126,6 +132,14 @@ SIGNATURES = {
     "qmoe_silu": (c_int, [_U, _U, _U, _I32, _I64, _I32, _U]),
     "qmoe_add": (c_int, [_U, _U, _U, _I32, _I64, _U]),
     "qmoe_normal_fill": (c_int, [_U, _I32, _I64, c_double, c_double, _U, _U]),
+    "qmoe_rms_inverse": (c_int, [_U, _I32, _U, _I64, _I64, c_double, _U]),
+    "qmoe_scale_f32": (c_int, [_U, _U, _U, _U, _I64, _I64, _U]),
+    "qmoe_permute_norm": (c_int, [_RP, _U, _U, _U, _U, _I32, _I64, _U]),
+    "qmoe_combine_residual": (c_int, [_RP, _U, _U, _U, _I32, _I64, _U]),
+    "qmoe_norm_backward_partials": (c_int64, [_I64, _I64]),
+    "qmoe_unpermute_norm_backward": (c_int, [_RP] + [_U] * 9 + [_I32, _I64, _U]),
+    "qmoe_block_forward": (c_int, [POINTER(Block), _U]),
+    "qmoe_block_backward": (c_int, [POINTER(Block), _U]),
     "qmoe_layer_forward": (c_int, [_LP, _U]),
     "qmoe_layer_backward": (c_int, [_LP, _U]),
     "qmoe_ep_unique_id": (c_int, [c_void_p]),

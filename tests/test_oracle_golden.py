@@ -107,3 +107,27 @@ def test_bf16_rounding_helper():
     assert r[0] == 1.0 and r[1] == 1.0 and r[2] == 1.0            # 1+2^-8 ties to even (1.0)
     assert r[3] == 1.0 + 2 ** -6                                  # 1+3*2^-8 ties to even upward
     assert r[4] == -2.5 and abs(r[5] - 3.140625) < 1e-12
+
+
+@pytest.mark.parametrize("path", golden_files("block"), ids=os.path.basename)
+def test_block_oracle_matches_the_upstream_norm_layer_and_residual(path):
+    """``x + ffn(ffn_norm(x))`` (RMS norm, the layer, the residual add) against what the upstream package produced
+    for it on its CPU float64 path (tests/golden/make_golden_block.py)."""
+    g = np.load(path)
+    experts, step = g["gate"].shape[0], int(g["sample"])
+    out, aux, ctx = oracle.block_ffn_forward(g["x"], g["norm_weight"], float(g["eps"]), g["router"], g["gate"], g["up"],
+                                             g["down"], int(g["top_k"]))
+    grads = oracle.block_ffn_backward(ctx, g["grad_out"], float(g["grad_aux"]))
+    assert ctx["moe"]["route"]["counts"] == tuple(g["counts"].tolist())
+    close(out, g["out"])
+    close(aux, g["aux"])
+    close(grads["x"], g["dx"])
+    close(grads["norm_weight"], g["d_norm_weight"])
+    close(grads["router"], g["d_router"])
+    for e in range(experts):
+        for key in ("gate", "up", "down"):
+            mine, theirs = grads[key][e], g[f"d_{key}_{e}"]
+            if not g["has_grad"][e]:
+                assert mine is None and theirs.size == 0
+            else:
+                close(mine.reshape(-1)[::step], theirs)

@@ -80,8 +80,9 @@ def test_a_route_filled_without_caller_scratch_feeds_the_other_entry_points():
             tables.struct.block_counts = tables.struct.block_base = tables.struct.block_colsum = 0
         lib.call(entry, tables.ref, scores.ptr, 0)
         R = tables.rows_bound
-        dispatched, out = DeviceStorage(R * d, "float32"), DeviceStorage(T * d, "float32")
-        dy, dw = DeviceStorage(R * d, "float32"), DeviceStorage(T * k, "float32")
+        # rows past the last expert group are never written: start them equal on both sides
+        dispatched, out = DeviceStorage.zeros(R * d, "float32"), DeviceStorage(T * d, "float32")
+        dy, dw = DeviceStorage.zeros(R * d, "float32"), DeviceStorage(T * k, "float32")
         back, d_scores = DeviceStorage(T * d, "float32"), DeviceStorage(T * E, "float32")
         lib.call("qmoe_permute", tables.ref, x.ptr, dispatched.ptr, lib.QMOE_F32, d, 0)
         lib.call("qmoe_combine", tables.ref, dispatched.ptr, out.ptr, lib.QMOE_F32, d, 0)
