@@ -421,7 +421,7 @@ def run_gpu(args, w, rank, world):
         point a long job sees under the power cap, whatever --warmup says."""
         done = 0
         begin = time.perf_counter()
-        while True:
+        while seconds > 0:
             for _ in range(10):
                 step()
             done += 10
@@ -430,7 +430,8 @@ def run_gpu(args, w, rank, world):
             if world > 1:   # every rank must leave the loop after the same number of steps
                 dist.all_reduce(elapsed, op=dist.ReduceOp.MIN)
             if float(elapsed.item()) >= seconds:
-                return done
+                break
+        return done
 
     sampler = ClockSampler(local)
     sampler.start()

@@ -119,7 +119,9 @@ def test_fused_block_agrees_with_the_unfused_chain_at_full_size():
     """C2's shape (16384 tokens, d 1024, 8 experts top-2, hidden 2816, bf16): routing bit-exact on the device's own
     logits; out and dx of sampled tokens against the oracle on those tokens; and the norm weight's gradient — a sum
     over ALL tokens — against the oracle's norm backward applied to the input gradient that the UNFUSED layer
-    returns for the same normalised activations."""
+    returns for the same normalised activations (run in fp32, so that it routes the tokens the same way: the sum
+    over tokens is a sum of terms of either sign, and re-routing even one token in a hundred moves it by more than
+    a tenth of its size)."""
     from gpu_util import make_layer, to_device, to_host
     from qutai_b200 import lib
     from qutai_b200.layers import Tensor
@@ -147,15 +149,14 @@ def test_fused_block_agrees_with_the_unfused_chain_at_full_size():
     assert rel(got["dx"][sample], grads["x"]) <= BF16_TOL
     # the unfused chain on the same normalised activations: its input gradient is the gradient of rms_norm(x)
     normed, inverse = oracle.rms_norm(x, norm_weight, 1e-6)
-    plain = make_layer(None, router, gate, up, down, k, engine="tcgen05")
-    xn = Tensor(to_device(normed, "bfloat16"), (T, d))
+    plain = make_layer(None, router, gate, up, down, k)
+    xn = Tensor(to_device(normed, "float32"), (T, d))
     plain(xn)
-    d_normed = to_host(plain.backward(Tensor(to_device(grad_out, "bfloat16"), (T, d)), None).storage, (T, d))
-    # the unfused layer sees the normalised activations rounded to bf16, so a few tokens whose logits nearly tie
-    # may be routed differently; everything else must agree
+    d_normed = to_host(plain.backward(Tensor(to_device(grad_out, "float32"), (T, d)), None).storage, (T, d))
+    # logits that nearly tie may still order differently by a rounding: those few tokens are left out of the row-wise check
     routed_alike = np.all(to_host(plain._saved[0]["buf"]["expert_index"], (T, k)) ==
                           to_host(block.ffn._saved[0]["buf"]["expert_index"], (T, k)), axis=1)
-    assert routed_alike.mean() >= 0.99
+    assert routed_alike.mean() >= 0.999
     dx_norm, d_weight = oracle.rms_norm_backward(d_normed, x, norm_weight, inverse)
     assert rel(got["d_norm_weight"], d_weight) <= BF16_TOL
     assert rel(got["dx"][routed_alike], (grad_out.astype(np.float64) + dx_norm)[routed_alike]) <= BF16_TOL
