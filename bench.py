@@ -672,12 +672,14 @@ def run_gpu(args, w, rank, world):
                                       bytes=adam_bytes, achieved_gbs=adam_bytes / (adam_ms * 1e-3) / 1e9,
                                       frac=adam_bytes / (adam_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], bound="hbm")
         del optimizer
+    if world == 1 and not forward_only and not args.no_block:
+        line["block_ffn"] = block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, args.steps, ms, torch, np)
     if forward_only:
         line["latency_ms"] = call_latency(step, torch, dist, world, device)
     elif args.workload == "c3" and not args.no_decode:
         # the decode-shaped configuration (c3's layer on 64 tokens, forward only): per-call latency of 200 calls
         line["decode"] = decode_latency(layer, w, rank, world, torch, dist, device, Tensor, wrap, peaks)
-    ok = bool(check["ok"])
+    ok = bool(check["ok"]) and bool(line.get("block_ffn", {}).get("check", {}).get("ok", True))
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -735,6 +737,72 @@ def decode_latency(layer, w, rank, world, torch, dist, device, Tensor, wrap, pea
                weight_bytes_per_gpu=weight_bytes, weight_stream_gbs_at_p50=weight_bytes / (out["p50"] * 1e-3) / 1e9,
                weight_stream_frac_of_hbm_peak=weight_bytes / (out["p50"] * 1e-3) / 1e9 / peaks["hbm_gbs"])
     return out
+
+
+def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
+    """The step either side of the layer fused into it: ``out = x + MoE(rms_norm(x))`` forward + backward
+    (``MoEFeedForward``), timed like the layer alone, and its values checked against the CPU oracle on sampled
+    tokens (out and dx of a token depend on that token alone when the auxiliary gradient is left out)."""
+    from oracle import moe_oracle as oracle
+    from qutai_b200.layers import MoEFeedForward, RMSNorm
+
+    T, d, E, k, h = w["tokens"], w["d"], w["E"], w["k"], w["h"]
+    eps = 1e-6
+    block = MoEFeedForward(RMSNorm(d, eps, stream=layer.stream), layer)
+    norm_weight = (1.0 + 0.1 * np.random.default_rng(3).standard_normal(d)).astype(np.float32)
+    block.ffn_norm.weight.storage.upload_bytes(norm_weight.tobytes(), layer.stream)
+    parameters = block.parameters()
+
+    def step(grad_aux):
+        for parameter in parameters:
+            parameter.grad = None
+        out, aux = block(xs)
+        return out, block.backward(gs, grad_aux)
+
+    for _ in range(5):
+        step(ga)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        step(ga)
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / steps
+    out, dx = step(None)
+    torch.cuda.synchronize()
+    device = x_dev.device
+    buf = layer._saved[0]["buf"]
+
+    def as_tensor(storage, shape, dtype):
+        from qutai_b200 import lib
+
+        t = torch.empty(shape, dtype=dtype, device=device)
+        lib.call("qmoe_memcpy_d2d", t.data_ptr(), storage.ptr, storage.nbytes, layer.stream)
+        return t
+
+    sample = torch.from_numpy(np.sort(np.random.default_rng(4321).choice(T, size=min(48, T), replace=False))).to(device)
+    scores = as_tensor(buf["scores"], (T, E), torch.float32)[sample]
+    out_s, dx_s = as_tensor(out.storage, (T, d), torch.bfloat16)[sample], as_tensor(dx.storage, (T, d), torch.bfloat16)[sample]
+    weights = {name: StackedWeights(as_tensor(buf[name], shape, torch.bfloat16))
+               for name, shape in (("w_gate", (E, h, d)), ("w_up", (E, h, d)), ("w_down", (E, d, h)))}
+    torch.cuda.synchronize()
+    x_s = x_dev[sample].float().cpu().numpy().astype(np.float64)
+    g_s = g_dev[sample].float().cpu().numpy().astype(np.float64)
+    want_out, _, ctx = oracle.block_ffn_forward(x_s, norm_weight, eps, router_weights(w).astype(np.float64), weights["w_gate"],
+                                                weights["w_up"], weights["w_down"], k, scores=scores.cpu().numpy().astype(np.float64))
+    grads = oracle.block_ffn_backward(ctx, g_s, 0.0)
+    out_err = oracle.max_rel_err(out_s.float().cpu().numpy(), want_out)
+    dx_err = oracle.max_rel_err(dx_s.float().cpu().numpy(), grads["x"])
+    # what the unfused chain moves on top of the layer: the norm kernel reads x and writes an fp32 copy (2 + 4 bytes per
+    # element), the residual kernel reads x and the layer's output and writes the sum (2 + 2 + 2); mirrored in the
+    # backward.  Fused, one statistics pass and one residual read per direction remain (2 + 2).
+    elements = T * d
+    return dict(ms_per_step=ms, layer_alone_ms_per_step=layer_ms, added_ms=ms - layer_ms,
+                what="x + MoE(rms_norm(x)) forward + backward, norm and residual fused into the layer (qmoe_block_forward / _backward)",
+                unfused_extra_bytes_per_step=2 * elements * (6 + 6), fused_extra_bytes_per_step=2 * elements * (2 + 2),
+                check=dict(ok=bool(out_err <= BF16_TOL and dx_err <= BF16_TOL), out=out_err, dx=dx_err, tolerance=BF16_TOL,
+                           sampled_tokens=int(sample.numel())))
 
 
 class StackedWeights:
@@ -844,6 +912,7 @@ def main():
     parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-decode", action="store_true", help="leave the decode-shaped latency block out of the c3 line")
+    parser.add_argument("--no-block", action="store_true", help="leave the fused norm + layer + residual block out of the line")
     parser.add_argument("--preroll", type=float, default=2.0,
                         help="seconds of back-to-back steps before the timed ones (the power-capped operating point)")
     parser.add_argument("--trace", default="", help="write a chrome trace of a few steps (rank 0) to this path")

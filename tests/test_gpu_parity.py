@@ -86,6 +86,32 @@ def test_routing_random_and_quantised(T, E, k, skew):
         check_route_against_oracle(tables, oracle.routing(scores.astype(np.float64), k), float_tol=4e-6)
 
 
+def test_routing_orders_logits_one_ulp_apart_like_the_float64_oracle():
+    """Ranking runs on the raw fp32 logits (softmax is monotone).  Two logits one ulp apart have distinct float64
+    probabilities, so the float64 CPU path — the oracle — prefers the larger one, as this kernel does.  (A path
+    that ranks on fp32 probabilities, like the upstream CUDA kernel src/qutai/backends/cuda/lm.cu:345-352, may see
+    them round to the same probability and then prefer the LOWER index: that deviation from the float64 path is
+    not reproduced here.)"""
+    from gpu_util import RouteTables, check_route_against_oracle, to_device
+
+    rng = np.random.default_rng(77)
+    T, E, k = 512, 16, 4
+    scores = rng.standard_normal((T, E)).astype(np.float32)
+    # in every row make the higher-index expert of a pair the larger one by exactly one ulp, near the top of the row
+    top = scores.max(axis=1) + np.float32(0.5)
+    low = rng.integers(0, E - 1, size=T)
+    high = low + 1 + rng.integers(0, E - 1 - low)
+    rows = np.arange(T)
+    scores[rows, low] = top
+    scores[rows, high] = np.nextafter(top, np.float32(np.inf))
+    assert np.all(scores[rows, high] > scores[rows, low])
+    expected = oracle.routing(scores.astype(np.float64), k)
+    assert np.array_equal(expected["indices"][:, 0], high) and np.array_equal(expected["indices"][:, 1], low)
+    tables = RouteTables(T, E, k)
+    tables.run(to_device(scores, "float32"))
+    check_route_against_oracle(tables, expected, float_tol=4e-6)
+
+
 def test_routing_rejects_bad_arguments():
     from gpu_util import RouteTables, to_device
     from qutai_b200 import lib
