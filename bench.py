@@ -304,10 +304,10 @@ def build_layer(w, seed=0):
     return layer
 
 
-def build_ep_layer(w, rank, world, seed=0, transport="p2p", gather=None):
+def build_ep_layer(w, rank, world, seed=0, transport="p2p", gather=None, overlap=True):
     from qutai_b200.expert_parallel import ExpertParallelMoE
 
-    layer = ExpertParallelMoE(Cfg(w), rank=rank, world=world, seed=seed, transport=transport, gather=gather)
+    layer = ExpertParallelMoE(Cfg(w), rank=rank, world=world, seed=seed, transport=transport, gather=gather, overlap=overlap)
     fill_experts(layer, w, layer.expert_ids)
     layer.router.weight.storage.upload_bytes(router_weights(w, seed).tobytes())
     return layer
@@ -358,7 +358,7 @@ def run_gpu(args, w, rank, world):
             return box
 
         init_communicator(rank, world, share=share)
-        layer = build_ep_layer(w, rank, world, transport=args.transport, gather=gather)
+        layer = build_ep_layer(w, rank, world, transport=args.transport, gather=gather, overlap=not args.no_overlap)
     else:
         layer = build_layer(w)
     layer.stream = stream
@@ -632,6 +632,8 @@ def run_gpu(args, w, rank, world):
     )
     if world > 1:
         line["expert_parallel"] = dict(placement=placement_label, transport=args.transport,
+                                       overlap=("rows of half of every rank's experts travel behind the first product on the other half"
+                                                if not args.no_overlap and args.transport == "p2p" else "none"),
                                        per_rank_rows=[sum(counts[p * L:(p + 1) * L]) for p in range(world)],
                                        contiguous=contiguous)
 
@@ -918,6 +920,7 @@ def main():
     parser.add_argument("--trace", default="", help="write a chrome trace of a few steps (rank 0) to this path")
     parser.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                         help="N > 1: 'balanced' times the contiguous placement first and reports it beside the headline")
+    parser.add_argument("--no-overlap", action="store_true", help="N > 1: the serial order of push and first product")
     parser.add_argument("--transport", default="p2p", choices=["p2p", "nccl"],
                         help="expert-parallel exchange: direct peer-memory stores, or NCCL send/receive")
     args = parser.parse_args()

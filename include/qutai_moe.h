@@ -500,9 +500,19 @@ int qmoe_ep_set_barrier_timeout_ms(int64_t milliseconds);
  *   qmoe_ep_expert_dx_push          dX = dG Wg + dU Wu address (peers: every rank's token-side buffer)
  * The two tensor-core variants need bf16 activations and widths that are multiples of 8 (else
  * QMOE_ERR_UNSUPPORTED: use the unfused entry points).  Order a qmoe_ep_barrier after each before the
- * destination is read. */
+ * destination is read.
+ * The _range forms move only the slots whose expert is one of the owner's local experts [local_begin, local_end)
+ * (every rank's experts with those local numbers): a host sends one group of experts, starts the first product on
+ * it, and lets the rest travel meanwhile. */
 int qmoe_ep_permute_push(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t x,
                          const qmoe_ep_peers_t* peers, int32_t dtype, int64_t width, uint64_t stream);
+int qmoe_ep_permute_push_range(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t x,
+                               const qmoe_ep_peers_t* peers, int32_t local_begin, int32_t local_end, int32_t dtype,
+                               int64_t width, uint64_t stream);
+int qmoe_ep_combine_backward_push_range(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t grad_out,
+                                        uint64_t y_local, const qmoe_ep_peers_t* peers, uint64_t d_gate_weights,
+                                        int32_t local_begin, int32_t local_end, int32_t dtype, int64_t width,
+                                        uint64_t stream);
 int qmoe_ep_combine_backward_push(const qmoe_route_t* token_route, uint64_t dest_base, uint64_t grad_out,
                                   uint64_t y_local, const qmoe_ep_peers_t* peers, uint64_t d_gate_weights,
                                   int32_t dtype, int64_t width, uint64_t stream);

@@ -543,37 +543,41 @@ template <int KMAX>
 __global__ void __launch_bounds__(256)
 ep_permute_push_kernel(const uint4* __restrict__ x, long long row_vecs, const int* __restrict__ expert_index,
                        const int* __restrict__ dest_row, const int* __restrict__ offsets, const int* __restrict__ dest_base,
-                       long long tokens, int k, int E_loc, int rank, PeerTable peers) {
+                       long long tokens, int k, int E_loc, int rank, int local_begin, int local_end, PeerTable peers) {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long t = warp; t < tokens; t += nwarps) {
         uint4* target[KMAX];
+        bool any = false;
 #pragma unroll
         for (int s = 0; s < KMAX; ++s) {
             target[s] = nullptr;
             if (s < k) {
                 const long long a = t * k + s;
                 const int e = expert_index[a], r = dest_row[a];
-                const int p = e / E_loc;
+                const int p = e / E_loc, local = e - p * E_loc;
+                if (local < local_begin || local >= local_end) continue;  // this slot's expert travels with another call
                 const long long dest = (long long)dest_base[e] + (r - offsets[e]);
                 target[s] = peers.buffer[p] + dest * row_vecs;
+                any = true;
                 if (lane == 0) peers.ret[p][dest] = (rank << kRetRankShift) | r;
             }
         }
+        if (!any) continue;
         const uint4* src = x + t * row_vecs;
         long long c = lane;
         for (; c + 32 < row_vecs; c += 64) {
             const uint4 v0 = ldg16_stream(src + c), v1 = ldg16_stream(src + c + 32);
 #pragma unroll
             for (int s = 0; s < KMAX; ++s)
-                if (s < k) { target[s][c] = v0; target[s][c + 32] = v1; }
+                if (target[s]) { target[s][c] = v0; target[s][c + 32] = v1; }
         }
         for (; c < row_vecs; c += 32) {
             const uint4 v0 = ldg16_stream(src + c);
 #pragma unroll
             for (int s = 0; s < KMAX; ++s)
-                if (s < k) target[s][c] = v0;
+                if (target[s]) target[s][c] = v0;
         }
     }
     __threadfence_system();
@@ -585,7 +589,8 @@ __global__ void __launch_bounds__(256)
 ep_combine_backward_push_kernel(const T* __restrict__ g, const T* __restrict__ y, const float* __restrict__ gate_w,
                                 const int* __restrict__ expert_index, const int* __restrict__ dest_row,
                                 const int* __restrict__ offsets, const int* __restrict__ dest_base, float* __restrict__ dw,
-                                long long tokens, int k, long long width, int E_loc, PeerTable peers) {
+                                long long tokens, int k, long long width, int E_loc, int local_begin, int local_end,
+                                PeerTable peers) {
     constexpr int N = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -595,18 +600,23 @@ ep_combine_backward_push_kernel(const T* __restrict__ g, const T* __restrict__ y
         T* target[KMAX];
         long long local[KMAX];
         float w[KMAX], dot[KMAX];
+        bool any = false;
 #pragma unroll
         for (int s = 0; s < KMAX; ++s) {
             target[s] = nullptr; local[s] = 0; w[s] = 0.f; dot[s] = 0.f;
             if (s < k) {
                 const long long a = t * k + s;
                 const int e = expert_index[a], r = dest_row[a];
+                const int owner = e / E_loc, slot = e - owner * E_loc;
+                if (slot < local_begin || slot >= local_end) continue;  // this slot's expert travels with another call
                 const long long dest = (long long)dest_base[e] + (r - offsets[e]);
-                target[s] = (T*)peers.buffer[e / E_loc] + dest * width;
+                target[s] = (T*)peers.buffer[owner] + dest * width;
                 local[s] = r;
                 w[s] = gate_w[a];
+                any = true;
             }
         }
+        if (!any) continue;
         const T* gs = g + t * width;
         for (int c = lane; c < chunks; c += 32) {
             float fg[N];
@@ -614,10 +624,10 @@ ep_combine_backward_push_kernel(const T* __restrict__ g, const T* __restrict__ y
             uint4 v[KMAX];
 #pragma unroll
             for (int s = 0; s < KMAX; ++s)
-                if (s < k) v[s] = ldg16_stream(y + local[s] * width + (long long)c * N);
+                if (target[s]) v[s] = ldg16_stream(y + local[s] * width + (long long)c * N);
 #pragma unroll
             for (int s = 0; s < KMAX; ++s)
-                if (s < k) {
+                if (target[s]) {
                     float fy[N], o[N];
                     Vec16<T>::unpack(v[s], fy);
 #pragma unroll
@@ -627,7 +637,7 @@ ep_combine_backward_push_kernel(const T* __restrict__ g, const T* __restrict__ y
         }
 #pragma unroll
         for (int s = 0; s < KMAX; ++s)
-            if (s < k) {
+            if (target[s]) {   // uniform over the warp: every lane holds the same targets
                 const float total = warp_sum(dot[s]);
                 if (lane == 0) dw[t * k + s] = total;
             }
@@ -658,8 +668,15 @@ void fill_scatter(TcScatter& s, uint64_t ret, const qmoe_ep_peers_t* peers) {
 }  // namespace qmoe
 
 extern "C" int qmoe_ep_permute_push(const qmoe_route_t* r, uint64_t dest_base, uint64_t x, const qmoe_ep_peers_t* peers,
-                                    int32_t dtype, int64_t width, uint64_t stream_) {
+                                    int32_t dtype, int64_t width, uint64_t stream) {
+    return qmoe_ep_permute_push_range(r, dest_base, x, peers, 0, QMOE_MAX_EXPERTS, dtype, width, stream);
+}
+
+extern "C" int qmoe_ep_permute_push_range(const qmoe_route_t* r, uint64_t dest_base, uint64_t x, const qmoe_ep_peers_t* peers,
+                                          int32_t local_begin, int32_t local_end, int32_t dtype, int64_t width,
+                                          uint64_t stream_) {
     if (int rc = route_check(r)) return rc;
+    if (local_begin < 0 || local_end < local_begin) return fail_arg("ep_permute_push: bad local expert range [%d, %d)", local_begin, local_end);
     if (int rc = check_peers(peers, true)) return rc;
     if (int rc = check_push_rows(dtype, width, {x, dest_base})) return rc;
     if (r->experts % peers->world) return fail_arg("ep_permute_push: experts must divide evenly over the ranks");
@@ -670,7 +687,8 @@ extern "C" int qmoe_ep_permute_push(const qmoe_route_t* r, uint64_t dest_base, u
     const int E_loc = r->experts / peers->world, grid = token_grid(r->tokens);
     const PeerTable table = make_table(peers, true);
 #define LAUNCH(K) ep_permute_push_kernel<K><<<grid, 256, 0, stream>>>((const uint4*)x, row_vecs, (const int*)r->expert_index, \
-        (const int*)r->dest_row, (const int*)r->offsets, (const int*)dest_base, r->tokens, r->top_k, E_loc, peers->rank, table)
+        (const int*)r->dest_row, (const int*)r->offsets, (const int*)dest_base, r->tokens, r->top_k, E_loc, peers->rank,      \
+        local_begin, local_end, table)
     if (r->top_k <= 1) LAUNCH(1); else if (r->top_k <= 2) LAUNCH(2); else if (r->top_k <= 4) LAUNCH(4);
     else if (r->top_k <= 6) LAUNCH(6); else LAUNCH(8);
 #undef LAUNCH
@@ -680,8 +698,17 @@ extern "C" int qmoe_ep_permute_push(const qmoe_route_t* r, uint64_t dest_base, u
 
 extern "C" int qmoe_ep_combine_backward_push(const qmoe_route_t* r, uint64_t dest_base, uint64_t grad_out, uint64_t y_local,
                                              const qmoe_ep_peers_t* peers, uint64_t d_gate_weights, int32_t dtype,
-                                             int64_t width, uint64_t stream_) {
+                                             int64_t width, uint64_t stream) {
+    return qmoe_ep_combine_backward_push_range(r, dest_base, grad_out, y_local, peers, d_gate_weights, 0, QMOE_MAX_EXPERTS,
+                                               dtype, width, stream);
+}
+
+extern "C" int qmoe_ep_combine_backward_push_range(const qmoe_route_t* r, uint64_t dest_base, uint64_t grad_out,
+                                                   uint64_t y_local, const qmoe_ep_peers_t* peers, uint64_t d_gate_weights,
+                                                   int32_t local_begin, int32_t local_end, int32_t dtype, int64_t width,
+                                                   uint64_t stream_) {
     if (int rc = route_check(r)) return rc;
+    if (local_begin < 0 || local_end < local_begin) return fail_arg("ep_combine_backward_push: bad local expert range [%d, %d)", local_begin, local_end);
     if (int rc = check_peers(peers, false)) return rc;
     if (int rc = check_push_rows(dtype, width, {grad_out, y_local, dest_base})) return rc;
     if (!d_gate_weights) return fail_arg("ep_combine_backward_push: d_gate_weights is null");
@@ -692,7 +719,7 @@ extern "C" int qmoe_ep_combine_backward_push(const qmoe_route_t* r, uint64_t des
     const PeerTable table = make_table(peers, false);
 #define LAUNCH(T, K) ep_combine_backward_push_kernel<T, K><<<grid, 256, 0, stream>>>((const T*)grad_out, (const T*)y_local, \
         (const float*)r->gate_weights, (const int*)r->expert_index, (const int*)r->dest_row, (const int*)r->offsets,            \
-        (const int*)dest_base, (float*)d_gate_weights, r->tokens, r->top_k, (long long)width, E_loc, table)
+        (const int*)dest_base, (float*)d_gate_weights, r->tokens, r->top_k, (long long)width, E_loc, local_begin, local_end, table)
 #define BY_K(T) do { if (r->top_k <= 1) LAUNCH(T, 1); else if (r->top_k <= 2) LAUNCH(T, 2); else if (r->top_k <= 4) LAUNCH(T, 4); \
                      else if (r->top_k <= 6) LAUNCH(T, 6); else LAUNCH(T, 8); } while (0)
     if (dtype == QMOE_BF16) BY_K(__nv_bfloat16); else BY_K(float);

@@ -249,7 +249,7 @@ class ExpertParallelMoE:
     model's number of ``experts[j]``), ``router`` is replicated and its gradient is summed over ranks."""
 
     def __init__(self, config, *, rank, world, device="cuda", dtype="float32", seed=None, engine="auto", stream=0,
-                 transport="p2p", barrier="flags", placement=None, gather=None):
+                 transport="p2p", barrier="flags", placement=None, gather=None, overlap=True):
         """``transport``: "p2p" (default) = rows pushed straight into the peers' buffers over NVLink (CUDA IPC
         mappings, destinations computed on the device, no host read in the forward); "nccl" = grouped NCCL
         send/receive sized by counts the host reads once per step.  ``barrier`` (p2p only): "flags" = the
@@ -257,7 +257,10 @@ class ExpertParallelMoE:
         collectives instead.  ``placement[e]`` = rank owning expert ``e`` (default: contiguous blocks); every
         rank passes the same list.  ``gather(payload) -> [payload of rank 0, ...]`` all-gathers a bytes object
         between the ranks (needed for "p2p" to swap the IPC handles); without it files in a per-job directory
-        are used."""
+        are used.  ``overlap`` (p2p with the flag barrier and the tensor-core engine, at least two local experts):
+        the rows of the second half of every rank's experts travel on a side stream while the first product
+        already runs on the first half (forward: dispatch behind SwiGLU; backward: the gradient rows behind
+        dSwiGLU); the results are bit-identical to the serial order."""
         if device != "cuda" or dtype != "float32":
             raise ValueError("parameters are float32 on device='cuda'")
         if transport not in ("nccl", "p2p"):
@@ -266,7 +269,7 @@ class ExpertParallelMoE:
             raise ValueError("barrier must be 'flags' or 'nccl'")
         if world > lib.EP_MAX_RANKS:
             raise ValueError(f"at most {lib.EP_MAX_RANKS} ranks")
-        self.transport, self.barrier, self._gather = transport, barrier, gather
+        self.transport, self.barrier, self._gather, self.overlap = transport, barrier, gather, bool(overlap)
         d, E, h = config.d_model, config.n_experts, config.d_expert
         if E % world:
             raise ValueError("n_experts must be a multiple of the number of ranks")
@@ -457,7 +460,7 @@ class ExpertParallelMoE:
             side = ctypes.c_uint64()
             lib.call("qmoe_stream_create", ctypes.byref(side))
             self._side = {"stream": side.value}
-            for name in ("ready", "done", "stats", "grads", "reduced", "ended"):
+            for name in ("ready", "done", "stats", "grads", "reduced", "ended", "first_sent", "rest_landed"):
                 event = ctypes.c_uint64()
                 lib.call("qmoe_event_create", ctypes.byref(event))
                 self._side[name] = event.value
@@ -465,6 +468,21 @@ class ExpertParallelMoE:
             self._work["peers"] = self._open_peers(buf, self._work["opened"])
             # barriers and the count all-gather go through flags in peer memory unless NCCL is asked for
             self._work["flag_barrier"] = self.barrier == "flags"
+        self._work["groups"] = None
+        if self.overlap and self._work["fused"] and self._work.get("flag_barrier") and L >= 2:
+            # two groups of local experts, [0, split) and [split, L): routes and weight tables that cover one group each
+            split, item = L // 2, lib.ITEM_BYTES[dtype]
+            groups = []
+            for begin, end in ((0, split), (split, L)):
+                route, experts = lib.Route(), lib.Experts()
+                ctypes.memmove(ctypes.byref(route), ctypes.byref(expert_route), ctypes.sizeof(route))
+                ctypes.memmove(ctypes.byref(experts), ctypes.byref(ex), ctypes.sizeof(experts))
+                route.experts = experts.experts = end - begin
+                route.counts, route.offsets = buf["x_counts"].ptr + 4 * begin, buf["x_offsets"].ptr + 4 * begin
+                experts.w_gate, experts.w_up = ex.w_gate + begin * h * d * item, ex.w_up + begin * h * d * item
+                experts.w_down = ex.w_down + begin * d * h * item
+                groups.append((begin, end, route, experts))
+            self._work["groups"] = groups
         return self._work
 
     def _open_peers(self, buf, opened):
@@ -511,13 +529,32 @@ class ExpertParallelMoE:
     def __call__(self, x):
         return self.forward(x)
 
-    def _barrier(self, w):
-        """Order everything the ranks enqueued so far against what they enqueue next."""
+    def _barrier(self, w, stream=None):
+        """Order everything the ranks enqueued so far (on ``stream``) against what they enqueue next."""
+        stream = self.stream if stream is None else stream
         if w.get("flag_barrier"):
             self._sequence += 1
-            lib.call("qmoe_ep_flag_barrier", ctypes.byref(w["peers"]["flags"]), self._sequence, 0, 0, None, self.stream)
+            lib.call("qmoe_ep_flag_barrier", ctypes.byref(w["peers"]["flags"]), self._sequence, 0, 0, None, stream)
         else:
-            lib.call("qmoe_ep_barrier", w["buf"]["barrier"].ptr, self.stream)
+            lib.call("qmoe_ep_barrier", w["buf"]["barrier"].ptr, stream)
+
+    def _two_phase(self, w, push, product):
+        """The overlapped order of one exchange: ``push(begin, end, stream)`` sends the rows of the local experts
+        [begin, end) of every rank, ``product(route, experts)`` runs the first tensor-core product on one group.
+        Group 0 travels and is waited for on the main stream; group 1 travels (and is waited for) on the side
+        stream while the product of group 0 runs."""
+        s, side = self.stream, self._side
+        (b0, e0, route0, experts0), (b1, e1, route1, experts1) = w["groups"]
+        push(b0, e0, s)
+        self._barrier(w)
+        lib.call("qmoe_event_record", side["first_sent"], s)
+        lib.call("qmoe_stream_wait_event", side["stream"], side["first_sent"])
+        push(b1, e1, side["stream"])
+        self._barrier(w, side["stream"])
+        lib.call("qmoe_event_record", side["rest_landed"], side["stream"])
+        product(route0, experts0)
+        lib.call("qmoe_stream_wait_event", s, side["rest_landed"])
+        product(route1, experts1)
 
     def _raise_on_status(self, code):
         if code:
@@ -622,6 +659,18 @@ class ExpertParallelMoE:
             lib.call("qmoe_event_record", done, side["stream"])
             route_and_plan()
             lib.call("qmoe_ep_dest_base", buf["stats_all"].ptr, E, L, buf["dest_base"].ptr, s)
+            if w["groups"]:
+                lib.call("qmoe_stream_wait_event", s, done)   # the first product starts right behind its rows
+                self._two_phase(
+                    w,
+                    lambda begin, end, stream: lib.call("qmoe_ep_permute_push_range", tr, buf["dest_base"].ptr, storage.ptr,
+                                                        ctypes.byref(peers["x_recv"]), begin, end, code, d, stream),
+                    lambda route, experts: lib.call("qmoe_expert_forward_parts", ctypes.byref(route), ctypes.byref(experts),
+                                                    *acts, 1, s))
+                lib.call("qmoe_ep_expert_down_push", xr, ex, buf["h"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["y_send"]), s)
+                self._barrier(w)
+                lib.call("qmoe_combine", tr, buf["y_send"].ptr, out.ptr, code, d, s)
+                return self._finish_forward(w, buf, out, storage, shape)
             if w["fused"]:
                 lib.call("qmoe_ep_permute_push", tr, buf["dest_base"].ptr, storage.ptr, ctypes.byref(peers["x_recv"]), code, d, s)
             else:
@@ -648,6 +697,10 @@ class ExpertParallelMoE:
             lib.call("qmoe_expert_forward", xr, ex, *acts, s)
             lib.call("qmoe_ep_exchange", buf["y_recv"].ptr, ra, rn, buf["y_send"].ptr, sa, sn, d, code, s)
         lib.call("qmoe_combine", tr, buf["y_send"].ptr, out.ptr, code, d, s)
+        return self._finish_forward(w, buf, out, storage, shape)
+
+    def _finish_forward(self, w, buf, out, storage, shape):
+        E, s = self.n_experts, self.stream
         if self._identity:
             self.utilization = Tensor(buf["utilization"], (E,))
         else:
@@ -706,10 +759,19 @@ class ExpertParallelMoE:
 
         if self.transport == "p2p" and w["fused"]:
             peers = w["peers"]
-            lib.call("qmoe_ep_combine_backward_push", tr, buf["dest_base"].ptr, g.ptr, buf["y_send"].ptr,
-                     ctypes.byref(peers["dy_recv"]), buf["d_gate_weights"].ptr, code, d, s)
-            self._barrier(w)
-            lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 1 | 4, s)
+            if w["groups"]:
+                self._two_phase(
+                    w,
+                    lambda begin, end, stream: lib.call("qmoe_ep_combine_backward_push_range", tr, buf["dest_base"].ptr, g.ptr,
+                                                        buf["y_send"].ptr, ctypes.byref(peers["dy_recv"]), buf["d_gate_weights"].ptr,
+                                                        begin, end, code, d, stream),
+                    lambda route, experts: lib.call("qmoe_expert_backward_parts", ctypes.byref(route), ctypes.byref(experts),
+                                                    buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 1 | 4, s))
+            else:
+                lib.call("qmoe_ep_combine_backward_push", tr, buf["dest_base"].ptr, g.ptr, buf["y_send"].ptr,
+                         ctypes.byref(peers["dy_recv"]), buf["d_gate_weights"].ptr, code, d, s)
+                self._barrier(w)
+                lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 1 | 4, s)
             # dX leaves from the tensor-core epilogue; it has landed long before the barrier below
             lib.call("qmoe_ep_expert_dx_push", xr, ex, buf["d_g"].ptr, buf["d_u"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["dy_send"]), s)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 2, s)

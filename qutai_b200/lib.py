@@ -162,6 +162,8 @@ SIGNATURES = {
     "qmoe_ep_pack_stats": (c_int, [_RP, _U, _U]),
     "qmoe_ep_permute_push": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I64, _U]),
     "qmoe_ep_combine_backward_push": (c_int, [_RP, _U, _U, _U, POINTER(Peers), _U, _I32, _I64, _U]),
+    "qmoe_ep_permute_push_range": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I32, _I64, _U]),
+    "qmoe_ep_combine_backward_push_range": (c_int, [_RP, _U, _U, _U, POINTER(Peers), _U, _I32, _I32, _I32, _I64, _U]),
     "qmoe_ep_expert_down_push": (c_int, [_RP, _EP, _U, _U, POINTER(Peers), _U]),
     "qmoe_ep_expert_dx_push": (c_int, [_RP, _EP, _U, _U, _U, POINTER(Peers), _U]),
     "qmoe_ep_push_return": (c_int, [_RP, _U, _U, POINTER(Peers), _I32, _I32, _I32, _I32, _I64, _U]),

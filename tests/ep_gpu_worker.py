@@ -32,9 +32,11 @@ def problem():
 def main():
     rank, world, out_dir, transport = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
     placement_kind = sys.argv[5] if len(sys.argv) > 5 else "contiguous"
-    engine = "tcgen05"
+    engine, overlap = "tcgen05", True
     if transport.endswith("-simt"):  # the direct transport without the fused tensor-core producers
         transport, engine = transport[:-5], "simt"
+    if transport.endswith("-serial"):  # the fused direct transport without the two-phase overlap of push and product
+        transport, overlap = transport[:-7], False
     from gpu_util import Config, to_device, to_host
     from qutai_b200 import lib
     from qutai_b200.expert_parallel import ExpertParallelMoE, file_all_gather, finalize_communicator, init_communicator
@@ -49,7 +51,7 @@ def main():
     interleaved = [e % world for e in range(E)]
     exchanges = iter(range(100))   # a tag of its own for every exchange of IPC handles (a rebuilt workspace makes a second one)
     layer = ExpertParallelMoE(Config(d, E, k, h), rank=rank, world=world, seed=3, engine=engine, transport=transport,
-                              placement=interleaved if placement_kind == "interleaved" else None,
+                              placement=interleaved if placement_kind == "interleaved" else None, overlap=overlap,
                               gather=lambda data: file_all_gather(out_dir, f"ipc{next(exchanges)}", rank, world, data))
     mine = list(layer.expert_ids)   # the model's numbers of this rank's experts, in slot order
     layer.router.weight.storage.upload_bytes(p["router"].tobytes())
