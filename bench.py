@@ -304,7 +304,7 @@ def build_layer(w, seed=0):
     return layer
 
 
-def build_ep_layer(w, rank, world, seed=0, transport="p2p", gather=None, overlap=True):
+def build_ep_layer(w, rank, world, seed=0, transport="p2p", gather=None, overlap=False):
     from qutai_b200.expert_parallel import ExpertParallelMoE
 
     layer = ExpertParallelMoE(Cfg(w), rank=rank, world=world, seed=seed, transport=transport, gather=gather, overlap=overlap)
@@ -358,7 +358,7 @@ def run_gpu(args, w, rank, world):
             return box
 
         init_communicator(rank, world, share=share)
-        layer = build_ep_layer(w, rank, world, transport=args.transport, gather=gather, overlap=not args.no_overlap)
+        layer = build_ep_layer(w, rank, world, transport=args.transport, gather=gather, overlap=args.overlap)
     else:
         layer = build_layer(w)
     layer.stream = stream
@@ -633,7 +633,7 @@ def run_gpu(args, w, rank, world):
     if world > 1:
         line["expert_parallel"] = dict(placement=placement_label, transport=args.transport,
                                        overlap=("rows of half of every rank's experts travel behind the first product on the other half"
-                                                if not args.no_overlap and args.transport == "p2p" else "none"),
+                                                if args.overlap and args.transport == "p2p" else "none"),
                                        per_rank_rows=[sum(counts[p * L:(p + 1) * L]) for p in range(world)],
                                        contiguous=contiguous)
 
@@ -920,7 +920,8 @@ def main():
     parser.add_argument("--trace", default="", help="write a chrome trace of a few steps (rank 0) to this path")
     parser.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                         help="N > 1: 'balanced' times the contiguous placement first and reports it beside the headline")
-    parser.add_argument("--no-overlap", action="store_true", help="N > 1: the serial order of push and first product")
+    parser.add_argument("--overlap", action="store_true",
+                        help="N > 1: let half of the experts' rows travel behind the first product on the other half")
     parser.add_argument("--transport", default="p2p", choices=["p2p", "nccl"],
                         help="expert-parallel exchange: direct peer-memory stores, or NCCL send/receive")
     args = parser.parse_args()

@@ -366,14 +366,16 @@ int qmoe_permute_norm(const qmoe_route_t* route, uint64_t x, uint64_t inverse, u
 int qmoe_combine_residual(const qmoe_route_t* route, uint64_t y_dispatched, uint64_t residual, uint64_t out, int32_t dtype,
                           int64_t width, uint64_t stream);
 /* qmoe_unpermute_reduce with the norm's backward (lm_rms_dx, lm_rms_dw) and the residual's gradient folded in.  With
- * d_n[t] = sum_s d_dispatched[dest_row(t, s)] + extra_f32[t] (gradient of the normalised input; extra may be 0):
+ * d_n[t] = sum_s d_dispatched[dest_row(t, s)] + extra_f32[t] (gradient of the normalised input; extra may be 0;
+ * with extra_row_scaled != 0 the buffer holds inverse[t] * addend and the kernel divides the row scale out):
  *   dx[t, j] = round(grad_out[t, j] + inverse[t] * (d_n[j] w[j] - x[t, j] inverse[t]^2 mean_j(d_n[j] w[j] x[t, j])))
  *   d_norm_weight[j] (f32 [d], written) = sum_t d_n[t, j] x[t, j] inverse[t], reduced in a fixed order.
  * partials: scratch of qmoe_norm_backward_partials(T, d) floats.  width <= 4096, else QMOE_ERR_UNSUPPORTED. */
 int64_t qmoe_norm_backward_partials(int64_t tokens, int64_t width);
-int qmoe_unpermute_norm_backward(const qmoe_route_t* route, uint64_t d_dispatched, uint64_t extra_f32, uint64_t x,
-                                 uint64_t inverse, uint64_t norm_weight, uint64_t grad_out, uint64_t dx,
-                                 uint64_t d_norm_weight, uint64_t partials, int32_t dtype, int64_t width, uint64_t stream);
+int qmoe_unpermute_norm_backward(const qmoe_route_t* route, uint64_t d_dispatched, uint64_t extra_f32,
+                                 int32_t extra_row_scaled, uint64_t x, uint64_t inverse, uint64_t norm_weight,
+                                 uint64_t grad_out, uint64_t dx, uint64_t d_norm_weight, uint64_t partials, int32_t dtype,
+                                 int64_t width, uint64_t stream);
 /* The whole feed-forward half of a block in one call per direction: layer.out = layer.x + MoE(rms_norm(layer.x)),
  * and its backward (layer.dx = gradient of layer.x including the residual's, d_norm_weight written).  `layer` is
  * filled as for qmoe_layer_forward / qmoe_layer_backward; layer.out must not alias layer.x. */
@@ -384,7 +386,6 @@ typedef struct qmoe_block {
     uint64_t w_router_folded;  /* f32 [E, d]   scratch: router weight times the norm weight */
     uint64_t d_norm_weight;    /* f32 [d]      backward output */
     uint64_t norm_partials;    /* f32 [qmoe_norm_backward_partials(T, d)] scratch */
-    uint64_t d_scores_scaled;  /* f32 [T, E]   scratch */
     double norm_eps;
 } qmoe_block_t;
 int qmoe_block_forward(const qmoe_block_t* block, uint64_t stream);

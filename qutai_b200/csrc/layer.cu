@@ -262,21 +262,20 @@ extern "C" int qmoe_block_backward(const qmoe_block_t* B, uint64_t stream) {
     if (int rc = check_experts(r, ex, &engine)) return rc;
     if (!L->grad_out || !L->dy_dispatched || !L->d_h || !L->d_g || !L->d_u || !L->dx_dispatched || !L->d_gate_weights ||
         !L->d_scores || !L->dx_router || !L->router_partials || !L->dx || !L->d_w_router || !B->d_norm_weight ||
-        !B->norm_partials || !B->d_scores_scaled)
+        !B->norm_partials)
         return fail_arg("block_backward: null buffer address");
     const long long d = ex->width, E = ex->experts;
     if (int rc = qmoe_combine_backward(r, L->grad_out, L->y_dispatched, L->dy_dispatched, L->d_gate_weights, ex->dtype, d, stream)) return rc;
     if (int rc = qmoe_expert_backward(r, ex, L->dy_dispatched, L->x_dispatched, L->g, L->u, L->h, L->d_h, L->d_g, L->d_u,
                                       L->dx_dispatched, L->d_w_gate, L->d_w_up, L->d_w_down, stream)) return rc;
     if (int rc = qmoe_route_backward(r, L->d_gate_weights, L->grad_aux, L->d_scores, stream)) return rc;
-    // router: the gradient of the NORMALISED input is d_scores . W_r; the weight gradient is d_scores^T . rms_norm(x)
-    // = ((inverse * d_scores)^T . x) * w, again from the raw activations
-    if (int rc = qmoe_router_backward(L->d_scores, L->x, ex->dtype, L->w_router, L->dx_router, 0, L->router_partials,
-                                      r->tokens, d, r->experts, stream)) return rc;
-    if (int rc = qmoe_scale_f32(L->d_scores, B->d_scores_scaled, B->inverse, 0, r->tokens, E, stream)) return rc;
-    if (int rc = qmoe_router_backward(B->d_scores_scaled, L->x, ex->dtype, L->w_router, 0, L->d_w_router, L->router_partials,
+    // router: the weight gradient is d_scores^T . rms_norm(x) = ((inverse * d_scores)^T . x) * w, from the raw
+    // activations; the same product call returns (inverse * d_scores) . W_r, i.e. inverse[t] times the gradient of
+    // the NORMALISED input, and the kernel below takes the row scale back out
+    if (int rc = qmoe_scale_f32(L->d_scores, L->d_scores, B->inverse, 0, r->tokens, E, stream)) return rc;
+    if (int rc = qmoe_router_backward(L->d_scores, L->x, ex->dtype, L->w_router, L->dx_router, L->d_w_router, L->router_partials,
                                       r->tokens, d, r->experts, stream)) return rc;
     if (int rc = qmoe_scale_f32(L->d_w_router, L->d_w_router, 0, B->norm_weight, E, d, stream)) return rc;
-    return qmoe_unpermute_norm_backward(r, L->dx_dispatched, L->dx_router, L->x, B->inverse, B->norm_weight, L->grad_out,
+    return qmoe_unpermute_norm_backward(r, L->dx_dispatched, L->dx_router, 1, L->x, B->inverse, B->norm_weight, L->grad_out,
                                         L->dx, B->d_norm_weight, B->norm_partials, ex->dtype, d, stream);
 }

@@ -191,10 +191,10 @@ combine_residual_kernel(const T* __restrict__ y, const float* __restrict__ gate_
 // accumulators in warp order and writes one row of `partials` [blocks, width].
 template <typename T, bool VEC, int KMAX>
 __global__ void __launch_bounds__(kThreads)
-unpermute_norm_backward_kernel(const T* __restrict__ dxd, const float* __restrict__ extra, const int* __restrict__ dest_row,
-                               const T* __restrict__ x, const float* __restrict__ inverse, const float* __restrict__ weight,
-                               const T* __restrict__ grad_out, T* __restrict__ dx, float* __restrict__ partials,
-                               long long tokens, int k, long long width) {
+unpermute_norm_backward_kernel(const T* __restrict__ dxd, const float* __restrict__ extra, int extra_row_scaled,
+                               const int* __restrict__ dest_row, const T* __restrict__ x, const float* __restrict__ inverse,
+                               const float* __restrict__ weight, const T* __restrict__ grad_out, T* __restrict__ dx,
+                               float* __restrict__ partials, long long tokens, int k, long long width) {
     extern __shared__ float s_dw[];  // [warps][width]
     const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
     const long long warp = (long long)blockIdx.x * kWarpsPerBlock + warp_in_block;
@@ -208,6 +208,8 @@ unpermute_norm_backward_kernel(const T* __restrict__ dxd, const float* __restric
         for (int s = 0; s < KMAX; ++s) rows[s] = s < k ? dest_row[t * k + s] : 0;
         const T* xs = x + t * width;
         const float inv = inverse[t];
+        // extra_row_scaled: `extra` holds inverse[t] times the addend (the router's product ran on row-scaled logit gradients)
+        const float extra_scale = extra_row_scaled ? 1.f / inv : 1.f;
         float projected = 0.f;
         if constexpr (VEC) {
             constexpr int N = Vec16<T>::N;
@@ -217,8 +219,11 @@ unpermute_norm_backward_kernel(const T* __restrict__ dxd, const float* __restric
 #pragma unroll
                 for (int s = 0; s < KMAX; ++s)
                     if (s < k) v[s] = *reinterpret_cast<const uint4*>(dxd + (long long)rows[s] * width + (long long)c * N);
-                if (extra) load_f32<N>(extra + t * width + (long long)c * N, acc);
-                else {
+                if (extra) {
+                    load_f32<N>(extra + t * width + (long long)c * N, acc);
+#pragma unroll
+                    for (int i = 0; i < N; ++i) acc[i] *= extra_scale;
+                } else {
 #pragma unroll
                     for (int i = 0; i < N; ++i) acc[i] = 0.f;
                 }
@@ -256,7 +261,7 @@ unpermute_norm_backward_kernel(const T* __restrict__ dxd, const float* __restric
             }
         } else {
             auto gather = [&](long long c) {
-                float acc = extra ? extra[t * width + c] : 0.f;
+                float acc = extra ? extra[t * width + c] * extra_scale : 0.f;
                 for (int s = 0; s < k; ++s) acc += Act<T>::load(dxd + (long long)rows[s] * width + c);
                 return acc;
             };
@@ -297,7 +302,32 @@ int check_dtype(int dtype) {
     if (dtype != QMOE_F32 && dtype != QMOE_BF16) return fail_arg("dtype must be QMOE_F32 or QMOE_BF16 (got %d)", dtype);
     return 0;
 }
-int backward_grid(long long tokens) { return grid_for_rows(tokens, 2); }
+// blocks of the backward kernel: as many per SM as their shared-memory accumulators (8 warps x width floats) allow
+int backward_grid(long long tokens, long long width) {
+    const long long per_block = (long long)kWarpsPerBlock * width * (long long)sizeof(float);
+    long long per_sm = (216ll * 1024) / (per_block > 0 ? per_block : 1);
+    per_sm = per_sm < 1 ? 1 : per_sm > 8 ? 8 : per_sm;
+    return grid_for_rows(tokens, (int)per_sm);
+}
+
+// out[c] = sum over rows of partials[row, c] in a fixed order: 8 strided partial sums per column, then those 8 in order
+__global__ void __launch_bounds__(256)
+reduce_rows_kernel(const float* __restrict__ partials, float* __restrict__ out, int rows, long long width) {
+    __shared__ float s_part[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const long long c = (long long)blockIdx.x * 32 + tx;
+    float total = 0.f;
+    if (c < width)
+        for (int r = ty; r < rows; r += 8) total += partials[(long long)r * width + c];
+    s_part[ty][tx] = total;
+    __syncthreads();
+    if (ty == 0 && c < width) {
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += s_part[i][tx];
+        out[c] = sum;
+    }
+}
 
 }  // namespace
 }  // namespace qmoe
@@ -392,13 +422,13 @@ extern "C" int qmoe_combine_residual(const qmoe_route_t* r, uint64_t y, uint64_t
 
 extern "C" int64_t qmoe_norm_backward_partials(int64_t tokens, int64_t width) {
     if (tokens <= 0 || width <= 0) return 0;
-    return (int64_t)backward_grid(tokens) * width;
+    return (int64_t)backward_grid(tokens, width) * width;
 }
 
-extern "C" int qmoe_unpermute_norm_backward(const qmoe_route_t* r, uint64_t d_dispatched, uint64_t extra_f32, uint64_t x,
-                                            uint64_t inverse, uint64_t norm_weight, uint64_t grad_out, uint64_t dx,
-                                            uint64_t d_norm_weight, uint64_t partials, int32_t dtype, int64_t width,
-                                            uint64_t stream_) {
+extern "C" int qmoe_unpermute_norm_backward(const qmoe_route_t* r, uint64_t d_dispatched, uint64_t extra_f32,
+                                            int32_t extra_row_scaled, uint64_t x, uint64_t inverse, uint64_t norm_weight,
+                                            uint64_t grad_out, uint64_t dx, uint64_t d_norm_weight, uint64_t partials,
+                                            int32_t dtype, int64_t width, uint64_t stream_) {
     if (int rc = route_check(r)) return rc;
     if (int rc = check_dtype(dtype)) return rc;
     if (!d_dispatched || !x || !inverse || !norm_weight || !grad_out || !dx || !d_norm_weight || !partials || width <= 0)
@@ -411,13 +441,14 @@ extern "C" int qmoe_unpermute_norm_backward(const qmoe_route_t* r, uint64_t d_di
     TimedScope timed(KC_UNPERMUTE, stream);
     const bool vec = dtype == QMOE_BF16 ? can_vec<__nv_bfloat16>(width, {d_dispatched, extra_f32, x, norm_weight, grad_out, dx})
                                         : can_vec<float>(width, {d_dispatched, extra_f32, x, norm_weight, grad_out, dx});
-    const int grid = backward_grid(r->tokens);
+    const int grid = backward_grid(r->tokens, width);
     const size_t smem = (size_t)kWarpsPerBlock * width * sizeof(float);
 #define LAUNCH(T, V, K)                                                                                                        \
     do {                                                                                                                       \
         auto kernel = unpermute_norm_backward_kernel<T, V, K>;                                                                 \
         if (smem > 48 * 1024) QMOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        kernel<<<grid, kThreads, smem, stream>>>((const T*)d_dispatched, (const float*)extra_f32, (const int*)r->dest_row,     \
+        kernel<<<grid, kThreads, smem, stream>>>((const T*)d_dispatched, (const float*)extra_f32, extra_row_scaled,            \
+            (const int*)r->dest_row,                                                                                           \
             (const T*)x, (const float*)inverse, (const float*)norm_weight, (const T*)grad_out, (T*)dx, (float*)partials,      \
             (long long)r->tokens, r->top_k, (long long)width);                                                                 \
     } while (0)
@@ -431,5 +462,7 @@ extern "C" int qmoe_unpermute_norm_backward(const qmoe_route_t* r, uint64_t d_di
 #undef LAUNCH_K
 #undef LAUNCH
     QMOE_LAUNCH_CHECK("unpermute_norm_backward_kernel");
-    return launch_reduce_partials((const float*)partials, (float*)d_norm_weight, width, grid, stream);
+    reduce_rows_kernel<<<(int)((width + 31) / 32), 256, 0, stream>>>((const float*)partials, (float*)d_norm_weight, grid, width);
+    QMOE_LAUNCH_CHECK("reduce_rows_kernel");
+    return 0;
 }

@@ -249,7 +249,7 @@ class ExpertParallelMoE:
     model's number of ``experts[j]``), ``router`` is replicated and its gradient is summed over ranks."""
 
     def __init__(self, config, *, rank, world, device="cuda", dtype="float32", seed=None, engine="auto", stream=0,
-                 transport="p2p", barrier="flags", placement=None, gather=None, overlap=True):
+                 transport="p2p", barrier="flags", placement=None, gather=None, overlap=False):
         """``transport``: "p2p" (default) = rows pushed straight into the peers' buffers over NVLink (CUDA IPC
         mappings, destinations computed on the device, no host read in the forward); "nccl" = grouped NCCL
         send/receive sized by counts the host reads once per step.  ``barrier`` (p2p only): "flags" = the
@@ -260,7 +260,9 @@ class ExpertParallelMoE:
         are used.  ``overlap`` (p2p with the flag barrier and the tensor-core engine, at least two local experts):
         the rows of the second half of every rank's experts travel on a side stream while the first product
         already runs on the first half (forward: dispatch behind SwiGLU; backward: the gradient rows behind
-        dSwiGLU); the results are bit-identical to the serial order."""
+        dSwiGLU); the results are bit-identical to the serial order.  Off by default: at two GPUs it measured
+        no faster than the serial order (two more barriers, two smaller product launches, and the push slows the
+        product it runs beside)."""
         if device != "cuda" or dtype != "float32":
             raise ValueError("parameters are float32 on device='cuda'")
         if transport not in ("nccl", "p2p"):

@@ -463,8 +463,7 @@ class MoEFeedForward:
             E, d = moe.n_experts, moe.d_model
             S = DeviceStorage
             extra = dict(inverse=S(tokens, "float32"), w_router_folded=S(E * d, "float32"), d_norm_weight=S(d, "float32"),
-                         norm_partials=S(int(lib.load().qmoe_norm_backward_partials(tokens, d)), "float32"),
-                         d_scores_scaled=S(tokens * E, "float32"))
+                         norm_partials=S(int(lib.load().qmoe_norm_backward_partials(tokens, d)), "float32"))
             block = dict(struct=lib.Block(), extra=extra, work=work)
             for name, storage in extra.items():
                 setattr(block["struct"], name, storage.ptr)

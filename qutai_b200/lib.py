@@ -69,7 +69,7 @@ class Layer(Structure):
 class Block(Structure):
     """``qmoe_block_t``."""
     _fields_ = [("layer", Layer)] + [(name, c_uint64) for name in (
-        "norm_weight", "inverse", "w_router_folded", "d_norm_weight", "norm_partials", "d_scores_scaled")] + [("norm_eps", c_double)]
+        "norm_weight", "inverse", "w_router_folded", "d_norm_weight", "norm_partials")] + [("norm_eps", c_double)]
 
 
 _U, _I32, _I64 = c_uint64, c_int32, c_int64
@@ -137,7 +137,7 @@ SIGNATURES = {
     "qmoe_permute_norm": (c_int, [_RP, _U, _U, _U, _U, _I32, _I64, _U]),
     "qmoe_combine_residual": (c_int, [_RP, _U, _U, _U, _I32, _I64, _U]),
     "qmoe_norm_backward_partials": (c_int64, [_I64, _I64]),
-    "qmoe_unpermute_norm_backward": (c_int, [_RP] + [_U] * 9 + [_I32, _I64, _U]),
+    "qmoe_unpermute_norm_backward": (c_int, [_RP, _U, _U, _I32] + [_U] * 7 + [_I32, _I64, _U]),
     "qmoe_block_forward": (c_int, [POINTER(Block), _U]),
     "qmoe_block_backward": (c_int, [POINTER(Block), _U]),
     "qmoe_layer_forward": (c_int, [_LP, _U]),

@@ -32,11 +32,11 @@ def problem():
 def main():
     rank, world, out_dir, transport = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
     placement_kind = sys.argv[5] if len(sys.argv) > 5 else "contiguous"
-    engine, overlap = "tcgen05", True
+    engine, overlap = "tcgen05", False
     if transport.endswith("-simt"):  # the direct transport without the fused tensor-core producers
         transport, engine = transport[:-5], "simt"
-    if transport.endswith("-serial"):  # the fused direct transport without the two-phase overlap of push and product
-        transport, overlap = transport[:-7], False
+    if transport.endswith("-overlap"):  # the fused direct transport with the two-phase overlap of push and first product
+        transport, overlap = transport[:-8], True
     from gpu_util import Config, to_device, to_host
     from qutai_b200 import lib
     from qutai_b200.expert_parallel import ExpertParallelMoE, file_all_gather, finalize_communicator, init_communicator

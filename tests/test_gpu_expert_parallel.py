@@ -42,8 +42,8 @@ def run_ranks(world, out_dir, transport, placement="contiguous"):
     return [np.load(os.path.join(out_dir, f"rank{rank}.npz")) for rank in range(world)]
 
 
-CASES = [(1, "nccl", "contiguous"), (1, "p2p", "contiguous"), (1, "p2p-simt", "contiguous"), (1, "p2p-serial", "contiguous"),
-         (2, "nccl", "contiguous"), (2, "p2p", "contiguous"), (2, "p2p-simt", "contiguous"), (2, "p2p-serial", "contiguous"),
+CASES = [(1, "nccl", "contiguous"), (1, "p2p", "contiguous"), (1, "p2p-simt", "contiguous"), (1, "p2p-overlap", "contiguous"),
+         (2, "nccl", "contiguous"), (2, "p2p", "contiguous"), (2, "p2p-simt", "contiguous"), (2, "p2p-overlap", "contiguous"),
          (2, "p2p", "interleaved"), (2, "p2p", "rebalanced"), (2, "nccl", "interleaved"),
          (4, "p2p", "contiguous"), (4, "p2p", "interleaved"),
          (8, "p2p", "contiguous"), (8, "p2p", "rebalanced")]
