@@ -761,16 +761,31 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
         out, aux = block(xs)
         return out, block.backward(gs, grad_aux)
 
+    layer_parameters = layer.parameters()
+
+    def layer_step():
+        for parameter in layer_parameters:
+            parameter.grad = None
+        layer(xs)
+        layer.backward(gs, ga)
+
+    def timed(fn):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / steps
+
     for _ in range(5):
         step(ga)
     torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for _ in range(steps):
-        step(ga)
-    end.record()
-    torch.cuda.synchronize()
-    ms = begin.elapsed_time(end) / steps
+    # the block and the layer alone in turn, three rounds each: the SM clock drifts under the power cap, so only
+    # measurements taken side by side compare
+    rounds = [(timed(lambda: step(ga)), timed(layer_step)) for _ in range(3)]
+    ms = sorted(r[0] for r in rounds)[1]
+    layer_ms = sorted(r[1] for r in rounds)[1]
     out, dx = step(None)
     torch.cuda.synchronize()
     device = x_dev.device
@@ -801,6 +816,7 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
     # backward.  Fused, one statistics pass and one residual read per direction remain (2 + 2).
     elements = T * d
     return dict(ms_per_step=ms, layer_alone_ms_per_step=layer_ms, added_ms=ms - layer_ms,
+                rounds_ms=[(round(a, 4), round(b, 4)) for a, b in rounds],
                 what="x + MoE(rms_norm(x)) forward + backward, norm and residual fused into the layer (qmoe_block_forward / _backward)",
                 unfused_extra_bytes_per_step=2 * elements * (6 + 6), fused_extra_bytes_per_step=2 * elements * (2 + 2),
                 check=dict(ok=bool(out_err <= BF16_TOL and dx_err <= BF16_TOL), out=out_err, dx=dx_err, tolerance=BF16_TOL,

@@ -255,7 +255,8 @@ unpermute_norm_backward_kernel(const T* __restrict__ dxd, const float* __restric
 #pragma unroll
                 for (int i = 0; i < N; ++i) {
                     o[i] = g[i] + inv * (dn[i] * w[i] - fx[i] * pull);
-                    mine[(long long)c * N + i] += dn[i] * fx[i] * inv;
+                    // column c * N + i is kept at i * chunks + c: the 32 lanes of a warp touch consecutive words
+                    mine[(long long)i * chunks + c] += dn[i] * fx[i] * inv;
                 }
                 st16(dx + t * width + (long long)c * N, Vec16<T>::pack(o));
             }
@@ -276,11 +277,17 @@ unpermute_norm_backward_kernel(const T* __restrict__ dxd, const float* __restric
         }
     }
     __syncthreads();
-    for (long long c = threadIdx.x; c < width; c += kThreads) {
+    for (long long at = threadIdx.x; at < width; at += kThreads) {
         float total = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarpsPerBlock; ++w) total += s_dw[(long long)w * width + c];
-        partials[(long long)blockIdx.x * width + c] = total;
+        for (int w = 0; w < kWarpsPerBlock; ++w) total += s_dw[(long long)w * width + at];
+        long long column = at;
+        if constexpr (VEC) {  // undo the interleaved placement of the accumulators
+            constexpr int N = Vec16<T>::N;
+            const long long chunks = width / N;
+            column = (at % chunks) * N + at / chunks;
+        }
+        partials[(long long)blockIdx.x * width + column] = total;
     }
 }
 
@@ -310,21 +317,21 @@ int backward_grid(long long tokens, long long width) {
     return grid_for_rows(tokens, (int)per_sm);
 }
 
-// out[c] = sum over rows of partials[row, c] in a fixed order: 8 strided partial sums per column, then those 8 in order
-__global__ void __launch_bounds__(256)
+// out[c] = sum over rows of partials[row, c] in a fixed order: 32 strided partial sums per column, then those 32 in order
+__global__ void __launch_bounds__(1024)
 reduce_rows_kernel(const float* __restrict__ partials, float* __restrict__ out, int rows, long long width) {
-    __shared__ float s_part[8][33];
+    __shared__ float s_part[32][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const long long c = (long long)blockIdx.x * 32 + tx;
     float total = 0.f;
     if (c < width)
-        for (int r = ty; r < rows; r += 8) total += partials[(long long)r * width + c];
+        for (int r = ty; r < rows; r += 32) total += partials[(long long)r * width + c];
     s_part[ty][tx] = total;
     __syncthreads();
     if (ty == 0 && c < width) {
         float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum += s_part[i][tx];
+        for (int i = 0; i < 32; ++i) sum += s_part[i][tx];
         out[c] = sum;
     }
 }
@@ -462,7 +469,7 @@ extern "C" int qmoe_unpermute_norm_backward(const qmoe_route_t* r, uint64_t d_di
 #undef LAUNCH_K
 #undef LAUNCH
     QMOE_LAUNCH_CHECK("unpermute_norm_backward_kernel");
-    reduce_rows_kernel<<<(int)((width + 31) / 32), 256, 0, stream>>>((const float*)partials, (float*)d_norm_weight, grid, width);
+    reduce_rows_kernel<<<(int)((width + 31) / 32), 1024, 0, stream>>>((const float*)partials, (float*)d_norm_weight, grid, width);
     QMOE_LAUNCH_CHECK("reduce_rows_kernel");
     return 0;
 }
