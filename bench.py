@@ -8,7 +8,8 @@ outputs copied back, inside the timed region); ``roofline`` describes the domina
 tcgen05 grouped GEMM) against the measured bf16 peak; ``cpu_baseline`` is the CPU oracle timed on
 this host on a bounded token sample; ``ep_check`` compares the values the timed path produces with the
 CPU oracle (routing counts bit-exact over all ranks' tokens, sampled outputs and gradients at the bf16
-bar) and the process exits non-zero when it fails; ``decode`` is the decode-shaped forward latency (c5).
+bar) and the process exits non-zero when it fails; ``decode`` is the decode-shaped forward latency (c5);
+``block_ffn`` times the layer with the RMS norm before it and the residual add after it fused in.
 ``--impl reference`` times the CPU implementation alone.
 
 Workloads are the synthetic shapes of the upstream project's MoE layer study: c2 = 16384 tokens,
@@ -466,6 +467,10 @@ def run_gpu(args, w, rank, world):
             torch.cuda.synchronize()
         if rank == 0:
             prof.export_chrome_trace(args.trace)
+    # the same steps timed right after the warm-up, before the GPU has settled against its power cap: what a short
+    # run reads (reported beside the steady-state headline, not instead of it)
+    ms_short = timed(step, args.steps)
+    sampler.t0 = None
     prerolled = preroll(args.preroll)
     logical_counts = layer.last_counts
     physical = getattr(layer, "_logical_of_physical", list(range(E)))
@@ -613,7 +618,7 @@ def run_gpu(args, w, rank, world):
                  d2h_bytes_per_step=bytes_out, copies_alone_ms_per_step=ms_copies,
                  note="copies_alone = the same pinned-host copies, both directions at once, without the layer: the floor this box's host link sets"),
         gpu_launches=int(launches), clocks=clocks,
-        steady_state=dict(preroll_steps=prerolled, preroll_seconds=args.preroll,
+        steady_state=dict(preroll_steps=prerolled, preroll_seconds=args.preroll, ms_per_step_before_preroll=ms_short,
                           ms_x_mhz=(ms * mhz if mhz else None), gemm_ms_x_mhz=(gemm_ms * mhz if mhz else None),
                           note="back-to-back steps ran for preroll_seconds before the timed ones; ms_x_mhz = ms_per_step x median SM MHz under load, comparable across boxes"),
         roofline=dict(bound="tensor", kernel="grouped_gemm_kernel (tcgen05)", achieved=achieved, peak=peak,
