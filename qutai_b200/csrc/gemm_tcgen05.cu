@@ -51,20 +51,21 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64 x 64 bf16 TMA box (8 KiB)
 //           rows of A and HALF of B (16 + 16 KiB per stage, 6 stages), so every byte fetched from L2 feeds
 //           1.5x more math, and the issuing CTA's MMA reads both halves.
 // Shared memory of a CTA: [operand ring][epilogue staging, one slice per epilogue warp][mbarriers].  The dSwiGLU
-// epilogue keeps two {G, U} boxes of 32 rows x 32 columns per warp in its slice (fetched and written back by TMA),
-// which costs the ring two stages; the other modes only need a small transpose buffer per warp.
+// epilogue keeps two {G, U} pairs of 32-row x 64-column boxes for every two warps that share rows (fetched and written
+// back by TMA), which costs the ring a stage; the other modes only need a small transpose buffer per warp.
 constexpr int EPILOGUE_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * EPILOGUE_WARPS;  // TMA warp + MMA warp + epilogue warps
 constexpr int MODE_DSWIGLU_ID = 3;
-constexpr int BOX_BYTES = 32 * 32 * 2;            // one 32 x 32 bf16 box of the dSwiGLU epilogue (2 KiB, 64-byte rows)
+constexpr int BOX_BYTES = 32 * 64 * 2;            // one 32 x 64 bf16 box of the dSwiGLU epilogue (4 KiB, 128-byte rows)
 constexpr int BARRIER_BYTES = 512;
 template <int CTAS, int MODE> struct Cfg {
     static constexpr bool STAGED = MODE == MODE_DSWIGLU_ID;
-    static constexpr int STAGES = CTAS == 2 ? (STAGED ? 4 : 6) : (STAGED ? 3 : 4);
+    static constexpr int STAGES = CTAS == 2 ? (STAGED ? 5 : 6) : (STAGED ? 3 : 4);
     static constexpr int B_STAGE_BYTES = (CTAS == 2 ? BN / 2 : BN) * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int EPI_WARP_BYTES = STAGED ? 4 * BOX_BYTES : 32 * 80;   // per epilogue warp
-    static constexpr int EPI_BYTES = EPILOGUE_WARPS * EPI_WARP_BYTES;        // a multiple of 1 KiB either way
+    static constexpr int EPI_WARP_BYTES = 32 * 80;            // transpose buffer of one epilogue warp (not dSwiGLU)
+    static constexpr int EPI_SLICE_BYTES = 4 * BOX_BYTES;     // dSwiGLU: two {G, U} buffers for each two warps on the same rows
+    static constexpr int EPI_BYTES = STAGED ? (EPILOGUE_WARPS / 2) * EPI_SLICE_BYTES : EPILOGUE_WARPS * EPI_WARP_BYTES;  // a multiple of 1 KiB either way
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + EPI_BYTES + BARRIER_BYTES;
 };
 constexpr uint32_t TMEM_COLS = 512;
@@ -236,11 +237,20 @@ struct Tile {
     bool rows_valid;  // CTAS == 2: false when this CTA's 128 rows lie past the end of the expert (compute, do not store)
 };
 
+// First 128-row tile of each expert: a table in shared memory, except where the epilogue's boxes leave no room for it
+// (dSwiGLU on CTA pairs) and the two values a tile needs come from the offsets in global memory instead.
+template <bool IN_SHARED> struct StartTable {
+    const int* shared;
+    const int* offsets;
+    __device__ __forceinline__ int operator[](int e) const { return IN_SHARED ? shared[e] : __ldg(offsets + e) / kRowPad; }
+};
+template <int MODE, int CTAS> constexpr bool starts_in_shared() { return !(MODE == MODE_DSWIGLU && CTAS == 2); }
+
 // s_start[e]: first 128-row tile of expert e.  s_pair[e] (CTAS == 2): first 256-row pair-tile of expert e, an
 // expert with an odd number of 128-row tiles gets a last pair-tile whose second half is not stored.
 template <int MODE, bool B_MN, int CTAS>
-__device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_start, const int* s_pair, const int* s_order,
-                                            int t, int cta_rank) {
+__device__ __forceinline__ Tile decode_tile(const GemmParams& p, const StartTable<starts_in_shared<MODE, CTAS>()>& s_start,
+                                            const int* s_pair, const int* s_order, int t, int cta_rank) {
     Tile tile;
     tile.valid = true;
     tile.rows_valid = true;
@@ -268,20 +278,21 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_st
     } else {
         // tiles are numbered from the first group's first row (a caller may pass a sub-range of the
         // experts, whose offsets do not start at row 0)
-        const int* first_of = CTAS == 2 ? s_pair : s_start;
-        const int first = first_of[0];
-        int lo = 0, hi = p.experts;  // largest e with (first_of[e] - first) * n_tiles <= t
+        auto first_of = [&](int e) { return CTAS == 2 ? s_pair[e] : s_start[e]; };
+        const int first = first_of(0);
+        int lo = 0, hi = p.experts;  // largest e with (first_of(e) - first) * n_tiles <= t
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if ((long long)(first_of[mid] - first) * p.n_tiles <= t) lo = mid; else hi = mid;
+            if ((long long)(first_of(mid) - first) * p.n_tiles <= t) lo = mid; else hi = mid;
         }
         const int e = lo;
-        const int groups = first_of[e + 1] - first_of[e];
-        const int local = t - (first_of[e] - first) * p.n_tiles;
+        const int groups = first_of(e + 1) - first_of(e);
+        const int local = t - (first_of(e) - first) * p.n_tiles;
         const int m_tile = (local % groups) * CTAS + cta_rank;  // 128-row tile inside the expert
+        const int start = s_start[e];
         tile.expert = e;
-        tile.row0 = (s_start[e] + m_tile) * BM;
-        tile.rows_valid = m_tile < s_start[e + 1] - s_start[e];
+        tile.row0 = (start + m_tile) * BM;
+        tile.rows_valid = m_tile < s_start[e + 1] - start;
         tile.n0 = (local / groups) * (MODE == MODE_SWIGLU ? 128 : BN);
         tile.kblocks = ((p.K + BK - 1) / BK) * p.segments;
         tile.krow0 = 0;
@@ -436,7 +447,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     using Config = Cfg<CTAS, MODE>;
     constexpr int STAGES = Config::STAGES, B_STAGE_BYTES = Config::B_STAGE_BYTES, STAGE_BYTES = Config::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ int s_start[kMaxExperts + 1];  // first 128-row tile of each expert
+    constexpr bool STARTS_IN_SHARED = starts_in_shared<MODE, CTAS>();
+    __shared__ int s_start_table[STARTS_IN_SHARED ? kMaxExperts + 1 : 1];  // first 128-row tile of each expert
+    const StartTable<STARTS_IN_SHARED> s_start{s_start_table, p.offsets};
     __shared__ int s_pair[kMaxExperts + 1];   // CTAS == 2: first 256-row pair-tile of each expert
     __shared__ int s_order[kMaxExperts];      // WGRAD: experts by decreasing row count (ties by index)
     __shared__ uint32_t s_tmem_base;
@@ -454,10 +467,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
 
-    if (p.plain_rows > 0) {
-        if (threadIdx.x == 0) { s_start[0] = 0; s_start[1] = (p.plain_rows + kRowPad - 1) / kRowPad; }
+    if (!STARTS_IN_SHARED) {
+        // nothing to fill: the table reads the offsets
+    } else if (p.plain_rows > 0) {
+        if (threadIdx.x == 0) { s_start_table[0] = 0; s_start_table[1] = (p.plain_rows + kRowPad - 1) / kRowPad; }
     } else {
-        for (int i = threadIdx.x; i <= p.experts; i += NUM_THREADS) s_start[i] = p.offsets[i] / kRowPad;
+        for (int i = threadIdx.x; i <= p.experts; i += NUM_THREADS) s_start_table[i] = p.offsets[i] / kRowPad;
     }
     if (MODE == MODE_WGRAD) {
         // Tiles of large experts cost more (longer contraction).  Walking the experts from large to
@@ -479,7 +494,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         // of both hand an accumulator back on the first CTA's barrier
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPILOGUE_WARPS * CTAS); }
-        if (MODE == MODE_DSWIGLU) {  // per epilogue warp: one barrier per {G, U} box pair
+        if (MODE == MODE_DSWIGLU) {  // per two warps on the same rows: for each buffer "loaded" and "second half written"
             for (int i = 0; i < 2 * EPILOGUE_WARPS; ++i) mbar_init(bars + 8u * (2 * STAGES + 4 + i), 1);
             prefetch_map(&p.map_a2); prefetch_map(&p.map_b2); prefetch_map(&p.map_a3); prefetch_map(&p.map_b3);
         }
@@ -633,42 +648,44 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     } else if (MODE == MODE_DSWIGLU) {
         // ------------------------------ epilogue of dSwiGLU -------------------------
         // dG = dH . U . silu'(G), dU = dH . silu(G), with dH only ever in tensor memory.  G and U arrive, and dG and
-        // dU leave, through TMA in boxes of 32 rows x 32 columns laid out like the accumulator is read (one thread =
-        // one row, 64-byte swizzle so the 32 rows of a warp do not collide on the banks): no transposes and no
-        // per-thread global accesses.  Each warp owns two {G, U} buffers; while it works on one chunk the boxes of its
-        // next chunk (of this tile or of its next tile) are already on their way, and results overwrite their inputs
-        // in place before the store.
-        const int warp_e = warp - 2, quad = warp & 3, half = warp_e >> 2;
-        const uint32_t slice = epi0 + (uint32_t)warp_e * Config::EPI_WARP_BYTES;
-        auto load_bar = [&](uint32_t n) { return bars + 8u * (2 * STAGES + 4 + warp_e * 2 + (n & 1u)); };
+        // dU leave, through TMA in boxes of 32 rows x 64 columns laid out like the accumulator is read (one thread =
+        // one row; 128-byte rows under the 128-byte swizzle, so the rows of a quarter warp fall on different banks):
+        // no transposes and no per-thread global accesses.  Full 128-byte rows matter: the same bytes moved as 64-byte
+        // rows took twice the TMA requests and slowed the operand feed of the main loop by a tenth.  The two warps
+        // that read the same 32 lanes of tensor memory share two {G, U} buffers and split every box between them,
+        // columns 0-31 and 32-63: the first of the two (the leader) asks for the boxes and stores them, the second
+        // tells it through a barrier when its half is written.  While a chunk is worked on, the boxes of the next
+        // (of this tile or of the pair's next tile) are already on their way, and results overwrite their inputs in
+        // place before the store.
+        const int warp_e = warp - 2, quad = warp & 3, slot = warp_e & 3, side = warp_e >> 2;
+        const bool leader = side == 0;
+        const uint32_t slice = epi0 + (uint32_t)slot * Config::EPI_SLICE_BYTES;
+        auto load_bar = [&](uint32_t n) { return bars + 8u * (2 * STAGES + 4 + slot * 4 + (n & 1u)); };
+        auto half_done_bar = [&](uint32_t n) { return bars + 8u * (2 * STAGES + 4 + slot * 4 + 2 + (n & 1u)); };
         auto buffer = [&](uint32_t n) { return slice + (n & 1u) * 2u * BOX_BYTES; };
-        // chunks [c, c_last) of 32 columns this warp converts in `tile` (none when its rows lie past the expert's end)
-        auto chunks_of = [&](const Tile& tile, int& c, int& c_last) {
-            c = c_last = 0;
-            if (!tile.valid || (CTAS == 2 && !tile.rows_valid)) return;
-            const int per = tile.bn / 64, in_range = (p.N - tile.n0 + 31) / 32;
-            c = half * per;
-            c_last = c + per < in_range ? c + per : in_range;
-            if (c_last < c) c_last = c;
+        // chunks [0, c_last) of 64 columns these warps convert in `tile` (none when their rows lie past the expert's end)
+        auto chunks_of = [&](const Tile& tile) {
+            if (!tile.valid || (CTAS == 2 && !tile.rows_valid)) return 0;
+            const int in_tile = tile.bn / 64, in_range = (p.N - tile.n0 + 63) / 64;
+            return in_tile < in_range ? in_tile : in_range;
         };
         auto issue_load = [&](const Tile& tile, int c, uint32_t n) {  // one lane: boxes of chunk c into buffer n & 1
             const uint32_t bar = load_bar(n), dst = buffer(n);
-            const int col = tile.n0 + c * 32, row = tile.row0 + quad * 32;
+            const int col = tile.n0 + c * 64, row = tile.row0 + quad * 32;
             mbar_expect_tx(bar, 2 * BOX_BYTES);
             tma_load_2d(&p.map_a2, dst, bar, col, row);
             tma_load_2d(&p.map_b2, dst + BOX_BYTES, bar, col, row);
         };
-        uint32_t n = 0;            // chunks this warp has consumed: buffer n & 1, barrier phase (n >> 1) & 1
-        bool on_its_way = false;   // the boxes of chunk number n have been asked for
+        uint32_t n = 0;            // chunks consumed: buffer n & 1, barrier phase (n >> 1) & 1
+        bool on_its_way = false;   // leader: the boxes of chunk number n have been asked for
         int iter = 0;
         bool gave_up = false;
         for (int t = first_tile; t < total_tiles && !*abort_flag && !gave_up; t += tile_stride) {
             const Tile tile = decode_tile<MODE, B_MN, CTAS>(p, s_start, s_pair, s_order, t, cta_rank);
             if (!tile.valid) continue;
-            int c_begin, c_end;
-            chunks_of(tile, c_begin, c_end);
-            if (c_begin < c_end && !on_its_way) {  // only the first chunk of the kernel is not prefetched
-                if (lane == 0) issue_load(tile, c_begin, n);
+            const int c_end = chunks_of(tile);
+            if (leader && c_end > 0 && !on_its_way) {  // only the first chunk of the kernel is not prefetched
+                if (lane == 0) issue_load(tile, 0, n);
                 on_its_way = true;
             }
             const int acc = iter & 1;
@@ -678,21 +695,21 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 break;
             }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN + (uint32_t)side * 32u;
 #pragma unroll 1
-            for (int c = c_begin; c < c_end; ++c) {
+            for (int c = 0; c < c_end; ++c) {
                 uint32_t r[32];
-                tmem_ld32(taddr + c * 32, r);
-                // the chunk after this one: the next of this tile, else the first of this warp's next tile with work
-                {
+                tmem_ld32(taddr + c * 64, r);
+                if (leader) {
+                    // the chunk after this one: the next of this tile, else the first of the next tile with work
                     Tile next_tile = tile;
                     int next_c = c + 1, next_last = c_end;
                     if (next_c >= c_end) {
                         next_c = next_last = 0;
                         for (int u = t + tile_stride; u < total_tiles; u += tile_stride) {
                             next_tile = decode_tile<MODE, B_MN, CTAS>(p, s_start, s_pair, s_order, u, cta_rank);
-                            chunks_of(next_tile, next_c, next_last);
-                            if (next_c < next_last) break;
+                            next_last = chunks_of(next_tile);
+                            if (next_last > 0) break;
                         }
                     }
                     on_its_way = next_c < next_last;
@@ -707,11 +724,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     gave_up = true;
                     break;
                 }
-                const uint32_t row_g = buffer(n) + (uint32_t)lane * 64u, row_u = row_g + BOX_BYTES;
-                const uint32_t twist = ((uint32_t)lane >> 1) & 3u;   // 64-byte swizzle: 16-byte piece j of row r sits at j ^ ((r >> 1) & 3)
+                const uint32_t row_g = buffer(n) + (uint32_t)lane * 128u, row_u = row_g + BOX_BYTES;
+                const uint32_t twist = (uint32_t)lane & 7u;   // 128-byte swizzle: 16-byte piece j of row r sits at j ^ (r & 7)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint32_t at = ((uint32_t)j ^ twist) * 16u;
+                    const uint32_t at = ((uint32_t)(4 * side + j) ^ twist) * 16u;
                     uint32_t gw[4], uw[4], og[4], ou[4];
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(gw[0]), "=r"(gw[1]), "=r"(gw[2]), "=r"(gw[3]) : "r"(row_g + at) : "memory");
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(uw[0]), "=r"(uw[1]), "=r"(uw[2]), "=r"(uw[3]) : "r"(row_u + at) : "memory");
@@ -729,11 +746,20 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 }
                 fence_async_shared();
                 __syncwarp();
-                if (lane == 0) {
-                    const int col = tile.n0 + c * 32, row = tile.row0 + quad * 32;
-                    tma_store_2d(&p.map_a3, buffer(n), col, row);
-                    tma_store_2d(&p.map_b3, buffer(n) + BOX_BYTES, col, row);
-                    bulk_commit();
+                if (!leader) {
+                    if (lane == 0) mbar_arrive(half_done_bar(n));
+                } else {
+                    if (!mbar_wait(half_done_bar(n), (n >> 1) & 1u, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_EPILOGUE); }
+                        gave_up = true;
+                        break;
+                    }
+                    if (lane == 0) {
+                        const int col = tile.n0 + c * 64, row = tile.row0 + quad * 32;
+                        tma_store_2d(&p.map_a3, buffer(n), col, row);
+                        tma_store_2d(&p.map_b3, buffer(n) + BOX_BYTES, col, row);
+                        bulk_commit();
+                    }
                 }
                 ++n;
             }
@@ -745,7 +771,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
             ++iter;
         }
-        if (lane == 0) bulk_wait_all();   // shared memory stays until the last store has left it
+        if (leader && lane == 0) bulk_wait_all();   // shared memory stays until the last store has left it
         __syncwarp();
     } else {
         // ------------------------------ epilogue ----------------------------------
@@ -966,10 +992,10 @@ EncodeTiledFn encode_fn() {
 std::mutex g_map_mutex;
 std::map<std::tuple<uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> g_maps;
 
-// 2-D bf16 row-major matrix [outer, inner], box {box_inner, box_outer}: 64 columns with the 128-byte swizzle (the
-// operand tiles), or 32 columns with the 64-byte swizzle (the epilogue boxes of dSwiGLU).
-int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uint32_t box_outer, uint64_t pitch = 0,
-             uint32_t box_inner = 64) {
+// 2-D bf16 row-major matrix [outer, inner], box {64, box_outer}: 64 columns (128 bytes) with the 128-byte swizzle,
+// for the operand tiles and for the epilogue boxes of dSwiGLU alike.
+int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uint32_t box_outer, uint64_t pitch = 0) {
+    constexpr uint32_t box_inner = 64;
     if (!pitch) pitch = inner;  // elements between consecutive rows
     auto key = std::make_tuple(ptr, inner | (pitch << 32), outer, box_inner, box_outer);
     {
@@ -986,7 +1012,7 @@ int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uin
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) {
@@ -1004,6 +1030,9 @@ template <int MODE, bool A_MN, bool B_MN, int CTAS = 1>
 int launch(const GemmParams& p, cudaStream_t stream) {
     static int grid_of[64] = {0};  // per device: blocks to launch (0: not configured yet)
     constexpr int SMEM_BYTES = Cfg<CTAS, MODE>::SMEM_BYTES;
+    // a block has 227 KiB, its static tables included: two or three of (kMaxExperts + 1) ints plus two words
+    static_assert(SMEM_BYTES + (starts_in_shared<MODE, CTAS>() ? 3 : 1) * 4 * (kMaxExperts + 1) + 16 <= 227 * 1024,
+                  "operand ring + epilogue staging + tables exceed the shared memory of a block");
     int dev = 0;
     QMOE_CUDA(cudaGetDevice(&dev));
     if (dev >= 64) return fail_arg("device ordinal beyond 63");
@@ -1120,10 +1149,10 @@ int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down,
     if (int rc = make_map(&p.map_b, w_down, (uint64_t)h, (uint64_t)experts * d, 64)) return rc;
     // the epilogue's boxes: G and U in, dG and dU out, 32 rows x 32 columns each
     const uint64_t rows = (uint64_t)r->rows_bound;
-    if (int rc = make_map(&p.map_a2, g, (uint64_t)h, rows, 32, 0, 32)) return rc;
-    if (int rc = make_map(&p.map_b2, u, (uint64_t)h, rows, 32, 0, 32)) return rc;
-    if (int rc = make_map(&p.map_a3, dg, (uint64_t)h, rows, 32, 0, 32)) return rc;
-    if (int rc = make_map(&p.map_b3, du, (uint64_t)h, rows, 32, 0, 32)) return rc;
+    if (int rc = make_map(&p.map_a2, g, (uint64_t)h, rows, 32)) return rc;
+    if (int rc = make_map(&p.map_b2, u, (uint64_t)h, rows, 32)) return rc;
+    if (int rc = make_map(&p.map_a3, dg, (uint64_t)h, rows, 32)) return rc;
+    if (int rc = make_map(&p.map_b3, du, (uint64_t)h, rows, 32)) return rc;
     p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
     p.out0 = (void*)dg; p.out1 = (void*)du; p.in0 = (const void*)g; p.in1 = (const void*)u;
     p.ldc = h; p.experts = experts; p.n_tiles = ceil_div(h, BN);
