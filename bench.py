@@ -681,12 +681,15 @@ def run_gpu(args, w, rank, world):
         del optimizer
     if world == 1 and not forward_only and not args.no_block:
         line["block_ffn"] = block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, args.steps, ms, torch, np)
+    if world == 1 and not forward_only and not args.no_head:
+        line["lm_head"] = lm_head(args.steps, peaks, torch, np)
     if forward_only:
         line["latency_ms"] = call_latency(step, torch, dist, world, device)
     elif args.workload == "c3" and not args.no_decode:
         # the decode-shaped configuration (c3's layer on 64 tokens, forward only): per-call latency of 200 calls
         line["decode"] = decode_latency(layer, w, rank, world, torch, dist, device, Tensor, wrap, peaks)
-    ok = bool(check["ok"]) and bool(line.get("block_ffn", {}).get("check", {}).get("ok", True))
+    ok = (bool(check["ok"]) and bool(line.get("block_ffn", {}).get("check", {}).get("ok", True))
+          and bool(line.get("lm_head", {}).get("check", {}).get("ok", True)))
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -828,6 +831,72 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
                            sampled_tokens=int(sample.numel())))
 
 
+def lm_head(steps, peaks, torch, np):
+    """The language-model head with its cross-entropy loss (``qutai_b200.head``) at one rank's share of the full
+    decoder step: 4 sequences of 2048 positions, width 1024, vocabulary 32000, bf16; forward (logits once, loss and
+    gradient of the logits in one pass) + backward (two products), timed with events, the losses of sampled rows
+    checked against float64 arithmetic on the same bf16 values."""
+    from oracle import moe_oracle as oracle
+    from qutai_b200.head import LMHead
+    from qutai_b200.layers import Tensor
+    from qutai_b200.storage import DeviceStorage
+
+    batch, time, width, vocab = 4, 2048, 1024, 32000
+    generator = torch.Generator(device="cuda").manual_seed(11)
+    hidden = torch.randn((batch, time, width), device="cuda", generator=generator).to(torch.bfloat16)
+    weight = (torch.randn((vocab, width), device="cuda", generator=generator) * 0.02).to(torch.bfloat16)
+    rng = np.random.default_rng(12)
+    labels_host = np.minimum(rng.zipf(1.1, size=(batch, time)) - 1, vocab - 1).astype(np.int64)
+    labels = torch.from_numpy(labels_host).cuda()
+    wrap = lambda t, dtype: DeviceStorage.wrap(t.data_ptr(), t.numel(), dtype, owner=t)
+    h, wt = Tensor(wrap(hidden, "bfloat16"), tuple(hidden.shape)), Tensor(wrap(weight, "bfloat16"), tuple(weight.shape))
+    label_storage = wrap(labels, "int64")
+    stream = torch.cuda.current_stream().cuda_stream    # the events below are recorded on this stream
+    head = LMHead(stream=stream)
+
+    def step():
+        loss = head.forward(h, wt, label_storage)
+        head.backward()
+        return loss
+
+    for _ in range(3):
+        loss = step()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        loss = step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / steps
+    rows = batch * (time - 1)
+    flops = 3 * 2.0 * rows * width * vocab
+    # one read and one write of the logits by the loss pass; each product streams them once more
+    logits_bytes = rows * vocab * 2
+    row_loss = torch.empty(rows, dtype=torch.float32, device="cuda")
+    from qutai_b200 import lib
+
+    lib.call("qmoe_memcpy_d2d", row_loss.data_ptr(), head._buffers["row_loss"].ptr, rows * 4, stream)
+    torch.cuda.synchronize()
+    sample = np.sort(rng.choice(rows, size=32, replace=False))
+    inputs = hidden[:, :-1, :].reshape(rows, width)[torch.from_numpy(sample).cuda()].float().cpu().numpy().astype(np.float64)
+    z = oracle.round_bf16(inputs @ weight.float().cpu().numpy().astype(np.float64).T)
+    peak = z.max(axis=1)
+    targets = labels_host[:, 1:].reshape(-1)[sample]
+    want = np.log(np.exp(z - peak[:, None]).sum(axis=1)) - (z[np.arange(len(sample)), targets] - peak)
+    got = row_loss.cpu().numpy()[sample]
+    error = float(np.abs(got - want).max() / max(1.0, float(np.abs(want).max())))
+    total = float(row_loss.double().sum().item() / rows)
+    value = float(loss.storage.tolist(stream)[0])
+    return dict(ms_per_step=ms, rows=rows, width=width, vocab=vocab, dtype="bf16", tflops=flops / (ms * 1e-3) / 1e12,
+                frac_of_sustained_peak=flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                logits_bytes=logits_bytes, launches_per_step=9,
+                what="LM head + cross-entropy forward + backward (qmoe_head_forward / _backward): 3 tcgen05 products, one pass over the logits",
+                loss=value,
+                check=dict(ok=bool(error <= BF16_TOL and abs(value - total) <= 1e-3 * abs(total)), row_loss=error,
+                           mean_of_rows=total, tolerance=BF16_TOL, sampled_rows=int(len(sample))))
+
+
 class StackedWeights:
     """Per-expert view of a gathered [experts, rows, columns] bf16 tensor on the device; an expert's block
     crosses to the host only when the oracle asks for it."""
@@ -935,6 +1004,7 @@ def main():
     parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-decode", action="store_true", help="leave the decode-shaped latency block out of the c3 line")
+    parser.add_argument("--no-head", action="store_true", help="leave the language-model head out of the line")
     parser.add_argument("--no-block", action="store_true", help="leave the fused norm + layer + residual block out of the line")
     parser.add_argument("--preroll", type=float, default=2.0,
                         help="seconds of back-to-back steps before the timed ones (the power-capped operating point)")

@@ -392,6 +392,40 @@ int qmoe_block_forward(const qmoe_block_t* block, uint64_t stream);
 int qmoe_block_backward(const qmoe_block_t* block, uint64_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The language-model head and its cross-entropy loss (the caller after the last block):
+ *     loss = mean over counted rows r of  log sum_c exp(z[r, c]) - z[r, label(r)],   z = rows(hidden) . weight^T
+ * where the rows are every position but the last of each sequence and label(r) is the token that follows it
+ * (-100 = not counted; the mean divides by max(1, counted rows)).  Replaces `projection_loss`
+ * (src/qutai/lm/layers.py:187-257) with its lm_head_rows / gemm / lm_head_loss / lm_head_gradient launches per
+ * chunk (src/qutai/backends/cuda_lm.py, kernels src/qutai/backends/cuda/lm.cu:430-444; CPU statement
+ * src/qutai/backends/cpu_lm.py:323-371).  The logits of all rows are formed once and kept: the forward leaves the
+ * loss and, in place of the logits, their gradient for an incoming gradient of 1; the backward is the two
+ * remaining products.  dtype QMOE_BF16 (bf16 hidden, bf16 weight operand, bf16 logits: tcgen05 when width and vocab
+ * are multiples of 8) or QMOE_F32 (CUDA cores).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qmoe_head {
+    int32_t batch, time;       /* hidden is [batch, time, width]; head rows = batch * (time - 1) */
+    int32_t dtype;             /* QMOE_BF16 / QMOE_F32: hidden, weight, inputs, logits, d_inputs, d_hidden */
+    int32_t reserved;
+    int64_t width, vocab;
+    int64_t rows_bound;        /* head rows rounded up to a multiple of 128: row count of inputs, logits, d_inputs */
+    uint64_t hidden;           /* [batch * time, width] */
+    uint64_t weight;           /* [vocab, width] */
+    uint64_t labels;           /* i64 [batch, time] token ids; the label of position t is labels[b, t + 1] */
+    uint64_t inputs;           /* [rows_bound, width]  the gathered rows (kept for the backward) */
+    uint64_t logits;           /* [rows_bound, vocab]  logits, overwritten by their gradient */
+    uint64_t row_loss;         /* f32 [rows] */
+    uint64_t loss;             /* f32 [1] */
+    uint64_t meta;             /* 32 bytes scratch, 16-byte aligned: 1 / count and the one group of the products */
+    uint64_t d_inputs;         /* [rows_bound, width] scratch of the backward (0 with d_hidden == 0) */
+    uint64_t d_hidden;         /* [batch * time, width], every row written (the last positions zero); 0 = not wanted */
+    uint64_t d_weight;         /* f32 [vocab, width], overwritten; 0 = not wanted */
+} qmoe_head_t;
+int qmoe_head_forward(const qmoe_head_t* head, uint64_t stream);
+/* gradient: f32 [1] on the device, the gradient of whatever follows with respect to the loss; 0 = 1.0 */
+int qmoe_head_backward(const qmoe_head_t* head, uint64_t gradient, uint64_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Expert parallelism (one process per GPU, NCCL over NVLink / NVSwitch).  The upstream project is
  * single-GPU (src/qutai/backends/cuda_runtime.py:82, :105), so these entry points have no upstream
  * counterpart; they keep the layer's semantics when tokens are sharded T/N per rank (contiguous

@@ -310,6 +310,53 @@ def block_ffn_backward(ctx, grad_out, grad_aux=0.0):
 
 
 # --------------------------------------------------------------------------------------
+# the language-model head and its loss (the caller after the last block)
+# --------------------------------------------------------------------------------------
+def head_loss_forward(hidden, weight, labels):
+    """``projection_loss`` (src/qutai/lm/layers.py:187-257) without its chunking: every position but the last of
+    each sequence (``head_rows``, src/qutai/backends/cpu_lm.py:323-331) times ``weight^T``, then per row
+    ``log sum exp(z - max) - (z[label] - max)`` for labels other than -100 (``head_loss``, :345-355; the label
+    of position t is the token at t + 1, layers.py:193), summed and divided by ``max(1, counted rows)``
+    (:198, :213).  ``hidden`` [batch, time, width], ``weight`` [vocab, width], ``labels`` [batch, time] integers.
+    Returns ``(loss, ctx)``."""
+    hidden = np.asarray(hidden, dtype=np.float64)
+    weight = np.asarray(weight, dtype=np.float64)
+    labels = np.asarray(labels, dtype=np.int64)
+    batch, time, width = hidden.shape
+    inputs = hidden[:, :-1, :].reshape(batch * (time - 1), width)
+    targets = labels[:, 1:].reshape(-1)
+    counted = targets != -100
+    count = max(1, int(counted.sum()))
+    logits = inputs @ weight.T
+    peak = logits.max(axis=1, keepdims=True)
+    exps = np.exp(logits - peak)
+    total = exps.sum(axis=1, keepdims=True)
+    safe = np.where(counted, targets, 0)
+    picked = logits[np.arange(len(targets)), safe] - peak[:, 0]
+    row_loss = np.where(counted, np.log(total[:, 0]) - picked, 0.0)
+    loss = row_loss.sum() / count
+    ctx = dict(inputs=inputs, weight=weight, shape=hidden.shape, probabilities=exps / total, targets=safe, counted=counted,
+               count=count, logits=logits)
+    return loss, ctx
+
+
+def head_loss_backward(ctx, gradient=1.0):
+    """Backward closure of ``projection_loss`` (src/qutai/lm/layers.py:215-255): per row
+    ``gradient / count * (softmax - one_hot)``, zero for rows that are not counted (``head_gradient``,
+    src/qutai/backends/cpu_lm.py:358-371); ``dx`` rows = that times ``weight`` put back at their positions, the last
+    position of each sequence getting nothing (``head_rows_backward``, :334-338); ``dw`` = its transpose times the
+    gathered rows.  Returns ``(d_hidden [batch, time, width], d_weight [vocab, width], d_logits)``."""
+    batch, time, width = ctx["shape"]
+    g = ctx["probabilities"].copy()
+    g[np.arange(g.shape[0]), ctx["targets"]] -= 1.0
+    g *= float(gradient) / ctx["count"]
+    g[~ctx["counted"]] = 0.0
+    d_hidden = np.zeros((batch, time, width))
+    d_hidden[:, :-1, :] = (g @ ctx["weight"]).reshape(batch, time - 1, width)
+    return d_hidden, g.T @ ctx["inputs"], g
+
+
+# --------------------------------------------------------------------------------------
 # helpers used by tests and by the benchmark's CPU leg
 # --------------------------------------------------------------------------------------
 def round_bf16(a):

@@ -158,6 +158,7 @@ int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down,
                uint64_t du, long long d, long long h, cudaStream_t stream);
 int tc_wgrad3(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t h_act, uint64_t x, uint64_t dg, uint64_t du,
               uint64_t d_w_down, uint64_t d_w_gate, uint64_t d_w_up, long long d, long long h, cudaStream_t stream);
+int tc_wgrad1(const qmoe_route_t* r, uint64_t a, uint64_t b, uint64_t out, long long M, long long N, cudaStream_t stream);
 int tc_router_forward(uint64_t x, uint64_t w3, uint64_t scores, long long T, long long d, int E, int S, cudaStream_t stream);
 int tc_plain_f32_nn(uint64_t a, uint64_t b, uint64_t c, long long T, long long K, long long N, cudaStream_t stream);
 int tc_split_wgrad(uint64_t a, long long a_pitch, uint64_t b, uint64_t partial, const int* offsets, const int* counts,

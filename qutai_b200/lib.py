@@ -72,6 +72,13 @@ class Block(Structure):
         "norm_weight", "inverse", "w_router_folded", "d_norm_weight", "norm_partials")] + [("norm_eps", c_double)]
 
 
+class Head(Structure):
+    """``qmoe_head_t``."""
+    _fields_ = [("batch", c_int32), ("time", c_int32), ("dtype", c_int32), ("reserved", c_int32),
+                ("width", c_int64), ("vocab", c_int64), ("rows_bound", c_int64)] + [(name, c_uint64) for name in (
+        "hidden", "weight", "labels", "inputs", "logits", "row_loss", "loss", "meta", "d_inputs", "d_hidden", "d_weight")]
+
+
 _U, _I32, _I64 = c_uint64, c_int32, c_int64
 _RP, _EP, _LP, _SP = POINTER(Route), POINTER(Experts), POINTER(Layer), POINTER(Segment)
 
@@ -140,6 +147,8 @@ SIGNATURES = {
     "qmoe_unpermute_norm_backward": (c_int, [_RP, _U, _U, _I32] + [_U] * 7 + [_I32, _I64, _U]),
     "qmoe_block_forward": (c_int, [POINTER(Block), _U]),
     "qmoe_block_backward": (c_int, [POINTER(Block), _U]),
+    "qmoe_head_forward": (c_int, [POINTER(Head), _U]),
+    "qmoe_head_backward": (c_int, [POINTER(Head), _U, _U]),
     "qmoe_layer_forward": (c_int, [_LP, _U]),
     "qmoe_layer_backward": (c_int, [_LP, _U]),
     "qmoe_ep_unique_id": (c_int, [c_void_p]),

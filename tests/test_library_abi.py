@@ -51,6 +51,7 @@ def test_ctypes_structures_match_the_c_layout(tmp_path):
               "qmoe_experts_t": [f[0] for f in lib.Experts._fields_],
               "qmoe_layer_t": [f[0] for f in lib.Layer._fields_],
               "qmoe_block_t": [f[0] for f in lib.Block._fields_],
+              "qmoe_head_t": [f[0] for f in lib.Head._fields_],
               "qmoe_optim_item_t": [f[0] for f in lib.OptimItem._fields_]}
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for struct, names in fields.items():
@@ -63,7 +64,7 @@ def test_ctypes_structures_match_the_c_layout(tmp_path):
     subprocess.run(["gcc", "-o", str(binary), str(source)], check=True)
     reported = dict(line.rsplit(" ", 1) for line in subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.splitlines())
     for struct, cls in (("qmoe_route_t", lib.Route), ("qmoe_experts_t", lib.Experts), ("qmoe_layer_t", lib.Layer),
-                        ("qmoe_block_t", lib.Block), ("qmoe_optim_item_t", lib.OptimItem)):
+                        ("qmoe_block_t", lib.Block), ("qmoe_head_t", lib.Head), ("qmoe_optim_item_t", lib.OptimItem)):
         assert int(reported[struct]) == ctypes.sizeof(cls)
         for name, _ in cls._fields_:
             assert int(reported[f"{struct}.{name}"]) == getattr(cls, name).offset, (struct, name)
@@ -79,6 +80,13 @@ def test_argument_errors_raise_value_error_without_a_device(library_path):
         lib.call("qmoe_route", ctypes.byref(route), 1, 0)
     with pytest.raises(ValueError):
         lib.call("qmoe_cast_bf16", 8, 16, 4, 0)  # misaligned addresses
+    head = lib.Head()
+    head.batch, head.time, head.width, head.vocab, head.rows_bound = 2, 1, 8, 16, 128
+    with pytest.raises(ValueError):
+        lib.call("qmoe_head_forward", ctypes.byref(head), 0)   # a sequence of one position has no target
+    head.time, head.rows_bound = 3, 100
+    with pytest.raises(ValueError):
+        lib.call("qmoe_head_forward", ctypes.byref(head), 0)   # rows_bound is not a multiple of 128
 
 
 def test_bf16_rounding_on_the_host():

@@ -131,3 +131,17 @@ def test_block_oracle_matches_the_upstream_norm_layer_and_residual(path):
                 assert mine is None and theirs.size == 0
             else:
                 close(mine.reshape(-1)[::step], theirs)
+
+
+@pytest.mark.parametrize("path", golden_files("head"), ids=os.path.basename)
+def test_head_oracle_matches_the_upstream_projection_loss(path):
+    """The language-model head and its cross-entropy loss against what the upstream package's chunked
+    ``projection_loss`` produced on its CPU float64 path (tests/golden/make_golden_head.py): the loss, and the
+    gradients of the hidden states and of the weight for the stored incoming gradient."""
+    g = np.load(path)
+    loss, ctx = oracle.head_loss_forward(g["hidden"], g["weight"], g["labels"])
+    d_hidden, d_weight, _ = oracle.head_loss_backward(ctx, float(g["gradient"]))
+    close(loss, g["loss"])
+    close(d_hidden, g["d_hidden"])
+    close(d_weight, g["d_weight"])
+    assert not d_hidden[:, -1, :].any()          # the last position of a sequence has no target
