@@ -395,7 +395,7 @@ int qmoe_block_backward(const qmoe_block_t* block, uint64_t stream);
  * The language-model head and its cross-entropy loss (the caller after the last block):
  *     loss = mean over counted rows r of  log sum_c exp(z[r, c]) - z[r, label(r)],   z = rows(hidden) . weight^T
  * where the rows are every position but the last of each sequence and label(r) is the token that follows it
- * (-100 = not counted; the mean divides by max(1, counted rows)).  Replaces `projection_loss`
+ * (-100, like any value outside [0, vocab), = not counted; the mean divides by max(1, counted rows)).  Replaces `projection_loss`
  * (src/qutai/lm/layers.py:187-257) with its lm_head_rows / gemm / lm_head_loss / lm_head_gradient launches per
  * chunk (src/qutai/backends/cuda_lm.py, kernels src/qutai/backends/cuda/lm.cu:430-444; CPU statement
  * src/qutai/backends/cpu_lm.py:323-371).  The logits of all rows are formed once and kept: the forward leaves the

@@ -47,18 +47,20 @@ __device__ __forceinline__ float block_sum(float v, float* tmp) {
     return r;
 }
 
-// Label of head row r: the token that follows position (r mod (time - 1)) of sequence r / (time - 1)
-__device__ __forceinline__ long long label_of(const long long* labels, long long r, int time) {
-    return labels[(r / (time - 1)) * time + r % (time - 1) + 1];
+// Label of head row r: the token that follows position (r mod (time - 1)) of sequence r / (time - 1).  A value
+// outside [0, vocab) is returned as -100 (not counted), so that no label can send a read outside its row.
+__device__ __forceinline__ long long label_of(const long long* labels, long long r, int time, long long vocab) {
+    const long long label = labels[(r / (time - 1)) * time + r % (time - 1) + 1];
+    return label >= 0 && label < vocab ? label : -100;
 }
 
 // meta[0] = number of rows with a label other than -100 (at least 1, as upstream divides), as a float: 1 / that
 __global__ void __launch_bounds__(1024) head_count_kernel(const long long* __restrict__ labels, long long rows, int time,
-                                                          float* __restrict__ factor, int* __restrict__ group,
+                                                          long long vocab, float* __restrict__ factor, int* __restrict__ group,
                                                           int rows_bound) {
     __shared__ int tmp[32];
     int mine = 0;
-    for (long long r = threadIdx.x; r < rows; r += blockDim.x) mine += label_of(labels, r, time) != -100;
+    for (long long r = threadIdx.x; r < rows; r += blockDim.x) mine += label_of(labels, r, time, vocab) != -100;
 #pragma unroll
     for (int o = 16; o; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
     if ((threadIdx.x & 31) == 0) tmp[threadIdx.x >> 5] = mine;
@@ -104,7 +106,7 @@ head_loss_gradient_kernel(T* __restrict__ logits, const long long* __restrict__ 
     const long long r = blockIdx.x;
     if (r >= rows) return;
     T* row = logits + r * vocab;
-    const long long label = label_of(labels, r, time);
+    const long long label = label_of(labels, r, time, vocab);
     const bool vec = vocab % N == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
     const int pieces = vec ? (int)(vocab / N) : 0;
     if (label == -100) {   // not counted: no loss, no gradient
@@ -238,7 +240,7 @@ extern "C" int qmoe_head_forward(const qmoe_head_t* h, uint64_t stream_) {
     const long long rows = (long long)h->batch * (h->time - 1), element = h->dtype == QMOE_BF16 ? 2 : 4;
     {
         TimedScope timed(KC_OTHER, stream);
-        head_count_kernel<<<1, 1024, 0, stream>>>((const long long*)h->labels, rows, h->time, (float*)h->meta, (int*)(h->meta + 16),
+        head_count_kernel<<<1, 1024, 0, stream>>>((const long long*)h->labels, rows, h->time, h->vocab, (float*)h->meta, (int*)(h->meta + 16),
                                                   (int)h->rows_bound);
         QMOE_LAUNCH_CHECK("head_count_kernel");
         const long long pieces = h->width * element / 16;

@@ -65,7 +65,13 @@ route_topk_kernel(const float* __restrict__ scores, float* __restrict__ probs,
             if (e < E) probs[row * E + e] = p[j];
             col[j] += p[j];
         }
-        // top-k by (score descending, expert index ascending)
+        // top-k by (score descending, expert index ascending).  A NaN score ranks as -inf: every comparison below
+        // then has the same outcome in every lane, so the lanes agree on each winner (with NaNs left in, each lane
+        // would keep its own candidate, mark only that one as taken, and run out of candidates before slot k).
+        // The probabilities and gate weights still carry the NaN to the output.
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)
+            if (v[j] != v[j]) v[j] = -INFINITY;
         unsigned taken = 0;
         float wsel[kMaxTopK];
         float total = 0.f;
@@ -100,7 +106,7 @@ route_topk_kernel(const float* __restrict__ scores, float* __restrict__ probs,
                 const float pw = __shfl_sync(0xffffffffu, mine, be & 31);
                 wsel[slot] = pw;
                 total += pw;  // left-to-right sum over the slots, like the upstream `sum(...)`
-                if (lane == 0) {
+                if (lane == 0) {   // be < E here: k <= E and the ranking is a total order
                     expert_idx[row * k + slot] = be;
                     atomicAdd(&s_cnt[be], 1);  // integer: order does not matter
                 }

@@ -70,6 +70,21 @@ def test_head_bf16_matches_the_oracle(path, master):
         assert oracle.elementwise_err(got[name], want, bf16=True, unit=oracle.rms(want)) <= BF16_ELEMENT_TOL, name
 
 
+def test_head_labels_outside_the_vocabulary_count_as_ignored():
+    """A label that is not a class (negative other than -100, or >= vocab) must not be used as an index: such rows
+    are left out exactly like -100."""
+    g = np.load([p for p in golden_files("head") if p.endswith("head_mid.npz")][0])
+    vocab = g["weight"].shape[0]
+    labels = g["labels"].copy()
+    wild = labels.copy()
+    wild[0, 1], wild[1, 2], wild[2, 3] = vocab, -7, 2 ** 40
+    labels[0, 1] = labels[1, 2] = labels[2, 3] = -100
+    got = run_head(g["hidden"], g["weight"], wild, "float32")
+    want = run_head(g["hidden"], g["weight"], labels, "float32")
+    for name in ("loss", "d_hidden", "d_weight"):
+        assert np.array_equal(got[name], want[name]), name
+
+
 def test_head_rejects_bad_arguments():
     from gpu_util import to_device
     from qutai_b200.head import LMHead
@@ -138,3 +153,26 @@ def test_head_at_the_size_of_a_training_step():
     want_dw = kept[:, classes].T.astype(np.float64) @ inputs
     got_dw = got["d_weight"][classes]
     assert oracle.max_rel_err(got_dw, want_dw) <= 1e-3       # fp32 accumulation of exact bf16 products
+
+
+def test_projection_loss_keeps_the_upstream_signature_and_record_shape():
+    """``projection_loss(hidden, weight, labels, chunk_size, prepared_labels=...)`` returns the loss with
+    ``parents = (hidden, weight)`` and a rule that maps the incoming gradient to one contribution per parent
+    (``None`` for a parent that needs no gradient), the shape upstream's ``record`` takes
+    (src/qutai/core/grad.py:7-13, src/qutai/lm/layers.py:215-257)."""
+    from gpu_util import to_device, to_host
+    from qutai_b200.head import prepare_labels, projection_loss
+    from qutai_b200.layers import Tensor
+
+    g = np.load([p for p in golden_files("head") if p.endswith("head_mid.npz")][0])
+    hidden = Tensor(to_device(g["hidden"], "float32"), g["hidden"].shape, requires_grad=True)
+    weight = Tensor(to_device(g["weight"], "float32"), g["weight"].shape, requires_grad=False)
+    labels = [list(map(int, row)) for row in g["labels"]]
+    loss = projection_loss(hidden, weight, labels, 7)
+    assert loss.shape == () and loss.parents == (hidden, weight)
+    assert abs(to_host(loss.storage)[0] - float(g["loss"])) <= FP32_ELEMENT_TOL * (1 + abs(float(g["loss"])))
+    d_hidden, d_weight = loss.backward_rule(to_device(np.array([float(g["gradient"])]), "float32"))
+    assert d_weight is None                                         # the weight did not ask for a gradient
+    assert oracle.elementwise_err(to_host(d_hidden, g["hidden"].shape), g["d_hidden"]) <= FP32_ELEMENT_TOL
+    again = projection_loss(hidden, weight, None, 7, prepared_labels=prepare_labels(labels))
+    assert to_host(again.storage)[0] == to_host(loss.storage)[0]

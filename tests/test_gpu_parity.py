@@ -112,6 +112,42 @@ def test_routing_orders_logits_one_ulp_apart_like_the_float64_oracle():
     check_route_against_oracle(tables, expected, float_tol=4e-6)
 
 
+@pytest.mark.parametrize("E,k", [(8, 2), (64, 6), (33, 8)])
+def test_routing_of_rows_with_nan_or_infinite_logits_stays_inside_the_tables(E, k):
+    """Logits that are not numbers (a diverged step) must not send an index outside the tables: a NaN ranks as
+    -inf, every row still gets k distinct experts in [0, E), the counts add up to T * k, and rows of ordinary
+    numbers are routed exactly as without their neighbours."""
+    from gpu_util import RouteTables, to_device
+
+    rng = np.random.default_rng(E * 7 + k)
+    T = 700
+    scores = rng.standard_normal((T, E)).astype(np.float32)
+    clean = scores.copy()
+    scores[5] = np.nan                                   # a whole row of NaN
+    scores[6, ::2] = np.nan                              # half a row
+    scores[7] = np.inf
+    scores[8] = -np.inf
+    scores[9, 1] = np.inf
+    scores[10, : E - 1] = np.nan                         # a single number left
+    bad = (5, 6, 7, 8, 9, 10)
+    tables = RouteTables(T, E, k)
+    tables.run(to_device(scores, "float32"))
+    indices = tables.host("expert_index", (T, k))
+    assert indices.min() >= 0 and indices.max() < E
+    assert all(len(set(row)) == k for row in indices.tolist())
+    counts = tables.host("counts")
+    assert counts.sum() == T * k and np.array_equal(counts, np.bincount(indices.reshape(-1), minlength=E))
+    dest = tables.host("dest_row")
+    assert dest.min() >= 0 and dest.max() < tables.rows_bound and len(set(dest.tolist())) == T * k
+    expected = oracle.routing(clean.astype(np.float64), k)
+    good = np.setdiff1d(np.arange(T), bad)
+    assert np.array_equal(indices[good], np.asarray(expected["indices"]).reshape(T, k)[good])
+    assert np.isfinite(tables.host("gate_weights", (T, k))[good]).all()
+    numbers = np.flatnonzero(~np.isnan(scores[6]))       # in the half-NaN row the numbers win, largest first
+    assert set(indices[6, : min(k, len(numbers))]) <= set(numbers.tolist())
+    assert indices[10, 0] == E - 1
+
+
 def test_routing_rejects_bad_arguments():
     from gpu_util import RouteTables, to_device
     from qutai_b200 import lib
