@@ -54,7 +54,8 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64 x 64 bf16 TMA box (8 KiB)
 // epilogue keeps two {G, U} pairs of 32-row x 64-column boxes for every two warps that share rows (fetched and written
 // back by TMA), which costs the ring a stage; the other modes only need a small transpose buffer per warp.
 constexpr int EPILOGUE_WARPS = 8;
-constexpr int NUM_THREADS = 64 + 32 * EPILOGUE_WARPS;  // TMA warp + MMA warp + epilogue warps
+constexpr int NUM_THREADS = 64 + 32 * EPILOGUE_WARPS + 32;  // TMA warp for A, MMA warp, epilogue warps, TMA warp for B
+constexpr int B_PRODUCER_WARP = 2 + EPILOGUE_WARPS;
 constexpr int MODE_DSWIGLU_ID = 3;
 constexpr int BOX_BYTES = 32 * 64 * 2;            // one 32 x 64 bf16 box of the dSwiGLU epilogue (4 KiB, 128-byte rows)
 constexpr int BARRIER_BYTES = 512;
@@ -188,8 +189,12 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, 
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+// One commit that arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair.  The issuing thread
+// pays about ninety cycles for every tcgen05 instruction whatever its size, and a k-block of four MMAs has 512 cycles
+// of tensor work: a second commit per k-block made the issuer, not the tensor pipe, the limit.
+__device__ __forceinline__ void umma_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -534,8 +539,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     else total_tiles = (s_start[p.experts] - s_start[0]) * p.n_tiles;
     volatile int* abort_flag = &s_abort;
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+    if (warp == 0 || warp == B_PRODUCER_WARP) {
+        // ------------------------------ TMA producers -----------------------------
+        // Two threads: one asks for the A boxes of every stage (and announces the stage's bytes), the other for the B
+        // boxes.  Issuing a TMA instruction costs its thread of the order of a hundred cycles whatever the box holds;
+        // with announce + A + B in one thread a k-block took that thread longer than its 512 cycles of tensor work.
+        const bool does_a = warp == 0;
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
@@ -553,8 +562,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     const uint32_t bar = CTAS == 2 ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
                     const int bn_mine = tile.bn / CTAS;      // columns of the B tile this CTA stages
                     const uint32_t stage_bytes = A_STAGE_BYTES + (uint32_t)bn_mine * BK * 2;
-                    if (CTAS == 1) mbar_expect_tx(bar, stage_bytes);
-                    else if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * stage_bytes);
+                    if (does_a) {
+                        if (CTAS == 1) mbar_expect_tx(bar, stage_bytes);
+                        else if (cta_rank == 0) mbar_expect_tx(full_bar(stage), 2 * stage_bytes);
+                    }
                     auto load = [&](const CUtensorMap* map, uint32_t dst, int c0, int c1) {
                         if (CTAS == 2) tma_load_2d_pair(map, dst, bar, c0, c1);
                         else tma_load_2d(map, dst, bar, c0, c1);
@@ -564,11 +575,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         const int krow = tile.krow0 + kb * BK;
                         const CUtensorMap* ma = tile.problem == 0 ? &p.map_a : tile.problem == 1 ? &p.map_a2 : &p.map_a3;
                         const CUtensorMap* mb = tile.problem == 0 ? &p.map_b : tile.problem == 1 ? &p.map_b2 : &p.map_b3;
+                        if (does_a) {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) load(ma, sa + j * CHUNK_BYTES, tile.row0 + 64 * j, krow);
+                            for (int j = 0; j < BM / 64; ++j) load(ma, sa + j * CHUNK_BYTES, tile.row0 + 64 * j, krow);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BN / CTAS / 64; ++j)
-                            if (64 * j < bn_mine) load(mb, sb + j * CHUNK_BYTES, n_mine + 64 * j, krow);
+                            for (int j = 0; j < BN / CTAS / 64; ++j)
+                                if (64 * j < bn_mine) load(mb, sb + j * CHUNK_BYTES, n_mine + 64 * j, krow);
+                        }
                     } else {
                         const int seg = kb / kb_per_seg;
                         const int k0 = (kb - seg * kb_per_seg) * BK;
@@ -577,8 +591,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         // A is K-major in these modes.  The unused half of an odd pair-tile reads past the end of
                         // the matrix: TMA fills zeros without touching memory, and a tensor core fed zeros draws
                         // far less power than one fed another expert's rows (the result is discarded either way).
-                        load(ma, sa, k0, (CTAS == 2 && !tile.rows_valid) ? 0x3fffff00 : tile.row0);
-                        if (MODE == MODE_SWIGLU) {
+                        if (does_a) {
+                            load(ma, sa, k0, (CTAS == 2 && !tile.rows_valid) ? 0x3fffff00 : tile.row0);
+                        } else if (MODE == MODE_SWIGLU) {
                             // accumulator columns [0, 128) = gate, [128, 256) = up; a pair splits them between its CTAs
                             if (CTAS == 2) {
                                 load(cta_rank ? &p.map_b2 : &p.map_b, sb, k0, tile.expert * p.b_rows + tile.n0);
@@ -604,9 +619,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             int stage = 0;
             uint32_t phase = 0;
             int iter = 0;
-            // one commit per CTA whose barrier has to hear about it
+            // a pair's commit reaches the barrier of both CTAs
             auto commit = [&](uint32_t bar) {
-                if (CTAS == 2) { umma_commit_pair(bar); umma_commit_pair(map_to_cta(bar, 1)); }
+                if (CTAS == 2) umma_commit_both(bar);
                 else umma_commit(bar);
             };
             for (int t = first_tile; t < total_tiles && !*abort_flag; t += tile_stride) {
@@ -618,11 +633,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
                 const uint32_t idesc = make_idesc<A_MN, B_MN, BM * CTAS>(tile.bn);
+                bool ready = false;   // the stage of this k-block was seen full while the k-block before it was issued
                 for (int kb = 0; ok && kb < tile.kblocks; ++kb) {
-                    ok = mbar_wait(full_bar(stage), phase, abort_flag);
-                    if (!ok) break;
+                    if (!ready) {
+                        ok = mbar_wait(full_bar(stage), phase, abort_flag);
+                        if (!ok) break;
+                    }
                     tc_fence_after();
                     const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+                    int next_stage = stage + 1;
+                    uint32_t next_phase = phase;
+                    if (next_stage == STAGES) { next_stage = 0; next_phase ^= 1u; }
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // K-major: 128-byte rows, 8-row groups 1024 B apart, +32 B per 16 k.
@@ -631,11 +652,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                                     : make_desc(sa + kk * 32, 16, 1024);
                         const uint64_t bdesc = B_MN ? make_desc(sb + kk * 2048, CHUNK_BYTES, 1024)
                                                     : make_desc(sb + kk * 32, 16, 1024);
+                        // the look at the next stage's barrier goes between the MMAs, where the tensor pipe has work queued,
+                        // rather than after the last one, where its latency would leave the pipe idle
+                        if (kk == BK / UMMA_K - 1) ready = kb + 1 < tile.kblocks && mbar_try(full_bar(next_stage), next_phase);
                         if (CTAS == 2) umma_bf16_pair(tmem_d, adesc, bdesc, idesc, (kb | kk) ? 1u : 0u);
                         else umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | kk) ? 1u : 0u);
                     }
                     commit(empty_bar(stage));  // the stage is free once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    stage = next_stage; phase = next_phase;
                 }
                 if (!ok) {
                     if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, STATUS_WAIT_MMA); }
