@@ -683,6 +683,10 @@ def run_gpu(args, w, rank, world):
         line["block_ffn"] = block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, args.steps, ms, torch, np)
     if world == 1 and not forward_only and not args.no_head:
         line["lm_head"] = lm_head(args.steps, peaks, torch, np)
+    if world == 1 and not forward_only and not args.no_library_gemm:
+        here = library_gemm_here(torch)
+        line["roofline"]["library_gemm_on_this_gpu"] = here
+        line["roofline"]["frac_of_library_gemm_on_this_gpu"] = achieved / here["tflops"]
     if forward_only:
         line["latency_ms"] = call_latency(step, torch, dist, world, device)
     elif args.workload == "c3" and not args.no_decode:
@@ -829,6 +833,36 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
                 unfused_extra_bytes_per_step=2 * elements * (6 + 6), fused_extra_bytes_per_step=2 * elements * (2 + 2),
                 check=dict(ok=bool(out_err <= BF16_TOL and dx_err <= BF16_TOL), out=out_err, dx=dx_err, tolerance=BF16_TOL,
                            sampled_tokens=int(sample.numel())))
+
+
+def library_gemm_here(torch, seconds=2.0, n=8192):
+    """The denominator of the roofline measured again on THIS GPU in THIS run, the way the committed figure was taken
+    (a library bf16 product n^3, back to back for ``seconds``, CUDA events): boxes of the pool differ in their power
+    cap by a quarter, and every tensor-bound kernel runs against that cap, so a fraction of a figure measured on
+    another box mixes the kernel with the box.  Reported beside the official fraction, never instead of it."""
+    a = torch.randn((n, n), device="cuda").to(torch.bfloat16)
+    b = torch.randn((n, n), device="cuda").to(torch.bfloat16)
+    for _ in range(5):
+        torch.matmul(a, b)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    calls, begin, end = 0, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    started = time.time()
+    sampler.begin()
+    begin.record()
+    while time.time() - started < seconds:
+        for _ in range(20):
+            torch.matmul(a, b)
+        calls += 20
+        torch.cuda.synchronize()
+    end.record()
+    torch.cuda.synchronize()
+    sampler.end()
+    clocks = sampler.stop()
+    ms = begin.elapsed_time(end) / calls
+    return dict(tflops=2.0 * n ** 3 / (ms * 1e-3) / 1e12, n=n, calls=calls, sm_mhz=clocks.get("sm_mhz"),
+                power_w_max=clocks.get("power_w_max"), how="torch.matmul bf16 n^3 back to back for 2 s after the timed steps")
 
 
 def lm_head(steps, peaks, torch, np):
@@ -1004,6 +1038,7 @@ def main():
     parser.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-decode", action="store_true", help="leave the decode-shaped latency block out of the c3 line")
+    parser.add_argument("--no-library-gemm", action="store_true", help="do not time the library bf16 product on this GPU")
     parser.add_argument("--no-head", action="store_true", help="leave the language-model head out of the line")
     parser.add_argument("--no-block", action="store_true", help="leave the fused norm + layer + residual block out of the line")
     parser.add_argument("--preroll", type=float, default=2.0,
