@@ -25,10 +25,11 @@ from . import lib
 _FORMATS = {"float32": "f", "float64": "d", "int32": "i", "int64": "q"}
 _cache: dict[int, list[int]] = {}
 _cached_bytes = 0
-# Freed blocks are kept for reuse up to this many bytes (a B200 has 180 GB; activations of the benchmark
-# shapes are hundreds of MB each, and a block that is really freed costs a device-wide synchronisation);
-# QUTAI_MOE_CACHE_BYTES overrides it.
-CACHE_LIMIT_BYTES = int(os.environ.get("QUTAI_MOE_CACHE_BYTES", 16 << 30))
+# Freed blocks are kept for reuse up to this many bytes (a B200 has 180 GB; activations and gradients of the
+# benchmark shapes are hundreds of MB each, and a block that is really freed costs a device-wide synchronisation:
+# with 16 GB the 64-expert layer's step filled the cache and every later gradient buffer was freed and allocated
+# anew, 10 ms a time); QUTAI_MOE_CACHE_BYTES overrides it.
+CACHE_LIMIT_BYTES = int(os.environ.get("QUTAI_MOE_CACHE_BYTES", 64 << 30))
 
 
 def _bucket(nbytes):
@@ -42,7 +43,10 @@ def _allocate(nbytes):
     free = _cache.get(size)
     if free:
         _cached_bytes -= size
-        return free.pop(), size
+        address = free.pop()
+        if not free:
+            del _cache[size]
+        return address, size
     address = ctypes.c_uint64()
     try:
         lib.call("qmoe_malloc", ctypes.byref(address), size)
@@ -53,10 +57,19 @@ def _allocate(nbytes):
 
 
 def _release(address, size):
+    """Keep the block for reuse.  Over the limit the blocks that have waited longest go first (the one just released
+    is the likeliest to be asked for again: a gradient buffer of the next step)."""
     global _cached_bytes
-    if _cached_bytes + size > CACHE_LIMIT_BYTES:
+    if size > CACHE_LIMIT_BYTES:
         lib.load().qmoe_free(address)
         return
+    while _cached_bytes + size > CACHE_LIMIT_BYTES and _cache:
+        oldest = next(iter(_cache))            # dicts keep insertion order: the size that entered the cache first
+        blocks = _cache[oldest]
+        lib.load().qmoe_free(blocks.pop(0))
+        _cached_bytes -= oldest
+        if not blocks:
+            del _cache[oldest]
     _cache.setdefault(size, []).append(address)
     _cached_bytes += size
 
@@ -91,7 +104,9 @@ class DeviceStorage:
         self.nbytes = self.size * lib.ITEM_BYTES[dtype]
         self._owner = owner
         self._block = None
-        self._root = self          # a view shares the generation counter of the storage it was cut from
+        self._parent = None        # a view shares the generation counter of the storage it was cut from; an owning
+                                   # storage refers to nobody (a reference to itself would keep its block from
+                                   # being released until the cycle collector runs)
         self._generation = 0
         self._synced = {}          # id(source root) -> generation of the source this storage was last derived from
         if ptr is None:
@@ -118,10 +133,14 @@ class DeviceStorage:
         if start < 0 or size < 0 or start + size > self.size:
             raise ValueError("view exceeds the storage")
         out = DeviceStorage(size, self.dtype, ptr=self.ptr + start * lib.ITEM_BYTES[self.dtype], owner=self)
-        out._root = self._root
+        out._parent = self._root
         return out
 
     # -- change tracking ------------------------------------------------------------------
+    @property
+    def _root(self):
+        return self._parent if self._parent is not None else self
+
     @property
     def generation(self):
         """Grows with every write made through this package (shared by all views of one allocation)."""
