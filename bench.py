@@ -683,6 +683,8 @@ def run_gpu(args, w, rank, world):
         line["block_ffn"] = block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, args.steps, ms, torch, np)
     if world == 1 and not forward_only and not args.no_head:
         line["lm_head"] = lm_head(args.steps, peaks, torch, np)
+    if world == 1 and not forward_only and not args.no_attention:
+        line["attention"] = attention_block(args.steps, peaks, torch, np)
     if world == 1 and not forward_only and not args.no_library_gemm:
         here = library_gemm_here(torch)
         line["roofline"]["library_gemm_on_this_gpu"] = here
@@ -693,7 +695,8 @@ def run_gpu(args, w, rank, world):
         # the decode-shaped configuration (c3's layer on 64 tokens, forward only): per-call latency of 200 calls
         line["decode"] = decode_latency(layer, w, rank, world, torch, dist, device, Tensor, wrap, peaks)
     ok = (bool(check["ok"]) and bool(line.get("block_ffn", {}).get("check", {}).get("ok", True))
-          and bool(line.get("lm_head", {}).get("check", {}).get("ok", True)))
+          and bool(line.get("lm_head", {}).get("check", {}).get("ok", True))
+          and bool(line.get("attention", {}).get("check", {}).get("ok", True)))
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -833,6 +836,67 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
                 unfused_extra_bytes_per_step=2 * elements * (6 + 6), fused_extra_bytes_per_step=2 * elements * (2 + 2),
                 check=dict(ok=bool(out_err <= BF16_TOL and dx_err <= BF16_TOL), out=out_err, dx=dx_err, tolerance=BF16_TOL,
                            sampled_tokens=int(sample.numel())))
+
+
+def attention_block(steps, peaks, torch, np):
+    """Causal self-attention with grouped key/value heads (``qutai_b200.attention``) at one rank's share of the full
+    decoder step: 4 sequences of 2048 positions, 16 heads of width 64 in 4 key/value groups, bf16; forward + backward,
+    timed with events, one (sequence, group) checked against the float64 oracle on the same bf16 values."""
+    from oracle import moe_oracle as oracle
+    from qutai_b200.attention import attention_backward, attention_forward
+    from qutai_b200.layers import Tensor
+    from qutai_b200.storage import DeviceStorage
+
+    batch, time_, heads, kv_heads, dim = 4, 2048, 16, 4, 64
+    generator = torch.Generator(device="cuda").manual_seed(21)
+    make = lambda width, scale: (torch.randn((batch, time_, width), device="cuda", generator=generator) * scale).to(torch.bfloat16)
+    q, k, v, grad = make(heads * dim, 0.6), make(kv_heads * dim, 0.6), make(kv_heads * dim, 1.0), make(heads * dim, 1.0)
+    wrap = lambda t: Tensor(DeviceStorage.wrap(t.data_ptr(), t.numel(), "bfloat16", owner=t), tuple(t.shape))
+    qt, kt, vt, gt = wrap(q), wrap(k), wrap(v), wrap(grad)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        out, lse = attention_forward(qt, kt, vt, heads, kv_heads, stream)
+        return out, attention_backward(gt, qt, kt, vt, out, lse, heads, kv_heads, stream)
+
+    for _ in range(3):
+        out, grads = step()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        out, grads = step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / steps
+    # the products of the causal half: forward 2 (Q K^T, P V), backward 5 (S and dP once per kernel = 4, dQ, dV, dK = 3,
+    # of which S and dP are formed in both backward kernels), each 2 * 64 flops per (query, key <= query) pair and head
+    pairs = batch * heads * time_ * (time_ + 1) / 2
+    flops = (2 + 7) * 2.0 * dim * pairs
+
+    def host(storage, like):
+        t = torch.empty_like(like)
+        from qutai_b200 import lib
+
+        lib.call("qmoe_memcpy_d2d", t.data_ptr(), storage.ptr, storage.nbytes, stream)
+        torch.cuda.synchronize()
+        return t.float().cpu().numpy().astype(np.float64)
+
+    group = heads // kv_heads
+    b, g = 1, 2
+    wide, narrow = slice(g * group * dim, (g + 1) * group * dim), slice(g * dim, (g + 1) * dim)
+    f = lambda t, cols: t[b:b + 1, :, cols].float().cpu().numpy().astype(np.float64)
+    want_out, lse = oracle.attention_forward(f(q, wide), f(k, narrow), f(v, narrow), group, 1)
+    want = oracle.attention_backward(f(grad, wide), f(q, wide), f(k, narrow), f(v, narrow), want_out, lse, group, 1)
+    got_out = host(out, q)[b:b + 1, :, wide]
+    got = (host(grads[0], q)[b:b + 1, :, wide], host(grads[1], k)[b:b + 1, :, narrow], host(grads[2], v)[b:b + 1, :, narrow])
+    errors = dict(out=oracle.max_rel_err(got_out, want_out), dq=oracle.max_rel_err(got[0], want[0]),
+                  dk=oracle.max_rel_err(got[1], want[1]), dv=oracle.max_rel_err(got[2], want[2]))
+    return dict(ms_per_step=ms, batch=batch, time=time_, heads=heads, kv_heads=kv_heads, dim=dim, dtype="bf16",
+                tflops=flops / (ms * 1e-3) / 1e12, frac_of_sustained_peak=flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                launches_per_step=3,
+                what="causal attention forward + backward (qmoe_attention_forward / _backward): tcgen05, the scores never leave the chip",
+                check=dict(ok=bool(max(errors.values()) <= BF16_TOL), tolerance=BF16_TOL, sampled="sequence 1, key/value group 2", **errors))
 
 
 def library_gemm_here(torch, seconds=2.0, n=8192):
@@ -1039,6 +1103,7 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-decode", action="store_true", help="leave the decode-shaped latency block out of the c3 line")
     parser.add_argument("--no-library-gemm", action="store_true", help="do not time the library bf16 product on this GPU")
+    parser.add_argument("--no-attention", action="store_true", help="leave the attention block out of the line")
     parser.add_argument("--no-head", action="store_true", help="leave the language-model head out of the line")
     parser.add_argument("--no-block", action="store_true", help="leave the fused norm + layer + residual block out of the line")
     parser.add_argument("--preroll", type=float, default=2.0,

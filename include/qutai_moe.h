@@ -426,6 +426,30 @@ int qmoe_head_forward(const qmoe_head_t* head, uint64_t stream);
 int qmoe_head_backward(const qmoe_head_t* head, uint64_t gradient, uint64_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Causal self-attention with grouped key/value heads (the other half of a decoder block):
+ *     out[b, t, h, :] = sum_{s <= t} softmax_s(q[b, t, h, :] . k[b, s, h / (heads / kv_heads), :] / sqrt(dim)) v[b, s, ..., :]
+ * and its backward.  Replaces `attention` / `attention_backward` (src/qutai/lm/layers.py:119-130, launchers
+ * src/qutai/backends/cuda_lm.py, kernels lm_attention_bf16_d64 / _dq / _dkv src/qutai/backends/cuda/lm.cu:91-285;
+ * CPU statement src/qutai/backends/cpu_lm.py:141-201).  Head width 64 and bf16 only (the upstream tensor-core
+ * kernels' case), any sequence length; tcgen05, the time x time scores are never written.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct qmoe_attention {
+    int32_t batch, time, heads, kv_heads;
+    int32_t dim;               /* 64 */
+    int32_t dtype;             /* QMOE_BF16 */
+    uint64_t q;                /* [batch, time, heads, dim] */
+    uint64_t k, v;             /* [batch, time, kv_heads, dim] */
+    uint64_t out;              /* [batch, time, heads, dim] */
+    uint64_t lse;              /* f32 [batch, time, heads]: log sum exp of the scaled scores of every row */
+    uint64_t grad_out;         /* backward: gradient of out */
+    uint64_t delta;            /* backward: f32 [batch, time, heads] scratch */
+    uint64_t dq, dk, dv;       /* backward: like q, k, v */
+} qmoe_attention_t;
+int qmoe_attention_forward(const qmoe_attention_t* attention, uint64_t stream);
+/* needs q, k, v, out and lse as the forward left them */
+int qmoe_attention_backward(const qmoe_attention_t* attention, uint64_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Expert parallelism (one process per GPU, NCCL over NVLink / NVSwitch).  The upstream project is
  * single-GPU (src/qutai/backends/cuda_runtime.py:82, :105), so these entry points have no upstream
  * counterpart; they keep the layer's semantics when tokens are sharded T/N per rank (contiguous

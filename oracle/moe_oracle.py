@@ -357,6 +357,61 @@ def head_loss_backward(ctx, gradient=1.0):
 
 
 # --------------------------------------------------------------------------------------
+# causal self-attention with grouped key/value heads
+# --------------------------------------------------------------------------------------
+def attention_forward(q, k, v, heads, kv_heads):
+    """``attention`` of the CPU backend, src/qutai/backends/cpu_lm.py:141-173: per sequence, query position t and
+    head h, scores ``q . k[s] / sqrt(dim)`` over the key positions ``s <= t`` of key/value head
+    ``h // (heads // kv_heads)``, a softmax over them, and the weighted sum of the values; ``lse`` is
+    ``max + log(sum exp(score - max))`` of each row.  ``q`` [batch, time, heads * dim], ``k``, ``v``
+    [batch, time, kv_heads * dim].  Returns ``(out [batch, time, heads * dim], lse [batch, time, heads])``."""
+    q, k, v = (np.asarray(a, dtype=np.float64) for a in (q, k, v))
+    batch, time, features = q.shape
+    dim = features // heads
+    group = heads // kv_heads
+    qh = q.reshape(batch, time, heads, dim)
+    kh = k.reshape(batch, time, kv_heads, dim)[:, :, np.arange(heads) // group, :]
+    vh = v.reshape(batch, time, kv_heads, dim)[:, :, np.arange(heads) // group, :]
+    scores = np.einsum("bthd,bshd->bhts", qh, kh) / np.sqrt(dim)
+    mask = np.tril(np.ones((time, time), dtype=bool))
+    scores = np.where(mask, scores, -np.inf)
+    peak = scores.max(axis=-1, keepdims=True)
+    weights = np.exp(scores - peak)
+    total = weights.sum(axis=-1, keepdims=True)
+    out = np.einsum("bhts,bshd->bthd", weights / total, vh).reshape(batch, time, features)
+    lse = (peak + np.log(total))[..., 0].transpose(0, 2, 1)
+    return out, lse
+
+
+def attention_backward(gradient, q, k, v, out, lse, heads, kv_heads):
+    """``attention_backward``, src/qutai/backends/cpu_lm.py:176-201: with ``p = exp(score - lse)``,
+    ``delta = <gradient, out>`` per row and ``ds = p (gradient . v[s] - delta) / sqrt(dim)``:
+    ``dq += ds k[s]``, ``dk[s] += ds q``, ``dv[s] += p gradient`` (the key/value gradients summed over the query heads
+    of a group).  Returns ``(dq, dk, dv)`` in the shapes of ``q, k, v``."""
+    gradient, q, k, v, out, lse = (np.asarray(a, dtype=np.float64) for a in (gradient, q, k, v, out, lse))
+    batch, time, features = q.shape
+    dim = features // heads
+    group = heads // kv_heads
+    head_of = np.arange(heads) // group
+    qh, gh, oh = (a.reshape(batch, time, heads, dim) for a in (q, gradient, out))
+    kh = k.reshape(batch, time, kv_heads, dim)[:, :, head_of, :]
+    vh = v.reshape(batch, time, kv_heads, dim)[:, :, head_of, :]
+    scale = 1.0 / np.sqrt(dim)
+    scores = np.einsum("bthd,bshd->bhts", qh, kh) * scale
+    mask = np.tril(np.ones((time, time), dtype=bool))
+    p = np.where(mask, np.exp(scores - lse.transpose(0, 2, 1)[..., None]), 0.0)
+    delta = np.einsum("bthd,bthd->bht", gh, oh)
+    dp = np.einsum("bthd,bshd->bhts", gh, vh)
+    ds = p * (dp - delta[..., None]) * scale
+    dq = np.einsum("bhts,bshd->bthd", ds, kh).reshape(batch, time, features)
+    dk_heads = np.einsum("bhts,bthd->bshd", ds, qh)
+    dv_heads = np.einsum("bhts,bthd->bshd", p, gh)
+    dk = dk_heads.reshape(batch, time, kv_heads, group, dim).sum(axis=3).reshape(batch, time, kv_heads * dim)
+    dv = dv_heads.reshape(batch, time, kv_heads, group, dim).sum(axis=3).reshape(batch, time, kv_heads * dim)
+    return dq, dk, dv
+
+
+# --------------------------------------------------------------------------------------
 # helpers used by tests and by the benchmark's CPU leg
 # --------------------------------------------------------------------------------------
 def round_bf16(a):

@@ -38,6 +38,7 @@
 #include <tuple>
 
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace qmoe {
 
@@ -70,7 +71,6 @@ template <int CTAS, int MODE> struct Cfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + EPI_BYTES + BARRIER_BYTES;
 };
 constexpr uint32_t TMEM_COLS = 512;
-constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
 enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_WGRAD = 2, MODE_DSWIGLU = MODE_DSWIGLU_ID, MODE_ROUTER = 4, MODE_PLAIN_F32 = 5 };
 enum { STATUS_WAIT_PRODUCER = 101, STATUS_WAIT_MMA = 102, STATUS_WAIT_EPILOGUE = 103 };
@@ -104,135 +104,6 @@ struct alignas(64) GemmParams {
     int problems;         // WGRAD: 1, or 3 products of the same shape (outputs out0, out1, out2) sharing the tile queue
     int group_stride;     // ROUTER: accumulator columns [0,S), [S,2S), [2S,3S) hold the three bf16 terms of the weights
 };
-
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try(bar, parity)) return true;
-    const unsigned long long start = global_ns();
-    for (unsigned i = 1;; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 63u) == 0) {
-            if (*abort_flag) return false;
-            if (global_ns() - start > WAIT_LIMIT_NS) return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t dst, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-// TMA store of one box from this CTA's shared memory (bulk async group of the issuing thread)
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// the issuing thread's bulk stores have finished READING shared memory (all of them / all but the newest group)
-__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// writes made with ordinary stores become visible to the TMA unit (async proxy)
-__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-// ---- cluster / CTA-pair helpers (CTAS == 2) ----------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-    return remote;
-}
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-// TMA load issued by one CTA of a pair: the data lands in this CTA's shared memory, the transaction
-// bytes are counted on the barrier of the pair's first CTA (same offset, CTA-rank bit cleared).
-__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t dst, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// One commit that arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair.  The issuing thread
-// pays about ninety cycles for every tcgen05 instruction whatever its size, and a k-block of four MMAs has 512 cycles
-// of tensor work: a second commit per k-block made the issuer, not the tensor pipe, the limit.
-__device__ __forceinline__ void umma_commit_both(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(bar), "h"((uint16_t)3) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (bit layout per the PTX ISA "matrix descriptor" for tcgen05):
-// [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
-// [46,48) version = 1, [61,64) swizzle mode (2 = 128-byte).
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M = 128, N = 256.
-template <bool A_MN, bool B_MN, int M>
-__device__ __forceinline__ constexpr uint32_t make_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
 
 struct Tile {
     int expert, row0, n0, kblocks, krow0;
@@ -1049,6 +920,32 @@ int make_map(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t outer, uin
     g_maps[key] = *out;
     return 0;
 }
+
+}  // namespace
+
+// 3-D bf16 tensor [outer][mid][inner] (dense), box {64, box_mid, 1}, 128-byte swizzle: the attention kernels' view of
+// [batch][time][heads * 64], in which a box never crosses from one sequence into the next and positions past the end
+// of a sequence arrive as zeros.
+int make_map_3d(CUtensorMap* out, uint64_t ptr, uint64_t inner, uint64_t mid, uint64_t outer, uint32_t box_mid) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return QMOE_ERR_STATE; }
+    if (ptr & 15u) return fail_arg("tensor-core operand address must be 16-byte aligned");
+    if ((inner * 2) % 16) return fail_arg("tensor-core operand row pitch must be a multiple of 16 bytes");
+    cuuint64_t dims[3] = {inner, mid, outer};
+    cuuint64_t strides[2] = {inner * 2, inner * mid * 2};
+    cuuint32_t box[3] = {64, box_mid, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (3-D: inner %llu, mid %llu, outer %llu)", (int)rc,
+                  (unsigned long long)inner, (unsigned long long)mid, (unsigned long long)outer);
+        return 999;
+    }
+    return 0;
+}
+
+namespace {
 
 template <int MODE, bool A_MN, bool B_MN, int CTAS = 1>
 int launch(const GemmParams& p, cudaStream_t stream) {

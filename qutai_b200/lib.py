@@ -79,6 +79,12 @@ class Head(Structure):
         "hidden", "weight", "labels", "inputs", "logits", "row_loss", "loss", "meta", "d_inputs", "d_hidden", "d_weight")]
 
 
+class Attention(Structure):
+    """``qmoe_attention_t``."""
+    _fields_ = [(name, c_int32) for name in ("batch", "time", "heads", "kv_heads", "dim", "dtype")] + [(name, c_uint64) for name in (
+        "q", "k", "v", "out", "lse", "grad_out", "delta", "dq", "dk", "dv")]
+
+
 _U, _I32, _I64 = c_uint64, c_int32, c_int64
 _RP, _EP, _LP, _SP = POINTER(Route), POINTER(Experts), POINTER(Layer), POINTER(Segment)
 
@@ -149,6 +155,8 @@ SIGNATURES = {
     "qmoe_block_backward": (c_int, [POINTER(Block), _U]),
     "qmoe_head_forward": (c_int, [POINTER(Head), _U]),
     "qmoe_head_backward": (c_int, [POINTER(Head), _U, _U]),
+    "qmoe_attention_forward": (c_int, [POINTER(Attention), _U]),
+    "qmoe_attention_backward": (c_int, [POINTER(Attention), _U]),
     "qmoe_layer_forward": (c_int, [_LP, _U]),
     "qmoe_layer_backward": (c_int, [_LP, _U]),
     "qmoe_ep_unique_id": (c_int, [c_void_p]),

@@ -52,6 +52,7 @@ def test_ctypes_structures_match_the_c_layout(tmp_path):
               "qmoe_layer_t": [f[0] for f in lib.Layer._fields_],
               "qmoe_block_t": [f[0] for f in lib.Block._fields_],
               "qmoe_head_t": [f[0] for f in lib.Head._fields_],
+              "qmoe_attention_t": [f[0] for f in lib.Attention._fields_],
               "qmoe_optim_item_t": [f[0] for f in lib.OptimItem._fields_]}
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for struct, names in fields.items():
@@ -64,7 +65,8 @@ def test_ctypes_structures_match_the_c_layout(tmp_path):
     subprocess.run(["gcc", "-o", str(binary), str(source)], check=True)
     reported = dict(line.rsplit(" ", 1) for line in subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.splitlines())
     for struct, cls in (("qmoe_route_t", lib.Route), ("qmoe_experts_t", lib.Experts), ("qmoe_layer_t", lib.Layer),
-                        ("qmoe_block_t", lib.Block), ("qmoe_head_t", lib.Head), ("qmoe_optim_item_t", lib.OptimItem)):
+                        ("qmoe_block_t", lib.Block), ("qmoe_head_t", lib.Head), ("qmoe_attention_t", lib.Attention),
+                        ("qmoe_optim_item_t", lib.OptimItem)):
         assert int(reported[struct]) == ctypes.sizeof(cls)
         for name, _ in cls._fields_:
             assert int(reported[f"{struct}.{name}"]) == getattr(cls, name).offset, (struct, name)

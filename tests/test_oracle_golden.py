@@ -1,6 +1,7 @@
 """Pin the CPU oracle: every function of ``oracle/moe_oracle.py`` (and the pure-Python restatement)
 against the fixtures produced by the upstream package itself (``tests/golden/make_golden.py``)."""
 import os
+import sys
 
 import numpy as np
 import pytest
@@ -145,3 +146,19 @@ def test_head_oracle_matches_the_upstream_projection_loss(path):
     close(d_hidden, g["d_hidden"])
     close(d_weight, g["d_weight"])
     assert not d_hidden[:, -1, :].any()          # the last position of a sequence has no target
+
+
+@pytest.mark.parametrize("path", golden_files("attention"), ids=os.path.basename)
+def test_attention_oracle_matches_the_upstream_cpu_backend(path):
+    """Causal attention with grouped key/value heads, forward and backward, against what the upstream pure-Python
+    CPU backend produced (tests/golden/make_golden_attention.py)."""
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    from attention_inputs import attention_inputs
+
+    g = np.load(path)
+    heads, kv_heads = int(g["heads"]), int(g["kv_heads"])
+    q, k, v, grad = attention_inputs(int(g["batch"]), int(g["time"]), heads, kv_heads, int(g["seed"]), float(g["scale"]))
+    out, lse = oracle.attention_forward(q, k, v, heads, kv_heads)
+    dq, dk, dv = oracle.attention_backward(grad, q, k, v, out, lse, heads, kv_heads)
+    for mine, theirs in ((out, g["out"]), (lse, g["lse"]), (dq, g["dq"]), (dk, g["dk"]), (dv, g["dv"])):
+        assert np.abs(mine - theirs).max() <= 2e-6 * (1 + np.abs(theirs).max())      # the fixtures are stored in float32
