@@ -92,9 +92,9 @@ __device__ __forceinline__ void linger_after_abort(const volatile int* abort_fla
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(THREADS)
 attention_forward_kernel(const __grid_constant__ AttentionParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ uint32_t s_tmem_base;
-    __shared__ int s_abort;
+    // No static shared memory and a 1 KiB-aligned dynamic block: 112 KiB of tiles + the barriers and two words fit
+    // twice into an SM, and the second resident CTA is what overlaps one CTA's row work with another's MMAs.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int blocks = (p.time + BLOCK - 1) / BLOCK;
     // heaviest query blocks first: the last block of a sequence has the most key blocks to walk
@@ -102,11 +102,17 @@ attention_forward_kernel(const __grid_constant__ AttentionParams p) {
     const int h = (int)(blockIdx.x / blocks) % p.heads, b = (int)(blockIdx.x / blocks) / p.heads;
     const int g = h / (p.heads / p.kv_heads);
     const int n = i + 1;                       // key blocks 0 .. i
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t base = smem_u32(smem_raw);
     const uint32_t q_tile = base, k_tile = base + TILE_BYTES, v_tile = k_tile + 2 * TILE_BYTES, p_tile = v_tile + 2 * TILE_BYTES;
     const uint32_t bars = p_tile + 2 * SLAB_BYTES;
     enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, P_FULL = 6, O_FULL = 7, O_TAKEN = 8, BARS = 9 };
     auto bar = [&](int which) { return bars + 8u * which; };
+    uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(smem_raw + 5 * TILE_BYTES + 2 * SLAB_BYTES + 8 * BARS);
+    volatile int& s_abort = *reinterpret_cast<volatile int*>(smem_raw + 5 * TILE_BYTES + 2 * SLAB_BYTES + 8 * BARS + 4);
+    if (base & 1023u) {   // the operand tiles need the alignment the declaration asks for
+        if (threadIdx.x == 0) atomicExch(p.status, STATUS_ATTENTION_WAIT + 1);
+        return;
+    }
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int w = 0; w < BARS; ++w) mbar_init(bar(w), (w == P_FULL || w == O_TAKEN) ? 4 : 1);
@@ -575,7 +581,7 @@ attention_dkv_kernel(const __grid_constant__ AttentionParams p) {
     }
 }
 
-constexpr int FORWARD_SMEM = 1024 + 5 * TILE_BYTES + 2 * SLAB_BYTES + 128;
+constexpr int FORWARD_SMEM = 5 * TILE_BYTES + 2 * SLAB_BYTES + 128;
 constexpr int DQ_SMEM = 1024 + 6 * TILE_BYTES + 2 * SLAB_BYTES + 128;
 constexpr int DKV_SMEM = 1024 + 6 * TILE_BYTES + 4 * SLAB_BYTES + 128;
 
