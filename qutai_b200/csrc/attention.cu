@@ -32,6 +32,7 @@ enum { STATUS_ATTENTION_WAIT = 301 };
 
 struct alignas(64) AttentionParams {
     CUtensorMap map_q, map_k, map_v, map_do;     // 3-D [batch][time][heads * 64] bf16, boxes of 64 x 128 x 1
+    CUtensorMap map_k2, map_v2;                  // the same tensors in boxes of 64 x 64 x 1 (dq kernel with key blocks of 64)
     const __nv_bfloat16* out_in;  // backward: the forward's output
     const __nv_bfloat16* grad_out;
     __nv_bfloat16* out;           // forward: out; backward for dq: dq; backward for dk, dv: dk
@@ -257,40 +258,50 @@ attention_forward_kernel(const __grid_constant__ AttentionParams p) {
 
 
 // ------------------------------------------------------------------------------------------------
-// backward, part 1: dq (and delta), one CTA per (sequence, head, query block)
+// backward, part 1: dq (and delta), one CTA per (sequence, head, query block); key blocks of KV positions.  With
+// KV = 64 a CTA needs 192 TMEM columns and 80 KiB, so two are resident per SM and overlap each other's chains.
 // ------------------------------------------------------------------------------------------------
+template <int KV>
 __global__ void __launch_bounds__(THREADS)
 attention_dq_kernel(const __grid_constant__ AttentionParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ uint32_t s_tmem_base;
-    __shared__ int s_abort;
+    constexpr int KV_TILE = KV * 128, SLABS = KV / 64, TMEM_COLUMNS = KV == 64 ? 256 : 512;
+    constexpr int TILES = 2 * TILE_BYTES + 4 * KV_TILE + SLABS * SLAB_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int blocks = (p.time + BLOCK - 1) / BLOCK;
     const int i = blocks - 1 - (int)(blockIdx.x % blocks);
     const int h = (int)(blockIdx.x / blocks) % p.heads, b = (int)(blockIdx.x / blocks) / p.heads;
     const int g = h / (p.heads / p.kv_heads);
-    const int n = i + 1;
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_tile = base, do_tile = base + TILE_BYTES, k_tile = do_tile + TILE_BYTES, v_tile = k_tile + 2 * TILE_BYTES,
-                   ds_tile = v_tile + 2 * TILE_BYTES;
-    const uint32_t bars = ds_tile + 2 * SLAB_BYTES;
+    const int n = (i + 1) * (BLOCK / KV);      // key blocks that hold a position <= the last query of this block
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t q_tile = base, do_tile = base + TILE_BYTES, k_tile = do_tile + TILE_BYTES, v_tile = k_tile + 2 * KV_TILE,
+                   ds_tile = v_tile + 2 * KV_TILE;
+    const uint32_t bars = ds_tile + SLABS * SLAB_BYTES;
     enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, SP_FULL = 5, DS_FULL = 6, DQ_DONE = 7, BARS = 8 };
     auto bar = [&](int which) { return bars + 8u * which; };
+    uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(smem_raw + TILES + 8 * BARS);
+    volatile int& s_abort = *reinterpret_cast<volatile int*>(smem_raw + TILES + 8 * BARS + 4);
+    if (base & 1023u) {
+        if (threadIdx.x == 0) atomicExch(p.status, STATUS_ATTENTION_WAIT + 1);
+        return;
+    }
+    const CUtensorMap* map_k = KV == 64 ? &p.map_k2 : &p.map_k;
+    const CUtensorMap* map_v = KV == 64 ? &p.map_v2 : &p.map_v;
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int w = 0; w < BARS; ++w) mbar_init(bar(w), w == DS_FULL ? 4 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        prefetch_map(&p.map_q); prefetch_map(&p.map_k); prefetch_map(&p.map_v); prefetch_map(&p.map_do);
+        prefetch_map(&p.map_q); prefetch_map(map_k); prefetch_map(map_v); prefetch_map(&p.map_do);
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLUMNS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem_base;
-    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+    const uint32_t tmem_s = tmem, tmem_dp = tmem + KV, tmem_dq = tmem + 2 * KV;
     const Wait wait{&s_abort, p.status};
 
     if (warp == 0) {
@@ -301,14 +312,14 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
             for (int j = 0; j < n && !s_abort; ++j) {
                 const int st = j & 1;
                 if (!wait(bar(KV_EMPTY + st), ((uint32_t)(j >> 1) & 1u) ^ 1u)) break;
-                mbar_expect_tx(bar(KV_FULL + st), 2 * TILE_BYTES);
-                tma_load_3d(&p.map_k, k_tile + st * TILE_BYTES, bar(KV_FULL + st), g * D, j * BLOCK, b);
-                tma_load_3d(&p.map_v, v_tile + st * TILE_BYTES, bar(KV_FULL + st), g * D, j * BLOCK, b);
+                mbar_expect_tx(bar(KV_FULL + st), 2 * KV_TILE);
+                tma_load_3d(map_k, k_tile + st * KV_TILE, bar(KV_FULL + st), g * D, j * KV, b);
+                tma_load_3d(map_v, v_tile + st * KV_TILE, bar(KV_FULL + st), g * D, j * KV, b);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc<false, false, 128>(128), idesc_dq = make_idesc<false, true, 128>(D);
+            constexpr uint32_t idesc_s = make_idesc<false, false, 128>(KV), idesc_dq = make_idesc<false, true, 128>(D);
             bool ok = wait(bar(Q_FULL), 0);
             for (int j = 0; ok && j < n; ++j) {
                 const int st = j & 1;
@@ -318,19 +329,19 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
                 // S = Q K^T and dP = dO V^T (the rows that read both of the block before have arrived on DS_FULL)
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
-                    umma_bf16(tmem_s, make_desc(q_tile + kk * 32, 16, 1024), make_desc(k_tile + st * TILE_BYTES + kk * 32, 16, 1024), idesc_s, kk ? 1u : 0u);
+                    umma_bf16(tmem_s, make_desc(q_tile + kk * 32, 16, 1024), make_desc(k_tile + st * KV_TILE + kk * 32, 16, 1024), idesc_s, kk ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
-                    umma_bf16(tmem_dp, make_desc(do_tile + kk * 32, 16, 1024), make_desc(v_tile + st * TILE_BYTES + kk * 32, 16, 1024), idesc_s, kk ? 1u : 0u);
+                    umma_bf16(tmem_dp, make_desc(do_tile + kk * 32, 16, 1024), make_desc(v_tile + st * KV_TILE + kk * 32, 16, 1024), idesc_s, kk ? 1u : 0u);
                 umma_commit(bar(SP_FULL));
                 ok = wait(bar(DS_FULL), (uint32_t)j & 1u);
                 if (!ok) break;
                 tc_fence_after();
-                // dQ += dS K: dS K-major (two slabs), the K tile read as the MN-major operand (rows = key positions)
+                // dQ += dS K: dS K-major (slabs of 64 key positions), the K tile read as the MN-major operand (rows = key positions)
 #pragma unroll
-                for (int kk = 0; kk < BLOCK / 16; ++kk)
+                for (int kk = 0; kk < KV / 16; ++kk)
                     umma_bf16(tmem_dq, make_desc(ds_tile + (kk >> 2) * SLAB_BYTES + (kk & 3) * 32, 16, 1024),
-                              make_desc(k_tile + st * TILE_BYTES + kk * 2048, 8192, 1024), idesc_dq, (j | kk) ? 1u : 0u);
+                              make_desc(k_tile + st * KV_TILE + kk * 2048, 8192, 1024), idesc_dq, (j | kk) ? 1u : 0u);
                 umma_commit(bar(DQ_DONE));          // dS may be overwritten, and after the last block dQ is complete
                 umma_commit(bar(KV_EMPTY + st));
             }
@@ -366,9 +377,10 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
             if (ok && j > 0) ok = wait(bar(DQ_DONE), (uint32_t)(j - 1) & 1u);     // the MMAs that read dS of the block before are done
             if (!ok) break;
             tc_fence_after();
-            const bool diagonal = j == i;
+            const int first = j * KV;                              // key position of this block's column 0
+            const bool masked = first + KV - 1 > i * BLOCK;        // the block reaches past the first query of this CTA
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < KV / 32; ++c) {
                 uint32_t rs[32], rp[32], packed[16];
                 tmem_ld32(tmem_s + lane_base + c * 32, rs);
                 tmem_ld32(tmem_dp + lane_base + c * 32, rp);
@@ -376,9 +388,9 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
                     float d0 = 0.f, d1 = 0.f;
-                    if (live && !(diagonal && c * 32 + e > row))
+                    if (live && !(masked && first + c * 32 + e > tq))
                         d0 = exp2_fast(__uint_as_float(rs[e]) * scale2 - lse2) * (__uint_as_float(rp[e]) - delta) * 0.125f;
-                    if (live && !(diagonal && c * 32 + e + 1 > row))
+                    if (live && !(masked && first + c * 32 + e + 1 > tq))
                         d1 = exp2_fast(__uint_as_float(rs[e + 1]) * scale2 - lse2) * (__uint_as_float(rp[e + 1]) - delta) * 0.125f;
                     packed[e >> 1] = pack2(d0, d1);
                 }
@@ -414,7 +426,7 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLUMNS) : "memory");
     }
 }
 
@@ -582,7 +594,8 @@ attention_dkv_kernel(const __grid_constant__ AttentionParams p) {
 }
 
 constexpr int FORWARD_SMEM = 5 * TILE_BYTES + 2 * SLAB_BYTES + 128;
-constexpr int DQ_SMEM = 1024 + 6 * TILE_BYTES + 2 * SLAB_BYTES + 128;
+constexpr int DQ_KV = 64;
+constexpr int DQ_SMEM = 2 * TILE_BYTES + 4 * DQ_KV * 128 + (DQ_KV / 64) * SLAB_BYTES + 128;
 constexpr int DKV_SMEM = 1024 + 6 * TILE_BYTES + 4 * SLAB_BYTES + 128;
 
 }  // namespace
@@ -637,10 +650,12 @@ extern "C" int qmoe_attention_backward(const qmoe_attention_t* a, uint64_t strea
     p.lse = (float*)a->lse; p.delta = (float*)a->delta; p.status = device_status_address();
     p.batch = a->batch; p.time = a->time; p.heads = a->heads; p.kv_heads = a->kv_heads;
     const int blocks = (a->time + BLOCK - 1) / BLOCK;
-    QMOE_CUDA(cudaFuncSetAttribute(attention_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
+    if (int rc = make_map_3d(&p.map_k2, a->k, narrow, (uint64_t)a->time, (uint64_t)a->batch, DQ_KV)) return rc;
+    if (int rc = make_map_3d(&p.map_v2, a->v, narrow, (uint64_t)a->time, (uint64_t)a->batch, DQ_KV)) return rc;
+    QMOE_CUDA(cudaFuncSetAttribute(attention_dq_kernel<DQ_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
     QMOE_CUDA(cudaFuncSetAttribute(attention_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM));
     p.out = (__nv_bfloat16*)a->dq; p.out2 = nullptr;
-    attention_dq_kernel<<<(unsigned)(blocks * a->heads * a->batch), THREADS, DQ_SMEM, stream>>>(p);
+    attention_dq_kernel<DQ_KV><<<(unsigned)(blocks * a->heads * a->batch), THREADS, DQ_SMEM, stream>>>(p);
     count_tensor_core_launch();
     QMOE_LAUNCH_CHECK("attention_dq_kernel");
     p.out = (__nv_bfloat16*)a->dk; p.out2 = (__nv_bfloat16*)a->dv;
