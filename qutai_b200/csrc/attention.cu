@@ -26,7 +26,12 @@ constexpr int D = 64;                 // head width
 constexpr int BLOCK = 128;            // query rows of a CTA = key positions of a block
 constexpr int TILE_BYTES = BLOCK * D * 2;          // 16 KiB: 128 rows x 128 bytes
 constexpr int SLAB_BYTES = BLOCK * 128;            // one 64-column half of a 128 x 128 bf16 operand tile
-constexpr int THREADS = 192;
+constexpr int THREADS = 192;              // forward: TMA warp, MMA warp, four row warps
+// The backward kernels have no reduction along a row (lse and delta are known), so the columns of a block are split
+// between several warps per 32 rows: one warp per scheduler cannot hide its own arithmetic latency (measured: 4900 of
+// the 7300 cycles of a dk/dv iteration were the four row warps' work).
+constexpr int DQ_PARTS = 2, DKV_PARTS = 4;
+constexpr int DQ_THREADS = 64 + 128 * DQ_PARTS, DKV_THREADS = 64 + 128 * DKV_PARTS;
 constexpr float LOG2E = 1.4426950408889634f;
 enum { STATUS_ATTENTION_WAIT = 301 };
 
@@ -262,7 +267,7 @@ attention_forward_kernel(const __grid_constant__ AttentionParams p) {
 // KV = 64 a CTA needs 192 TMEM columns and 80 KiB, so two are resident per SM and overlap each other's chains.
 // ------------------------------------------------------------------------------------------------
 template <int KV>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(DQ_THREADS)
 attention_dq_kernel(const __grid_constant__ AttentionParams p) {
     constexpr int KV_TILE = KV * 128, SLABS = KV / 64, TMEM_COLUMNS = KV == 64 ? 256 : 512;
     constexpr int TILES = 2 * TILE_BYTES + 4 * KV_TILE + SLABS * SLAB_BYTES;
@@ -289,7 +294,7 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
     const CUtensorMap* map_v = KV == 64 ? &p.map_v2 : &p.map_v;
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int w = 0; w < BARS; ++w) mbar_init(bar(w), w == DS_FULL ? 4 : 1);
+        for (int w = 0; w < BARS; ++w) mbar_init(bar(w), w == DS_FULL ? 4 * DQ_PARTS : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_map(&p.map_q); prefetch_map(map_k); prefetch_map(map_v); prefetch_map(&p.map_do);
     }
@@ -348,7 +353,9 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
             if (ok) wait(bar(KV_EMPTY + ((n - 1) & 1)), (uint32_t)((n - 1) >> 1) & 1u);   // the last commit has arrived
         }
     } else {
-        const int quad = warp & 3, row = quad * 32 + lane;
+        const int quad = warp & 3, row = quad * 32 + lane, part = (warp - 2) >> 2;     // part: which columns of a block
+        constexpr int CHUNKS = KV / 32 / DQ_PARTS;
+        static_assert(CHUNKS >= 1, "a key block has fewer 32-column chunks than there are row warps per 32 rows");
         const int tq = i * BLOCK + row;
         const bool live = tq < p.time;
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
@@ -367,7 +374,7 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
                     delta += __uint_as_float(aw[e] << 16) * __uint_as_float(ow[e] << 16) +
                              __uint_as_float(aw[e] & 0xffff0000u) * __uint_as_float(ow[e] & 0xffff0000u);
             }
-            p.delta[at] = delta;
+            if (part == 0) p.delta[at] = delta;
             lse2 = p.lse[at] * LOG2E;
         }
         const float scale2 = 0.125f * LOG2E;
@@ -380,7 +387,7 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
             const int first = j * KV;                              // key position of this block's column 0
             const bool masked = first + KV - 1 > i * BLOCK;        // the block reaches past the first query of this CTA
 #pragma unroll 1
-            for (int c = 0; c < KV / 32; ++c) {
+            for (int c = part * CHUNKS; c < (part + 1) * CHUNKS; ++c) {
                 uint32_t rs[32], rp[32], packed[16];
                 tmem_ld32(tmem_s + lane_base + c * 32, rs);
                 tmem_ld32(tmem_dp + lane_base + c * 32, rp);
@@ -406,7 +413,7 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
             tc_fence_after();
             uint4* dst = reinterpret_cast<uint4*>(p.out + at * D);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = part; c < 2; c += DQ_PARTS) {
                 uint32_t r[32];
                 tmem_ld32(tmem_dq + lane_base + c * 32, r);
                 tmem_ld_wait();
@@ -433,7 +440,7 @@ attention_dq_kernel(const __grid_constant__ AttentionParams p) {
 // ------------------------------------------------------------------------------------------------
 // backward, part 2: dk and dv, one CTA per (sequence, key/value head, key block)
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(DKV_THREADS)
 attention_dkv_kernel(const __grid_constant__ AttentionParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
@@ -453,7 +460,7 @@ attention_dkv_kernel(const __grid_constant__ AttentionParams p) {
     auto bar = [&](int which) { return bars + 8u * which; };
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int w = 0; w < BARS; ++w) mbar_init(bar(w), w == PDS_FULL ? 4 : 1);
+        for (int w = 0; w < BARS; ++w) mbar_init(bar(w), w == PDS_FULL ? 4 * DKV_PARTS : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_map(&p.map_q); prefetch_map(&p.map_k); prefetch_map(&p.map_v); prefetch_map(&p.map_do);
     }
@@ -518,7 +525,8 @@ attention_dkv_kernel(const __grid_constant__ AttentionParams p) {
             if (ok) wait(bar(Q_EMPTY + ((n - 1) & 1)), (uint32_t)((n - 1) >> 1) & 1u);    // the last commit has arrived
         }
     } else {
-        const int quad = warp & 3, row = quad * 32 + lane;
+        const int quad = warp & 3, row = quad * 32 + lane, part = (warp - 2) >> 2;     // part: which 32 columns of a block
+        static_assert(DKV_PARTS == 4, "one 32-column chunk of S and dP, and one of the four chunks of dV and dK, per row warp");
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const float scale2 = 0.125f * LOG2E;
         bool ok = true;
@@ -537,8 +545,8 @@ attention_dkv_kernel(const __grid_constant__ AttentionParams p) {
             if (!ok) break;
             tc_fence_after();
             const bool diagonal = i == j;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            {
+                const int c = part;
                 uint32_t rs[32], rp[32], pp[16], pd[16];
                 tmem_ld32(tmem_s + lane_base + c * 32, rs);
                 tmem_ld32(tmem_dp + lane_base + c * 32, rp);
@@ -564,11 +572,11 @@ attention_dkv_kernel(const __grid_constant__ AttentionParams p) {
             tc_fence_after();
             const int tk = j * BLOCK + row;                     // this thread's key position
             const long long at = ((long long)b * p.time + (tk < p.time ? tk : 0)) * p.kv_heads + g;
-#pragma unroll
-            for (int which = 0; which < 2; ++which) {
-                uint4* dst = reinterpret_cast<uint4*>((which ? p.out : p.out2) + at * D);     // dv first (columns 256..319), then dk
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
+            {
+                const int which = part >> 1;                                                  // parts 0, 1: dv; parts 2, 3: dk
+                uint4* dst = reinterpret_cast<uint4*>((which ? p.out : p.out2) + at * D);
+                {
+                    const int c = part & 1;
                     uint32_t r[32];
                     tmem_ld32((which ? tmem_dk : tmem_dv) + lane_base + c * 32, r);
                     tmem_ld_wait();
@@ -655,11 +663,11 @@ extern "C" int qmoe_attention_backward(const qmoe_attention_t* a, uint64_t strea
     QMOE_CUDA(cudaFuncSetAttribute(attention_dq_kernel<DQ_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
     QMOE_CUDA(cudaFuncSetAttribute(attention_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM));
     p.out = (__nv_bfloat16*)a->dq; p.out2 = nullptr;
-    attention_dq_kernel<DQ_KV><<<(unsigned)(blocks * a->heads * a->batch), THREADS, DQ_SMEM, stream>>>(p);
+    attention_dq_kernel<DQ_KV><<<(unsigned)(blocks * a->heads * a->batch), DQ_THREADS, DQ_SMEM, stream>>>(p);
     count_tensor_core_launch();
     QMOE_LAUNCH_CHECK("attention_dq_kernel");
     p.out = (__nv_bfloat16*)a->dk; p.out2 = (__nv_bfloat16*)a->dv;
-    attention_dkv_kernel<<<(unsigned)(blocks * a->kv_heads * a->batch), THREADS, DKV_SMEM, stream>>>(p);
+    attention_dkv_kernel<<<(unsigned)(blocks * a->kv_heads * a->batch), DKV_THREADS, DKV_SMEM, stream>>>(p);
     count_tensor_core_launch();
     QMOE_LAUNCH_CHECK("attention_dkv_kernel");
     return 0;
