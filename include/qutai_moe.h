@@ -426,6 +426,34 @@ int qmoe_head_forward(const qmoe_head_t* head, uint64_t stream);
 int qmoe_head_backward(const qmoe_head_t* head, uint64_t gradient, uint64_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The small operations around attention and the feed-forward half of a block, with the upstream launchers' meaning of
+ * the arguments (src/qutai/backends/cuda_lm.py:77-228, kernels src/qutai/backends/cuda/lm.cu:11-64, CPU statements
+ * src/qutai/backends/cpu_lm.py:54-140).  Weights are f32; activations f32 or bf16 per argument.
+ * ------------------------------------------------------------------------------------------- */
+/* out[r, :] = x[r, :] * inverse[r] * weight, inverse[r] (f32) = 1 / sqrt(mean(x[r, :]^2) + eps).  Replaces `rms_norm` (lm_rms). */
+int qmoe_rms_norm(uint64_t x, int32_t x_dtype, uint64_t weight, uint64_t out, int32_t out_dtype, uint64_t inverse,
+                  int64_t rows, int64_t width, double eps, uint64_t stream);
+/* dx (dtype of x) and d_weight (f32 [width], overwritten; summed over rows in a fixed order).  `partials`: f32 scratch of
+ * qmoe_rms_norm_partials(rows, width) elements.  Replaces `rms_norm_backward` (lm_rms_dx, lm_rms_dw). */
+int64_t qmoe_rms_norm_partials(int64_t rows, int64_t width);
+int qmoe_rms_norm_backward(uint64_t gradient, int32_t g_dtype, uint64_t x, int32_t x_dtype, uint64_t weight,
+                           uint64_t inverse, uint64_t dx, uint64_t d_weight, uint64_t partials, int64_t rows,
+                           int64_t width, uint64_t stream);
+/* Rotary position embedding of [batch, time, heads, dim]: pairs (2 i, 2 i + 1) turned by (offset + t) theta^(-2 i / dim),
+ * the other way round with inverse != 0 (its own backward).  Replaces `rope` (lm_rope). */
+int qmoe_rope(uint64_t values, uint64_t out, int32_t dtype, int64_t batch, int64_t time, int32_t heads, int32_t dim,
+              double theta, int32_t offset, int32_t inverse, uint64_t stream);
+/* out[i, :] = weight[ids[i], :] (ids i64; an id outside [0, vocab) gives a zero row).  Replaces `embedding` (lm_embedding). */
+int qmoe_embedding(uint64_t weight, uint64_t ids, uint64_t out, int32_t out_dtype, int64_t count, int64_t width,
+                   int64_t vocab, uint64_t stream);
+/* d_weight[tokens[s], :] += sum of gradient[p, :] over positions[starts[s] .. starts[s + 1]), in that order (i64 tables made
+ * on the host as upstream makes them: distinct tokens ascending, each with its positions ascending).  d_weight f32
+ * [vocab, width] is added to: zero it first for upstream's `embedding_backward` (lm_embedding_backward). */
+int qmoe_embedding_backward(uint64_t gradient, int32_t g_dtype, uint64_t tokens, uint64_t starts, uint64_t positions,
+                            uint64_t d_weight, int64_t segments, int64_t count, int64_t width, int64_t vocab,
+                            uint64_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Causal self-attention with grouped key/value heads (the other half of a decoder block):
  *     out[b, t, h, :] = sum_{s <= t} softmax_s(q[b, t, h, :] . k[b, s, h / (heads / kv_heads), :] / sqrt(dim)) v[b, s, ..., :]
  * and its backward.  Replaces `attention` / `attention_backward` (src/qutai/lm/layers.py:119-130, launchers

@@ -357,6 +357,39 @@ def head_loss_backward(ctx, gradient=1.0):
 
 
 # --------------------------------------------------------------------------------------
+# rotary position embedding, token embedding
+# --------------------------------------------------------------------------------------
+def rope(values, heads, theta, offset=0, inverse=False):
+    """``rope`` of the CPU backend, src/qutai/backends/cpu_lm.py:125-138: in every head of ``values``
+    [batch, time, heads * dim] the pair ``(2 i, 2 i + 1)`` is turned by ``(offset + t) theta ** (-2 i / dim)``
+    (the other way round with ``inverse``, which is the backward)."""
+    values = np.asarray(values, dtype=np.float64)
+    batch, time, features = values.shape
+    dim = features // heads
+    x = values.reshape(batch, time, heads, dim // 2, 2)
+    angle = (offset + np.arange(time))[:, None] * theta ** (-np.arange(0, dim, 2) / dim)[None, :]
+    if inverse:
+        angle = -angle
+    c, s = np.cos(angle)[None, :, None, :], np.sin(angle)[None, :, None, :]
+    out = np.stack([x[..., 0] * c - x[..., 1] * s, x[..., 0] * s + x[..., 1] * c], axis=-1)
+    return out.reshape(batch, time, features)
+
+
+def embedding(weight, ids):
+    """Rows ``ids`` of ``weight`` (src/qutai/backends/cpu_lm.py:54-58)."""
+    return np.asarray(weight, dtype=np.float64)[np.asarray(ids, dtype=np.int64)]
+
+
+def embedding_backward(gradient, ids, count):
+    """Row ``token`` = the sum of the gradient rows of the positions that held it
+    (src/qutai/backends/cpu_lm.py:61-66)."""
+    gradient = np.asarray(gradient, dtype=np.float64)
+    result = np.zeros((count, gradient.shape[-1]))
+    np.add.at(result, np.asarray(ids, dtype=np.int64), gradient.reshape(-1, gradient.shape[-1]))
+    return result
+
+
+# --------------------------------------------------------------------------------------
 # causal self-attention with grouped key/value heads
 # --------------------------------------------------------------------------------------
 def attention_forward(q, k, v, heads, kv_heads):

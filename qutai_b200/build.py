@@ -15,7 +15,7 @@ PACKAGE_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PACKAGE_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PACKAGE_DIR), "include")
 LIBRARY = os.path.join(PACKAGE_DIR, "libqutai_moe.so")
-SOURCES = ("runtime.cu", "routing.cu", "permute.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "router.cu", "layer.cu", "ep.cu", "optim.cu", "norm.cu", "head.cu", "attention.cu")
+SOURCES = ("runtime.cu", "routing.cu", "permute.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "router.cu", "layer.cu", "ep.cu", "optim.cu", "norm.cu", "head.cu", "attention.cu", "lm_ops.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 

@@ -247,3 +247,99 @@ def combine_backward(gradient, outputs, weights, route, width):
         start, count = _expert_rows(route, expert)
         grads.append(dy.view(start * width, count * width))
     return (*grads, dw)
+
+
+# ------------------------------------------------------------------------------------------------
+# the operations around attention and the feed-forward half of a block
+# ------------------------------------------------------------------------------------------------
+def _acc_dtype(dtype):
+    """Upstream's accumulation dtype (src/qutai/backends/cuda_lm.py:9-10): bfloat16 activations are paired with
+    float32 weights, statistics and norm outputs."""
+    return "float32" if dtype == "bfloat16" else dtype
+
+
+def embedding(weight, ids, width, *, out_dtype=None):
+    """Rows ``ids`` of the float32 table ``weight`` (src/qutai/backends/cuda_lm.py:77-93)."""
+    dtype = out_dtype or weight.dtype
+    if _acc_dtype(dtype) != weight.dtype or weight.dtype != "float32":
+        raise ValueError("the embedding table must be float32 and the output float32 or bfloat16")
+    ids = list(ids)
+    identifiers = DeviceStorage.from_values(ids, "int64")
+    result = DeviceStorage(len(ids) * width, dtype)
+    if ids:
+        lib.call("qmoe_embedding", weight.ptr, identifiers.ptr, result.ptr, _code(dtype), len(ids), width, weight.size // width, 0)
+    return result
+
+
+def embedding_backward(gradient, ids, count, width):
+    """Gradient of the table, ``[count, width]`` float32: row ``token`` is the sum of the gradient rows of the
+    positions that held it, added in ascending position order (src/qutai/backends/cuda_lm.py:96-123 builds the same
+    three tables on the host)."""
+    groups = {}
+    for row, token in enumerate(ids):
+        groups.setdefault(token, []).append(row)
+    tokens = sorted(groups)
+    starts, positions = [0], []
+    for token in tokens:
+        positions.extend(groups[token])
+        starts.append(len(positions))
+    result = DeviceStorage.zeros(count * width, _acc_dtype(gradient.dtype))
+    if tokens:
+        tables = [DeviceStorage.from_values(values, "int64") for values in (tokens, starts, positions)]
+        lib.call("qmoe_embedding_backward", gradient.ptr, _code(gradient.dtype), tables[0].ptr, tables[1].ptr, tables[2].ptr,
+                 result.ptr, len(tokens), len(positions), width, count, 0)
+    return result
+
+
+def rms_norm(values, weight, width, eps):
+    """``(out, inverse)``, both in the accumulation dtype (src/qutai/backends/cuda_lm.py:126-145)."""
+    rows = values.size // width
+    out = DeviceStorage(values.size, _acc_dtype(values.dtype))
+    inverse = DeviceStorage(rows, "float32")
+    lib.call("qmoe_rms_norm", values.ptr, _code(values.dtype), weight.ptr, out.ptr, _code(out.dtype), inverse.ptr, rows, width,
+             float(eps), 0)
+    return out, inverse
+
+
+def rms_norm_backward(gradient, values, weight, inverse, width):
+    """``(dx, dw)``: ``dx`` in the dtype of ``values``, ``dw`` float32 (src/qutai/backends/cuda_lm.py:148-177)."""
+    rows = inverse.size
+    dx = DeviceStorage(values.size, values.dtype)
+    dw = DeviceStorage(width, "float32")
+    partials = DeviceStorage(lib.load().qmoe_rms_norm_partials(rows, width), "float32")
+    lib.call("qmoe_rms_norm_backward", gradient.ptr, _code(gradient.dtype), values.ptr, _code(values.dtype), weight.ptr,
+             inverse.ptr, dx.ptr, dw.ptr, partials.ptr, rows, width, 0)
+    return dx, dw
+
+
+def rope(values, batch, time, heads, dim, theta, offset=0, inverse=False):
+    """Rotary position embedding (src/qutai/backends/cuda_lm.py:210-226); ``inverse`` is its backward."""
+    result = DeviceStorage(values.size, values.dtype)
+    lib.call("qmoe_rope", values.ptr, result.ptr, _code(values.dtype), batch, time, heads, dim, float(theta), int(offset),
+             1 if inverse else 0, 0)
+    return result
+
+
+class _View:
+    """A storage seen as a tensor of some shape (what ``qutai_b200.attention`` reads: ``storage`` and ``shape``)."""
+
+    def __init__(self, storage, shape):
+        self.storage, self.shape = storage, shape
+
+
+def attention(q, k, v, batch, time, heads, kv_heads, dim):
+    """``(out, lse)`` of causal attention with grouped key/value heads (src/qutai/backends/cuda_lm.py:229-275):
+    bfloat16 and head width 64 on the tensor cores; anything else raises ``ValueError`` (upstream serves it with
+    its CUDA-core kernel)."""
+    from .attention import attention_forward
+
+    return attention_forward(_View(q, (batch, time, heads * dim)), _View(k, (batch, time, kv_heads * dim)),
+                             _View(v, (batch, time, kv_heads * dim)), heads, kv_heads)
+
+
+def attention_backward(gradient, q, k, v, out, lse, batch, time, heads, kv_heads, dim):
+    """``(dq, dk, dv)`` (src/qutai/backends/cuda_lm.py:278-365)."""
+    from .attention import attention_backward as backward
+
+    return backward(gradient, _View(q, (batch, time, heads * dim)), _View(k, (batch, time, kv_heads * dim)),
+                    _View(v, (batch, time, kv_heads * dim)), out, lse, heads, kv_heads)

@@ -162,3 +162,19 @@ def test_attention_oracle_matches_the_upstream_cpu_backend(path):
     dq, dk, dv = oracle.attention_backward(grad, q, k, v, out, lse, heads, kv_heads)
     for mine, theirs in ((out, g["out"]), (lse, g["lse"]), (dq, g["dq"]), (dk, g["dk"]), (dv, g["dv"])):
         assert np.abs(mine - theirs).max() <= 2e-6 * (1 + np.abs(theirs).max())      # the fixtures are stored in float32
+
+
+def test_small_lm_operations_of_the_oracle_match_the_upstream_cpu_backend():
+    """RMS norm and its backward, the rotary embedding and its inverse, the token embedding and its backward against
+    what the upstream pure-Python CPU backend produced (tests/golden/make_golden_lm_ops.py)."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "lm_ops.npz"))
+    out, inverse = oracle.rms_norm(g["norm_x"], g["norm_w"], float(g["norm_eps"]))
+    dx, dw = oracle.rms_norm_backward(g["norm_g"], g["norm_x"], g["norm_w"], inverse)
+    for mine, theirs in ((out, g["norm_out"]), (inverse, g["norm_inverse"]), (dx, g["norm_dx"]), (dw, g["norm_dw"])):
+        close(mine, theirs)
+    heads, theta, offset = int(g["rope_heads"]), float(g["rope_theta"]), int(g["rope_offset"])
+    close(oracle.rope(g["rope_v"], heads, theta, offset), g["rope_out"])
+    close(oracle.rope(g["rope_v"], heads, theta, offset, inverse=True), g["rope_inverse"])
+    close(oracle.rope(oracle.rope(g["rope_v"], heads, theta, offset), heads, theta, offset, inverse=True), g["rope_v"])
+    close(oracle.embedding(g["emb_table"], g["emb_ids"]), g["emb_out"])
+    close(oracle.embedding_backward(g["emb_grad"], g["emb_ids"], g["emb_table"].shape[0]), g["emb_d_table"])
