@@ -424,6 +424,20 @@ typedef struct qmoe_head {
 int qmoe_head_forward(const qmoe_head_t* head, uint64_t stream);
 /* gradient: f32 [1] on the device, the gradient of whatever follows with respect to the loss; 0 = 1.0 */
 int qmoe_head_backward(const qmoe_head_t* head, uint64_t gradient, uint64_t stream);
+/* The per-chunk functions of the upstream backend table, for hosts that keep its chunked loop
+ * (src/qutai/backends/cuda_lm.py:584-660, src/qutai/lm/layers.py:199-255).  `labels`: i64 targets, one per head row (the
+ * upstream prepared labels); rows [start, start + rows) are the chunk.
+ * qmoe_head_rows: out[i, :] = values[position(start + i), :], or with backward != 0 out[position(start + i), :] += values[i, :]
+ *   (position(r) = (r / (time - 1)) * time + r % (time - 1));
+ * qmoe_head_loss: out[0] (f32) = sum over the chunk's counted rows of log sum exp - picked logit (row_loss: f32 [rows] scratch);
+ * qmoe_head_gradient: logits[r, :] <- gradient[0] / count * (softmax - one_hot), zero for rows that are not counted
+ *   (factor: f32 [1] scratch). */
+int qmoe_head_rows(uint64_t values, uint64_t out, int32_t dtype, int64_t start, int64_t count, int64_t width,
+                   int64_t time, int32_t backward, uint64_t stream);
+int qmoe_head_loss(uint64_t logits, int32_t dtype, uint64_t labels, uint64_t row_loss, uint64_t out, int64_t rows,
+                   int64_t vocab, int64_t start, uint64_t stream);
+int qmoe_head_gradient(uint64_t logits, int32_t dtype, uint64_t labels, uint64_t gradient, uint64_t factor, int64_t count,
+                       int64_t rows, int64_t vocab, int64_t start, uint64_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * The small operations around attention and the feed-forward half of a block, with the upstream launchers' meaning of

@@ -49,8 +49,9 @@ __device__ __forceinline__ float block_sum(float v, float* tmp) {
 
 // Label of head row r: the token that follows position (r mod (time - 1)) of sequence r / (time - 1).  A value
 // outside [0, vocab) is returned as -100 (not counted), so that no label can send a read outside its row.
+// time == 0: `labels` is the flat list of targets (one per head row), as upstream's prepared labels are.
 __device__ __forceinline__ long long label_of(const long long* labels, long long r, int time, long long vocab) {
-    const long long label = labels[(r / (time - 1)) * time + r % (time - 1) + 1];
+    const long long label = time ? labels[(r / (time - 1)) * time + r % (time - 1) + 1] : labels[r];
     return label >= 0 && label < vocab ? label : -100;
 }
 
@@ -93,12 +94,12 @@ __global__ void __launch_bounds__(256) head_rows_kernel(const uint4* __restrict_
     }
 }
 
-// One block per row: row_loss[r] and, in place, the gradient of the mean loss with respect to the row's logits.
+// One block per row: row_loss[r] (when given) and, in place (when write_gradient), factor[0] * (softmax - one_hot).
 // CACHED: the row is read from global memory once and kept in shared memory (in its storage type).
 template <typename T, bool CACHED>
 __global__ void __launch_bounds__(kThreads)
 head_loss_gradient_kernel(T* __restrict__ logits, const long long* __restrict__ labels, const float* __restrict__ factor,
-                          float* __restrict__ row_loss, long long rows, long long vocab, int time) {
+                          float* __restrict__ row_loss, long long rows, long long vocab, int time, int write_gradient) {
     extern __shared__ __align__(16) uint8_t cache_raw[];
     __shared__ float tmp[kWarps];
     T* cache = reinterpret_cast<T*>(cache_raw);
@@ -110,9 +111,11 @@ head_loss_gradient_kernel(T* __restrict__ logits, const long long* __restrict__ 
     const bool vec = vocab % N == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
     const int pieces = vec ? (int)(vocab / N) : 0;
     if (label == -100) {   // not counted: no loss, no gradient
-        if (vec) for (int c = threadIdx.x; c < pieces; c += kThreads) reinterpret_cast<uint4*>(row)[c] = make_uint4(0, 0, 0, 0);
-        else for (long long c = threadIdx.x; c < vocab; c += kThreads) Act<T>::store(row + c, 0.f);
-        if (threadIdx.x == 0) row_loss[r] = 0.f;
+        if (write_gradient) {
+            if (vec) for (int c = threadIdx.x; c < pieces; c += kThreads) reinterpret_cast<uint4*>(row)[c] = make_uint4(0, 0, 0, 0);
+            else for (long long c = threadIdx.x; c < vocab; c += kThreads) Act<T>::store(row + c, 0.f);
+        }
+        if (threadIdx.x == 0 && row_loss) row_loss[r] = 0.f;
         return;
     }
     const T* from = CACHED ? cache : row;
@@ -146,7 +149,8 @@ head_loss_gradient_kernel(T* __restrict__ logits, const long long* __restrict__ 
         for (long long c = threadIdx.x; c < vocab; c += kThreads) total += exp_for<T>(Act<T>::load(from + c) - peak);
     }
     total = block_sum(total, tmp);
-    if (threadIdx.x == 0) row_loss[r] = log_for<T>(total) - (Act<T>::load(from + label) - peak);
+    if (threadIdx.x == 0 && row_loss) row_loss[r] = log_for<T>(total) - (Act<T>::load(from + label) - peak);
+    if (!write_gradient) return;
     __syncthreads();   // the label's logit has been read before anything is overwritten (uncached form)
     const float scale = factor[0], inverse = 1.f / total;
     if (vec) {
@@ -211,22 +215,57 @@ qmoe_route_t one_group(const qmoe_head_t* h) {   // the fields the grouped tenso
 }
 int grid_for(long long n) { const long long blocks = (n + 255) / 256; return (int)(blocks > 8 * 148 ? 8 * 148 : blocks); }
 
+// the loss pass over `rows` rows of logits: row losses (row_loss may be null) and / or the gradient in place
 template <typename T>
-int launch_loss_gradient(const qmoe_head_t* h, long long rows, cudaStream_t stream) {
-    const long long bytes = h->vocab * (long long)sizeof(T);
-    const long long* labels = (const long long*)h->labels;
-    const float* factor = (const float*)h->meta;
+int launch_loss_pass(T* logits, const long long* labels, const float* factor, float* row_loss, long long rows, long long vocab,
+                     int time, int write_gradient, cudaStream_t stream) {
+    const long long bytes = vocab * (long long)sizeof(T);
     if (bytes <= kMaxCachedRowBytes) {
         auto kernel = head_loss_gradient_kernel<T, true>;
         const int smem = (int)((bytes + 15) / 16 * 16);
         QMOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxCachedRowBytes));
-        kernel<<<(unsigned)rows, kThreads, smem, stream>>>((T*)h->logits, labels, factor, (float*)h->row_loss, rows, h->vocab, h->time);
+        kernel<<<(unsigned)rows, kThreads, smem, stream>>>(logits, labels, factor, row_loss, rows, vocab, time, write_gradient);
     } else {
-        head_loss_gradient_kernel<T, false><<<(unsigned)rows, kThreads, 0, stream>>>((T*)h->logits, labels, factor, (float*)h->row_loss,
-                                                                                      rows, h->vocab, h->time);
+        head_loss_gradient_kernel<T, false><<<(unsigned)rows, kThreads, 0, stream>>>(logits, labels, factor, row_loss, rows, vocab, time,
+                                                                                      write_gradient);
     }
     QMOE_LAUNCH_CHECK("head_loss_gradient_kernel");
     return 0;
+}
+template <typename T>
+int launch_loss_gradient(const qmoe_head_t* h, long long rows, cudaStream_t stream) {
+    return launch_loss_pass<T>((T*)h->logits, (const long long*)h->labels, (const float*)h->meta, (float*)h->row_loss, rows, h->vocab,
+                               h->time, 1, stream);
+}
+
+// rows [start, start + count) of the head's inputs: out[i, :] = values[position(start + i), :] (backward == 0) or
+// target[position(start + i), :] += gradient[i, :] (backward != 0); position(r) = (r / (time - 1)) * time + r % (time - 1)
+template <typename T>
+__global__ void __launch_bounds__(256) head_rows_range_kernel(const T* __restrict__ src, T* __restrict__ dst, long long start,
+                                                              long long count, long long width, int time, int backward) {
+    const long long total = count * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long row = start + i / width, at = ((row / (time - 1)) * time + row % (time - 1)) * width + i % width;
+        if (backward) Act<T>::store(dst + at, Act<T>::load(dst + at) + Act<T>::load(src + i));
+        else dst[i] = src[at];
+    }
+}
+// out[0] = scale * sum of values (fixed order); scale = numerator[0] / denominator when numerator is given
+__global__ void __launch_bounds__(1024) head_sum_kernel(const float* __restrict__ values, float* __restrict__ out, long long n) {
+    __shared__ float tmp[32];
+    float mine = 0.f;
+    for (long long r = threadIdx.x; r < n; r += blockDim.x) mine += values[r];
+    mine = warp_sum(mine);
+    if ((threadIdx.x & 31) == 0) tmp[threadIdx.x >> 5] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) total += tmp[i];
+        out[0] = total;
+    }
+}
+__global__ void head_factor_kernel(const float* __restrict__ gradient, float count, float* __restrict__ factor) {
+    factor[0] = gradient[0] / count;
 }
 
 }  // namespace
@@ -323,4 +362,53 @@ extern "C" int qmoe_head_backward(const qmoe_head_t* h, uint64_t gradient, uint6
         }
     }
     return 0;
+}
+
+// ---- the per-chunk functions of upstream's backend table (src/qutai/backends/cuda_lm.py:584-660) -----------------
+extern "C" int qmoe_head_rows(uint64_t values, uint64_t out, int32_t dtype, int64_t start, int64_t count, int64_t width,
+                              int64_t time, int32_t backward, uint64_t stream_) {
+    if (!values || !out) return fail_arg("head_rows: null address");
+    if (start < 0 || count <= 0 || width <= 0 || time < 2) return fail_arg("head_rows: sizes must be positive and time at least 2");
+    if (dtype != QMOE_BF16 && dtype != QMOE_F32) return fail_arg("head_rows: dtype must be QMOE_F32 or QMOE_BF16");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_OTHER, stream);
+    // forward: values = hidden, out = the rows; backward: values = the rows' gradient, out = the hidden gradient added to
+    if (dtype == QMOE_BF16)
+        head_rows_range_kernel<<<grid_for(count * width), 256, 0, stream>>>((const __nv_bfloat16*)values, (__nv_bfloat16*)out, start, count, width,
+                                                                            (int)time, backward);
+    else
+        head_rows_range_kernel<<<grid_for(count * width), 256, 0, stream>>>((const float*)values, (float*)out, start, count, width, (int)time,
+                                                                            backward);
+    QMOE_LAUNCH_CHECK("head_rows_range_kernel");
+    return 0;
+}
+
+extern "C" int qmoe_head_loss(uint64_t logits, int32_t dtype, uint64_t labels, uint64_t row_loss, uint64_t out, int64_t rows,
+                              int64_t vocab, int64_t start, uint64_t stream_) {
+    if (!logits || !labels || !row_loss || !out) return fail_arg("head_loss: null address");
+    if (rows <= 0 || vocab <= 0 || start < 0) return fail_arg("head_loss: sizes must be positive");
+    if (dtype != QMOE_BF16 && dtype != QMOE_F32) return fail_arg("head_loss: dtype must be QMOE_F32 or QMOE_BF16");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_OTHER, stream);
+    const long long* targets = (const long long*)labels + start;
+    if (int rc = dtype == QMOE_BF16 ? launch_loss_pass<__nv_bfloat16>((__nv_bfloat16*)logits, targets, nullptr, (float*)row_loss, rows, vocab, 0, 0, stream)
+                                    : launch_loss_pass<float>((float*)logits, targets, nullptr, (float*)row_loss, rows, vocab, 0, 0, stream))
+        return rc;
+    head_sum_kernel<<<1, 1024, 0, stream>>>((const float*)row_loss, (float*)out, rows);
+    QMOE_LAUNCH_CHECK("head_sum_kernel");
+    return 0;
+}
+
+extern "C" int qmoe_head_gradient(uint64_t logits, int32_t dtype, uint64_t labels, uint64_t gradient, uint64_t factor, int64_t count,
+                                  int64_t rows, int64_t vocab, int64_t start, uint64_t stream_) {
+    if (!logits || !labels || !gradient || !factor) return fail_arg("head_gradient: null address");
+    if (rows <= 0 || vocab <= 0 || start < 0 || count <= 0) return fail_arg("head_gradient: sizes must be positive");
+    if (dtype != QMOE_BF16 && dtype != QMOE_F32) return fail_arg("head_gradient: dtype must be QMOE_F32 or QMOE_BF16");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_OTHER, stream);
+    head_factor_kernel<<<1, 1, 0, stream>>>((const float*)gradient, (float)count, (float*)factor);
+    QMOE_LAUNCH_CHECK("head_factor_kernel");
+    const long long* targets = (const long long*)labels + start;
+    return dtype == QMOE_BF16 ? launch_loss_pass<__nv_bfloat16>((__nv_bfloat16*)logits, targets, (const float*)factor, nullptr, rows, vocab, 0, 1, stream)
+                              : launch_loss_pass<float>((float*)logits, targets, (const float*)factor, nullptr, rows, vocab, 0, 1, stream);
 }

@@ -343,3 +343,43 @@ def attention_backward(gradient, q, k, v, out, lse, batch, time, heads, kv_heads
 
     return backward(gradient, _View(q, (batch, time, heads * dim)), _View(k, (batch, time, kv_heads * dim)),
                     _View(v, (batch, time, kv_heads * dim)), out, lse, heads, kv_heads)
+
+
+# ------------------------------------------------------------------------------------------------
+# the language-model head, chunk by chunk (the fused form is qutai_b200.head)
+# ------------------------------------------------------------------------------------------------
+def head_rows(values, start, count, width, time):
+    """Rows ``start .. start + count`` of the head's inputs: every position but the last of each sequence
+    (src/qutai/backends/cuda_lm.py:584-598)."""
+    out = DeviceStorage(count * width, values.dtype)
+    if count:
+        lib.call("qmoe_head_rows", values.ptr, out.ptr, _code(values.dtype), start, count, width, time, 0, 0)
+    return out
+
+
+def head_rows_backward(target, gradient, start, count, width, time):
+    """``target[position(start + i)] += gradient[i]`` (src/qutai/backends/cuda_lm.py:601-613)."""
+    if count:
+        lib.call("qmoe_head_rows", gradient.ptr, target.ptr, _code(target.dtype), start, count, width, time, 1, 0)
+
+
+def prepare_labels(labels):
+    """The targets as an int64 device storage (src/qutai/backends/cuda_lm.py:616-617)."""
+    return DeviceStorage.from_values(list(labels), "int64")
+
+
+def head_loss(logits, labels, rows, vocab, *, start=0):
+    """One-element float32 storage: the sum over the chunk's counted rows of ``log sum exp - picked logit``
+    (src/qutai/backends/cuda_lm.py:629-643); ``labels`` from ``prepare_labels``."""
+    out = DeviceStorage(1, "float32")
+    scratch = DeviceStorage(rows, "float32")
+    lib.call("qmoe_head_loss", logits.ptr, _code(logits.dtype), labels.ptr, scratch.ptr, out.ptr, rows, vocab, start, 0)
+    return out
+
+
+def head_gradient(logits, labels, rows, vocab, gradient, count, *, start=0):
+    """``logits`` overwritten by ``gradient[0] / count * (softmax - one_hot)``, zero rows where the label is -100
+    (src/qutai/backends/cuda_lm.py:646-660).  Returns ``logits``."""
+    factor = DeviceStorage(1, "float32")
+    lib.call("qmoe_head_gradient", logits.ptr, _code(logits.dtype), labels.ptr, gradient.ptr, factor.ptr, int(count), rows, vocab, start, 0)
+    return logits

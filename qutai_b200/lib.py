@@ -155,6 +155,9 @@ SIGNATURES = {
     "qmoe_block_backward": (c_int, [POINTER(Block), _U]),
     "qmoe_head_forward": (c_int, [POINTER(Head), _U]),
     "qmoe_head_backward": (c_int, [POINTER(Head), _U, _U]),
+    "qmoe_head_rows": (c_int, [_U, _U, _I32, _I64, _I64, _I64, _I64, _I32, _U]),
+    "qmoe_head_loss": (c_int, [_U, _I32, _U, _U, _U, _I64, _I64, _I64, _U]),
+    "qmoe_head_gradient": (c_int, [_U, _I32, _U, _U, _U, _I64, _I64, _I64, _I64, _U]),
     "qmoe_rms_norm": (c_int, [_U, _I32, _U, _U, _I32, _U, _I64, _I64, c_double, _U]),
     "qmoe_rms_norm_partials": (c_int64, [_I64, _I64]),
     "qmoe_rms_norm_backward": (c_int, [_U, _I32, _U, _I32, _U, _U, _U, _U, _U, _I64, _I64, _U]),

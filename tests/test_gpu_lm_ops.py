@@ -127,3 +127,50 @@ def test_attention_of_the_function_table_has_upstreams_signature():
         assert oracle.max_rel_err(to_host(got, shape), expected) <= BF16_TOL
     with pytest.raises(ValueError):
         cuda_lm.attention(qs, ks, vs, batch, time, heads * 2, kv_heads * 2, dim // 2)      # head width 32
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_chunked_head_loop_over_the_function_table_reproduces_the_upstream_loss(dtype):
+    """A host that keeps upstream's chunk loop (src/qutai/lm/layers.py:199-255: head_rows, gemm, head_loss and, in
+    the backward, head_gradient, two more gemms, head_rows_backward) and points every call at this table gets the
+    fixture's loss and gradients (float32), or the oracle's on bf16 values."""
+    from gpu_util import to_device, to_host
+    from qutai_b200 import cuda_lm
+
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "head_mid.npz"))
+    hidden, weight, labels = g["hidden"], g["weight"], g["labels"]
+    if dtype == "bfloat16":
+        hidden, weight = oracle.round_bf16(hidden), oracle.round_bf16(weight)
+    batch, time, width = hidden.shape
+    vocab, chunk = weight.shape[0], 7
+    targets = labels[:, 1:].reshape(-1).tolist()
+    count = max(1, sum(t != -100 for t in targets))
+    hs, ws = to_device(hidden, dtype), to_device(weight, dtype)
+    prepared = cuda_lm.prepare_labels(targets)
+    total = to_device(np.zeros(1), "float32")
+    for start in range(0, len(targets), chunk):
+        rows = min(chunk, len(targets) - start)
+        inputs = cuda_lm.head_rows(hs, start, rows, width, time)
+        logits = cuda_lm.gemm(inputs, ws, rows, width, vocab, transpose_right=True, out_dtype=dtype)
+        cuda_lm.add_into(total, cuda_lm.head_loss(logits, prepared, rows, vocab, start=start))
+    loss = to_host(total)[0] / count
+    incoming = to_device(np.array([float(g["gradient"])]), "float32")
+    dx = to_device(np.zeros(hidden.size), dtype)
+    dw = to_device(np.zeros(weight.size), "float32")
+    for start in range(0, len(targets), chunk):
+        rows = min(chunk, len(targets) - start)
+        inputs = cuda_lm.head_rows(hs, start, rows, width, time)
+        logits = cuda_lm.gemm(inputs, ws, rows, width, vocab, transpose_right=True, out_dtype=dtype)
+        cuda_lm.head_gradient(logits, prepared, rows, vocab, incoming, count, start=start)
+        cuda_lm.head_rows_backward(dx, cuda_lm.gemm(logits, ws, rows, vocab, width, out_dtype=dtype), start, rows, width, time)
+        cuda_lm.gemm(logits, inputs, vocab, rows, width, transpose_left=True, out_dtype="float32", out=dw, accumulate=True)
+    got_dx, got_dw = to_host(dx, hidden.shape), to_host(dw, weight.shape)
+    if dtype == "float32":
+        assert abs(loss - float(g["loss"])) <= FP32_ELEMENT_TOL * (1 + abs(float(g["loss"])))
+        near(got_dx, g["d_hidden"])
+        near(got_dw, g["d_weight"])
+    else:
+        want_loss, ctx = oracle.head_loss_forward(hidden, weight, labels)
+        want_dx, want_dw, _ = oracle.head_loss_backward(ctx, float(g["gradient"]))
+        assert abs(loss - want_loss) <= BF16_TOL * max(1.0, abs(want_loss))
+        assert oracle.max_rel_err(got_dx, want_dx) <= BF16_TOL and oracle.max_rel_err(got_dw, want_dw) <= BF16_TOL
