@@ -117,7 +117,8 @@ enum {
     QMOE_VARIANT_SINGLE_CTA_GEMM = 0,   /* expert GEMMs with one CTA per 128 x 256 tile instead of a CTA pair per 256 x 256 */
     QMOE_VARIANT_WGRAD_PER_PRODUCT = 1, /* one launch per weight-gradient product instead of one for all three */
     QMOE_VARIANT_NARROW_SCATTER = 2,    /* 64-byte instead of 256-byte row pieces in the peer-memory scatter epilogues */
-    QMOE_VARIANT_COUNT = 3
+    QMOE_VARIANT_PLAIN_GEMM_ON_CUDA_CORES = 3, /* qmoe_gemm never takes the tensor-core kernels */
+    QMOE_VARIANT_COUNT = 4
 };
 int qmoe_test_select_variant(int32_t which, int32_t value);
 
@@ -283,7 +284,11 @@ int qmoe_expert_backward_parts(const qmoe_route_t* route, const qmoe_experts_t* 
 
 /* Plain (single-group) product C[M, N] = op(A) op(B) with the upstream dispatcher's meaning of
  * the arguments (src/qutai/backends/cuda.py:305-362): A is [M, K] ([K, M] when transpose_a),
- * B is [K, N] ([N, K] when transpose_b); dtypes per operand; accumulate adds into C. */
+ * B is [K, N] ([N, K] when transpose_b); dtypes per operand; accumulate adds into C.  Like upstream's
+ * dispatcher (:346-355) it picks a kernel by shape and dtype: bf16 x bf16 without accumulate runs on the
+ * tcgen05 kernels when the sizes are multiples of 8 and the addresses of 16 bytes — A . B^T and A . B with a
+ * bf16 result and M a multiple of 128, A^T . B with an fp32 result (a weight gradient); everything else on
+ * the CUDA cores. */
 int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtype, uint64_t c, int32_t c_dtype,
               int64_t m, int64_t k, int64_t n, int32_t transpose_a, int32_t transpose_b,
               int32_t accumulate, uint64_t stream);

@@ -1,5 +1,7 @@
 // Expert FFN forward/backward (engine selection between the tcgen05 kernels and the CUDA-core
 // kernels), the single-group GEMM of the host function table, and the whole-layer entry points.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace qmoe {
@@ -156,6 +158,40 @@ extern "C" int qmoe_expert_backward(const qmoe_route_t* r, const qmoe_experts_t*
                                       QMOE_BWD_ACTIVATIONS | QMOE_BWD_WEIGHTS, stream);
 }
 
+// ---- plain products on the tensor cores: the grouped kernels with ONE group --------------------------------------
+namespace qmoe {
+namespace {
+constexpr int kGroupSlots = 256;                 // products in flight at once that may each need a table of their own
+__device__ int g_group_tables[kGroupSlots * 4];  // per slot: offsets {0, rows}, counts {rows}
+__global__ void fill_group_kernel(int* table, int rows) { table[0] = 0; table[1] = rows; table[2] = rows; table[3] = 0; }
+
+// the one-group route of a product with `rows` rows (nullptr and an error recorded when the table cannot be reached)
+int one_group_route(qmoe_route_t* r, long long rows, cudaStream_t stream) {
+    static std::atomic<unsigned> next{0};
+    static int* base[64] = {nullptr};
+    int dev = 0;
+    QMOE_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail_arg("gemm: device index out of range");
+    if (!base[dev]) {
+        void* address = nullptr;
+        QMOE_CUDA(cudaGetSymbolAddress(&address, g_group_tables));
+        base[dev] = (int*)address;
+    }
+    int* table = base[dev] + 4 * (next.fetch_add(1, std::memory_order_relaxed) % kGroupSlots);
+    fill_group_kernel<<<1, 1, 0, stream>>>(table, (int)rows);
+    QMOE_LAUNCH_CHECK("fill_group_kernel");
+    *r = qmoe_route_t{};
+    r->rows_bound = rows;
+    r->offsets = (uint64_t)table;
+    r->counts = (uint64_t)(table + 2);
+    return 0;
+}
+}  // namespace
+}  // namespace qmoe
+
+// Plain product.  bf16 x bf16 in the three forms a linear layer needs goes to the tcgen05 kernels (A [M, K] . B[N, K]^T and
+// A [M, K] . B [K, N] with bf16 results and M a multiple of 128, the rows a tile writes; A [K, M]^T . B [K, N] with fp32
+// results: a weight gradient); everything else, and every accumulating call, to the CUDA-core kernel.
 extern "C" int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtype, uint64_t c, int32_t c_dtype, int64_t m,
                          int64_t k, int64_t n, int32_t transpose_a, int32_t transpose_b, int32_t accumulate, uint64_t stream_) {
     if (!a || !b || !c) return fail_arg("gemm: null address");
@@ -164,6 +200,20 @@ extern "C" int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtyp
         if (dt != QMOE_F32 && dt != QMOE_BF16) return fail_arg("gemm: dtype must be QMOE_F32 or QMOE_BF16");
     if (c == a || c == b) return fail_arg("gemm: the output must not alias an input");
     cudaStream_t stream = (cudaStream_t)stream_;
+    const bool aligned = !((a | b | c) & 15u) && k % 8 == 0 && n % 8 == 0 && m % 8 == 0 && m < (1ll << 30) && k < (1ll << 30) && n < (1ll << 30);
+    if (a_dtype == QMOE_BF16 && b_dtype == QMOE_BF16 && aligned && !accumulate && !kernel_variant(QMOE_VARIANT_PLAIN_GEMM_ON_CUDA_CORES)) {
+        qmoe_route_t r;
+        if (!transpose_a && c_dtype == QMOE_BF16 && m % kRowPad == 0) {
+            TimedScope timed(KC_EXPERT_GEMM, stream);
+            if (int rc = one_group_route(&r, m, stream)) return rc;
+            return transpose_b ? tc_rows_nt(&r, 1, a, b, c, k, n, stream, nullptr) : tc_rows_nn(&r, 1, a, b, 0, 0, c, k, n, stream, nullptr);
+        }
+        if (transpose_a && !transpose_b && c_dtype == QMOE_F32) {
+            TimedScope timed(KC_WGRAD_GEMM, stream);
+            if (int rc = one_group_route(&r, k, stream)) return rc;     // the contraction runs over the k rows of both operands
+            return tc_wgrad1(&r, a, b, c, m, n, stream);
+        }
+    }
     TimedScope timed(KC_OTHER, stream);
     SimtGemmArgs g = {};
     g.A = (const void*)a; g.B = (const void*)b; g.C = (void*)c;

@@ -15,7 +15,7 @@ from ctypes import (POINTER, Structure, byref, c_char_p, c_double, c_float, c_in
 
 QMOE_F32, QMOE_BF16 = 0, 1
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TCGEN05 = 0, 1, 2
-VARIANT_SINGLE_CTA_GEMM, VARIANT_WGRAD_PER_PRODUCT, VARIANT_NARROW_SCATTER = 0, 1, 2
+VARIANT_SINGLE_CTA_GEMM, VARIANT_WGRAD_PER_PRODUCT, VARIANT_NARROW_SCATTER, VARIANT_PLAIN_GEMM_ON_CUDA_CORES = 0, 1, 2, 3
 ROW_PAD, MAX_EXPERTS, MAX_TOP_K = 128, 256, 8
 DTYPE_CODES = {"float32": QMOE_F32, "bfloat16": QMOE_BF16}
 ITEM_BYTES = {"float32": 4, "bfloat16": 2, "int32": 4, "int64": 8, "float64": 8}

@@ -35,8 +35,8 @@ def kernel_variant():
 
     chosen = []
 
-    def select(which):
-        lib.call("qmoe_test_select_variant", which, 1)
+    def select(which, value=1):
+        lib.call("qmoe_test_select_variant", which, value)
         chosen.append(which)
 
     yield select

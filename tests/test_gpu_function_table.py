@@ -168,3 +168,39 @@ def test_upstream_style_expert_loop_matches_golden_layer():
     scattered = to_host(b.route_gather_backward(to_device(grad_rows, "float32"), route, e0, d), (T, d))
     cpu_route = oracle.routing(to_host(scores, (T, E)), k)
     assert np.array_equal(scattered, oracle.route_gather_backward(grad_rows, cpu_route, e0))
+
+
+@pytest.mark.parametrize("rows,inner,cols", [(128, 64, 72), (384, 1024, 264), (1024, 264, 1024)])
+def test_gemm_takes_the_tensor_cores_for_the_three_products_of_a_linear_layer(rows, inner, cols, kernel_variant):
+    """bf16 x bf16 in the forms of a linear layer's forward (x W^T), input gradient (g W) and weight gradient
+    (g^T x, float32) run on the tcgen05 kernels when the sizes allow, and give what the CUDA-core kernel gives."""
+    from gpu_util import to_device, to_host
+    from qutai_b200 import cuda_lm, lib
+
+    rng = np.random.default_rng(rows + cols)
+    x, w = oracle.round_bf16(rng.standard_normal((rows, inner))), oracle.round_bf16(rng.standard_normal((cols, inner)) * 0.1)
+    g = oracle.round_bf16(rng.standard_normal((rows, cols)))
+    xs, ws, gs = to_device(x, "bfloat16"), to_device(w, "bfloat16"), to_device(g, "bfloat16")
+    count = lib.load().qmoe_tensor_core_launch_count
+
+    def products():
+        y = cuda_lm.gemm(xs, ws, rows, inner, cols, transpose_right=True, out_dtype="bfloat16")
+        dx = cuda_lm.gemm(gs, ws, rows, cols, inner, out_dtype="bfloat16")
+        dw = cuda_lm.gemm(gs, xs, cols, rows, inner, transpose_left=True, out_dtype="float32")
+        return to_host(y, (rows, cols)), to_host(dx, (rows, inner)), to_host(dw, (cols, inner))
+
+    before = count()
+    fast = products()
+    assert count() - before == 3
+    kernel_variant(lib.VARIANT_PLAIN_GEMM_ON_CUDA_CORES)
+    before = count()
+    slow = products()
+    assert count() == before
+    for got, reference, exact in zip(fast, slow, (x @ w.T, g @ w, g.T @ x)):
+        assert oracle.max_rel_err(got, exact) <= 1e-2
+        assert oracle.max_rel_err(got, reference) <= 8e-3          # both round fp32 sums of the same products to bf16 (or keep fp32)
+    # a row count that is not a multiple of 128 stays on the CUDA cores (a tile of the tensor-core kernel writes 128 rows)
+    kernel_variant(lib.VARIANT_PLAIN_GEMM_ON_CUDA_CORES, 0)
+    before = count()
+    cuda_lm.gemm(to_device(x[:100], "bfloat16"), ws, 100, inner, cols, transpose_right=True, out_dtype="bfloat16")
+    assert count() == before
