@@ -685,6 +685,8 @@ def run_gpu(args, w, rank, world):
         line["lm_head"] = lm_head(args.steps, peaks, torch, np)
     if world == 1 and not forward_only and not args.no_attention:
         line["attention"] = attention_block(args.steps, peaks, torch, np)
+    if world == 1 and not forward_only and not args.no_decoder:
+        line["decoder_step"] = decoder_step(torch, np)
     if world == 1 and not forward_only and not args.no_library_gemm:
         here = library_gemm_here(torch)
         line["roofline"]["library_gemm_on_this_gpu"] = here
@@ -696,7 +698,8 @@ def run_gpu(args, w, rank, world):
         line["decode"] = decode_latency(layer, w, rank, world, torch, dist, device, Tensor, wrap, peaks)
     ok = (bool(check["ok"]) and bool(line.get("block_ffn", {}).get("check", {}).get("ok", True))
           and bool(line.get("lm_head", {}).get("check", {}).get("ok", True))
-          and bool(line.get("attention", {}).get("check", {}).get("ok", True)))
+          and bool(line.get("attention", {}).get("check", {}).get("ok", True))
+          and bool(line.get("decoder_step", {}).get("check", {}).get("ok", True)))
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -836,6 +839,53 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
                 unfused_extra_bytes_per_step=2 * elements * (6 + 6), fused_extra_bytes_per_step=2 * elements * (2 + 2),
                 check=dict(ok=bool(out_err <= BF16_TOL and dx_err <= BF16_TOL), out=out_err, dx=dx_err, tolerance=BF16_TOL,
                            sampled_tokens=int(sample.numel())))
+
+
+def decoder_step(torch, np, steps=3):
+    """One rank's share of the full decoder training step (12 blocks, d_model 1024, 16 heads in 4 key/value groups,
+    16 experts top-2 of hidden width 2048, vocabulary 32000; 4 sequences of 2048 tokens, Zipf(1.1) ids): loss,
+    backward and the AdamW step of ``qutai_b200.decoder.Decoder``, all experts on this GPU."""
+    import gc
+
+    from qutai_b200.decoder import Config, Decoder
+    from qutai_b200.optim import AdamW
+    from qutai_b200.storage import empty_cache
+
+    gc.collect()
+    empty_cache()
+    config = Config(vocab_size=32000, d_model=1024, n_heads=16, n_kv_heads=4, n_layers=12, n_experts=16, top_k=2, d_expert=2048)
+    batch, time_ = 4, 2048
+    stream = torch.cuda.current_stream().cuda_stream
+    model = Decoder(config, seed=7, stream=stream)
+    optimizer = AdamW(model.parameters(), learning_rate=1e-4, stream=stream)
+    rng = np.random.default_rng(31)
+    tokens = np.minimum(rng.zipf(1.1, size=(batch, time_)) - 1, config.vocab_size - 1).tolist()
+
+    def step():
+        model.zero_grad()
+        loss = model.loss(tokens)
+        model.backward()
+        optimizer.step()
+        return loss
+
+    losses = [float(step().storage.tolist(stream)[0]) for _ in range(2)]
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        loss = step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / steps
+    losses.append(float(loss.storage.tolist(stream)[0]))
+    parameters = sum(p.storage.size for p in model.parameters())
+    del model, optimizer
+    gc.collect()
+    empty_cache()
+    return dict(ms_per_step=ms, tokens_per_s=batch * time_ / (ms * 1e-3), tokens=batch * time_, parameters=parameters,
+                config="12 blocks, d_model 1024, 16 heads / 4 kv heads, 16 experts top-2 hidden 2048, vocab 32000, 4 x 2048 tokens, bf16 activations, fp32 parameters",
+                what="loss + backward + AdamW of qutai_b200.decoder.Decoder (all experts local)",
+                losses=losses, check=dict(ok=bool(np.isfinite(losses).all() and losses[-1] < losses[0]), how="finite, and falling over the steps on the same batch"))
 
 
 def attention_block(steps, peaks, torch, np):
@@ -1103,6 +1153,7 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-decode", action="store_true", help="leave the decode-shaped latency block out of the c3 line")
     parser.add_argument("--no-library-gemm", action="store_true", help="do not time the library bf16 product on this GPU")
+    parser.add_argument("--no-decoder", action="store_true", help="leave the whole-decoder training step out of the line")
     parser.add_argument("--no-attention", action="store_true", help="leave the attention block out of the line")
     parser.add_argument("--no-head", action="store_true", help="leave the language-model head out of the line")
     parser.add_argument("--no-block", action="store_true", help="leave the fused norm + layer + residual block out of the line")
