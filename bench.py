@@ -857,9 +857,10 @@ def decoder_step(torch, np, steps=3):
     batch, time_ = 4, 2048
     stream = torch.cuda.current_stream().cuda_stream
     model = Decoder(config, seed=7, stream=stream)
-    optimizer = AdamW(model.parameters(), learning_rate=1e-4, stream=stream)
     rng = np.random.default_rng(31)
     tokens = np.minimum(rng.zipf(1.1, size=(batch, time_)) - 1, config.vocab_size - 1).tolist()
+    model.loss(tokens)            # a first forward makes the bf16 operand copies that the optimizer then keeps current
+    optimizer = AdamW(model.parameters(), learning_rate=1e-4, shadows=model.operand_shadows(), stream=stream)
 
     def step():
         model.zero_grad()
@@ -879,12 +880,25 @@ def decoder_step(torch, np, steps=3):
     ms = begin.elapsed_time(end) / steps
     losses.append(float(loss.storage.tolist(stream)[0]))
     parameters = sum(p.storage.size for p in model.parameters())
+    # where the step's device time goes, by kernel class (a pass of its own: the events sit between the launches)
+    from qutai_b200 import lib
+
+    lib.timing(True)
+    step()
+    torch.cuda.synchronize()
+    classes = {name: round(value[0], 3) for name, value in lib.timing_read().items() if value[1]}
+    lib.timing(False)
+    host_begin = time.time()
+    step()
+    host_ms = (time.time() - host_begin) * 1e3          # the host's share: issuing one step without waiting for it
+    torch.cuda.synchronize()
     del model, optimizer
     gc.collect()
     empty_cache()
     return dict(ms_per_step=ms, tokens_per_s=batch * time_ / (ms * 1e-3), tokens=batch * time_, parameters=parameters,
                 config="12 blocks, d_model 1024, 16 heads / 4 kv heads, 16 experts top-2 hidden 2048, vocab 32000, 4 x 2048 tokens, bf16 activations, fp32 parameters",
                 what="loss + backward + AdamW of qutai_b200.decoder.Decoder (all experts local)",
+                class_ms=classes, host_issue_ms=host_ms,
                 losses=losses, check=dict(ok=bool(np.isfinite(losses).all() and losses[-1] < losses[0]), how="finite, and falling over the steps on the same batch"))
 
 

@@ -235,6 +235,19 @@ class Decoder:
         for parameter in self.parameters():
             parameter.grad = None
 
+    def operand_shadows(self):
+        """``{parameter: bf16 storage}`` of the tensor-core operand copies (expert weights, projections, the tied table)
+        once a forward has made them: an ``AdamW(shadows=...)`` that writes the rounded weights there keeps them
+        current, and no forward after a step converts anything."""
+        shadows = {}
+        for block in self.blocks:
+            shadows.update(block.ffn.operand_shadows())
+            for layer in (block.attn.q, block.attn.k, block.attn.v, block.attn.out):
+                shadows[layer.weight] = layer.operand()
+        if self.head._operand is not None:
+            shadows[self.embedding.weight] = self.head._operand
+        return shadows
+
     # -- forward ------------------------------------------------------------------------------------------------
     def loss(self, tokens, labels=None):
         """``tokens`` (and ``labels``, default the tokens): nested sequences [batch][time] of token ids (-100 in the

@@ -60,17 +60,23 @@ def test_decoder_steps_with_adamw_and_the_loss_falls():
     from gpu_util import to_host
     from qutai_b200.optim import AdamW
 
-    model, named = build()
     tokens, labels = fixture.decoder_tokens()
-    optimizer = AdamW(model.parameters(), learning_rate=3e-3)
-    losses = []
-    for _ in range(6):
-        model.zero_grad()
-        loss = model.loss(tokens, labels)
-        model.backward()
-        optimizer.step()
-        losses.append(float(to_host(loss.storage)[0]))
-    assert losses[-1] < losses[0] - 0.3, losses
+    curves = []
+    for with_shadows in (False, True):
+        model, named = build()
+        if with_shadows:
+            model.loss(tokens, labels)                     # makes the operand copies the optimizer is to keep current
+        optimizer = AdamW(model.parameters(), learning_rate=3e-3, shadows=model.operand_shadows() if with_shadows else None)
+        losses = []
+        for _ in range(6):
+            model.zero_grad()
+            loss = model.loss(tokens, labels)
+            model.backward()
+            optimizer.step()
+            losses.append(float(to_host(loss.storage)[0]))
+        assert losses[-1] < losses[0] - 0.3, losses
+        curves.append(losses)
+    assert curves[0] == curves[1]          # the copies the optimizer writes are the ones a forward would have made
 
 
 def test_decoder_rejects_what_it_does_not_cover():
