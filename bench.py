@@ -685,8 +685,8 @@ def run_gpu(args, w, rank, world):
         line["lm_head"] = lm_head(args.steps, peaks, torch, np)
     if world == 1 and not forward_only and not args.no_attention:
         line["attention"] = attention_block(args.steps, peaks, torch, np)
-    if world == 1 and not forward_only and not args.no_decoder:
-        line["decoder_step"] = decoder_step(torch, np)
+    if not forward_only and not args.no_decoder:
+        line["decoder_step"] = decoder_step(torch, np, rank=rank, world=world, dist=dist, gather=gather, device=device)
     if world == 1 and not forward_only and not args.no_library_gemm:
         here = library_gemm_here(torch)
         line["roofline"]["library_gemm_on_this_gpu"] = here
@@ -841,10 +841,13 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
                            sampled_tokens=int(sample.numel())))
 
 
-def decoder_step(torch, np, steps=3):
+def decoder_step(torch, np, steps=3, rank=0, world=1, dist=None, gather=None, device=None):
     """One rank's share of the full decoder training step (12 blocks, d_model 1024, 16 heads in 4 key/value groups,
     16 experts top-2 of hidden width 2048, vocabulary 32000; 4 sequences of 2048 tokens, Zipf(1.1) ids): loss,
-    backward and the AdamW step of ``qutai_b200.decoder.Decoder``, all experts on this GPU."""
+    backward and the AdamW step of ``qutai_b200.decoder.Decoder``.  One GPU: all experts local.  N GPUs: every rank
+    has 4 sequences of its own (weak scaling, the configuration's 32 at N = 8), the 16 experts of every block are
+    spread over the ranks, the gradients of the replicated parameters are summed over the ranks inside ``backward``;
+    the time is the slowest rank's."""
     import gc
 
     from qutai_b200.decoder import Config, Decoder
@@ -856,8 +859,8 @@ def decoder_step(torch, np, steps=3):
     config = Config(vocab_size=32000, d_model=1024, n_heads=16, n_kv_heads=4, n_layers=12, n_experts=16, top_k=2, d_expert=2048)
     batch, time_ = 4, 2048
     stream = torch.cuda.current_stream().cuda_stream
-    model = Decoder(config, seed=7, stream=stream)
-    rng = np.random.default_rng(31)
+    model = Decoder(config, seed=7, stream=stream, rank=rank, world=world, parallel=dict(gather=gather) if world > 1 else None)
+    rng = np.random.default_rng(31 + rank)
     tokens = np.minimum(rng.zipf(1.1, size=(batch, time_)) - 1, config.vocab_size - 1).tolist()
     model.loss(tokens)            # a first forward makes the bf16 operand copies that the optimizer then keeps current
     optimizer = AdamW(model.parameters(), learning_rate=1e-4, shadows=model.operand_shadows(), stream=stream)
@@ -880,6 +883,18 @@ def decoder_step(torch, np, steps=3):
     ms = begin.elapsed_time(end) / steps
     losses.append(float(loss.storage.tolist(stream)[0]))
     parameters = sum(p.storage.size for p in model.parameters())
+    same_on_every_rank = True
+    if world > 1:
+        slowest = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        ms = float(slowest.item())
+        seen = [None] * world
+        dist.all_gather_object(seen, losses)
+        same_on_every_rank = all(other == seen[0] for other in seen)
+        local = sum(p.storage.size for block in model.blocks for expert in block.ffn.experts for p in expert.parameters())
+        held = torch.tensor([local], dtype=torch.int64, device=device)
+        dist.all_reduce(held)     # the model = one copy of the replicated parameters + every rank's experts
+        parameters = parameters - local + int(held.item())
     # where the step's device time goes, by kernel class (a pass of its own: the events sit between the launches)
     from qutai_b200 import lib
 
@@ -895,11 +910,13 @@ def decoder_step(torch, np, steps=3):
     del model, optimizer
     gc.collect()
     empty_cache()
-    return dict(ms_per_step=ms, tokens_per_s=batch * time_ / (ms * 1e-3), tokens=batch * time_, parameters=parameters,
-                config="12 blocks, d_model 1024, 16 heads / 4 kv heads, 16 experts top-2 hidden 2048, vocab 32000, 4 x 2048 tokens, bf16 activations, fp32 parameters",
-                what="loss + backward + AdamW of qutai_b200.decoder.Decoder (all experts local)",
-                class_ms=classes, host_issue_ms=host_ms,
-                losses=losses, check=dict(ok=bool(np.isfinite(losses).all() and losses[-1] < losses[0]), how="finite, and falling over the steps on the same batch"))
+    return dict(ms_per_step=ms, tokens_per_s=world * batch * time_ / (ms * 1e-3), tokens=world * batch * time_, parameters=parameters,
+                config=f"12 blocks, d_model 1024, 16 heads / 4 kv heads, 16 experts top-2 hidden 2048, vocab 32000, {world} x 4 x 2048 tokens, bf16 activations, fp32 parameters",
+                what="loss + backward + AdamW of qutai_b200.decoder.Decoder"
+                     + (" (all experts local)" if world == 1 else f" on {world} ranks: experts spread over the ranks, replicated gradients summed (NCCL)"),
+                class_ms=classes, host_issue_ms=host_ms, losses=losses,
+                check=dict(ok=bool(np.isfinite(losses).all() and losses[-1] < losses[0] and same_on_every_rank),
+                           how="finite, falling over the steps on the same batch, the same value on every rank"))
 
 
 def attention_block(steps, peaks, torch, np):

@@ -7,7 +7,10 @@ auxiliary loss of the blocks.
 Same constructor fields, parameter names (``named_parameters``) and loss as upstream; forward and backward are
 written out by hand over the fused pieces instead of a general autograd: ``loss(tokens)`` runs the forward and keeps
 what the backward needs, ``backward()`` fills ``parameter.grad`` of every parameter (float32), ready for
-``qutai_b200.optim.AdamW``.  Activations are bfloat16 throughout (the residual stream too: upstream keeps float32
+``qutai_b200.optim.AdamW``.  With ``world > 1`` the decoder is one rank of a data- and expert-parallel job (upstream has
+no such mode): every rank holds its own sequences, the dense parameters are replicated and their gradients summed over
+the ranks, every block's experts are spread over the ranks (``ExpertParallelMoE``), and the loss is the mean over all
+ranks' targets.  Activations are bfloat16 throughout (the residual stream too: upstream keeps float32
 there and hands float32 from its norms to bf16 products), parameters float32 with bf16 operand copies that are
 renewed only when a parameter's storage changed.  Head width 64 only (``qutai_b200.attention``).  Dependency-free.
 """
@@ -19,6 +22,7 @@ from math import sqrt
 
 from . import lib
 from .attention import attention_backward, attention_forward
+from .expert_parallel import ExpertParallelMoE
 from .head import LMHead
 from .layers import MoEFeedForward, RMSNorm, SparseMoE, Tensor
 from .storage import DeviceStorage
@@ -158,15 +162,22 @@ class GQA:
 
 
 class Block:
-    """``x += attn(attn_norm(x)); x += ffn(ffn_norm(x))`` (src/qutai/lm/layers.py:412-449), the second half fused
-    (``MoEFeedForward``)."""
+    """``x += attn(attn_norm(x)); x += ffn(ffn_norm(x))`` (src/qutai/lm/layers.py:412-449).  On one GPU the second half
+    is the fused ``MoEFeedForward``; as a rank of an expert-parallel job it is norm, ``ExpertParallelMoE`` (experts
+    spread over the ranks, rows exchanged over NVLink) and the residual add as three steps."""
 
-    def __init__(self, config, *, seed, stream=0):
+    def __init__(self, config, *, seed, stream=0, rank=0, world=1, parallel=None):
         self.attn_norm = RMSNorm(config.d_model, config.norm_eps, stream=stream)
         self.ffn_norm = RMSNorm(config.d_model, config.norm_eps, stream=stream)
         self.attn = GQA(config, seed=seed, stream=stream)
-        self.ffn = SparseMoE(config, seed=None if seed is None else seed + 4, stream=stream)
-        self.feed_forward = MoEFeedForward(self.ffn_norm, self.ffn)
+        ffn_seed = None if seed is None else seed + 4
+        if world == 1:
+            self.ffn = SparseMoE(config, seed=ffn_seed, stream=stream)
+            self.feed_forward = MoEFeedForward(self.ffn_norm, self.ffn)
+        else:
+            self.ffn = ExpertParallelMoE(config, rank=rank, world=world, seed=ffn_seed, stream=stream, **(parallel or {}))
+            self.feed_forward = None
+        self._aux_gradient_value = config.aux_loss_coef / config.n_layers
         self.width, self.stream = config.d_model, stream
         self._saved = None
 
@@ -178,14 +189,24 @@ class Block:
         normed, inverse = _rms_norm(x, self.attn_norm, rows, self.width, self.stream)
         y, attention_saved = self.attn.forward(normed, batch, time)
         middle = _add(x, y, self.stream)
-        out, aux = self.feed_forward(Tensor(middle, (rows, self.width)))
-        self._saved = (x, inverse, attention_saved)
-        return out.storage, aux
+        if self.feed_forward is not None:
+            out, aux = self.feed_forward(Tensor(middle, (rows, self.width)))
+            self._saved = (x, inverse, attention_saved, None, None)
+            return out.storage, aux
+        normed, ffn_inverse = _rms_norm(middle, self.ffn_norm, rows, self.width, self.stream)
+        y, aux = self.ffn.forward(Tensor(normed, (rows, self.width)))
+        self._saved = (x, inverse, attention_saved, middle, ffn_inverse)
+        return _add(middle, y.storage, self.stream), aux
 
     def backward(self, d_out, d_aux, batch, time):
         rows = batch * time
-        x, inverse, attention_saved = self._saved
-        d_middle = self.feed_forward.backward(Tensor(d_out, (rows, self.width)), d_aux).storage
+        x, inverse, attention_saved, middle, ffn_inverse = self._saved
+        if self.feed_forward is not None:
+            d_middle = self.feed_forward.backward(Tensor(d_out, (rows, self.width)), d_aux).storage
+        else:   # every rank hands the layer the same gradient of the auxiliary loss over all ranks' tokens
+            d_normed = self.ffn.backward(Tensor(d_out, (rows, self.width)), self._aux_gradient_value).storage
+            d_middle = _add(_rms_norm_backward(d_normed, middle, self.ffn_norm, ffn_inverse, rows, self.width, self.stream), d_out,
+                            self.stream)
         d_normed = self.attn.backward(d_middle, attention_saved, batch, time)
         dx = _rms_norm_backward(d_normed, x, self.attn_norm, inverse, rows, self.width, self.stream)
         self._saved = None
@@ -193,9 +214,17 @@ class Block:
 
 
 class Decoder:
-    def __init__(self, config, *, device="cuda", dtype="float32", seed=None, stream=0):
+    def __init__(self, config, *, device="cuda", dtype="float32", seed=None, stream=0, rank=0, world=1, parallel=None):
+        """``rank`` / ``world``: this process's place in a data- and expert-parallel job (the communicator of
+        ``qutai_b200.expert_parallel.init_communicator`` must be up when ``world > 1``); every rank passes the same
+        ``seed``, so the replicated parameters start equal and an expert's weights depend on its number in the model,
+        not on where it lives.  ``parallel``: keyword arguments for every block's ``ExpertParallelMoE``
+        (``transport``, ``placement``, ``gather`` ...)."""
         if device != "cuda" or dtype != "float32":
             raise ValueError("parameters are float32 on device='cuda' (there is no CPU fallback)")
+        if not 0 <= rank < world:
+            raise ValueError("rank must be in [0, world)")
+        self.rank, self.world = rank, world
         if config.ffn_type != "moe":
             raise ValueError("this decoder has mixture-of-experts blocks only")
         if config.d_model % config.n_heads or config.d_model // config.n_heads != 64:
@@ -205,7 +234,8 @@ class Decoder:
         table.fill_normal(0.0, 0.02, 0x5EED if seed is None else seed, stream)
         self.embedding = type("Projection", (), {})()
         self.embedding.weight = Tensor(table, (config.vocab_size, config.d_model), requires_grad=True)
-        self.blocks = tuple(Block(config, seed=None if seed is None else seed + 1 + 100 * i, stream=stream) for i in range(config.n_layers))
+        self.blocks = tuple(Block(config, seed=None if seed is None else seed + 1 + 100 * i, stream=stream, rank=rank, world=world,
+                                  parallel=parallel) for i in range(config.n_layers))
         self.norm = RMSNorm(config.d_model, config.norm_eps, stream=stream)
         self.head = LMHead(stream=stream)
         self.last_lm_loss = self.last_auxiliary_loss = None
@@ -213,20 +243,31 @@ class Decoder:
         one = lambda value: DeviceStorage.from_values([value], "float32", stream)
         self._one_over_layers, self._aux_coef = one(1.0 / config.n_layers), one(config.aux_loss_coef)
         self._aux_gradient = one(config.aux_loss_coef / config.n_layers)     # d total / d (one block's auxiliary loss)
+        self._share = (None, None)     # this rank's share of all ranks' targets: (value, device storage)
 
     # -- parameters -------------------------------------------------------------------------------------------
     def named_parameters(self):
-        """Names and order of upstream's ``Decoder.named_parameters`` (src/qutai/lm/decoder.py:38-80)."""
+        """Names and order of upstream's ``Decoder.named_parameters`` (src/qutai/lm/decoder.py:38-80); as a rank of an
+        expert-parallel job, only the experts this rank holds, under their numbers in the model."""
         result = [("embedding.weight", self.embedding.weight)]
         for i, block in enumerate(self.blocks):
             prefix = f"blocks.{i}."
             result.extend((prefix + name + ".weight", getattr(block, name).weight) for name in ("attn_norm", "ffn_norm"))
             result.extend((prefix + "attn." + name + ".weight", getattr(block.attn, name).weight) for name in ("q", "k", "v", "out"))
             result.append((prefix + "ffn.router.weight", block.ffn.router.weight))
+            if self.world > 1:
+                result.extend(block.ffn.named_expert_parameters(prefix=prefix + "ffn.experts"))
+                continue
             for e, expert in enumerate(block.ffn.experts):
                 result.extend((f"{prefix}ffn.experts.{e}.{name}.weight", getattr(expert, name).weight) for name in ("gate", "up", "down"))
         result.append(("norm.weight", self.norm.weight))
         return result
+
+    def replicated_parameters(self):
+        """The parameters every rank holds a copy of and whose gradients ``backward`` sums over the ranks: everything
+        but the experts (the router's gradient is summed inside its layer)."""
+        skip = {id(p) for block in self.blocks for p in block.ffn.parameters()}
+        return tuple(p for p in self.parameters() if id(p) not in skip)
 
     def parameters(self):
         return tuple(parameter for _, parameter in self.named_parameters())
@@ -249,10 +290,12 @@ class Decoder:
         return shadows
 
     # -- forward ------------------------------------------------------------------------------------------------
-    def loss(self, tokens, labels=None):
+    def loss(self, tokens, labels=None, *, targets_of_all_ranks=None):
         """``tokens`` (and ``labels``, default the tokens): nested sequences [batch][time] of token ids (-100 in the
         labels = no target).  Returns the loss as a float32 device tensor of one element; ``last_lm_loss`` and
-        ``last_auxiliary_loss`` (mean over the blocks) are set like upstream's (src/qutai/lm/decoder.py:143-175)."""
+        ``last_auxiliary_loss`` (mean over the blocks) are set like upstream's (src/qutai/lm/decoder.py:143-175).
+        With ``world > 1`` the sequences are this rank's, and the loss (the same value on every rank) is the mean over
+        the targets of all ranks: ``targets_of_all_ranks`` is their number, by default ``world`` times this rank's."""
         c, stream = self.config, self.stream
         batch, time = len(tokens), len(tokens[0])
         if time < 2 or any(len(row) != time for row in tokens):
@@ -274,6 +317,18 @@ class Decoder:
             auxiliary.append(aux)
         hidden, inverse = _rms_norm(x, self.norm, rows, width, stream)
         lm = self.head.forward(Tensor(hidden, (batch, time, width)), self.embedding.weight, label_ids)
+        share = None
+        if self.world > 1:
+            # mean over all ranks' targets = sum over ranks of (this rank's mean) x (its share of the targets)
+            mine = sum(1 for b in range(batch) for t in range(1, time) if targets[b * time + t] != -100)
+            value = 1.0 / self.world if targets_of_all_ranks is None else max(mine, 1) / float(targets_of_all_ranks)
+            if self._share[0] != value:
+                self._share = (value, DeviceStorage.from_values([value], "float32", stream))
+            share = self._share[1]
+            weighted = DeviceStorage(1, "float32")
+            lib.call("qmoe_scale_f32", lm.storage.ptr, weighted.ptr, 0, share.ptr, 1, 1, stream)
+            lib.call("qmoe_ep_all_reduce_f32", weighted.ptr, 1, stream)
+            lm = Tensor(weighted, ())
         # total = lm + coef * mean(aux): three tiny device operations keep the host out of the step
         total = DeviceStorage.zeros(1, "float32", stream)
         mean_aux = DeviceStorage.zeros(1, "float32", stream)
@@ -284,7 +339,7 @@ class Decoder:
         lib.call("qmoe_scale_f32", mean_aux.ptr, scaled.ptr, 0, self._aux_coef.ptr, 1, 1, stream)
         lib.call("qmoe_add", lm.storage.ptr, scaled.ptr, total.ptr, lib.QMOE_F32, 1, stream)
         self.last_lm_loss, self.last_auxiliary_loss = lm, Tensor(mean_aux, ())
-        self._saved = (flat, batch, time, x, inverse)
+        self._saved = (flat, batch, time, x, inverse, share)
         return Tensor(total, ())
 
     # -- backward -----------------------------------------------------------------------------------------------
@@ -293,9 +348,9 @@ class Decoder:
         if self._saved is None:
             raise RuntimeError("backward needs a loss first")
         c, stream = self.config, self.stream
-        flat, batch, time, x_last, inverse = self._saved
+        flat, batch, time, x_last, inverse, share = self._saved
         rows, width = batch * time, c.d_model
-        d_hidden, d_table = self.head.backward()
+        d_hidden, d_table = self.head.backward(share)
         _accumulate(self.embedding.weight, d_table.storage, stream)
         dx = _rms_norm_backward(d_hidden.storage, x_last, self.norm, inverse, rows, width, stream)
         for block in reversed(self.blocks):
@@ -313,3 +368,13 @@ class Decoder:
         lib.call("qmoe_embedding_backward", dx.ptr, lib.QMOE_BF16, tables[0].ptr, tables[1].ptr, tables[2].ptr,
                  self.embedding.weight.grad.storage.ptr, len(tokens), len(positions), width, c.vocab_size, stream)
         self._saved = None
+        if self.world > 1:
+            self._sum_replicated_gradients(stream)
+
+    def _sum_replicated_gradients(self, stream):
+        """One all-reduce per replicated tensor's gradient of this backward.  A gradient that was already there before
+        (accumulation over several backwards) would be summed twice: the caller reduces once per optimizer step then,
+        by calling ``zero_grad`` between steps as upstream's training loop does."""
+        for parameter in self.replicated_parameters():
+            if parameter.grad is not None:
+                lib.call("qmoe_ep_all_reduce_f32", parameter.grad.storage.ptr, parameter.grad.storage.size, stream)

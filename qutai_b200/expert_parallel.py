@@ -340,6 +340,20 @@ class ExpertParallelMoE:
             yield f"{prefix}.{e}.up.weight", expert.up.weight
             yield f"{prefix}.{e}.down.weight", expert.down.weight
 
+    def operand_shadows(self):
+        """``{parameter: bf16 storage}`` of the tensor-core operand copies of this rank's expert weights, for
+        ``qutai_b200.optim.AdamW(shadows=...)`` (see ``SparseMoE.operand_shadows``)."""
+        work = self._work
+        if work is None or "w_gate" not in work["buf"]:
+            raise RuntimeError("no bfloat16 forward has run yet")
+        buf, h, d = work["buf"], self.d_expert, self.d_model
+        shadows = {}
+        for j, expert in enumerate(self.experts):
+            shadows[expert.gate.weight] = buf["w_gate"].view(j * h * d, h * d)
+            shadows[expert.up.weight] = buf["w_up"].view(j * h * d, h * d)
+            shadows[expert.down.weight] = buf["w_down"].view(j * d * h, d * h)
+        return shadows
+
     def rebalance(self, counts=None, placement=None):
         """Move the expert weights to a new placement: ``placement`` if given, else the load-balanced one for
         the per-expert ``counts`` (default: the counts of the last forward).  Every rank calls it with the same
