@@ -861,7 +861,8 @@ def decoder_step(torch, np, steps=3, rank=0, world=1, dist=None, gather=None, de
     stream = torch.cuda.current_stream().cuda_stream
     model = Decoder(config, seed=7, stream=stream, rank=rank, world=world, parallel=dict(gather=gather) if world > 1 else None)
     rng = np.random.default_rng(31 + rank)
-    tokens = np.minimum(rng.zipf(1.1, size=(batch, time_)) - 1, config.vocab_size - 1).tolist()
+    weights = np.arange(1, config.vocab_size + 1, dtype=np.float64) ** -1.1        # Zipf(1.1) over the vocabulary: P(id) ~ (id + 1)^-1.1
+    tokens = rng.choice(config.vocab_size, size=(batch, time_), p=weights / weights.sum()).tolist()
     model.loss(tokens)            # a first forward makes the bf16 operand copies that the optimizer then keeps current
     optimizer = AdamW(model.parameters(), learning_rate=1e-4, shadows=model.operand_shadows(), stream=stream)
 
@@ -1025,7 +1026,8 @@ def lm_head(steps, peaks, torch, np):
     hidden = torch.randn((batch, time, width), device="cuda", generator=generator).to(torch.bfloat16)
     weight = (torch.randn((vocab, width), device="cuda", generator=generator) * 0.02).to(torch.bfloat16)
     rng = np.random.default_rng(12)
-    labels_host = np.minimum(rng.zipf(1.1, size=(batch, time)) - 1, vocab - 1).astype(np.int64)
+    zipf = np.arange(1, vocab + 1, dtype=np.float64) ** -1.1                       # Zipf(1.1) over the vocabulary
+    labels_host = rng.choice(vocab, size=(batch, time), p=zipf / zipf.sum()).astype(np.int64)
     labels = torch.from_numpy(labels_host).cuda()
     wrap = lambda t, dtype: DeviceStorage.wrap(t.data_ptr(), t.numel(), dtype, owner=t)
     h, wt = Tensor(wrap(hidden, "bfloat16"), tuple(hidden.shape)), Tensor(wrap(weight, "bfloat16"), tuple(weight.shape))

@@ -292,6 +292,15 @@ int qmoe_expert_backward_parts(const qmoe_route_t* route, const qmoe_experts_t* 
 int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtype, uint64_t c, int32_t c_dtype,
               int64_t m, int64_t k, int64_t n, int32_t transpose_a, int32_t transpose_b,
               int32_t accumulate, uint64_t stream);
+/* The weight gradient of a linear layer, C[M, N] (fp32) = A^T . B with A [K, M] and B [K, N] in bf16 (qmoe_gemm with
+ * transpose_a), for shapes whose few 256 x 256 tiles would leave most of the GPU idle: the K rows are cut into ranges
+ * that run side by side on the tcgen05 kernels, each into a slab of `partials`, and the slabs are added in a fixed
+ * order (bit-identical from run to run).  `partials`: qmoe_gemm_wgrad_partials(m, k, n) 4-byte units, 16-byte aligned;
+ * that function gives 0 when the shape is not split, and qmoe_gemm is the call to make then.  Upstream has one product
+ * for this (the backward closure of `linear`, src/qutai/lm/layers.py:260-272). */
+int64_t qmoe_gemm_wgrad_partials(int64_t m, int64_t k, int64_t n);
+int qmoe_gemm_wgrad_split(uint64_t a, uint64_t b, uint64_t c, uint64_t partials, int64_t m, int64_t k, int64_t n,
+                          uint64_t stream);
 /* silu(v) (backward == 0) or g * silu'(v) (backward != 0), element-wise over n values.
  * Replaces lm_silu (src/qutai/backends/cuda/lm.cu:54). */
 int qmoe_silu(uint64_t values, uint64_t gradient, uint64_t out, int32_t dtype, int64_t n,

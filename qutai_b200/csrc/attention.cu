@@ -628,7 +628,7 @@ using namespace qmoe;
 extern "C" int qmoe_attention_forward(const qmoe_attention_t* a, uint64_t stream_) {
     if (int rc = attention_check(a, false)) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
-    TimedScope timed(KC_OTHER, stream);
+    TimedScope timed(KC_ATTENTION, stream);
     AttentionParams p = {};
     const uint64_t wide = (uint64_t)a->heads * D, narrow = (uint64_t)a->kv_heads * D;
     if (int rc = make_map_3d(&p.map_q, a->q, wide, (uint64_t)a->time, (uint64_t)a->batch, BLOCK)) return rc;
@@ -647,7 +647,7 @@ extern "C" int qmoe_attention_forward(const qmoe_attention_t* a, uint64_t stream
 extern "C" int qmoe_attention_backward(const qmoe_attention_t* a, uint64_t stream_) {
     if (int rc = attention_check(a, true)) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
-    TimedScope timed(KC_OTHER, stream);
+    TimedScope timed(KC_ATTENTION, stream);
     AttentionParams p = {};
     const uint64_t wide = (uint64_t)a->heads * D, narrow = (uint64_t)a->kv_heads * D;
     if (int rc = make_map_3d(&p.map_q, a->q, wide, (uint64_t)a->time, (uint64_t)a->batch, BLOCK)) return rc;

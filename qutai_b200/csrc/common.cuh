@@ -36,7 +36,8 @@ int after_launch(const char* name);  // cudaGetLastError (+ sync when QUTAI_MOE_
 // per-kernel-class timing (off unless enabled through the ABI)
 enum KernelClass {
     KC_ROUTER_GEMM = 0, KC_ROUTE, KC_PERMUTE, KC_EXPERT_GEMM, KC_SWIGLU, KC_COMBINE, KC_COMBINE_BWD,
-    KC_WGRAD_GEMM, KC_UNPERMUTE, KC_ROUTE_BWD, KC_CAST, KC_OTHER, KC_EXCHANGE, KC_OPTIMIZER, KC_NORM, KC_COUNT
+    KC_WGRAD_GEMM, KC_UNPERMUTE, KC_ROUTE_BWD, KC_CAST, KC_OTHER, KC_EXCHANGE, KC_OPTIMIZER, KC_NORM, KC_ATTENTION,
+    KC_HEAD_LOSS, KC_ELEMENTWISE, KC_COUNT
 };
 struct TimedScope {  // records a pair of events around the launches made while it is alive
     TimedScope(KernelClass kc, cudaStream_t s);
@@ -158,7 +159,8 @@ int tc_dswiglu(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t w_down,
                uint64_t du, long long d, long long h, cudaStream_t stream);
 int tc_wgrad3(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t h_act, uint64_t x, uint64_t dg, uint64_t du,
               uint64_t d_w_down, uint64_t d_w_gate, uint64_t d_w_up, long long d, long long h, cudaStream_t stream);
-int tc_wgrad1(const qmoe_route_t* r, uint64_t a, uint64_t b, uint64_t out, long long M, long long N, cudaStream_t stream);
+int tc_wgrad1(const qmoe_route_t* r, uint64_t a, uint64_t b, uint64_t out, long long M, long long N, cudaStream_t stream,
+              int groups = 1, long long slab = 0);
 int tc_router_forward(uint64_t x, uint64_t w3, uint64_t scores, long long T, long long d, int E, int S, cudaStream_t stream);
 int tc_plain_f32_nn(uint64_t a, uint64_t b, uint64_t c, long long T, long long K, long long N, cudaStream_t stream);
 int tc_split_wgrad(uint64_t a, long long a_pitch, uint64_t b, uint64_t partial, const int* offsets, const int* counts,

@@ -1169,8 +1169,11 @@ int tc_wgrad3(const qmoe_route_t* r, int experts, uint64_t dy, uint64_t h_act, u
 }
 
 // out [M, N] (fp32) = A^T . B over the rows of ONE group (counts[0] rows from row offsets[0]): A [rows, M], B [rows, N].
-// The weight gradient of a plain linear map (the language-model head), on CTA pairs.
-int tc_wgrad1(const qmoe_route_t* r, uint64_t a, uint64_t b, uint64_t out, long long M, long long N, cudaStream_t stream) {
+// The weight gradient of a plain linear map (the language-model head), on CTA pairs.  With `groups` > 1 the rows are cut
+// into that many ranges (offsets[g], counts[g]; every offset a multiple of 128) and range g leaves its own product in
+// out + g * slab: a short, wide product then fills the machine, and the caller adds the slabs in a fixed order.
+int tc_wgrad1(const qmoe_route_t* r, uint64_t a, uint64_t b, uint64_t out, long long M, long long N, cudaStream_t stream,
+              int groups, long long slab) {
     GemmParams p = {};
     if (out & 15u || (N * 4) % 16) return fail_arg("weight-gradient output must be 16-byte aligned with a 16-byte row pitch");
     const int ctas = gemm_ctas();
@@ -1179,7 +1182,7 @@ int tc_wgrad1(const qmoe_route_t* r, uint64_t a, uint64_t b, uint64_t out, long 
     if (int rc = make_map(&p.map_b, b, (uint64_t)N, rows, 64)) return rc;
     p.map_a2 = p.map_a; p.map_b2 = p.map_b; p.map_a3 = p.map_a; p.map_b3 = p.map_b;
     p.offsets = (const int*)r->offsets; p.counts = (const int*)r->counts; p.status = device_status_address();
-    p.out0 = (void*)out; p.ldc = N; p.c_slab = 0; p.experts = 1; p.problems = 1;
+    p.out0 = (void*)out; p.ldc = N; p.c_slab = slab; p.experts = groups; p.problems = 1;
     p.m_tiles = ceil_div(M, BM * ctas); p.n_tiles = ceil_div(N, BN);
     p.M = (int)M; p.N = (int)N; p.K = 0; p.segments = 1;
     if (ctas == 2) return launch<MODE_WGRAD, true, true, 2>(p, stream);

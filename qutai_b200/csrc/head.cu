@@ -301,7 +301,7 @@ extern "C" int qmoe_head_forward(const qmoe_head_t* h, uint64_t stream_) {
             if (int rc = launch_simt_gemm(g, h->dtype, h->dtype, h->dtype, rows, 1, stream)) return rc;
         }
     }
-    TimedScope timed(KC_OTHER, stream);
+    TimedScope timed(KC_HEAD_LOSS, stream);
     if (int rc = h->dtype == QMOE_BF16 ? launch_loss_gradient<__nv_bfloat16>(h, rows, stream) : launch_loss_gradient<float>(h, rows, stream)) return rc;
     head_mean_kernel<<<1, 1024, 0, stream>>>((const float*)h->row_loss, (const float*)h->meta, (float*)h->loss, rows);
     QMOE_LAUNCH_CHECK("head_mean_kernel");

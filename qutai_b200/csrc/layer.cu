@@ -224,6 +224,79 @@ extern "C" int qmoe_gemm(uint64_t a, int32_t a_dtype, uint64_t b, int32_t b_dtyp
     return launch_simt_gemm(g, a_dtype, b_dtype, c_dtype, m, 1, stream);
 }
 
+// ---- the weight gradient of a linear layer, its rows cut into ranges that run side by side ---------------------------
+namespace qmoe {
+namespace {
+constexpr int kSplitTableInts = 64;      // at the head of the scratch: offsets[splits + 1], counts[splits]
+constexpr int kMaxSplits = 16;
+
+long long split_rows(long long k, int splits) { return ((k + splits - 1) / splits + kRowPad - 1) / kRowPad * kRowPad; }
+// how many row ranges make m x n tiles of 256 x 256 fill the CTA pairs once, each range at least 512 rows long
+int wgrad_splits(long long m, long long k, long long n) {
+    const long long tiles = ((m + 255) / 256) * ((n + 255) / 256), pairs = sm_count() / 2;
+    long long splits = pairs / tiles;
+    if (splits > k / 512) splits = k / 512;
+    if (splits > kMaxSplits) splits = kMaxSplits;
+    if (splits < 2) return 1;
+    const long long rows = split_rows(k, (int)splits);
+    return (int)((k + rows - 1) / rows);        // ranges start on multiples of 128 rows: none of them may come out empty
+}
+
+__global__ void fill_split_table_kernel(int* table, int splits, int rows_per_split, int rows) {
+    const int i = threadIdx.x;
+    if (i <= splits) table[i] = i * rows_per_split;
+    if (i < splits) {
+        const int left = rows - i * rows_per_split;
+        table[splits + 1 + i] = left < 0 ? 0 : (left > rows_per_split ? rows_per_split : left);
+    }
+}
+// out = slab 0 + slab 1 + ... in that order, four values per thread
+__global__ void __launch_bounds__(256) sum_slabs_kernel(const float4* __restrict__ slabs, float4* __restrict__ out, int count, long long quads) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (long long)gridDim.x * blockDim.x) {
+        float4 total = slabs[i];
+        for (int s = 1; s < count; ++s) {
+            const float4 v = slabs[(long long)s * quads + i];
+            total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+        }
+        out[i] = total;
+    }
+}
+}  // namespace
+}  // namespace qmoe
+
+extern "C" int64_t qmoe_gemm_wgrad_partials(int64_t m, int64_t k, int64_t n) {
+    if (m <= 0 || k <= 0 || n <= 0 || m % 8 || n % 8 || k % 8) return 0;
+    const int splits = wgrad_splits(m, k, n);
+    return splits < 2 ? 0 : kSplitTableInts + (int64_t)splits * m * n;
+}
+
+extern "C" int qmoe_gemm_wgrad_split(uint64_t a, uint64_t b, uint64_t c, uint64_t partials, int64_t m, int64_t k, int64_t n,
+                                     uint64_t stream_) {
+    if (!a || !b || !c || !partials) return fail_arg("gemm_wgrad_split: null address");
+    if ((a | b | c | partials) & 15u) return fail_arg("gemm_wgrad_split: addresses must be multiples of 16 bytes");
+    if (c == a || c == b) return fail_arg("gemm_wgrad_split: the output must not alias an input");
+    if (m <= 0 || k <= 0 || n <= 0 || m % 8 || n % 8 || k % 8 || k >= (1ll << 30)) return fail_arg("gemm_wgrad_split: sizes must be positive multiples of 8");
+    const int splits = wgrad_splits(m, k, n);
+    if (splits < 2) return fail_arg("gemm_wgrad_split: this shape is not split (qmoe_gemm_wgrad_partials gives 0): use qmoe_gemm");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    TimedScope timed(KC_WGRAD_GEMM, stream);
+    int* table = (int*)partials;
+    float* slabs = (float*)partials + kSplitTableInts;
+    fill_split_table_kernel<<<1, 32, 0, stream>>>(table, splits, (int)split_rows(k, splits), (int)k);
+    QMOE_LAUNCH_CHECK("fill_split_table_kernel");
+    qmoe_route_t r = {};
+    r.rows_bound = k;
+    r.offsets = (uint64_t)table;
+    r.counts = (uint64_t)(table + splits + 1);
+    if (int rc = tc_wgrad1(&r, a, b, (uint64_t)slabs, m, n, stream, splits, m * n)) return rc;
+    const long long quads = m * n / 4;
+    long long blocks = (quads + 255) / 256;
+    if (blocks > 8ll * sm_count()) blocks = 8ll * sm_count();
+    sum_slabs_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const float4*)slabs, (float4*)c, splits, quads);
+    QMOE_LAUNCH_CHECK("sum_slabs_kernel");
+    return 0;
+}
+
 extern "C" int qmoe_layer_forward(const qmoe_layer_t* L, uint64_t stream) {
     if (!L) return fail_arg("layer is null");
     const qmoe_route_t* r = &L->route;

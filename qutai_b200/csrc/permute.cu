@@ -538,7 +538,7 @@ extern "C" int qmoe_add(uint64_t a, uint64_t b, uint64_t out, int32_t dtype, int
     if (!a || !b || !out || n < 0) return fail_arg("add: null address or negative size");
     if (n == 0) return 0;
     cudaStream_t stream = (cudaStream_t)stream_;
-    TimedScope timed(KC_OTHER, stream);
+    TimedScope timed(KC_ELEMENTWISE, stream);
     if (dtype == QMOE_BF16)
         add_kernel<__nv_bfloat16><<<grid_for_elems(n), kThreads, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
                                                                                (__nv_bfloat16*)out, n);

@@ -87,7 +87,12 @@ class Linear:
         dx = DeviceStorage(rows * self.width_in, "bfloat16")
         self._gemm(dy, self.operand(), dx, rows, self.width_out, self.width_in, 0, 0, lib.QMOE_BF16)
         dw = DeviceStorage(self.weight.storage.size, "float32")
-        self._gemm(dy, x, dw, self.width_out, rows, self.width_in, 1, 0, lib.QMOE_F32)
+        partials = lib.load().qmoe_gemm_wgrad_partials(self.width_out, rows, self.width_in)
+        if partials:    # few output tiles, many rows: the rows are cut into ranges that run side by side
+            scratch = DeviceStorage(partials, "float32")
+            lib.call("qmoe_gemm_wgrad_split", dy.ptr, x.ptr, dw.ptr, scratch.ptr, self.width_out, rows, self.width_in, self.stream)
+        else:
+            self._gemm(dy, x, dw, self.width_out, rows, self.width_in, 1, 0, lib.QMOE_F32)
         _accumulate(self.weight, dw, self.stream)
         return dx
 

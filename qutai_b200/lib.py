@@ -142,6 +142,8 @@ SIGNATURES = {
     "qmoe_expert_forward_parts": (c_int, [_RP, _EP, _U, _U, _U, _U, _U, _I32, _U]),
     "qmoe_expert_backward_parts": (c_int, [_RP, _EP] + [_U] * 12 + [_I32, _U]),
     "qmoe_gemm": (c_int, [_U, _I32, _U, _I32, _U, _I32, _I64, _I64, _I64, _I32, _I32, _I32, _U]),
+    "qmoe_gemm_wgrad_partials": (c_int64, [_I64, _I64, _I64]),
+    "qmoe_gemm_wgrad_split": (c_int, [_U, _U, _U, _U, _I64, _I64, _I64, _U]),
     "qmoe_silu": (c_int, [_U, _U, _U, _I32, _I64, _I32, _U]),
     "qmoe_add": (c_int, [_U, _U, _U, _I32, _I64, _U]),
     "qmoe_normal_fill": (c_int, [_U, _I32, _I64, c_double, c_double, _U, _U]),

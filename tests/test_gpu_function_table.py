@@ -204,3 +204,33 @@ def test_gemm_takes_the_tensor_cores_for_the_three_products_of_a_linear_layer(ro
     before = count()
     cuda_lm.gemm(to_device(x[:100], "bfloat16"), ws, 100, inner, cols, transpose_right=True, out_dtype="bfloat16")
     assert count() == before
+
+
+@pytest.mark.parametrize("rows,cols_out,cols_in", [(8192, 1024, 1024), (4104, 256, 1024), (1096, 512, 264)])
+def test_split_weight_gradient_of_a_linear_layer(rows, cols_out, cols_in):
+    """``qmoe_gemm_wgrad_split``: g^T x with the rows cut into ranges that run side by side, the ranges' products
+    added in a fixed order — the value of the one-launch product, the same bits on every run; row counts that leave a
+    ragged last range included."""
+    from gpu_util import to_device, to_host
+    from qutai_b200 import cuda_lm, lib
+    from qutai_b200.storage import DeviceStorage
+
+    rng = np.random.default_rng(rows)
+    x, g = oracle.round_bf16(rng.standard_normal((rows, cols_in))), oracle.round_bf16(rng.standard_normal((rows, cols_out)))
+    xs, gs = to_device(x, "bfloat16"), to_device(g, "bfloat16")
+    partials = lib.load().qmoe_gemm_wgrad_partials(cols_out, rows, cols_in)
+    assert partials > 64 + cols_out * cols_in                 # these shapes are split
+    scratch, out = DeviceStorage(partials, "float32"), DeviceStorage(cols_out * cols_in, "float32")
+    results = []
+    for _ in range(2):
+        lib.call("qmoe_gemm_wgrad_split", gs.ptr, xs.ptr, out.ptr, scratch.ptr, cols_out, rows, cols_in, 0)
+        results.append(to_host(out, (cols_out, cols_in)))
+    assert np.array_equal(results[0], results[1])
+    assert lib.device_status() == 0
+    assert oracle.max_rel_err(results[0], g.T @ x) <= 1e-5
+    whole = to_host(cuda_lm.gemm(gs, xs, cols_out, rows, cols_in, transpose_left=True, out_dtype="float32"), (cols_out, cols_in))
+    assert oracle.max_rel_err(results[0], whole) <= 1e-5
+    # a shape with enough tiles of its own is not split, and the call says so
+    assert lib.load().qmoe_gemm_wgrad_partials(32000, 8192, 1024) == 0
+    with pytest.raises(ValueError):
+        lib.call("qmoe_gemm_wgrad_split", gs.ptr, xs.ptr, out.ptr, scratch.ptr, 32000, 8192, 1024, 0)
