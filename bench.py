@@ -686,7 +686,8 @@ def run_gpu(args, w, rank, world):
     if world == 1 and not forward_only and not args.no_attention:
         line["attention"] = attention_block(args.steps, peaks, torch, np)
     if not forward_only and not args.no_decoder:
-        line["decoder_step"] = decoder_step(torch, np, rank=rank, world=world, dist=dist, gather=gather, device=device)
+        line["decoder_step"] = decoder_step(torch, np, rank=rank, world=world, dist=dist, gather=gather, device=device,
+                                            placement=args.placement)
     if world == 1 and not forward_only and not args.no_library_gemm:
         here = library_gemm_here(torch)
         line["roofline"]["library_gemm_on_this_gpu"] = here
@@ -841,7 +842,7 @@ def block_ffn(layer, w, xs, gs, ga, x_dev, g_dev, steps, layer_ms, torch, np):
                            sampled_tokens=int(sample.numel())))
 
 
-def decoder_step(torch, np, steps=3, rank=0, world=1, dist=None, gather=None, device=None):
+def decoder_step(torch, np, steps=3, rank=0, world=1, dist=None, gather=None, device=None, placement="balanced"):
     """One rank's share of the full decoder training step (12 blocks, d_model 1024, 16 heads in 4 key/value groups,
     16 experts top-2 of hidden width 2048, vocabulary 32000; 4 sequences of 2048 tokens, Zipf(1.1) ids): loss,
     backward and the AdamW step of ``qutai_b200.decoder.Decoder``.  One GPU: all experts local.  N GPUs: every rank
@@ -864,6 +865,12 @@ def decoder_step(torch, np, steps=3, rank=0, world=1, dist=None, gather=None, de
     weights = np.arange(1, config.vocab_size + 1, dtype=np.float64) ** -1.1        # Zipf(1.1) over the vocabulary: P(id) ~ (id + 1)^-1.1
     tokens = rng.choice(config.vocab_size, size=(batch, time_), p=weights / weights.sum()).tolist()
     model.loss(tokens)            # a first forward makes the bf16 operand copies that the optimizer then keeps current
+    if world > 1 and placement == "balanced":
+        # every block moves its experts to the placement that evens out the rows per rank of this first forward
+        # (the blocks' loads differ); the parameters are new objects afterwards, so this comes before the optimizer
+        for block in model.blocks:
+            block.ffn.rebalance()
+        model.loss(tokens)
     optimizer = AdamW(model.parameters(), learning_rate=1e-4, shadows=model.operand_shadows(), stream=stream)
 
     def step():
@@ -908,14 +915,30 @@ def decoder_step(torch, np, steps=3, rank=0, world=1, dist=None, gather=None, de
     step()
     host_ms = (time.time() - host_begin) * 1e3          # the host's share: issuing one step without waiting for it
     torch.cuda.synchronize()
+    by_rank = load = None
+    if world > 1:   # waiting shows up in different classes on different ranks: keep every rank's view of them
+        # rows every rank's experts received in the last step, block by block: the step walks the blocks in lockstep
+        # (barriers), so its expert time follows the sum over the blocks of the fullest rank, not the fullest sum
+        fullest = mean = 0.0
+        worst = []
+        for block in model.blocks:
+            counts, owner = block.ffn.last_counts, block.ffn.placement
+            rows = [sum(c for c, o in zip(counts, owner) if o == r) for r in range(world)]
+            fullest += max(rows)
+            mean += sum(rows) / world
+            worst.append(round(max(rows) * world / max(sum(rows), 1), 2))
+        load = dict(fullest_rank_over_mean=round(fullest / mean, 3), per_block=worst)
+        seen = [None] * world
+        dist.all_gather_object(seen, {name: classes.get(name, 0.0) for name in ("barrier", "all_reduce", "exchange", "expert_gemm", "wgrad_gemm")})
+        by_rank = {name: [other[name] for other in seen] for name in seen[0]}
     del model, optimizer
     gc.collect()
     empty_cache()
     return dict(ms_per_step=ms, tokens_per_s=world * batch * time_ / (ms * 1e-3), tokens=world * batch * time_, parameters=parameters,
                 config=f"12 blocks, d_model 1024, 16 heads / 4 kv heads, 16 experts top-2 hidden 2048, vocab 32000, {world} x 4 x 2048 tokens, bf16 activations, fp32 parameters",
                 what="loss + backward + AdamW of qutai_b200.decoder.Decoder"
-                     + (" (all experts local)" if world == 1 else f" on {world} ranks: experts spread over the ranks, replicated gradients summed (NCCL)"),
-                class_ms=classes, host_issue_ms=host_ms, losses=losses,
+                     + (" (all experts local)" if world == 1 else f" on {world} ranks: experts spread over the ranks ({placement} placement per block), replicated gradients summed (NCCL)"),
+                class_ms=classes, class_ms_by_rank=by_rank, expert_rows=load, host_issue_ms=host_ms, losses=losses,
                 check=dict(ok=bool(np.isfinite(losses).all() and losses[-1] < losses[0] and same_on_every_rank),
                            how="finite, falling over the steps on the same batch, the same value on every rank"))
 

@@ -37,7 +37,7 @@ int after_launch(const char* name);  // cudaGetLastError (+ sync when QUTAI_MOE_
 enum KernelClass {
     KC_ROUTER_GEMM = 0, KC_ROUTE, KC_PERMUTE, KC_EXPERT_GEMM, KC_SWIGLU, KC_COMBINE, KC_COMBINE_BWD,
     KC_WGRAD_GEMM, KC_UNPERMUTE, KC_ROUTE_BWD, KC_CAST, KC_OTHER, KC_EXCHANGE, KC_OPTIMIZER, KC_NORM, KC_ATTENTION,
-    KC_HEAD_LOSS, KC_ELEMENTWISE, KC_COUNT
+    KC_HEAD_LOSS, KC_ELEMENTWISE, KC_BARRIER, KC_ALL_REDUCE, KC_COUNT
 };
 struct TimedScope {  // records a pair of events around the launches made while it is alive
     TimedScope(KernelClass kc, cudaStream_t s);

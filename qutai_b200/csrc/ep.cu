@@ -298,7 +298,7 @@ extern "C" int qmoe_ep_all_reduce_f32(uint64_t buf, int64_t n, uint64_t stream_)
     if (!buf || n < 0) return fail_arg("ep_all_reduce_f32: null buffer or negative size");
     if (n == 0) return 0;
     cudaStream_t stream = (cudaStream_t)stream_;
-    TimedScope timed(KC_OTHER, stream);
+    TimedScope timed(KC_ALL_REDUCE, stream);
     QMOE_NCCL(g_nccl.AllReduce((const void*)buf, (void*)buf, (size_t)n, ncclFloat32, ncclSum, g_comm, stream));
     return 0;
 }
@@ -460,7 +460,7 @@ extern "C" int qmoe_ep_barrier(uint64_t scratch_i32, uint64_t stream_) {
     if (int rc = need_comm()) return rc;
     if (!scratch_i32) return fail_arg("ep_barrier: scratch is null");
     cudaStream_t stream = (cudaStream_t)stream_;
-    TimedScope timed(KC_EXCHANGE, stream);
+    TimedScope timed(KC_BARRIER, stream);
     QMOE_NCCL(g_nccl.AllReduce((const void*)scratch_i32, (void*)scratch_i32, 1, ncclInt32, ncclSum, g_comm, stream));
     return 0;
 }
@@ -837,7 +837,7 @@ extern "C" int qmoe_ep_flag_barrier(const qmoe_ep_peers_t* flags, int32_t sequen
         }
     }
     cudaStream_t stream = (cudaStream_t)stream_;
-    TimedScope timed(KC_EXCHANGE, stream);
+    TimedScope timed(KC_BARRIER, stream);
     ep_flag_barrier_kernel<<<1, 512, 0, stream>>>(table, flags->rank, flags->world, sequence, device_status_address(),
                                                   (const int*)stats_local, stats_words, stats,
                                                   (unsigned long long)g_barrier_wait_ns.load());

@@ -27,7 +27,7 @@ std::vector<Scope> g_scopes;
 const char* kClassNames[KC_COUNT] = {"router_gemm", "route", "permute", "expert_gemm", "swiglu", "combine",
                                      "combine_backward", "wgrad_gemm", "unpermute", "route_backward",
                                      "cast", "other", "exchange", "optimizer", "norm", "attention", "head_loss",
-                                     "elementwise"};
+                                     "elementwise", "barrier", "all_reduce"};
 __device__ int g_device_status;
 std::atomic<int> g_variants[QMOE_VARIANT_COUNT];  // zero-initialised: every kernel in its default form
 }  // namespace

@@ -299,6 +299,9 @@ class ExpertParallelMoE:
         # "auto": rebuild the bf16 weight copies only after a weight storage was written (DeviceStorage.generation);
         # True: at every forward; False: never after the first forward
         self.refresh_operands = "auto"
+        # False: backward leaves THIS rank's part of the router gradient in ``router.weight.grad`` and the caller sums
+        # it over the ranks (a model that reduces all its replicated gradients in one collective)
+        self.reduce_router_gradient = True
         self._sequence = 0  # barriers issued so far (the flag barrier's growing sequence number)
         self._work = None
         self._saved = None
@@ -754,7 +757,8 @@ class ExpertParallelMoE:
         lib.call("qmoe_ep_zero_pad_rows", xr, buf["dy_recv"].ptr, code, d, s)
         grads = (buf["d_w_gate"].ptr, buf["d_w_up"].ptr, buf["d_w_down"].ptr)
         saved = (buf["x_recv"].ptr, buf["g"].ptr, buf["u"].ptr, buf["h"].ptr, buf["d_h"].ptr, buf["d_g"].ptr, buf["d_u"].ptr)
-        overlapped = bool(w.get("flag_barrier"))   # no other NCCL call in the step: the all-reduce can leave the main stream
+        flags = bool(w.get("flag_barrier"))
+        overlapped = flags and self.reduce_router_gradient   # no other NCCL call in the step: the all-reduce can leave the main stream
 
         def router_backward():
             lib.call("qmoe_route_backward", tr, buf["d_gate_weights"].ptr, ga, buf["d_scores"].ptr, s)
@@ -766,7 +770,8 @@ class ExpertParallelMoE:
             if overlapped:
                 lib.call("qmoe_event_record", side["grads"], s)
                 lib.call("qmoe_stream_wait_event", stream, side["grads"])
-            lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, stream)
+            if self.reduce_router_gradient:
+                lib.call("qmoe_ep_all_reduce_f32", buf["d_w_router"].ptr, E * d, stream)
             if not self._identity:   # rows back into the model's expert order
                 lib.call("qmoe_gather_rows", buf["d_w_router"].ptr, buf["d_w_router_logical"].ptr, self._to_logical.ptr,
                          E, E, 4 * d, stream)
@@ -792,7 +797,7 @@ class ExpertParallelMoE:
             lib.call("qmoe_ep_expert_dx_push", xr, ex, buf["d_g"].ptr, buf["d_u"].ptr, buf["ret_table"].ptr, ctypes.byref(peers["dy_send"]), s)
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 2, s)
             router_backward()
-            if overlapped:  # peers overwrite the gathered counts after this barrier: the host's copy has left by then
+            if flags:  # peers overwrite the gathered counts after this barrier: the host's copy has left by then
                 lib.call("qmoe_stream_wait_event", s, w["stats_event"])
             self._barrier(w)
         elif self.transport == "p2p":
@@ -803,7 +808,7 @@ class ExpertParallelMoE:
             lib.call("qmoe_expert_backward_parts", xr, ex, buf["dy_recv"].ptr, *saved, buf["dx_recv"].ptr, *grads, 3, s)
             lib.call("qmoe_ep_push_return", xr, buf["ret_table"].ptr, buf["dx_recv"].ptr, ctypes.byref(peers["dy_send"]), 0, L, 0, code, d, s)
             router_backward()
-            if overlapped:
+            if flags:
                 lib.call("qmoe_stream_wait_event", s, w["stats_event"])
             self._barrier(w)
         else:
