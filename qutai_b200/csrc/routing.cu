@@ -308,7 +308,9 @@ int check_route(const qmoe_route_t* r, bool need_scratch) {
     if (r->tokens <= 0) return fail_arg("tokens must be positive (got %lld)", (long long)r->tokens);
     if (r->experts <= 0 || r->experts > kMaxExperts)
         return fail_arg("experts must be in [1, %d] (got %d)", kMaxExperts, r->experts);
-    if (r->top_k <= 0 || r->top_k > kMaxTopK || r->top_k > r->experts)
+    // top_k <= experts is a property of routing.  The consumers of a finished route also take the expert-side view an
+    // expert-parallel rank builds of its local experts, which can be fewer than top_k (8 experts top-2 over 8 ranks).
+    if (r->top_k <= 0 || r->top_k > kMaxTopK || (need_scratch && r->top_k > r->experts))
         return fail_arg("top_k must be in [1, min(experts, %d)] (got %d)", kMaxTopK, r->top_k);
     if (r->tokens * r->top_k > (1ll << 30)) return fail_arg("tokens * top_k exceeds 2^30");
     if (r->rows_bound < qmoe_rows_bound(r->tokens, r->experts, r->top_k))
