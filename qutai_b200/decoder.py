@@ -295,6 +295,18 @@ class Decoder:
             shadows[self.embedding.weight] = self.head._operand
         return shadows
 
+    def clip_grad_norm(self, max_norm=1.0):
+        """Upstream's ``clip_grad_norm(model.parameters(), max_norm)`` (src/qutai/nn/optimizers.py:19-31) over the WHOLE
+        model: with ``world > 1`` the experts of the other ranks count too (``clip_grad_norm_sharded``), and every
+        rank scales by the same factor.  Returns the norm before clipping."""
+        from .optim import clip_grad_norm, clip_grad_norm_sharded
+
+        if self.world == 1:
+            return clip_grad_norm(self.parameters(), max_norm, stream=self.stream)
+        replicated = self.replicated_parameters()
+        held = {id(p) for p in replicated}
+        return clip_grad_norm_sharded(replicated, [p for p in self.parameters() if id(p) not in held], max_norm, stream=self.stream)
+
     # -- forward ------------------------------------------------------------------------------------------------
     def loss(self, tokens, labels=None, *, targets_of_all_ranks=None):
         """``tokens`` (and ``labels``, default the tokens): nested sequences [batch][time] of token ids (-100 in the

@@ -63,6 +63,32 @@ def clip_grad_norm(parameters, max_norm=1.0, *, stream=0, scratch=None):
     return norm
 
 
+def clip_grad_norm_sharded(replicated, sharded, max_norm=1.0, *, stream=0):
+    """``clip_grad_norm`` for one rank of an expert-parallel job (no counterpart upstream, which is single-device):
+    the gradients of ``replicated`` parameters are the same on every rank and count once, those of ``sharded``
+    parameters (this rank's experts) exist only here and count together with the other ranks'.  Every rank calls it
+    at the same point; all return the same norm and scale by the same factor.  Built from the single-rank kernels:
+    two passes that only measure (replicated, sharded), one all-reduce of the sharded square, and one pass over all
+    local gradients whose limit is chosen so that the kernel's own ``max_norm / norm`` comes out as
+    ``max_norm / joint norm``."""
+    if not isfinite(max_norm) or max_norm < 0:
+        raise ValueError("max_norm must be a non-negative finite number")
+    replicated, sharded = _parameters(replicated), _parameters(sharded)
+    measure_only = 1.7e308      # the largest limit the kernel takes: nothing is scaled, the norm is reported
+    norm_replicated = clip_grad_norm(replicated, measure_only, stream=stream)
+    norm_sharded = clip_grad_norm(sharded, measure_only, stream=stream)
+    square = DeviceStorage.from_values([norm_sharded * norm_sharded], "float32", stream)
+    lib.call("qmoe_ep_all_reduce_f32", square.ptr, 1, stream)
+    joint = (norm_replicated * norm_replicated + float(square.tolist(stream)[0])) ** 0.5
+    if not isfinite(joint):
+        raise ValueError("the gradients contain non-finite values")
+    local = (norm_replicated * norm_replicated + norm_sharded * norm_sharded) ** 0.5
+    if joint > max_norm and local > 0:
+        # the kernel scales by limit / local when local > limit: limit = max_norm * local / joint gives max_norm / joint
+        clip_grad_norm(tuple(replicated) + tuple(sharded), max_norm * local / joint, stream=stream)
+    return joint
+
+
 class AdamW:
     """Adam with decoupled weight decay; state per parameter object (``steps``, ``averages``,
     ``square_averages``), created when the parameter first has a gradient."""

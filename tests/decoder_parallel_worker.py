@@ -62,6 +62,13 @@ def main():
         if parameter.grad is not None:
             out["grad:" + name] = to_host(parameter.grad.storage, tuple(parameter.shape))
 
+    # clipping over the whole model: the norm counts the other rank's experts too, both ranks scale alike
+    out["clip_norm"] = np.array(model.clip_grad_norm(1e-3))
+    out["clipped:embedding.weight"] = to_host(model.embedding.weight.grad.storage, tuple(model.embedding.weight.shape))
+    first_expert = next(name for name, p in named if ".ffn.experts." in name and p.grad is not None)
+    out["clipped_expert_name"] = np.array(first_expert)
+    out["clipped_expert"] = to_host(dict(named)[first_expert].grad.storage, tuple(dict(named)[first_expert].shape))
+
     optimizer = AdamW(model.parameters(), learning_rate=3e-3, shadows=model.operand_shadows())
     losses = []
     for _ in range(5):

@@ -68,6 +68,15 @@ def test_two_ranks_reproduce_the_upstream_decoder_on_the_whole_batch(tmp_path):
         assert np.median(list(worst.values())) <= 3e-2
         assert r["losses"][-1] < r["losses"][0] - 0.3, r["losses"]
     first, second = ranks
+    # gradient clipping over the whole model: upstream's joint norm of ALL gradients, the same on both ranks, and
+    # every gradient (replicated or one rank's expert) scaled by max_norm / norm
+    joint = np.sqrt(sum(float((g[key].astype(np.float64) ** 2).sum()) for key in g.files if key.startswith("grad:")))
+    assert float(first["clip_norm"]) == float(second["clip_norm"])
+    assert abs(float(first["clip_norm"]) - joint) <= 3e-2 * joint
+    factor = 1e-3 / float(first["clip_norm"])
+    for r in ranks:
+        assert oracle.max_rel_err(r["clipped:embedding.weight"], r["grad:embedding.weight"] * factor) <= 1e-5
+        assert oracle.max_rel_err(r["clipped_expert"], r["grad:" + str(r["clipped_expert_name"])] * factor) <= 1e-5
     assert float(first["loss"][0]) == float(second["loss"][0])
     for name in first["replicated"].tolist() + [n for n in first["names"].tolist() if n.endswith("router.weight")]:
         assert np.array_equal(first["grad:" + name], second["grad:" + name]), name
