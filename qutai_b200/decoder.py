@@ -325,7 +325,21 @@ class Decoder:
         if len(targets) != len(flat) or any(t != -100 and not 0 <= t < c.vocab_size for t in targets):
             raise ValueError("labels must have the shape of the tokens and be token ids or -100")
         rows, width = batch * time, c.d_model
+        # The embedding's backward wants, per distinct token, the list of its positions (upstream builds the same tables,
+        # src/qutai/backends/cuda_lm.py:97-106).  They depend on the ids alone, so they are built and uploaded here,
+        # next to the ids: an upload waits for the stream, and at this point of a training loop the device is just
+        # finishing the previous step, while at the end of the backward the wait would leave it idle through the
+        # host's preparation of the optimizer step.
+        groups = {}
+        for position, token in enumerate(flat):
+            groups.setdefault(token, []).append(position)
+        distinct = sorted(groups)
+        starts, positions = [0], []
+        for token in distinct:
+            positions.extend(groups[token])
+            starts.append(len(positions))
         ids = DeviceStorage.from_bytes(array("q", flat).tobytes(), "int64", stream)
+        tables = tuple(DeviceStorage.from_bytes(array("q", values).tobytes(), "int64", stream) for values in (distinct, starts, positions))
         label_ids = ids if labels is None else DeviceStorage.from_bytes(array("q", targets).tobytes(), "int64", stream)
         x = DeviceStorage(rows * width, "bfloat16")
         lib.call("qmoe_embedding", self.embedding.weight.storage.ptr, ids.ptr, x.ptr, lib.QMOE_BF16, rows, width, c.vocab_size, stream)
@@ -357,7 +371,7 @@ class Decoder:
         lib.call("qmoe_scale_f32", mean_aux.ptr, scaled.ptr, 0, self._aux_coef.ptr, 1, 1, stream)
         lib.call("qmoe_add", lm.storage.ptr, scaled.ptr, total.ptr, lib.QMOE_F32, 1, stream)
         self.last_lm_loss, self.last_auxiliary_loss = lm, Tensor(mean_aux, ())
-        self._saved = (flat, batch, time, x, inverse, share)
+        self._saved = (tables, len(distinct), len(positions), batch, time, x, inverse, share)
         return Tensor(total, ())
 
     # -- backward -----------------------------------------------------------------------------------------------
@@ -366,25 +380,16 @@ class Decoder:
         if self._saved is None:
             raise RuntimeError("backward needs a loss first")
         c, stream = self.config, self.stream
-        flat, batch, time, x_last, inverse, share = self._saved
+        tables, distinct, positions, batch, time, x_last, inverse, share = self._saved
         rows, width = batch * time, c.d_model
         d_hidden, d_table = self.head.backward(share)
         _accumulate(self.embedding.weight, d_table.storage, stream)
         dx = _rms_norm_backward(d_hidden.storage, x_last, self.norm, inverse, rows, width, stream)
         for block in reversed(self.blocks):
             dx = block.backward(dx, self._aux_gradient, batch, time)
-        # the embedding's share of the tied table's gradient: token -> positions tables as upstream builds them
-        groups = {}
-        for position, token in enumerate(flat):
-            groups.setdefault(token, []).append(position)
-        tokens = sorted(groups)
-        starts, positions = [0], []
-        for token in tokens:
-            positions.extend(groups[token])
-            starts.append(len(positions))
-        tables = [DeviceStorage.from_bytes(array("q", values).tobytes(), "int64", stream) for values in (tokens, starts, positions)]
+        # the embedding's share of the tied table's gradient, through the token -> positions tables of the forward
         lib.call("qmoe_embedding_backward", dx.ptr, lib.QMOE_BF16, tables[0].ptr, tables[1].ptr, tables[2].ptr,
-                 self.embedding.weight.grad.storage.ptr, len(tokens), len(positions), width, c.vocab_size, stream)
+                 self.embedding.weight.grad.storage.ptr, distinct, positions, width, c.vocab_size, stream)
         self._saved = None
         if self.world > 1:
             self._sum_replicated_gradients(stream)
