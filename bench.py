@@ -9,7 +9,10 @@ tcgen05 grouped GEMM) against the measured bf16 peak; ``cpu_baseline`` is the CP
 this host on a bounded token sample; ``ep_check`` compares the values the timed path produces with the
 CPU oracle (routing counts bit-exact over all ranks' tokens, sampled outputs and gradients at the bf16
 bar) and the process exits non-zero when it fails; ``decode`` is the decode-shaped forward latency (c5);
-``block_ffn`` times the layer with the RMS norm before it and the residual add after it fused in.
+``block_ffn`` times the layer with the RMS norm before it and the residual add after it fused in;
+``lm_head`` and ``attention`` time the language-model head with its loss and causal attention at the shapes of
+the 12-block decoder configuration, and ``decoder_step`` a whole training step of that decoder (loss, backward,
+AdamW): all experts on the GPU at N = 1, data- and expert-parallel ranks with 4 sequences each at N > 1.
 ``--impl reference`` times the CPU implementation alone.
 
 Workloads are the synthetic shapes of the upstream project's MoE layer study: c2 = 16384 tokens,
