@@ -49,6 +49,17 @@ def layer_tensors(layer, prefix, *, rank=0):
     return named
 
 
+def model_tensors(model):
+    """``(name, storage)`` of what this rank writes for a ``qutai_b200.decoder.Decoder``: every tensor of
+    ``named_parameters()`` on one GPU; as a rank of a data- and expert-parallel job the experts it holds (under their
+    numbers in the model) and, on rank 0 only, the replicated tensors — so every name is written exactly once."""
+    named = model.named_parameters()
+    if getattr(model, "world", 1) == 1 or model.rank == 0:
+        return [(name, parameter.storage) for name, parameter in named]
+    replicated = {id(parameter) for parameter in model.replicated_parameters()}
+    return [(name, parameter.storage) for name, parameter in named if id(parameter) not in replicated]
+
+
 def _pieces(storage, chunk_bytes):
     width = _WIDTHS[storage.dtype]
     step = max(1, chunk_bytes // width)

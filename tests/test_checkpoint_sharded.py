@@ -144,3 +144,41 @@ def test_layer_tensors_uses_the_models_expert_numbers():
         experts = [Expert(0), Expert(1)]
 
     assert [name for name, _ in checkpoint.layer_tensors(Single(), "ffn")][1:4] == [f"ffn.experts.0.{k}.weight" for k in ("gate", "up", "down")]
+
+
+def test_model_tensors_writes_every_name_exactly_once_across_ranks(tmp_path):
+    """``model_tensors`` over stand-ins with a decoder's interface: rank 0 writes the replicated tensors and its experts,
+    the other ranks only their experts; together the ranks' lists are the whole model's names, and a one-GPU model reads
+    all of it back."""
+    class Parameter:
+        def __init__(self, size, value):
+            self.storage = HostStorage(size)
+            self.storage.upload_bytes(bytes([value]) * self.storage.nbytes)
+
+    class Model:
+        def __init__(self, rank, world, experts):
+            self.rank, self.world = rank, world
+            self.replicated = [("embedding.weight", Parameter(8, 1)), ("blocks.0.ffn.router.weight", Parameter(4, 2)), ("norm.weight", Parameter(2, 3))]
+            self.experts = [(f"blocks.0.ffn.experts.{e}.gate.weight", Parameter(6, 10 + e)) for e in experts]
+
+        def named_parameters(self):
+            return self.replicated[:2] + self.experts + self.replicated[2:]
+
+        def replicated_parameters(self):
+            return tuple(p for _, p in self.replicated)
+
+    ranks = [Model(0, 2, [0, 3]), Model(1, 2, [1, 2])]
+    lists = [checkpoint.model_tensors(model) for model in ranks]
+    assert [name for name, _ in lists[1]] == ["blocks.0.ffn.experts.1.gate.weight", "blocks.0.ffn.experts.2.gate.weight"]
+    names = [name for named in lists for name, _ in named]
+    assert len(names) == len(set(names)) == 3 + 4
+    threads = [threading.Thread(target=checkpoint.save_sharded, args=(tmp_path, lists[r]), kwargs=dict(rank=r, world=2, generation=7)) for r in (1, 0)]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    whole = Model(0, 1, [0, 1, 2, 3])
+    for _, parameter in whole.named_parameters():
+        parameter.storage.upload_bytes(bytes(parameter.storage.nbytes))
+    checkpoint.load_sharded(tmp_path, checkpoint.model_tensors(whole), verify=True)
+    assert [p.storage.tobytes()[0] for _, p in whole.named_parameters()] == [1, 2, 10, 11, 12, 13, 3]

@@ -30,3 +30,23 @@ def test_a_layer_saved_in_two_pieces_loads_into_a_fresh_layer(tmp_path):
     for name in ("y", "dx", "d_router"):
         assert np.array_equal(got[name], want[name]), name
     assert got["counts"] == want["counts"]
+
+
+def test_a_decoder_saved_and_loaded_into_another_gives_the_same_loss_bits(tmp_path):
+    """``checkpoint.model_tensors`` over a whole decoder (the upstream parameter names): a second decoder built from
+    another seed computes the first one's loss, bit for bit, after loading — the bf16 operand copies of its first
+    forward are renewed."""
+    from gpu_util import to_host
+    from qutai_b200 import checkpoint
+    from qutai_b200.decoder import Config, Decoder
+
+    config = Config(vocab_size=40, d_model=128, n_heads=2, n_kv_heads=1, n_layers=2, n_experts=4, top_k=2, d_expert=16)
+    tokens = np.random.default_rng(2).integers(0, 40, size=(2, 9)).tolist()
+    first, second = Decoder(config, seed=11), Decoder(config, seed=12)
+    want = to_host(first.loss(tokens).storage)[0]
+    assert to_host(second.loss(tokens).storage)[0] != want
+    named = checkpoint.model_tensors(first)
+    assert [name for name, _ in named] == [name for name, _ in first.named_parameters()]
+    checkpoint.save_sharded(tmp_path, named, metadata={"step": 1})
+    assert checkpoint.load_sharded(tmp_path, checkpoint.model_tensors(second), verify=True) == {"step": 1}
+    assert to_host(second.loss(tokens).storage)[0] == want
