@@ -12,6 +12,8 @@ src/qutai/lm/decoder.py:57-68) and changes only who writes:
   into ``data-<generation>-rank<r>.bin`` and leaves ``manifest-<generation>-rank<r>.json`` beside it; rank 0 waits
   for all the pieces (files are the only channel, so it works under any launcher), merges them into
   ``manifest.json`` (atomic rename) and removes the pieces and the shards of the checkpoint it replaces.
+* ``wait_for_manifest(directory, generation)`` — what a rank other than 0 calls before it loads the checkpoint it has
+  just helped to write.
 * ``load_sharded(directory, named)`` — a rank reads the tensors it owns NOW, from whichever shard holds them: the
   world size and the expert placement may differ from those at saving time.  Sizes and dtypes are checked, and with
   ``verify=True`` every shard a rank touches is hashed first.
@@ -159,6 +161,24 @@ def read_manifest(directory):
     if document.get("format") != FORMAT or document.get("version") != VERSION:
         raise ValueError("not a sharded checkpoint of this format")
     return document
+
+
+def wait_for_manifest(directory, generation, *, timeout=600.0, poll=0.05):
+    """Wait until the published manifest is that of checkpoint ``generation`` and return it: what a rank other than 0
+    does between its ``save_sharded`` and a ``load_sharded`` of the same checkpoint (rank 0 publishes last; files are the
+    only channel between the ranks here)."""
+    deadline, path = time.monotonic() + timeout, Path(directory) / "manifest.json"
+    while True:
+        if path.exists():
+            try:
+                document = json.loads(path.read_text(encoding="utf8"))
+            except ValueError:
+                document = None         # replaced under our eyes: look again
+            if document is not None and str(document.get("generation")) == str(generation):
+                return document
+        if time.monotonic() > deadline:
+            raise TimeoutError(f"checkpoint {generation} was not published within {timeout} s")
+        time.sleep(poll)
 
 
 def _verify(directory, shard):

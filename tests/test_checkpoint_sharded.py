@@ -182,3 +182,27 @@ def test_model_tensors_writes_every_name_exactly_once_across_ranks(tmp_path):
         parameter.storage.upload_bytes(bytes(parameter.storage.nbytes))
     checkpoint.load_sharded(tmp_path, checkpoint.model_tensors(whole), verify=True)
     assert [p.storage.tobytes()[0] for _, p in whole.named_parameters()] == [1, 2, 10, 11, 12, 13, 3]
+
+
+def test_a_rank_waits_for_the_manifest_of_its_own_generation(tmp_path):
+    """Rank 1 saves, then waits for rank 0 to publish generation 2 (an older manifest of generation 1 lies there), and only
+    then loads; a generation nobody publishes runs into the time limit."""
+    import time
+
+    first = tensors_of([0], with_router=True)
+    checkpoint.save_sharded(tmp_path, first, generation=1)
+    mine, theirs = tensors_of([1]), tensors_of([0], with_router=True)
+    for _, storage in mine + theirs:
+        storage.upload_bytes(bytes([7]) * storage.nbytes)
+    checkpoint.save_sharded(tmp_path, mine, rank=1, world=2, generation=2)
+    late = threading.Timer(0.3, checkpoint.save_sharded, args=(tmp_path, theirs), kwargs=dict(rank=0, world=2, generation=2))
+    late.start()
+    begin = time.monotonic()
+    document = checkpoint.wait_for_manifest(tmp_path, 2, timeout=30)
+    assert time.monotonic() - begin >= 0.2 and document["generation"] == "2" and document["world"] == 2
+    late.join()
+    fresh = tensors_of([1])
+    checkpoint.load_sharded(tmp_path, fresh)
+    assert all(storage.tobytes() == bytes([7]) * storage.nbytes for _, storage in fresh)
+    with pytest.raises(TimeoutError):
+        checkpoint.wait_for_manifest(tmp_path, 3, timeout=0.2)
