@@ -480,7 +480,8 @@ def run_gpu(args, w, rank, world):
     counts = [logical_counts[e] for e in physical]          # in the layer's internal (rank-major) expert order
     launches_before = lib.load().qmoe_launch_count()
     ms = timed(step, args.steps)
-    launches = (lib.load().qmoe_launch_count() - launches_before) // args.steps
+    launches_timed = lib.load().qmoe_launch_count() - launches_before      # this library's kernels inside the timed region (this rank)
+    launches = launches_timed // args.steps
 
     # ---- end-to-end arm: every step's inputs come from pinned host memory and every step's outputs (y, dx, aux)
     # go back to pinned host memory.  The copies run on their own streams, double-buffered, so the H2D of step
@@ -620,7 +621,7 @@ def run_gpu(args, w, rank, world):
         e2e=dict(value=T_global / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=bytes_in,
                  d2h_bytes_per_step=bytes_out, copies_alone_ms_per_step=ms_copies,
                  note="copies_alone = the same pinned-host copies, both directions at once, without the layer: the floor this box's host link sets"),
-        gpu_launches=int(launches), clocks=clocks,
+        gpu_launches=int(launches_timed), gpu_launches_per_step=int(launches), clocks=clocks,
         steady_state=dict(preroll_steps=prerolled, preroll_seconds=args.preroll, ms_per_step_before_preroll=ms_short,
                           ms_x_mhz=(ms * mhz if mhz else None), gemm_ms_x_mhz=(gemm_ms * mhz if mhz else None),
                           note="back-to-back steps ran for preroll_seconds before the timed ones; ms_x_mhz = ms_per_step x median SM MHz under load, comparable across boxes"),
